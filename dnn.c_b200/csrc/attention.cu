@@ -1,0 +1,448 @@
+// Scaled-dot-product attention (causal / prefix-LM, per-batch sequence lengths),
+// forward and backward, without materialising the N x N probability matrix.
+// replaces src/attention.c:39-64 (visibility rule), :259-380 (forward),
+// :387-540 (backward) and :671-847 (API + tape node).
+//
+// The reference saves P[B,H,N,N] for backward.  Here forward keeps only the
+// per-row log-sum-exp (LSE = max + log(sum)); backward recomputes
+// P = exp(scale*Q.K^T - LSE) tile by tile, with D_i = sum_c dO_ic * O_ic in
+// place of the reference's rowsum(P o dP) (the two are equal).
+//
+// This file holds the exact-fp32 kernels: 64x64 tiles staged in shared memory
+// (row-major, row pitch HD+1 floats so that the 16 rows a half-warp touches
+// fall in different banks), 256 threads, each thread owning rows ty+16*i and
+// columns tx+16*j of a tile.
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace dnnb {
+
+constexpr int TB = 64;           // tile rows (queries) and tile columns (keys)
+constexpr int PS = TB + 1;       // pitch of the probability tile
+
+struct AttnParams {
+    const float *q, *k, *v;      // [B,H,N,d]
+    float *o;                    // [B,H,N,d]
+    float *lse;                  // [B,H,N]
+    const float *dout, *dvec;    // upstream gradient, D_i
+    float *dq, *dk, *dv;
+    const int *seq_lens;         // device [B] or null
+    int B, H, N, d;
+    int prefix;                  // 0 for causal
+    float scale;
+};
+
+__device__ __forceinline__ int visible_len(int i, int prefix, int nb) {
+    int v = (i < prefix) ? prefix : i + 1;       // prefix == 0 gives the causal rule
+    return v < nb ? v : nb;
+}
+
+// Loads rows [r0, r0+TB) x d of a [N,d] slice into shared memory (pitch HD+1),
+// zero-filling rows >= nrows and columns >= d.
+template <int HD>
+__device__ __forceinline__ void load_tile(float *sm, const float *g, int r0, int nrows, int d) {
+    for (int idx = threadIdx.x; idx < TB * HD; idx += blockDim.x) {
+        int r = idx / HD, c = idx - r * HD;
+        float v = 0.f;
+        if (r0 + r < nrows && c < d) v = g[(int64_t)(r0 + r) * d + c];
+        sm[r * (HD + 1) + c] = v;
+    }
+}
+
+// s[i][j] = sum_c A[ty+16i][c] * Bt[tx+16j][c]
+template <int HD>
+__device__ __forceinline__ void tile_dot(const float *A, const float *Bm, int ty, int tx, float s[4][4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) s[i][j] = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < HD; c++) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) a[i] = A[(ty + 16 * i) * (HD + 1) + c];
+#pragma unroll
+        for (int j = 0; j < 4; j++) b[j] = Bm[(tx + 16 * j) * (HD + 1) + c];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) s[i][j] = fmaf(a[i], b[j], s[i][j]);
+    }
+}
+
+__device__ __forceinline__ float half_warp_max(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---- forward -----------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(256) attn_fwd_kernel(AttnParams p) {
+    extern __shared__ float smem[];
+    float *Qs = smem, *Ks = Qs + TB * (HD + 1), *Vs = Ks + TB * (HD + 1), *Ps = Vs + TB * (HD + 1);
+    int b = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * TB;
+    int nb = p.seq_lens ? p.seq_lens[b] : p.N;
+    if (nb > p.N) nb = p.N;
+    int64_t slice = ((int64_t)b * p.H + h) * p.N;
+    const float *q = p.q + slice * p.d, *k = p.k + slice * p.d, *v = p.v + slice * p.d;
+    float *o = p.o + slice * p.d;
+    int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    constexpr int CC = HD / 16;
+
+    if (i0 >= nb) {          // padded rows: output is zero (src/attention.c:376-377)
+        for (int idx = threadIdx.x; idx < TB * p.d; idx += blockDim.x) {
+            int r = idx / p.d;
+            if (i0 + r < p.N) o[(int64_t)i0 * p.d + idx] = 0.f;
+        }
+        return;
+    }
+    load_tile<HD>(Qs, q, i0, nb, p.d);
+    float m[4], l[4], acc[4][CC];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < CC; c++) acc[i][c] = 0.f; }
+    int i_last = min(i0 + TB, nb) - 1;
+    int jmax = visible_len(i_last, p.prefix, nb);           // columns any row of this tile can see
+    if (p.prefix > 0 && i0 < p.prefix) jmax = max(jmax, min(p.prefix, nb));
+
+    for (int j0 = 0; j0 < jmax; j0 += TB) {
+        __syncthreads();
+        load_tile<HD>(Ks, k, j0, nb, p.d);
+        load_tile<HD>(Vs, v, j0, nb, p.d);
+        __syncthreads();
+        float s[4][4];
+        tile_dot<HD>(Qs, Ks, ty, tx, s);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int row = i0 + ty + 16 * i;
+            int vis = row < nb ? visible_len(row, p.prefix, nb) : 0;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                int col = j0 + tx + 16 * j;
+                s[i][j] = col < vis ? s[i][j] * p.scale : -INFINITY;
+                mx = fmaxf(mx, s[i][j]);
+            }
+            mx = half_warp_max(mx);
+            float mnew = fmaxf(m[i], mx);
+            float corr = (mnew == -INFINITY) ? 1.f : expf(m[i] - mnew);
+            float rs = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float pe = (s[i][j] == -INFINITY) ? 0.f : expf(s[i][j] - mnew);
+                Ps[(ty + 16 * i) * PS + tx + 16 * j] = pe;
+                rs += pe;
+            }
+            rs = half_warp_sum(rs);
+            l[i] = l[i] * corr + rs;
+            m[i] = mnew;
+#pragma unroll
+            for (int c = 0; c < CC; c++) acc[i][c] *= corr;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = 0; j < TB; j++) {
+            float pv[4], vv[CC];
+#pragma unroll
+            for (int i = 0; i < 4; i++) pv[i] = Ps[(ty + 16 * i) * PS + j];
+#pragma unroll
+            for (int c = 0; c < CC; c++) vv[c] = Vs[j * (HD + 1) + tx + 16 * c];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int c = 0; c < CC; c++) acc[i][c] = fmaf(pv[i], vv[c], acc[i][c]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int row = i0 + ty + 16 * i;
+        if (row >= p.N) continue;
+        bool live = row < nb;
+        float inv = live ? 1.f / l[i] : 0.f;
+#pragma unroll
+        for (int c = 0; c < CC; c++) {
+            int col = tx + 16 * c;
+            if (col < p.d) o[(int64_t)row * p.d + col] = live ? acc[i][c] * inv : 0.f;
+        }
+        if (tx == 0 && p.lse) p.lse[slice + row] = live ? m[i] + logf(l[i]) : 0.f;
+    }
+}
+
+// ---- backward: D_i = sum_c dO_ic * O_ic --------------------------------------
+__global__ void attn_bwd_prep_kernel(const float *__restrict__ dout, const float *__restrict__ o,
+                                     float *__restrict__ dvec, int64_t rows, int d) {
+    int lane = threadIdx.x & 31;
+    int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    float s = 0.f;
+    for (int c = lane; c < d; c += 32) s += dout[r * d + c] * o[r * d + c];
+    s = warp_sum(s);
+    if (lane == 0) dvec[r] = s;
+}
+
+// Recomputes P and dS for the (query tile at Qs/dOs, key tile at Ks/Vs) pair.
+template <int HD>
+__device__ __forceinline__ void recompute_p_ds(const AttnParams &p, const float *Qs, const float *Ks, const float *Vs,
+                                               const float *dOs, const float *lse_s, const float *d_s,
+                                               int i0, int j0, int nb, int ty, int tx, float *Ps, float *dSs) {
+    float s[4][4], dp[4][4];
+    tile_dot<HD>(Qs, Ks, ty, tx, s);
+    tile_dot<HD>(dOs, Vs, ty, tx, dp);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int r = ty + 16 * i, row = i0 + r;
+        int vis = row < nb ? visible_len(row, p.prefix, nb) : 0;
+        float lse = lse_s[r], dd = d_s[r];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int col = j0 + tx + 16 * j;
+            float pe = col < vis ? expf(s[i][j] * p.scale - lse) : 0.f;
+            Ps[r * PS + tx + 16 * j] = pe;
+            dSs[r * PS + tx + 16 * j] = pe * (dp[i][j] - dd) * p.scale;
+        }
+    }
+}
+
+// One CTA per key tile: dK_j += sum_i dS_ij Q_i, dV_j += sum_i P_ij dO_i.
+template <int HD>
+__global__ void __launch_bounds__(256) attn_bwd_dkv_kernel(AttnParams p) {
+    extern __shared__ float smem[];
+    constexpr int TS = TB * (HD + 1);
+    float *Qs = smem, *Ks = Qs + TS, *Vs = Ks + TS, *dOs = Vs + TS, *Ps = dOs + TS, *dSs = Ps + TB * PS;
+    float *lse_s = dSs + TB * PS, *d_s = lse_s + TB;
+    int b = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * TB;
+    int nb = p.seq_lens ? p.seq_lens[b] : p.N;
+    if (nb > p.N) nb = p.N;
+    if (j0 >= nb) return;
+    int64_t slice = ((int64_t)b * p.H + h) * p.N;
+    const float *q = p.q + slice * p.d, *k = p.k + slice * p.d, *v = p.v + slice * p.d, *dout = p.dout + slice * p.d;
+    int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    constexpr int CC = HD / 16;
+    float dk[4][CC], dv[4][CC];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < CC; c++) { dk[i][c] = 0.f; dv[i][c] = 0.f; }
+    load_tile<HD>(Ks, k, j0, nb, p.d);
+    load_tile<HD>(Vs, v, j0, nb, p.d);
+    // first query tile that can see a key of this tile
+    int i_begin = (p.prefix > 0 && j0 < p.prefix) ? 0 : (j0 / TB) * TB;
+    for (int i0 = i_begin; i0 < nb; i0 += TB) {
+        __syncthreads();
+        load_tile<HD>(Qs, q, i0, nb, p.d);
+        load_tile<HD>(dOs, dout, i0, nb, p.d);
+        if (threadIdx.x < TB) {
+            int row = i0 + threadIdx.x;
+            lse_s[threadIdx.x] = row < nb ? p.lse[slice + row] : 0.f;
+            d_s[threadIdx.x] = row < nb ? p.dvec[slice + row] : 0.f;
+        }
+        __syncthreads();
+        recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs);
+        __syncthreads();
+        // this thread owns key rows ty+16*jj and feature columns tx+16*c
+#pragma unroll 4
+        for (int i = 0; i < TB; i++) {
+            float pj[4], sj[4], go[CC], qq[CC];
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) { pj[jj] = Ps[i * PS + ty + 16 * jj]; sj[jj] = dSs[i * PS + ty + 16 * jj]; }
+#pragma unroll
+            for (int c = 0; c < CC; c++) { go[c] = dOs[i * (HD + 1) + tx + 16 * c]; qq[c] = Qs[i * (HD + 1) + tx + 16 * c]; }
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++)
+#pragma unroll
+                for (int c = 0; c < CC; c++) { dv[jj][c] = fmaf(pj[jj], go[c], dv[jj][c]); dk[jj][c] = fmaf(sj[jj], qq[c], dk[jj][c]); }
+        }
+    }
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+        int row = j0 + ty + 16 * jj;
+        if (row >= nb) continue;
+#pragma unroll
+        for (int c = 0; c < CC; c++) {
+            int col = tx + 16 * c;
+            if (col >= p.d) continue;
+            int64_t at = (slice + row) * p.d + col;
+            if (p.dk) p.dk[at] += dk[jj][c];
+            if (p.dv) p.dv[at] += dv[jj][c];
+        }
+    }
+}
+
+// One CTA per query tile: dQ_i += sum_j dS_ij K_j.
+template <int HD>
+__global__ void __launch_bounds__(256) attn_bwd_dq_kernel(AttnParams p) {
+    extern __shared__ float smem[];
+    constexpr int TS = TB * (HD + 1);
+    float *Qs = smem, *Ks = Qs + TS, *Vs = Ks + TS, *dOs = Vs + TS, *Ps = dOs + TS, *dSs = Ps + TB * PS;
+    float *lse_s = dSs + TB * PS, *d_s = lse_s + TB;
+    int b = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * TB;
+    int nb = p.seq_lens ? p.seq_lens[b] : p.N;
+    if (nb > p.N) nb = p.N;
+    if (i0 >= nb) return;
+    int64_t slice = ((int64_t)b * p.H + h) * p.N;
+    const float *q = p.q + slice * p.d, *k = p.k + slice * p.d, *v = p.v + slice * p.d, *dout = p.dout + slice * p.d;
+    int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    constexpr int CC = HD / 16;
+    float dq[4][CC];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < CC; c++) dq[i][c] = 0.f;
+    load_tile<HD>(Qs, q, i0, nb, p.d);
+    load_tile<HD>(dOs, dout, i0, nb, p.d);
+    if (threadIdx.x < TB) {
+        int row = i0 + threadIdx.x;
+        lse_s[threadIdx.x] = row < nb ? p.lse[slice + row] : 0.f;
+        d_s[threadIdx.x] = row < nb ? p.dvec[slice + row] : 0.f;
+    }
+    int i_last = min(i0 + TB, nb) - 1;
+    int jmax = visible_len(i_last, p.prefix, nb);
+    if (p.prefix > 0 && i0 < p.prefix) jmax = max(jmax, min(p.prefix, nb));
+    for (int j0 = 0; j0 < jmax; j0 += TB) {
+        __syncthreads();
+        load_tile<HD>(Ks, k, j0, nb, p.d);
+        load_tile<HD>(Vs, v, j0, nb, p.d);
+        __syncthreads();
+        recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs);
+        __syncthreads();
+#pragma unroll 4
+        for (int j = 0; j < TB; j++) {
+            float sv[4], kk[CC];
+#pragma unroll
+            for (int i = 0; i < 4; i++) sv[i] = dSs[(ty + 16 * i) * PS + j];
+#pragma unroll
+            for (int c = 0; c < CC; c++) kk[c] = Ks[j * (HD + 1) + tx + 16 * c];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int c = 0; c < CC; c++) dq[i][c] = fmaf(sv[i], kk[c], dq[i][c]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int row = i0 + ty + 16 * i;
+        if (row >= nb) continue;
+#pragma unroll
+        for (int c = 0; c < CC; c++) {
+            int col = tx + 16 * c;
+            if (col < p.d) p.dq[(slice + row) * p.d + col] += dq[i][c];
+        }
+    }
+}
+
+template <int HD> static size_t fwd_smem() { return (size_t)(3 * TB * (HD + 1) + TB * PS) * 4; }
+template <int HD> static size_t bwd_smem() { return (size_t)(4 * TB * (HD + 1) + 2 * TB * PS + 2 * TB) * 4; }
+
+template <int HD>
+static void attn_fwd_launch(const AttnParams &p) {
+    static bool once = false;
+    if (!once) { CUDA_OK(cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem<HD>())); once = true; }
+    dim3 grid((p.N + TB - 1) / TB, p.H, p.B);
+    attn_fwd_kernel<HD><<<grid, 256, fwd_smem<HD>(), stream()>>>(p);
+    LAUNCHED("attn_fwd_kernel");
+}
+template <int HD>
+static void attn_bwd_launch(const AttnParams &p) {
+    static bool once = false;
+    if (!once) {
+        CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem<HD>()));
+        CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem<HD>()));
+        once = true;
+    }
+    dim3 grid((p.N + TB - 1) / TB, p.H, p.B);
+    if (p.dk || p.dv) { attn_bwd_dkv_kernel<HD><<<grid, 256, bwd_smem<HD>(), stream()>>>(p); LAUNCHED("attn_bwd_dkv_kernel"); }
+    if (p.dq) { attn_bwd_dq_kernel<HD><<<grid, 256, bwd_smem<HD>(), stream()>>>(p); LAUNCHED("attn_bwd_dq_kernel"); }
+}
+
+void attn_forward_fp32(const AttnParams &p) {
+    if (p.d <= 32) attn_fwd_launch<32>(p);
+    else if (p.d <= 64) attn_fwd_launch<64>(p);
+    else attn_fwd_launch<128>(p);
+}
+void attn_backward_fp32(const AttnParams &p) {
+    if (p.d <= 32) attn_bwd_launch<32>(p);
+    else if (p.d <= 64) attn_bwd_launch<64>(p);
+    else attn_bwd_launch<128>(p);
+}
+
+struct AttnSaved { float *lse; const int *seq_lens_dev; int mode, prefix; float scale; tensor *out; };
+
+static void attention_backward(grad_fn *fn, tensor *go) {
+    tensor *q = fn->inputs[0], *k = fn->inputs[1], *v = fn->inputs[2];
+    AttnSaved *sv = (AttnSaved *)fn->saved_tensors[0];
+    AttnParams p;
+    memset(&p, 0, sizeof p);
+    p.B = q->shape[0]; p.H = q->shape[1]; p.N = q->shape[2]; p.d = q->shape[3];
+    p.q = (const float *)q->data; p.k = (const float *)k->data; p.v = (const float *)v->data;
+    p.o = (float *)sv->out->data; p.lse = sv->lse; p.seq_lens = sv->seq_lens_dev;
+    p.prefix = sv->mode == ATTENTION_PREFIX_LM ? sv->prefix : 0; p.scale = sv->scale;
+    p.dout = (const float *)go->data;
+    p.dq = wants_grad(q) ? _grad_ensure(q) : nullptr;
+    p.dk = wants_grad(k) ? _grad_ensure(k) : nullptr;
+    p.dv = wants_grad(v) ? _grad_ensure(v) : nullptr;
+    int64_t rows = (int64_t)p.B * p.H * p.N;
+    float *dvec = dev_alloc_t<float>(fn->pool, (size_t)rows);
+    attn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(p.dout, p.o, dvec, rows, p.d);
+    LAUNCHED("attn_bwd_prep_kernel");
+    p.dvec = dvec;
+    attn_backward_fp32(p);
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tensor *v, tensor *mask,
+                            attention_mode mode, int prefix_len, const int *seq_lens) {
+    DNN_CHECK(q && k && v, "tensor_attention: NULL operand");
+    DNN_CHECK(q->ndim == 4 && k->ndim == 4 && v->ndim == 4, "tensor_attention: operands must be [B,H,N,d]");
+    DNN_CHECK(q->contiguous && k->contiguous && v->contiguous, "tensor_attention: operands must be contiguous");
+    int B = q->shape[0], H = q->shape[1], N = q->shape[2], d = q->shape[3];
+    for (int i = 0; i < 4; i++)
+        DNN_CHECK(k->shape[i] == q->shape[i] && v->shape[i] == q->shape[i], "tensor_attention: shape mismatch");
+    if (mode == ATTENTION_PREFIX_LM) DNN_CHECK(prefix_len > 0 && prefix_len <= N, "tensor_attention: prefix_len out of range");
+    if (mode == ATTENTION_CAUSAL) DNN_CHECK(prefix_len == 0, "tensor_attention: prefix_len must be 0 in causal mode");
+    // The additive mask of the reference is forward-only and never differentiated
+    // (src/attention.c:315-326); the training path always passes NULL.
+    DNN_CHECK(mask == nullptr, "tensor_attention: additive masks are not supported on this path");
+    DNN_CHECK(d <= 128, "tensor_attention: head dim above 128 is not supported");
+
+    int shape[4] = {B, H, N, d};
+    tensor *out = tensor_scratch(scratch, 4, shape, 0);
+    bool needs_grad = dnn_grad_enabled() && (q->requires_grad || k->requires_grad || v->requires_grad);
+    AttnParams p;
+    memset(&p, 0, sizeof p);
+    p.B = B; p.H = H; p.N = N; p.d = d;
+    p.q = (const float *)q->data; p.k = (const float *)k->data; p.v = (const float *)v->data;   // offsets ignored, as in the reference
+    p.o = (float *)out->data;
+    p.lse = needs_grad ? dev_alloc_t<float>(scratch, (size_t)B * H * N) : nullptr;
+    p.seq_lens = seq_lens ? (const int *)dev_put(scratch, seq_lens, (size_t)B * sizeof(int)) : nullptr;
+    p.prefix = mode == ATTENTION_PREFIX_LM ? prefix_len : 0;
+    p.scale = 1.0f / sqrtf((float)d);
+    attn_forward_fp32(p);
+
+    if (needs_grad) {
+        grad_fn *fn = attach(scratch, out, attention_backward, 3, 1);
+        fn->inputs[0] = q; fn->inputs[1] = k; fn->inputs[2] = v;
+        AttnSaved *sv = host_alloc_t<AttnSaved>(scratch);
+        sv->lse = p.lse; sv->seq_lens_dev = p.seq_lens; sv->mode = (int)mode; sv->prefix = prefix_len;
+        sv->scale = p.scale; sv->out = out;
+        fn->saved_tensors[0] = (tensor *)sv;
+    }
+    return out;
+}
+
+tensor *tensor_attention(struct mem_pool *scratch, tensor *q, tensor *k, tensor *v, tensor *mask) {
+    return tensor_attention_ex(scratch, q, k, v, mask, ATTENTION_CAUSAL, 0, nullptr);
+}
+
+}  // extern "C"

@@ -1,0 +1,99 @@
+// Internal declarations shared by every translation unit of libdnn_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <cstdint>
+#include <cmath>
+#include "dnn_b200.h"
+#include "dnn_cuda.h"
+
+namespace dnnb {
+
+// Reference-style failure: print and abort (the reference uses assert()).
+#define DNN_CHECK(cond, msg)                                                        \
+    do { if (!(cond)) { fprintf(stderr, "dnn_b200: %s (%s:%d)\n", msg, __FILE__, __LINE__); \
+                        abort(); } } while (0)
+
+void cuda_fail(cudaError_t e, const char *what, const char *file, int line);
+#define CUDA_OK(expr)                                                               \
+    do { cudaError_t _e = (expr); if (_e != cudaSuccess) ::dnnb::cuda_fail(_e, #expr, __FILE__, __LINE__); } while (0)
+
+// Compute stream of this process (creates the runtime on first use; aborts
+// with a clear message when no CUDA device is usable).
+cudaStream_t stream();
+// Counts one kernel launch and checks the launch error.
+void launched(const char *name);
+#define LAUNCHED(name) ::dnnb::launched(name)
+
+// Device allocation from the arena attached to `pool` (256-byte aligned).
+void *dev_alloc(struct mem_pool *pool, size_t bytes, bool zero);
+// Device scratch valid until the pool is reset / released.
+template <typename T> inline T *dev_alloc_t(struct mem_pool *pool, size_t n, bool zero = false) {
+    return (T *)dev_alloc(pool, n * sizeof(T), zero);
+}
+// Host-side metadata allocation (zero-filled).
+template <typename T> inline T *host_alloc_t(struct mem_pool *pool, size_t n = 1) {
+    return (T *)_mem_pool_alloc(pool, n * sizeof(T), nullptr);
+}
+// Copies a small host array into the scratch arena of `pool` (ordered on the
+// compute stream) and returns the device pointer.
+void *dev_put(struct mem_pool *pool, const void *host, size_t bytes);
+
+int gemm_mode();
+
+inline int64_t numel_of(const tensor *t) {
+    int64_t n = 1;
+    for (int i = 0; i < t->ndim; i++) n *= t->shape[i];
+    return n;
+}
+inline bool wants_grad(const tensor *t) { return t->grad_fn || t->requires_grad; }
+
+// Logical shape + strides of a tensor, passed to kernels by value.
+struct View {
+    int ndim;
+    int shape[DNN_MAX_DIMS];
+    int strides[DNN_MAX_DIMS];
+    int offset;
+};
+inline View view_of(const tensor *t) {
+    View v; v.ndim = t->ndim; v.offset = t->offset;
+    for (int i = 0; i < DNN_MAX_DIMS; i++) { v.shape[i] = i < t->ndim ? t->shape[i] : 1;
+                                             v.strides[i] = i < t->ndim ? t->strides[i] : 0; }
+    return v;
+}
+// View of `t` broadcast to (out_ndim, out_shape): leading dims and size-1 dims
+// get stride 0 (src/broadcast.h:30-50 computes the same offsets per element).
+View bcast_view(const tensor *t, int out_ndim, const int *out_shape);
+int  bcast_shape(int na, const int *sa, int nb, const int *sb, int *out);   // src/broadcast.c
+
+// Attaches a tape node to `out` (src/autograd.c:29-33 + the per-op boilerplate).
+grad_fn *attach(struct mem_pool *scratch, tensor *out, void (*bw)(grad_fn *, tensor *),
+                int n_inputs, int n_saved);
+
+// ---- kernel-side entry points used across files -------------------------
+void k_fill(float *p, int64_t n, float v);
+void k_axpy_acc(float *dst, const float *src, int64_t n);                 // dst += src
+void k_copy(float *dst, const float *src, int64_t n);
+// dst[view(i)] (=|+=) src[i] and dst[i] = src[view(i)] for i in [0, n)
+void k_gather(float *dst, const float *src, const View &sv, int64_t n);
+void k_scatter(float *dst, const View &dv, const float *src, int64_t n, bool accumulate);
+// column sums: out[c] += sum_r g[r*C + c]
+void k_colsum_acc(float *out, const float *g, int64_t rows, int C);
+
+// General strided GEMM:  C[m,n] (=|+=) sum_k A[m,k]*B[k,n] (+ bias[n])
+struct GemmArgs {
+    const float *A; int64_t a_rs, a_cs, a_bs;
+    const float *B; int64_t b_rs, b_cs, b_bs;
+    float *C;       int64_t c_rs, c_cs, c_bs;
+    const float *bias;     // may be null; indexed by n
+    int M, N, K, batch;
+    bool accumulate;
+};
+void gemm(const GemmArgs &g);          // dispatches on gemm_mode() and layout
+void gemm_simt(const GemmArgs &g);
+bool gemm_tc_supported(const GemmArgs &g);
+void gemm_tc(const GemmArgs &g, bool split3);
+
+}  // namespace dnnb

@@ -1,0 +1,270 @@
+// conv2d (im2col + GEMM) and avg_pool2d, forward and backward.
+// replaces src/conv.c:50-919 and src/ops_pool.c:118-381 of the reference.
+//
+// conv2d.  The reference has two paths with different OUTPUT MEMORY LAYOUTS and
+// both are reproduced:
+//   * 3x3 / stride 1 / pad 1 takes a Winograd F(2x2,3x3) path and writes true
+//     NCHW (src/conv.c:719-800).  Here: im2col + GEMM into an (M, out_C) buffer
+//     followed by a permute to NCHW; Winograd is an exact algebraic rewrite, so
+//     the results agree to rounding.
+//   * every other geometry takes im2col + GEMM and writes the GEMM result
+//     (M, out_C), M = (n, oh, ow), straight into the tensor that is DECLARED
+//     [N, out_C, H_out, W_out] (src/conv.c:847-863), and its backward reads the
+//     upstream gradient the same way (:437-506).  Kept bit-for-bit in layout.
+// Both paths sum the bias gradient with NCHW indexing (src/conv.c:418-435,555-570).
+// The column matrix is stored (K, M) like the reference's and kept for backward.
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace dnnb {
+
+struct ConvGeom { int N, C, H, W, out_C, kH, kW, stride, pad, H_out, W_out, M, K; };
+
+// col[k][m], k = (c, kh, kw), m = (n, oh, ow); one thread per element, m fastest.
+__global__ void im2col_kernel(const float *__restrict__ x, float *__restrict__ col, ConvGeom g) {
+    int64_t total = (int64_t)g.K * g.M;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int m = (int)(idx % g.M); int k = (int)(idx / g.M);
+        int ow = m % g.W_out; int t = m / g.W_out; int oh = t % g.H_out; int n = t / g.H_out;
+        int kw = k % g.kW; t = k / g.kW; int kh = t % g.kH; int c = t / g.kH;
+        int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
+        float v = 0.f;
+        if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = x[(((int64_t)n * g.C + c) * g.H + ih) * g.W + iw];
+        col[idx] = v;
+    }
+}
+
+// dx[n,c,ih,iw] += sum over (kh,kw,oh,ow) that read this pixel of dcol[k][m]; gather form, deterministic.
+__global__ void col2im_kernel(const float *__restrict__ dcol, float *__restrict__ dx, ConvGeom g) {
+    int64_t total = (int64_t)g.N * g.C * g.H * g.W;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int iw = (int)(idx % g.W); int64_t t = idx / g.W; int ih = (int)(t % g.H); t /= g.H; int c = (int)(t % g.C); int n = (int)(t / g.C);
+        float s = 0.f;
+        for (int kh = 0; kh < g.kH; kh++) {
+            int a = ih + g.pad - kh;
+            if (a < 0 || a % g.stride) continue;
+            int oh = a / g.stride;
+            if (oh >= g.H_out) continue;
+            for (int kw = 0; kw < g.kW; kw++) {
+                int b = iw + g.pad - kw;
+                if (b < 0 || b % g.stride) continue;
+                int ow = b / g.stride;
+                if (ow >= g.W_out) continue;
+                int k = (c * g.kH + kh) * g.kW + kw;
+                int m = (n * g.H_out + oh) * g.W_out + ow;
+                s += dcol[(int64_t)k * g.M + m];
+            }
+        }
+        dx[idx] += s;
+    }
+}
+
+// (M, out_C) <-> NCHW: dst_nchw[n,oc,hw] = src_mc[(n*HW+hw), oc]   (TO_NCHW)
+template <bool TO_NCHW>
+__global__ void conv_permute_kernel(float *__restrict__ dst, const float *__restrict__ src, int N, int OC, int HW) {
+    int64_t total = (int64_t)N * OC * HW;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        if (TO_NCHW) {      // idx walks NCHW
+            int hw = (int)(idx % HW); int64_t t = idx / HW; int oc = (int)(t % OC); int n = (int)(t / OC);
+            dst[idx] = src[((int64_t)n * HW + hw) * OC + oc];
+        } else {            // idx walks (M, OC)
+            int oc = (int)(idx % OC); int64_t t = idx / OC; int hw = (int)(t % HW); int n = (int)(t / HW);
+            dst[idx] = src[((int64_t)n * OC + oc) * HW + hw];
+        }
+    }
+}
+
+// dbias[oc] += sum_{n,hw} g[(n*OC + oc)*HW + hw]; one CTA per channel, fixed order.
+__global__ void conv_dbias_kernel(float *__restrict__ db, const float *__restrict__ g, int N, int OC, int HW) {
+    __shared__ float sh[32];
+    int oc = blockIdx.x;
+    float s = 0.f;
+    int64_t per = (int64_t)N * HW;
+    for (int64_t i = threadIdx.x; i < per; i += blockDim.x) {
+        int n = (int)(i / HW), hw = (int)(i % HW);
+        s += g[((int64_t)n * OC + oc) * HW + hw];
+    }
+    s = block_sum(s, sh);
+    if (threadIdx.x == 0) db[oc] += s;
+}
+
+struct ConvSaved { ConvGeom g; float *col; tensor *bias; int nchw; };
+
+static void conv2d_backward(grad_fn *fn, tensor *go) {
+    tensor *input = fn->inputs[0], *weight = fn->inputs[1];
+    ConvSaved *sv = (ConvSaved *)fn->saved_tensors[0];
+    const ConvGeom &g = sv->g;
+    tensor *bias = sv->bias;
+    const float *gd = (const float *)go->data;
+    const float *wd = (const float *)weight->data + weight->offset;
+    int HW = g.H_out * g.W_out;
+
+    // Gradient buffers first: an activation's gradient comes from the same pool
+    // as the temporaries below and must survive the release at the end.
+    float *wg = weight->requires_grad ? _grad_ensure(weight) : nullptr;
+    float *xg = input->requires_grad ? _grad_ensure(input) : nullptr;
+    if (bias && bias->requires_grad) {
+        float *bg = _grad_ensure(bias);
+        conv_dbias_kernel<<<g.out_C, 256, 0, stream()>>>(bg, gd, g.N, g.out_C, HW);
+        LAUNCHED("conv_dbias_kernel");
+    }
+    size_t mark = mem_pool_mark(fn->pool);
+    const float *g_mc = gd;                 // upstream gradient read as (M, out_C)
+    if (sv->nchw) {
+        float *tmp = dev_alloc_t<float>(fn->pool, (size_t)g.M * g.out_C);
+        conv_permute_kernel<false><<<grid_for((int64_t)g.M * g.out_C, 256), 256, 0, stream()>>>(tmp, gd, g.N, g.out_C, HW);
+        LAUNCHED("conv_permute_kernel");
+        g_mc = tmp;
+    }
+    if (wg) {
+        GemmArgs a;     // dW[oc,k] += sum_m g_mc[m,oc] * col[k,m]
+        a.A = g_mc; a.a_rs = 1; a.a_cs = g.out_C; a.a_bs = 0;
+        a.B = sv->col; a.b_rs = 1; a.b_cs = g.M; a.b_bs = 0;
+        a.C = wg + weight->offset; a.c_rs = g.K; a.c_cs = 1; a.c_bs = 0;
+        a.bias = nullptr; a.M = g.out_C; a.N = g.K; a.K = g.M; a.batch = 1; a.accumulate = true;
+        gemm(a);
+    }
+    if (xg) {
+        float *dcol = dev_alloc_t<float>(fn->pool, (size_t)g.K * g.M);
+        GemmArgs a;     // dcol[k,m] = sum_oc W[oc,k] * g_mc[m,oc]
+        a.A = wd; a.a_rs = 1; a.a_cs = g.K; a.a_bs = 0;
+        a.B = g_mc; a.b_rs = 1; a.b_cs = g.out_C; a.b_bs = 0;
+        a.C = dcol; a.c_rs = g.M; a.c_cs = 1; a.c_bs = 0;
+        a.bias = nullptr; a.M = g.K; a.N = g.M; a.K = g.out_C; a.batch = 1; a.accumulate = false;
+        gemm(a);
+        col2im_kernel<<<grid_for((int64_t)g.N * g.C * g.H * g.W, 256), 256, 0, stream()>>>(dcol, xg + input->offset, g);
+        LAUNCHED("col2im_kernel");
+    }
+    mem_pool_release(fn->pool, mark);
+}
+
+// ---- avg_pool2d ------------------------------------------------------------------
+__global__ void avgpool_fwd_kernel(const float *__restrict__ x, float *__restrict__ out,
+                                   int64_t planes, int H, int W, int H_out, int W_out, int k, int stride, float inv_k2) {
+    int64_t total = planes * H_out * W_out;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int ow = (int)(idx % W_out); int64_t t = idx / W_out; int oh = (int)(t % H_out); int64_t pl = t / H_out;
+        const float *xp = x + pl * H * W + (int64_t)(oh * stride) * W + ow * stride;
+        float s = 0.f;
+        for (int di = 0; di < k; di++)
+            for (int dj = 0; dj < k; dj++) s += xp[di * W + dj];
+        out[idx] = s * inv_k2;
+    }
+}
+__global__ void avgpool_bwd_kernel(const float *__restrict__ g, float *__restrict__ dx,
+                                   int64_t planes, int H, int W, int H_out, int W_out, int k, int stride, float inv_k2) {
+    int64_t total = planes * H * W;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int iw = (int)(idx % W); int64_t t = idx / W; int ih = (int)(t % H); int64_t pl = t / H;
+        // windows (oh, ow) with oh*stride <= ih < oh*stride + k
+        int oh_lo = ih - k + 1 <= 0 ? 0 : (ih - k + stride) / stride;
+        int oh_hi = ih / stride; if (oh_hi > H_out - 1) oh_hi = H_out - 1;
+        int ow_lo = iw - k + 1 <= 0 ? 0 : (iw - k + stride) / stride;
+        int ow_hi = iw / stride; if (ow_hi > W_out - 1) ow_hi = W_out - 1;
+        float s = 0.f;
+        for (int oh = oh_lo; oh <= oh_hi; oh++)
+            for (int ow = ow_lo; ow <= ow_hi; ow++) s += g[pl * H_out * W_out + (int64_t)oh * W_out + ow] * inv_k2;
+        if (oh_lo <= oh_hi && ow_lo <= ow_hi) dx[idx] += s;
+    }
+}
+
+static void avg_pool2d_backward(grad_fn *fn, tensor *go) {
+    tensor *x = fn->inputs[0];
+    int k = *(int *)fn->saved_tensors[0], stride = *(int *)fn->saved_tensors[1];
+    if (!x->requires_grad) return;
+    int N = x->shape[0], C = x->shape[1], H = x->shape[2], W = x->shape[3];
+    int H_out = (H - k) / stride + 1, W_out = (W - k) / stride + 1;
+    float *xg = _grad_ensure(x);        // indexed from 0 with packed NCHW strides, as the reference does
+    int64_t planes = (int64_t)N * C;
+    avgpool_bwd_kernel<<<grid_for(planes * H * W, 256), 256, 0, stream()>>>((const float *)go->data, xg, planes, H, W,
+                                                                            H_out, W_out, k, stride, 1.0f / (float)(k * k));
+    LAUNCHED("avgpool_bwd_kernel");
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+tensor *tensor_conv2d(struct mem_pool *scratch, tensor *input, tensor *weight, tensor *bias, int stride, int pad) {
+    DNN_CHECK(input && weight, "conv2d: NULL operand");
+    DNN_CHECK(input->ndim == 4, "conv2d: input must be (N, C, H, W)");
+    DNN_CHECK(weight->ndim == 4, "conv2d: weight must be (out_C, in_C, kH, kW)");
+    DNN_CHECK(input->shape[1] == weight->shape[1], "conv2d: in_channels mismatch");
+    DNN_CHECK(input->contiguous && weight->contiguous, "conv2d: input and weight must be contiguous");
+    DNN_CHECK(!bias || (bias->ndim == 1 && bias->shape[0] == weight->shape[0]), "conv2d: bias shape");
+    DNN_CHECK(stride > 0, "conv2d: stride must be positive");
+    ConvGeom g;
+    g.N = input->shape[0]; g.C = input->shape[1]; g.H = input->shape[2]; g.W = input->shape[3];
+    g.out_C = weight->shape[0]; g.kH = weight->shape[2]; g.kW = weight->shape[3];
+    g.stride = stride; g.pad = pad;
+    g.H_out = (g.H + 2 * pad - g.kH) / stride + 1;
+    g.W_out = (g.W + 2 * pad - g.kW) / stride + 1;
+    DNN_CHECK(g.H_out > 0 && g.W_out > 0, "conv2d: kernel larger than padded input");
+    g.M = g.N * g.H_out * g.W_out; g.K = g.C * g.kH * g.kW;
+    int shape[4] = {g.N, g.out_C, g.H_out, g.W_out};
+    tensor *out = tensor_scratch(scratch, 4, shape, 0);
+    bool nchw = (g.kH == 3 && g.kW == 3 && stride == 1 && pad == 1);
+    bool needs_grad = dnn_grad_enabled() && (input->requires_grad || weight->requires_grad || (bias && bias->requires_grad));
+
+    size_t mark = mem_pool_mark(scratch);
+    float *col = dev_alloc_t<float>(scratch, (size_t)g.K * g.M);
+    im2col_kernel<<<grid_for((int64_t)g.K * g.M, 256), 256, 0, stream()>>>((const float *)input->data + input->offset, col, g);
+    LAUNCHED("im2col_kernel");
+    float *mc = nchw ? dev_alloc_t<float>(scratch, (size_t)g.M * g.out_C) : (float *)out->data;
+    GemmArgs a;         // mc[m,oc] = sum_k col[k,m] * W[oc,k] + bias[oc]
+    a.A = col; a.a_rs = 1; a.a_cs = g.M; a.a_bs = 0;
+    a.B = (const float *)weight->data + weight->offset; a.b_rs = 1; a.b_cs = g.K; a.b_bs = 0;
+    a.C = mc; a.c_rs = g.out_C; a.c_cs = 1; a.c_bs = 0;
+    a.bias = bias ? (const float *)bias->data + bias->offset : nullptr;
+    a.M = g.M; a.N = g.out_C; a.K = g.K; a.batch = 1; a.accumulate = false;
+    gemm(a);
+    if (nchw) {
+        conv_permute_kernel<true><<<grid_for((int64_t)g.M * g.out_C, 256), 256, 0, stream()>>>((float *)out->data, mc, g.N, g.out_C,
+                                                                                              g.H_out * g.W_out);
+        LAUNCHED("conv_permute_kernel");
+    }
+    if (needs_grad) {
+        grad_fn *fn = attach(scratch, out, conv2d_backward, 2, 1);
+        fn->inputs[0] = input; fn->inputs[1] = weight;
+        ConvSaved *sv = host_alloc_t<ConvSaved>(scratch);
+        sv->g = g; sv->col = col; sv->bias = bias; sv->nchw = nchw ? 1 : 0;
+        fn->saved_tensors[0] = (tensor *)sv;
+    } else {
+        mem_pool_release(scratch, mark);     // nothing kept: give the column matrix back
+    }
+    return out;
+}
+
+tensor *tensor_avg_pool2d(struct mem_pool *scratch, const tensor *x, int k, int stride) {
+    DNN_CHECK(x, "avg_pool2d: NULL input");
+    DNN_CHECK(x->ndim == 4, "avg_pool2d: input must be (N, C, H, W)");
+    DNN_CHECK(k > 0, "avg_pool2d: kernel size must be positive");
+    if (stride <= 0) stride = k;
+    int N = x->shape[0], C = x->shape[1], H = x->shape[2], W = x->shape[3];
+    int H_out = (H - k) / stride + 1, W_out = (W - k) / stride + 1;
+    DNN_CHECK(H_out > 0 && W_out > 0, "avg_pool2d: kernel too large for input");
+    int shape[4] = {N, C, H_out, W_out};
+    tensor *out = tensor_scratch(scratch, 4, shape, 0);
+    const float *xd = (const float *)x->data + x->offset;
+    if (!x->contiguous) {
+        float *tmp = dev_alloc_t<float>(scratch, (size_t)numel_of(x));
+        k_gather(tmp, (const float *)x->data, view_of(x), numel_of(x));
+        xd = tmp;
+    }
+    int64_t planes = (int64_t)N * C;
+    avgpool_fwd_kernel<<<grid_for(planes * H_out * W_out, 256), 256, 0, stream()>>>(xd, (float *)out->data, planes, H, W,
+                                                                                    H_out, W_out, k, stride, 1.0f / (float)(k * k));
+    LAUNCHED("avgpool_fwd_kernel");
+    if (dnn_grad_enabled() && x->requires_grad) {
+        grad_fn *fn = attach(scratch, out, avg_pool2d_backward, 1, 2);
+        fn->inputs[0] = (tensor *)x;
+        int *ks = host_alloc_t<int>(scratch), *ss = host_alloc_t<int>(scratch);
+        *ks = k; *ss = stride;
+        fn->saved_tensors[0] = (tensor *)ks; fn->saved_tensors[1] = (tensor *)ss;
+    }
+    return out;
+}
+
+}  // extern "C"

@@ -1,0 +1,96 @@
+// fp32 FMA GEMM with arbitrary element strides on every operand.
+//
+// This is the exact-fp32 path (DNN_CUDA_GEMM_FP32) and the path for shapes the
+// tensor-core kernel cannot take (row pitches that are not multiples of 16
+// bytes, e.g. a [128,10] weight).  64x64 output tile, K step 16, 256 threads,
+// 4x4 outputs per thread, operands staged through shared memory with the
+// thread->element mapping chosen so that the unit-stride dimension of each
+// operand is the one adjacent threads walk.
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace dnnb {
+
+constexpr int SBM = 64, SBN = 64, SBK = 16;
+
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(GemmArgs g) {
+    __shared__ float As[SBK][SBM + 4];
+    __shared__ float Bs[SBK][SBN + 4];
+    int tid = threadIdx.x;
+    int bz = blockIdx.z;
+    const float *A = g.A + (int64_t)bz * g.a_bs;
+    const float *B = g.B + (int64_t)bz * g.b_bs;
+    float *C = g.C + (int64_t)bz * g.c_bs;
+    int m0 = blockIdx.y * SBM, n0 = blockIdx.x * SBN;
+    int ty = tid >> 4, tx = tid & 15;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+    bool a_kfast = (g.a_cs == 1);      // K contiguous in A
+    bool b_nfast = (g.b_cs == 1);      // N contiguous in B
+    for (int k0 = 0; k0 < g.K; k0 += SBK) {
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            int idx = tid + t * 256;
+            int m, k;
+            if (a_kfast) { k = idx & (SBK - 1); m = idx >> 4; } else { m = idx & (SBM - 1); k = idx >> 6; }
+            int gm = m0 + m, gk = k0 + k;
+            As[k][m] = (gm < g.M && gk < g.K) ? A[(int64_t)gm * g.a_rs + (int64_t)gk * g.a_cs] : 0.f;
+            int n;
+            if (b_nfast) { n = idx & (SBN - 1); k = idx >> 6; } else { k = idx & (SBK - 1); n = idx >> 4; }
+            int gn = n0 + n; gk = k0 + k;
+            Bs[k][n] = (gn < g.N && gk < g.K) ? B[(int64_t)gk * g.b_rs + (int64_t)gn * g.b_cs] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < SBK; k++) {
+            float4 av = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
+            float4 bv = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4]);
+            float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int gm = m0 + ty * 4 + i;
+        if (gm >= g.M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int gn = n0 + tx * 4 + j;
+            if (gn >= g.N) continue;
+            float v = acc[i][j];
+            if (g.bias) v += g.bias[gn];
+            float *c = C + (int64_t)gm * g.c_rs + (int64_t)gn * g.c_cs;
+            *c = g.accumulate ? *c + v : v;
+        }
+    }
+}
+
+void gemm_simt(const GemmArgs &g) {
+    if (g.M <= 0 || g.N <= 0 || g.batch <= 0) return;
+    GemmArgs a = g;
+    // gridDim.z is limited to 65535: chunk very large batch counts
+    for (int b0 = 0; b0 < g.batch; b0 += 65535) {
+        int nb = g.batch - b0 < 65535 ? g.batch - b0 : 65535;
+        a.A = g.A + (int64_t)b0 * g.a_bs; a.B = g.B + (int64_t)b0 * g.b_bs; a.C = g.C + (int64_t)b0 * g.c_bs;
+        dim3 grid((g.N + SBN - 1) / SBN, (g.M + SBM - 1) / SBM, nb);
+        gemm_simt_kernel<<<grid, 256, 0, stream()>>>(a);
+        LAUNCHED("gemm_simt_kernel");
+    }
+}
+
+void gemm(const GemmArgs &g) {
+    int mode = gemm_mode();
+    if (mode != DNN_CUDA_GEMM_FP32 && gemm_tc_supported(g)) gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32);
+    else gemm_simt(g);
+}
+
+}  // namespace dnnb

@@ -1,0 +1,151 @@
+// Small bandwidth-bound utility kernels used by several ops: fill, copy,
+// accumulate, strided gather / scatter and column sums.
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace dnnb {
+
+// ---- fill / copy / accumulate (128-bit when the pointers allow it) -------
+__global__ void fill_kernel(float *__restrict__ p, int64_t n, float v) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) p[i] = v;
+}
+
+__global__ void acc_kernel_v4(float4 *__restrict__ dst, const float4 *__restrict__ src, int64_t n4) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i < n4; i += stride) {
+        float4 d = dst[i], s = src[i];
+        d.x += s.x; d.y += s.y; d.z += s.z; d.w += s.w;
+        dst[i] = d;
+    }
+}
+__global__ void acc_kernel(float *__restrict__ dst, const float *__restrict__ src, int64_t n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] += src[i];
+}
+
+void k_fill(float *p, int64_t n, float v) {
+    if (n <= 0) return;
+    if (v == 0.0f) { CUDA_OK(cudaMemsetAsync(p, 0, (size_t)n * 4, stream())); return; }
+    fill_kernel<<<grid_for(n, 256), 256, 0, stream()>>>(p, n, v);
+    LAUNCHED("fill_kernel");
+}
+
+void k_axpy_acc(float *dst, const float *src, int64_t n) {
+    if (n <= 0) return;
+    if (aligned16(dst) && aligned16(src) && n % 4 == 0) {
+        acc_kernel_v4<<<grid_for(n / 4, 256), 256, 0, stream()>>>((float4 *)dst, (const float4 *)src, n / 4);
+        LAUNCHED("acc_kernel_v4");
+    } else {
+        acc_kernel<<<grid_for(n, 256), 256, 0, stream()>>>(dst, src, n);
+        LAUNCHED("acc_kernel");
+    }
+}
+
+void k_copy(float *dst, const float *src, int64_t n) {
+    if (n <= 0) return;
+    CUDA_OK(cudaMemcpyAsync(dst, src, (size_t)n * 4, cudaMemcpyDeviceToDevice, stream()));
+}
+
+// ---- strided gather / scatter ---------------------------------------------
+__device__ __forceinline__ int64_t view_offset(const View &v, int64_t flat) {
+    int64_t off = v.offset;
+#pragma unroll
+    for (int d = DNN_MAX_DIMS - 1; d >= 0; d--) {
+        if (d < v.ndim) {
+            int c = (int)(flat % v.shape[d]);
+            flat /= v.shape[d];
+            off += (int64_t)c * v.strides[d];
+        }
+    }
+    return off;
+}
+
+__global__ void gather_kernel(float *__restrict__ dst, const float *__restrict__ src, View sv, int64_t n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = src[view_offset(sv, i)];
+}
+
+// Each destination address is written by exactly one i when the view has no
+// zero strides over extents > 1; callers guarantee that.
+__global__ void scatter_kernel(float *__restrict__ dst, View dv, const float *__restrict__ src, int64_t n, int acc) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        int64_t o = view_offset(dv, i);
+        dst[o] = acc ? dst[o] + src[i] : src[i];
+    }
+}
+
+void k_gather(float *dst, const float *src, const View &sv, int64_t n) {
+    if (n <= 0) return;
+    gather_kernel<<<grid_for(n, 256), 256, 0, stream()>>>(dst, src, sv, n);
+    LAUNCHED("gather_kernel");
+}
+
+void k_scatter(float *dst, const View &dv, const float *src, int64_t n, bool accumulate) {
+    if (n <= 0) return;
+    scatter_kernel<<<grid_for(n, 256), 256, 0, stream()>>>(dst, dv, src, n, accumulate ? 1 : 0);
+    LAUNCHED("scatter_kernel");
+}
+
+// ---- column sums: out[c] += sum_r g[r*C + c] ------------------------------
+// Stage 1: CTA (cx, ry) sums rows [ry*rows_per, ...) of 32 columns into
+// partial[ry][c]; stage 2 adds the partials in row-block order, so the result
+// does not depend on scheduling.
+__global__ void colsum_partial_kernel(const float *__restrict__ g, float *__restrict__ partial,
+                                      int64_t rows, int C, int rows_per) {
+    __shared__ float tile[32][33];
+    int c = blockIdx.x * 32 + threadIdx.x;
+    int64_t r0 = (int64_t)blockIdx.y * rows_per;
+    int64_t r1 = r0 + rows_per; if (r1 > rows) r1 = rows;
+    float s = 0.f;
+    if (c < C)
+        for (int64_t r = r0 + threadIdx.y; r < r1; r += blockDim.y) s += g[r * C + c];
+    tile[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float t = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; j++) t += tile[j][threadIdx.x];
+        partial[(int64_t)blockIdx.y * C + c] = t;
+    }
+}
+__global__ void colsum_final_kernel(float *__restrict__ out, const float *__restrict__ partial, int nparts, int C) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float s = 0.f;
+    for (int p = 0; p < nparts; p++) s += partial[(int64_t)p * C + c];
+    out[c] += s;
+}
+
+// Scratch for the partials lives in a small cache owned by this file, grown
+// on demand (never shrinks; one per process).
+static float *g_colsum_scratch = nullptr;
+static size_t g_colsum_cap = 0;
+
+void k_colsum_acc(float *out, const float *g, int64_t rows, int C) {
+    if (rows <= 0 || C <= 0) return;
+    int nparts = (int)((rows + 255) / 256);
+    if (nparts > 512) nparts = 512;
+    int rows_per = (int)((rows + nparts - 1) / nparts);
+    nparts = (int)((rows + rows_per - 1) / rows_per);
+    size_t need = (size_t)nparts * C * sizeof(float);
+    if (need > g_colsum_cap) {
+        CUDA_OK(cudaStreamSynchronize(stream()));
+        if (g_colsum_scratch) CUDA_OK(cudaFree(g_colsum_scratch));
+        g_colsum_cap = need * 2;
+        CUDA_OK(cudaMalloc((void **)&g_colsum_scratch, g_colsum_cap));
+    }
+    dim3 grid((C + 31) / 32, nparts), block(32, 32);
+    colsum_partial_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per);
+    LAUNCHED("colsum_partial_kernel");
+    colsum_final_kernel<<<(C + 127) / 128, 128, 0, stream()>>>(out, g_colsum_scratch, nparts, C);
+    LAUNCHED("colsum_final_kernel");
+}
+
+}  // namespace dnnb

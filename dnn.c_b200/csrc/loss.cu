@@ -1,0 +1,241 @@
+// Cross-entropy and masked cross-entropy, forward and backward.
+// replaces src/ops_activation.c:852-1145 (plain) and :1154-1410 (masked).
+//
+// A "slice" is one vector along the class dimension.  One CTA owns one slice:
+// forward makes a single pass (online max / sum-of-exponentials per thread,
+// merged across the CTA), backward makes one read pass over the logits and one
+// read-modify-write pass over their gradient.  Rows whose last stride is 1 and
+// whose start is 16-byte aligned move as float4.  The scalar loss is produced
+// by a single-CTA tree sum over the per-slice terms (fixed order).
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace dnnb {
+
+struct SliceMap {
+    int nd;                         // dims other than the class dim
+    int shape[DNN_MAX_DIMS];
+    int lstride[DNN_MAX_DIMS];      // logits strides for those dims
+    int mstride[DNN_MAX_DIMS];      // mask strides (0 where mask dim is 1 or no mask)
+    int loff, moff;
+    int C, cstride;                 // class count and stride along the class dim
+};
+
+__device__ __forceinline__ void slice_offsets(const SliceMap &m, int64_t s, int64_t &lo, int64_t &mo) {
+    lo = m.loff; mo = m.moff;
+    for (int d = m.nd - 1; d >= 0; d--) {
+        int c = (int)(s % m.shape[d]); s /= m.shape[d];
+        lo += (int64_t)c * m.lstride[d]; mo += (int64_t)c * m.mstride[d];
+    }
+}
+
+__device__ __forceinline__ void online_add(float &mx, float &se, float v) {
+    if (v > mx) { se *= expf(mx - v); mx = v; }
+    se += expf(v - mx);
+}
+__device__ __forceinline__ void online_merge(float &mx, float &se, float omx, float ose) {
+    if (omx == -INFINITY) return;
+    if (mx == -INFINITY) { mx = omx; se = ose; return; }
+    if (omx > mx) { se = se * expf(mx - omx) + ose; mx = omx; }
+    else se += ose * expf(omx - mx);
+}
+
+__global__ void ce_fwd_kernel(const float *__restrict__ logits, const int *__restrict__ target,
+                              const float *__restrict__ mask, SliceMap map,
+                              float *__restrict__ max_out, float *__restrict__ se_out,
+                              float *__restrict__ term_out, float *__restrict__ mval_out) {
+    __shared__ float smx[32], sse[32];
+    int64_t s = blockIdx.x;
+    int64_t lo, mo;
+    slice_offsets(map, s, lo, mo);
+    float m = mask ? mask[mo] : 1.0f;
+    if (mval_out && threadIdx.x == 0) mval_out[s] = m;
+    if (mask && m == 0.0f) {          // skipped slice: contributes nothing
+        if (threadIdx.x == 0) { term_out[s] = 0.f; max_out[s] = -INFINITY; se_out[s] = 0.f; }
+        return;
+    }
+    const float *row = logits + lo;
+    int C = map.C;
+    float mx = -INFINITY, se = 0.f;
+    if (map.cstride == 1 && (C & 3) == 0 && (((uintptr_t)row) & 15) == 0) {
+        const float4 *r4 = reinterpret_cast<const float4 *>(row);
+        for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
+            float4 v = r4[j];
+            float cm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+            if (cm > mx) { se *= expf(mx - cm); mx = cm; }
+            se += expf(v.x - mx) + expf(v.y - mx) + expf(v.z - mx) + expf(v.w - mx);
+        }
+    } else {
+        for (int j = threadIdx.x; j < C; j += blockDim.x) online_add(mx, se, row[(int64_t)j * map.cstride]);
+    }
+    // merge across the CTA
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float omx = __shfl_xor_sync(0xffffffffu, mx, o), ose = __shfl_xor_sync(0xffffffffu, se, o);
+        online_merge(mx, se, omx, ose);
+    }
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { smx[w] = mx; sse[w] = se; }
+    __syncthreads();
+    if (w == 0) {
+        mx = lane < nw ? smx[lane] : -INFINITY;
+        se = lane < nw ? sse[lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float omx = __shfl_xor_sync(0xffffffffu, mx, o), ose = __shfl_xor_sync(0xffffffffu, se, o);
+            online_merge(mx, se, omx, ose);
+        }
+        if (lane == 0) {
+            int t = target[s];
+            float xt = row[(int64_t)t * map.cstride];
+            max_out[s] = mx; se_out[s] = se;
+            term_out[s] = (logf(se) + mx - xt) * m;
+        }
+    }
+}
+
+// loss = sum(term) * inv, inv = 1/n_slices or 1/max(sum(mask),1); also stores inv.
+__global__ void ce_reduce_kernel(const float *__restrict__ term, const float *__restrict__ mval, int64_t n,
+                                 float inv_n, float *__restrict__ loss_out, float *__restrict__ inv_out) {
+    __shared__ float sh[32];
+    float s = 0.f, ms = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { s += term[i]; if (mval) ms += mval[i]; }
+    s = block_sum(s, sh);
+    float inv = inv_n;
+    if (mval) {
+        ms = block_sum(ms, sh);
+        if (ms < 1.0f) ms = 1.0f;
+        inv = 1.0f / ms;
+    }
+    if (threadIdx.x == 0) { loss_out[0] = s * inv; inv_out[0] = inv; }
+}
+
+__global__ void ce_bwd_kernel(const float *__restrict__ logits, const int *__restrict__ target,
+                              const float *__restrict__ mask, SliceMap map,
+                              const float *__restrict__ max_in, const float *__restrict__ se_in,
+                              const float *__restrict__ gout, const float *__restrict__ inv,
+                              float *__restrict__ dlogits) {
+    int64_t s = blockIdx.x;
+    int64_t lo, mo;
+    slice_offsets(map, s, lo, mo);
+    float m = mask ? mask[mo] : 1.0f;
+    if (mask && m == 0.0f) return;
+    const float *row = logits + lo;
+    float *drow = dlogits + lo;
+    float mx = max_in[s], se = se_in[s];
+    int tgt = target[s];
+    float scale = gout[0] * inv[0];
+    if (mask) scale *= m;
+    int C = map.C;
+    if (map.cstride == 1 && (C & 3) == 0 && (((uintptr_t)row) & 15) == 0) {
+        const float4 *r4 = reinterpret_cast<const float4 *>(row);
+        float4 *d4 = reinterpret_cast<float4 *>(drow);
+        for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
+            float4 v = r4[j], d = d4[j];
+            int c = j * 4;
+            d.x += (expf(v.x - mx) / se - (c == tgt ? 1.f : 0.f)) * scale;
+            d.y += (expf(v.y - mx) / se - (c + 1 == tgt ? 1.f : 0.f)) * scale;
+            d.z += (expf(v.z - mx) / se - (c + 2 == tgt ? 1.f : 0.f)) * scale;
+            d.w += (expf(v.w - mx) / se - (c + 3 == tgt ? 1.f : 0.f)) * scale;
+            d4[j] = d;
+        }
+    } else {
+        for (int j = threadIdx.x; j < C; j += blockDim.x) {
+            int64_t o = (int64_t)j * map.cstride;
+            drow[o] += (expf(row[o] - mx) / se - (j == tgt ? 1.f : 0.f)) * scale;
+        }
+    }
+}
+
+static SliceMap make_map(const tensor *logits, const tensor *mask, int dim) {
+    SliceMap m;
+    memset(&m, 0, sizeof m);
+    m.loff = logits->offset; m.moff = mask ? mask->offset : 0;
+    m.C = logits->shape[dim]; m.cstride = logits->strides[dim];
+    int k = 0;
+    for (int d = 0; d < logits->ndim; d++) {
+        if (d == dim) continue;
+        m.shape[k] = logits->shape[d];
+        m.lstride[k] = logits->strides[d];
+        // mask has the target's shape: dims of logits without the class dim (src/ops_activation.c:1154-1166)
+        m.mstride[k] = (mask && k < mask->ndim && mask->shape[k] != 1) ? mask->strides[k] : 0;
+        k++;
+    }
+    m.nd = k;
+    return m;
+}
+
+struct CeSaved { float *max_vals, *sum_exp, *inv; };
+
+static void ce_backward_common(grad_fn *fn, tensor *go, bool masked) {
+    tensor *logits = fn->inputs[0];
+    if (!wants_grad(logits)) return;
+    const float *max_vals = (const float *)fn->saved_tensors[0];
+    const float *sum_exp = (const float *)fn->saved_tensors[1];
+    tensor *target = fn->saved_tensors[2];
+    tensor *mask = masked ? fn->saved_tensors[3] : nullptr;
+    int dim = *(int *)fn->saved_tensors[masked ? 4 : 3];
+    const float *inv = (const float *)fn->saved_tensors[masked ? 5 : 4];
+    float *ag = _grad_ensure(logits);
+    SliceMap map = make_map(logits, mask, dim);
+    int64_t n_slices = numel_of(logits) / map.C;
+    if (n_slices <= 0) return;
+    ce_bwd_kernel<<<(unsigned)n_slices, 256, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
+        mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, ag);
+    LAUNCHED(masked ? "ce_masked_bwd_kernel" : "ce_bwd_kernel");
+}
+static void cross_entropy_backward(grad_fn *fn, tensor *go) { ce_backward_common(fn, go, false); }
+static void cross_entropy_masked_backward(grad_fn *fn, tensor *go) { ce_backward_common(fn, go, true); }
+
+static tensor *ce_forward(struct mem_pool *scratch, const tensor *logits, const tensor *target, const tensor *mask, int dim) {
+    int ndim = logits->ndim;
+    if (dim < 0) dim += ndim;
+    DNN_CHECK(dim >= 0 && dim < ndim, "tensor_cross_entropy: dim out of range");
+    SliceMap map = make_map(logits, mask, dim);
+    int64_t n_slices = numel_of(logits) / map.C;
+    DNN_CHECK(n_slices > 0, "tensor_cross_entropy: empty logits");
+    float *max_vals = dev_alloc_t<float>(scratch, (size_t)n_slices);
+    float *sum_exp = dev_alloc_t<float>(scratch, (size_t)n_slices);
+    float *term = dev_alloc_t<float>(scratch, (size_t)n_slices);
+    float *mval = mask ? dev_alloc_t<float>(scratch, (size_t)n_slices) : nullptr;
+    float *inv = dev_alloc_t<float>(scratch, 1);
+    int one = 1;
+    tensor *out = tensor_scratch(scratch, 1, &one, 0);
+    ce_fwd_kernel<<<(unsigned)n_slices, 256, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
+        mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, term, mval);
+    LAUNCHED(mask ? "ce_masked_fwd_kernel" : "ce_fwd_kernel");
+    ce_reduce_kernel<<<1, 1024, 0, stream()>>>(term, mval, n_slices, 1.0f / (float)n_slices, (float *)out->data, inv);
+    LAUNCHED("ce_reduce_kernel");
+    if (dnn_grad_enabled() && logits->requires_grad) {
+        int k = 0;
+        grad_fn *fn = attach(scratch, out, mask ? cross_entropy_masked_backward : cross_entropy_backward, 1, mask ? 6 : 5);
+        fn->inputs[0] = (tensor *)logits;
+        fn->saved_tensors[k++] = (tensor *)max_vals;
+        fn->saved_tensors[k++] = (tensor *)sum_exp;
+        fn->saved_tensors[k++] = (tensor *)target;
+        if (mask) fn->saved_tensors[k++] = (tensor *)mask;
+        int *sd = host_alloc_t<int>(scratch); *sd = dim;
+        fn->saved_tensors[k++] = (tensor *)sd;
+        fn->saved_tensors[k++] = (tensor *)inv;
+    }
+    return out;
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+tensor *tensor_cross_entropy(struct mem_pool *scratch, const tensor *logits, const tensor *target, int dim) {
+    DNN_CHECK(logits && target, "tensor_cross_entropy: NULL argument");
+    return ce_forward(scratch, logits, target, nullptr, dim);
+}
+
+tensor *tensor_cross_entropy_masked(struct mem_pool *scratch, const tensor *logits, const tensor *target,
+                                    const tensor *mask, int dim) {
+    DNN_CHECK(logits && target && mask, "tensor_cross_entropy_masked: NULL argument");
+    return ce_forward(scratch, logits, target, mask, dim);
+}
+
+}  // extern "C"

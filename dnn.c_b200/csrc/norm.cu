@@ -1,0 +1,312 @@
+// RMSNorm and LayerNorm, forward and backward.
+// replaces src/norm.c:13-495 of the reference.
+//
+// All four kernels are HBM-bound.  One warp owns one row at a time and walks
+// rows grid-stride; lanes read the row as float4 (128-bit, coalesced) and
+// reduce with warp shuffles.  In backward each lane also carries the partial
+// weight/bias gradients of the columns it owns across all the rows its warp
+// visits, writes them once to a [warps, d] partial buffer, and a second small
+// kernel adds the partials in a fixed order, so the result is deterministic
+// (the reference's own loop is racy under OpenMP, src/norm.c:299-321).
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace dnnb {
+
+constexpr int kWarpsPerCta = 8;
+
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+
+// ---- forward ---------------------------------------------------------------
+// LN=false: rstd = 1/sqrt(mean(x^2)+eps), y = x*rstd*w
+// LN=true : mean, rstd = 1/sqrt(var+eps), y = (x-mean)*rstd*w + b
+template <bool LN, bool VEC>
+__global__ void norm_fwd_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b,
+                                float *__restrict__ y, float *__restrict__ mean_out, float *__restrict__ rstd_out,
+                                int64_t rows, int d, float eps) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+    float inv_d = 1.0f / (float)d;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const float *xr = x + r * d;
+        float *yr = y + r * d;
+        float s = 0.f, mu = 0.f;
+        if (LN) {
+            if (VEC) for (int j = lane * 4; j < d; j += 128) { float4 v = ld4(xr + j); s += v.x + v.y + v.z + v.w; }
+            else     for (int j = lane; j < d; j += 32) s += xr[j];
+            mu = warp_sum(s) * inv_d;
+            s = 0.f;
+            if (VEC) for (int j = lane * 4; j < d; j += 128) { float4 v = ld4(xr + j);
+                float a = v.x - mu, bb = v.y - mu, c = v.z - mu, e = v.w - mu; s += a * a + bb * bb + c * c + e * e; }
+            else     for (int j = lane; j < d; j += 32) { float a = xr[j] - mu; s += a * a; }
+        } else {
+            if (VEC) for (int j = lane * 4; j < d; j += 128) { float4 v = ld4(xr + j); s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+            else     for (int j = lane; j < d; j += 32) { float a = xr[j]; s += a * a; }
+        }
+        s = warp_sum(s);
+        float rs = 1.0f / sqrtf(s * inv_d + eps);
+        if (lane == 0) { rstd_out[r] = rs; if (LN) mean_out[r] = mu; }
+        if (VEC) {
+            for (int j = lane * 4; j < d; j += 128) {
+                float4 v = ld4(xr + j);
+                float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+                float4 bb = (LN && b) ? ld4(b + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 o;
+                o.x = (v.x - mu) * rs * ww.x + bb.x; o.y = (v.y - mu) * rs * ww.y + bb.y;
+                o.z = (v.z - mu) * rs * ww.z + bb.z; o.w = (v.w - mu) * rs * ww.w + bb.w;
+                st4(yr + j, o);
+            }
+        } else {
+            for (int j = lane; j < d; j += 32)
+                yr[j] = (xr[j] - mu) * rs * (w ? w[j] : 1.f) + ((LN && b) ? b[j] : 0.f);
+        }
+    }
+}
+
+// ---- backward --------------------------------------------------------------
+// T = float4 slots per lane (d <= 128*T).  Per row:
+//   dy = g*w
+//   RMS: S = sum(dy*x); dx += rs*dy - rs*(rs^2/d*S)*x;                dw_j += g*x*rs
+//   LN : xmu=x-mu; a=mean(dy); c=mean(dy*xmu); dx += rs*(dy-a-xmu*c*rs^2); dw_j += g*xmu*rs; db_j += g
+template <bool LN, int T>
+__global__ void norm_bwd_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
+                                const float *__restrict__ mean, const float *__restrict__ rstd,
+                                float *__restrict__ dx, float *__restrict__ dw_part, float *__restrict__ db_part,
+                                int64_t rows, int d) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+    float inv_d = 1.0f / (float)d;
+    float4 aw[T], ab[LN ? T : 1];
+#pragma unroll
+    for (int t = 0; t < T; t++) { aw[t] = make_float4(0.f, 0.f, 0.f, 0.f); if (LN) ab[t] = aw[t]; }
+
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const float *xr = x + r * d, *gr = g + r * d;
+        float rs = rstd[r], mu = LN ? mean[r] : 0.f;
+        float4 xv[T], dyv[T];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int t = 0; t < T; t++) {
+            int j = (lane + 32 * t) * 4;
+            if (j < d) {
+                float4 v = ld4(xr + j), gg = ld4(gr + j);
+                float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+                v.x -= mu; v.y -= mu; v.z -= mu; v.w -= mu;
+                float4 dy = make_float4(gg.x * ww.x, gg.y * ww.y, gg.z * ww.z, gg.w * ww.w);
+                xv[t] = v; dyv[t] = dy;
+                s1 += dy.x * v.x + dy.y * v.y + dy.z * v.z + dy.w * v.w;
+                if (LN) s2 += dy.x + dy.y + dy.z + dy.w;
+                if (dw_part) {
+                    aw[t].x += gg.x * v.x * rs; aw[t].y += gg.y * v.y * rs;
+                    aw[t].z += gg.z * v.z * rs; aw[t].w += gg.w * v.w * rs;
+                }
+                if (LN && db_part) { ab[t].x += gg.x; ab[t].y += gg.y; ab[t].z += gg.z; ab[t].w += gg.w; }
+            }
+        }
+        s1 = warp_sum(s1);
+        if (LN) s2 = warp_sum(s2);
+        if (dx) {
+            float *dxr = dx + r * d;
+            float k1 = rs * rs * inv_d * s1;       // RMS: S_scaled ; LN: mean(dy*xmu)*rs^2
+            float mdy = LN ? s2 * inv_d : 0.f;
+#pragma unroll
+            for (int t = 0; t < T; t++) {
+                int j = (lane + 32 * t) * 4;
+                if (j < d) {
+                    float4 o = ld4(dxr + j), v = xv[t], dy = dyv[t];
+                    o.x += rs * (dy.x - mdy) - rs * k1 * v.x; o.y += rs * (dy.y - mdy) - rs * k1 * v.y;
+                    o.z += rs * (dy.z - mdy) - rs * k1 * v.z; o.w += rs * (dy.w - mdy) - rs * k1 * v.w;
+                    st4(dxr + j, o);
+                }
+            }
+        }
+    }
+    // every warp writes its partial (zeros when it saw no row)
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+        int j = (lane + 32 * t) * 4;
+        if (j < d) {
+            if (dw_part) st4(dw_part + warp * d + j, aw[t]);
+            if (LN && db_part) st4(db_part + warp * d + j, ab[t]);
+        }
+    }
+}
+
+// Scalar fallback for d not a multiple of 4, unaligned rows or d > 2048:
+// one CTA per row for dx, column sums done by separate kernels.
+template <bool LN>
+__global__ void norm_bwd_dx_scalar_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
+                                          const float *__restrict__ mean, const float *__restrict__ rstd,
+                                          float *__restrict__ dx, int d) {
+    __shared__ float sh[32];
+    int64_t r = blockIdx.x;
+    const float *xr = x + r * d, *gr = g + r * d;
+    float rs = rstd[r], mu = LN ? mean[r] : 0.f, inv_d = 1.0f / (float)d;
+    float s1 = 0.f, s2 = 0.f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float dy = gr[j] * (w ? w[j] : 1.f), v = xr[j] - mu;
+        s1 += dy * v; s2 += dy;
+    }
+    s1 = block_sum(s1, sh);
+    s2 = LN ? block_sum(s2, sh) : 0.f;
+    float k1 = rs * rs * inv_d * s1, mdy = LN ? s2 * inv_d : 0.f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float dy = gr[j] * (w ? w[j] : 1.f), v = xr[j] - mu;
+        dx[r * d + j] += rs * (dy - mdy) - rs * k1 * v;
+    }
+}
+// t[r,j] = g*(x-mu)*rs, to be column-summed
+template <bool LN>
+__global__ void norm_dw_terms_kernel(const float *__restrict__ x, const float *__restrict__ g, const float *__restrict__ mean,
+                                     const float *__restrict__ rstd, float *__restrict__ t, int64_t rows, int d) {
+    int64_t n = rows * d;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / d;
+        t[i] = g[i] * (x[i] - (LN ? mean[r] : 0.f)) * rstd[r];
+    }
+}
+
+// out[j] += sum_p part[p*d + j], p ascending
+__global__ void norm_part_reduce_kernel(float *__restrict__ out, const float *__restrict__ part, int nparts, int d) {
+    int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= d) return;
+    float s = 0.f;
+    for (int p = 0; p < nparts; p++) s += part[(int64_t)p * d + j];
+    out[j] += s;
+}
+
+template <bool LN>
+static void norm_forward(const float *x, const float *w, const float *b, float *y, float *mean, float *rstd,
+                         int64_t rows, int d, float eps) {
+    if (rows <= 0) return;
+    bool vec = d % 4 == 0 && aligned16(x) && aligned16(y) && (!w || aligned16(w)) && (!b || aligned16(b));
+    int grid = (int)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+    int cap = kNumSMs * 8;
+    if (grid > cap) grid = cap;
+    if (vec) norm_fwd_kernel<LN, true><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
+    else     norm_fwd_kernel<LN, false><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
+    LAUNCHED(LN ? "layernorm_fwd_kernel" : "rmsnorm_fwd_kernel");
+}
+
+template <bool LN, int T>
+static void launch_bwd(const float *x, const float *w, const float *g, const float *mean, const float *rstd,
+                       float *dx, float *dwp, float *dbp, int64_t rows, int d, int grid) {
+    norm_bwd_kernel<LN, T><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d);
+    LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
+}
+
+template <bool LN>
+static void norm_backward(struct mem_pool *pool, const float *x, const float *w, const float *g, const float *mean,
+                          const float *rstd, float *dx, float *dw, float *db, int64_t rows, int d) {
+    if (rows <= 0) return;
+    bool vec = d % 4 == 0 && d <= 2048 && aligned16(x) && aligned16(g) && (!w || aligned16(w)) && (!dx || aligned16(dx));
+    if (vec) {
+        int grid = (int)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+        int cap = kNumSMs * 2;
+        if (grid > cap) grid = cap;
+        int nparts = grid * kWarpsPerCta;
+        float *dwp = dw ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
+        float *dbp = (LN && db) ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
+        int T = (d + 127) / 128;
+        if (T <= 1)      launch_bwd<LN, 1>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
+        else if (T <= 2) launch_bwd<LN, 2>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
+        else if (T <= 4) launch_bwd<LN, 4>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
+        else if (T <= 6) launch_bwd<LN, 6>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
+        else if (T <= 8) launch_bwd<LN, 8>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
+        else             launch_bwd<LN, 16>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
+        if (dwp) { norm_part_reduce_kernel<<<(d + 127) / 128, 128, 0, stream()>>>(dw, dwp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
+        if (dbp) { norm_part_reduce_kernel<<<(d + 127) / 128, 128, 0, stream()>>>(db, dbp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
+        return;
+    }
+    if (dx) {
+        norm_bwd_dx_scalar_kernel<LN><<<(unsigned)rows, 256, 0, stream()>>>(x, w, g, mean, rstd, dx, d);
+        LAUNCHED("norm_bwd_dx_scalar_kernel");
+    }
+    if (dw) {
+        float *t = dev_alloc_t<float>(pool, (size_t)rows * d);
+        norm_dw_terms_kernel<LN><<<grid_for(rows * d, 256), 256, 0, stream()>>>(x, g, mean, rstd, t, rows, d);
+        LAUNCHED("norm_dw_terms_kernel");
+        k_colsum_acc(dw, t, rows, d);
+    }
+    if (LN && db) k_colsum_acc(db, g, rows, d);
+}
+
+static void rms_backward(grad_fn *fn, tensor *go) {
+    tensor *x = fn->inputs[0];
+    tensor *weight = fn->saved_tensors[0];
+    const float *rstd = (const float *)fn->saved_tensors[1];
+    int d = x->shape[x->ndim - 1];
+    int64_t rows = numel_of(x) / d;
+    const float *xd = (const float *)x->data + x->offset;
+    const float *gd = (const float *)go->data;
+    const float *wd = weight ? (const float *)weight->data + weight->offset : nullptr;
+    float *dw = (weight && weight->requires_grad) ? _grad_ensure(weight) : nullptr;
+    float *dx = x->requires_grad ? _grad_ensure(x) : nullptr;   // the reference indexes dx from 0 (src/norm.c:339)
+    norm_backward<false>(fn->pool, xd, wd, gd, nullptr, rstd, dx, dw, nullptr, rows, d);
+}
+
+static void ln_backward(grad_fn *fn, tensor *go) {
+    tensor *x = fn->inputs[0];
+    tensor *weight = fn->saved_tensors[0], *bias = fn->saved_tensors[1];
+    const float *mean = (const float *)fn->saved_tensors[2], *rstd = (const float *)fn->saved_tensors[3];
+    int d = x->shape[x->ndim - 1];
+    int64_t rows = numel_of(x) / d;
+    const float *xd = (const float *)x->data + x->offset;
+    const float *gd = (const float *)go->data;
+    const float *wd = weight ? (const float *)weight->data + weight->offset : nullptr;
+    float *dw = (weight && weight->requires_grad) ? _grad_ensure(weight) : nullptr;
+    float *db = (bias && bias->requires_grad) ? _grad_ensure(bias) : nullptr;
+    float *dx = x->requires_grad ? _grad_ensure(x) : nullptr;
+    norm_backward<true>(fn->pool, xd, wd, gd, mean, rstd, dx, dw, db, rows, d);
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+tensor *tensor_rms_norm(struct mem_pool *scratch, const tensor *x, const tensor *weight, float eps) {
+    DNN_CHECK(x, "tensor_rms_norm: x is NULL");
+    DNN_CHECK(x->contiguous, "tensor_rms_norm: x must be contiguous");
+    int d = x->shape[x->ndim - 1];
+    int64_t rows = numel_of(x) / d;
+    float *rstd = dev_alloc_t<float>(scratch, (size_t)rows);
+    tensor *out = tensor_scratch(scratch, x->ndim, x->shape, 0);
+    const float *wd = weight ? tensor_data_ptr((tensor *)weight) : nullptr;
+    norm_forward<false>((const float *)x->data + x->offset, wd, nullptr, (float *)out->data, nullptr, rstd, rows, d, eps);
+    if (dnn_grad_enabled() && (x->requires_grad || (weight && weight->requires_grad))) {
+        grad_fn *fn = attach(scratch, out, rms_backward, 1, 2);
+        fn->inputs[0] = (tensor *)x;
+        fn->saved_tensors[0] = (tensor *)weight;
+        fn->saved_tensors[1] = (tensor *)rstd;
+    }
+    return out;
+}
+
+tensor *tensor_layer_norm(struct mem_pool *scratch, const tensor *x, const tensor *weight, const tensor *bias, float eps) {
+    DNN_CHECK(x, "tensor_layer_norm: x is NULL");
+    DNN_CHECK(x->contiguous, "tensor_layer_norm: x must be contiguous");
+    int d = x->shape[x->ndim - 1];
+    int64_t rows = numel_of(x) / d;
+    float *mean = dev_alloc_t<float>(scratch, (size_t)rows);
+    float *rstd = dev_alloc_t<float>(scratch, (size_t)rows);
+    tensor *out = tensor_scratch(scratch, x->ndim, x->shape, 0);
+    const float *wd = weight ? tensor_data_ptr((tensor *)weight) : nullptr;
+    const float *bd = bias ? tensor_data_ptr((tensor *)bias) : nullptr;
+    norm_forward<true>((const float *)x->data + x->offset, wd, bd, (float *)out->data, mean, rstd, rows, d, eps);
+    if (dnn_grad_enabled() && (x->requires_grad || (weight && weight->requires_grad) || (bias && bias->requires_grad))) {
+        grad_fn *fn = attach(scratch, out, ln_backward, 1, 4);
+        fn->inputs[0] = (tensor *)x;
+        fn->saved_tensors[0] = (tensor *)weight;
+        fn->saved_tensors[1] = (tensor *)bias;
+        fn->saved_tensors[2] = (tensor *)mean;
+        fn->saved_tensors[3] = (tensor *)rstd;
+    }
+    return out;
+}
+
+}  // extern "C"

@@ -1,0 +1,341 @@
+// Layout and indexing ops: rotary embedding, head split / merge, embedding
+// gather and scatter-add.  All HBM-bound copies with 128-bit accesses.
+// replaces src/rope.c:60-171, src/multihead.c:74-348, src/embedding.c:18-110.
+#include "common.cuh"
+#include "device_utils.cuh"
+#include <vector>
+
+namespace dnnb {
+
+// ---- RoPE --------------------------------------------------------------------
+// x viewed as [outer, N, d]; pair k of position n rotates by (cos,sin)[n, k].
+// Forward rotates x in place.  Backward adds the inverse rotation of g to dx.
+// One thread handles one float4 = two adjacent pairs.
+template <bool BWD>
+__global__ void rope_kernel(float *__restrict__ dst, const float *__restrict__ g,
+                            const float *__restrict__ fc, const float *__restrict__ fs,
+                            int64_t total4, int N, int d) {
+    int d4 = d >> 2, dh = d >> 1;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+        int q = (int)(i % d4);
+        int n = (int)((i / d4) % N);
+        float2 c = *reinterpret_cast<const float2 *>(fc + (int64_t)n * dh + 2 * q);
+        float2 s = *reinterpret_cast<const float2 *>(fs + (int64_t)n * dh + 2 * q);
+        if (!BWD) {
+            float4 v = reinterpret_cast<float4 *>(dst)[i];
+            float4 o;
+            o.x = v.x * c.x - v.y * s.x; o.y = v.x * s.x + v.y * c.x;
+            o.z = v.z * c.y - v.w * s.y; o.w = v.z * s.y + v.w * c.y;
+            reinterpret_cast<float4 *>(dst)[i] = o;
+        } else {
+            float4 v = reinterpret_cast<const float4 *>(g)[i];
+            float4 o = reinterpret_cast<float4 *>(dst)[i];
+            o.x += v.x * c.x + v.y * s.x;  o.y += -v.x * s.x + v.y * c.x;
+            o.z += v.z * c.y + v.w * s.y;  o.w += -v.z * s.y + v.w * c.y;
+            reinterpret_cast<float4 *>(dst)[i] = o;
+        }
+    }
+}
+template <bool BWD>
+__global__ void rope_pair_kernel(float *__restrict__ dst, const float *__restrict__ g,
+                                 const float *__restrict__ fc, const float *__restrict__ fs,
+                                 int64_t pairs, int N, int d) {
+    int dh = d >> 1;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += (int64_t)gridDim.x * blockDim.x) {
+        int k = (int)(i % dh);
+        int n = (int)((i / dh) % N);
+        float c = fc[(int64_t)n * dh + k], s = fs[(int64_t)n * dh + k];
+        if (!BWD) {
+            float a = dst[2 * i], b = dst[2 * i + 1];
+            dst[2 * i] = a * c - b * s; dst[2 * i + 1] = a * s + b * c;
+        } else {
+            float a = g[2 * i], b = g[2 * i + 1];
+            dst[2 * i] += a * c + b * s; dst[2 * i + 1] += -a * s + b * c;
+        }
+    }
+}
+
+static void rope_run(bool bwd, float *dst, const float *g, const float *fc, const float *fs, int64_t numel, int N, int d) {
+    if (numel <= 0) return;
+    bool vec = d % 4 == 0 && aligned16(dst) && (!g || aligned16(g)) && (((uintptr_t)fc | (uintptr_t)fs) & 7) == 0;
+    if (vec) {
+        int64_t n4 = numel / 4;
+        if (bwd) rope_kernel<true><<<grid_for(n4, 256), 256, 0, stream()>>>(dst, g, fc, fs, n4, N, d);
+        else     rope_kernel<false><<<grid_for(n4, 256), 256, 0, stream()>>>(dst, g, fc, fs, n4, N, d);
+    } else {
+        int64_t np = numel / 2;
+        if (bwd) rope_pair_kernel<true><<<grid_for(np, 256), 256, 0, stream()>>>(dst, g, fc, fs, np, N, d);
+        else     rope_pair_kernel<false><<<grid_for(np, 256), 256, 0, stream()>>>(dst, g, fc, fs, np, N, d);
+    }
+    LAUNCHED(bwd ? "rope_bwd_kernel" : "rope_fwd_kernel");
+}
+
+static void rope_backward(grad_fn *fn, tensor *go) {
+    tensor *x = fn->inputs[0];
+    tensor *fc = fn->saved_tensors[0], *fs = fn->saved_tensors[1];
+    if (!wants_grad(x)) return;
+    int d = x->shape[x->ndim - 1], N = x->shape[x->ndim - 2];
+    float *grad = _grad_ensure(x);
+    rope_run(true, grad + x->offset, (const float *)go->data + go->offset,
+             (const float *)fc->data + fc->offset, (const float *)fs->data + fs->offset, numel_of(x), N, d);
+}
+
+// ---- [B,P,Q,dk] <-> strided permutations ---------------------------------------
+// The packed side is indexed (b,p,q,i) row-major; the strided side at
+// b*sb + p*sp + q*sq + i.  MODE 0: packed <- strided.  1: strided = packed.  2: strided += packed.
+template <int MODE, typename V>
+__global__ void permute_kernel(float *__restrict__ packed_or_dst, float *__restrict__ strided,
+                               int64_t total, int P, int Q, int dkv, int64_t sb, int64_t sp, int64_t sq) {
+    constexpr int W = sizeof(V) / 4;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int i = (int)(idx % dkv);
+        int64_t r = idx / dkv;
+        int q = (int)(r % Q); r /= Q;
+        int p = (int)(r % P);
+        int64_t b = r / P;
+        V *pk = reinterpret_cast<V *>(packed_or_dst) + idx;
+        V *st = reinterpret_cast<V *>(strided + b * sb + p * sp + q * sq + (int64_t)i * W);
+        if (MODE == 0) *pk = *st;
+        else if (MODE == 1) *st = *pk;
+        else {
+            V a = *st, c = *pk;
+            float *af = reinterpret_cast<float *>(&a); const float *cf = reinterpret_cast<const float *>(&c);
+#pragma unroll
+            for (int k = 0; k < W; k++) af[k] += cf[k];
+            *st = a;
+        }
+    }
+}
+
+template <int MODE>
+static void permute(const char *name, float *packed, float *strided, int64_t B, int P, int Q, int dk,
+                    int64_t sb, int64_t sp, int64_t sq) {
+    int64_t n = B * P * Q * dk;
+    if (n <= 0) return;
+    bool vec = dk % 4 == 0 && aligned16(packed) && aligned16(strided) && sb % 4 == 0 && sp % 4 == 0 && sq % 4 == 0;
+    if (vec) permute_kernel<MODE, float4><<<grid_for(n / 4, 256), 256, 0, stream()>>>(packed, strided, n / 4, P, Q, dk / 4, sb, sp, sq);
+    else     permute_kernel<MODE, float><<<grid_for(n, 256), 256, 0, stream()>>>(packed, strided, n, P, Q, dk, sb, sp, sq);
+    LAUNCHED(name);
+}
+
+static void split_qkv_heads_backward(grad_fn *fn, tensor *go) {
+    tensor *qkv = fn->inputs[0];
+    int B = qkv->shape[0], N = qkv->shape[1], D = qkv->shape[2];
+    int which = *(int *)fn->saved_tensors[0];
+    int H = go->shape[1], dk = go->shape[3];
+    float *ig = _grad_ensure(qkv);
+    // packed g is [B,H,N,dk]; destination [B,N,3,H,dk]
+    permute<2>("split_qkv_bwd_kernel", (float *)go->data + go->offset, ig + qkv->offset + (int64_t)which * H * dk,
+               B, H, N, dk, (int64_t)N * D, dk, D);
+}
+
+static void merge_heads_backward(grad_fn *fn, tensor *go) {
+    tensor *in = fn->inputs[0];
+    int B = in->shape[0], H = in->shape[1], N = in->shape[2], dk = in->shape[3];
+    float *ig = _grad_ensure(in);
+    // packed g is [B,N,H,dk]; destination [B,H,N,dk]; overwrites (src/multihead.c:177)
+    permute<1>("merge_heads_bwd_kernel", (float *)go->data + go->offset, ig + in->offset,
+               B, N, H, dk, (int64_t)H * N * dk, dk, (int64_t)N * dk);
+}
+
+static void split_heads_backward(grad_fn *fn, tensor *go) {
+    tensor *in = fn->inputs[0];
+    int B = in->shape[0], N = in->shape[1], D = in->shape[2];
+    int H = *(int *)fn->saved_tensors[0];
+    int dk = D / H;
+    float *ig = _grad_ensure(in);
+    // packed g is [B,H,N,dk]; destination [B,N,H*dk]; overwrites (src/multihead.c:92)
+    permute<1>("split_heads_bwd_kernel", (float *)go->data + go->offset, ig + in->offset,
+               B, H, N, dk, (int64_t)N * D, dk, D);
+}
+
+// ---- embedding -------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(float *__restrict__ out, const float *__restrict__ table, const int *__restrict__ ids,
+                                     int n_ids, int d, int vocab, int64_t t_s0, int64_t t_s1, int vec) {
+    int row = blockIdx.x;
+    if (row >= n_ids) return;
+    int id = ids[row];
+    bool ok = id >= 0 && id < vocab;       // the reference asserts; an invalid id yields zeros here
+    if (vec) {
+        const float4 *src = reinterpret_cast<const float4 *>(table + (int64_t)id * t_s0);
+        float4 *dst = reinterpret_cast<float4 *>(out + (int64_t)row * d);
+        for (int j = threadIdx.x; j < d / 4; j += blockDim.x) dst[j] = ok ? src[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x)
+            out[(int64_t)row * d + j] = ok ? table[(int64_t)id * t_s0 + (int64_t)j * t_s1] : 0.f;
+    }
+}
+
+// Scatter-add with duplicate ids, deterministic: the CTA of the FIRST
+// occurrence of an id adds the rows of all its occurrences in ascending order
+// (the order of the reference's serial loop, src/embedding.c:37-43).
+__global__ void embedding_bwd_kernel(float *__restrict__ tg, const float *__restrict__ g, const int *__restrict__ ids,
+                                     int n_ids, int d, int vocab, int64_t g_s0, int64_t t_s0, int64_t t_s1) {
+    __shared__ int flags[256];
+    int i = blockIdx.x;
+    int id = ids[i];
+    if (id < 0 || id >= vocab) return;
+    int dup = 0;
+    for (int j = threadIdx.x; j < i; j += blockDim.x) dup |= (ids[j] == id);
+    if (__syncthreads_or(dup)) return;
+    for (int j0 = i; j0 < n_ids; j0 += blockDim.x) {
+        int j = j0 + threadIdx.x;
+        int f = (j < n_ids) && (ids[j] == id);
+        flags[threadIdx.x] = f;
+        if (__syncthreads_or(f)) {
+            for (int t = 0; t < blockDim.x; t++) {
+                if (!flags[t]) continue;
+                const float *gr = g + (int64_t)(j0 + t) * g_s0;
+                for (int c = threadIdx.x; c < d; c += blockDim.x)
+                    tg[(int64_t)id * t_s0 + (int64_t)c * t_s1] += gr[c];
+            }
+        }
+        __syncthreads();
+    }
+}
+
+static void embedding_backward(grad_fn *fn, tensor *go) {
+    tensor *table = fn->inputs[0];
+    tensor *ids = fn->saved_tensors[0];
+    if (!wants_grad(table)) return;
+    int n = ids->shape[0], d = table->shape[1];
+    if (n <= 0) return;
+    float *tg = _grad_ensure(table);
+    embedding_bwd_kernel<<<n, 256, 0, stream()>>>(tg, (const float *)go->data, (const int *)ids->data, n, d,
+                                                  table->shape[0], go->strides[0], table->strides[0], table->strides[1]);
+    LAUNCHED("embedding_bwd_kernel");
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+tensor *tensor_rope(struct mem_pool *scratch, tensor *x, const tensor *freqs_cos, const tensor *freqs_sin) {
+    DNN_CHECK(x && freqs_cos && freqs_sin, "tensor_rope: NULL argument");
+    DNN_CHECK(x->contiguous && freqs_cos->contiguous && freqs_sin->contiguous, "tensor_rope: operands must be contiguous");
+    DNN_CHECK(x->ndim >= 2, "tensor_rope: x must have at least 2 dims");
+    int d = x->shape[x->ndim - 1], N = x->shape[x->ndim - 2];
+    DNN_CHECK(d % 2 == 0, "tensor_rope: last dim must be even");
+    DNN_CHECK(freqs_cos->ndim == 2 && freqs_cos->shape[0] == N && freqs_cos->shape[1] == d / 2, "tensor_rope: cos table shape");
+    DNN_CHECK(freqs_sin->ndim == 2 && freqs_sin->shape[0] == N && freqs_sin->shape[1] == d / 2, "tensor_rope: sin table shape");
+    rope_run(false, (float *)x->data + x->offset, nullptr, (const float *)freqs_cos->data + freqs_cos->offset,
+             (const float *)freqs_sin->data + freqs_sin->offset, numel_of(x), N, d);
+    // The result shares x's payload but is its own autograd node with its own
+    // gradient buffer (src/rope.c:117-126).
+    tensor *out = (tensor *)_mem_pool_alloc(scratch, sizeof(tensor), x);
+    out->parent = nullptr; out->grad_fn = nullptr; out->grad = nullptr;
+    if (dnn_grad_enabled() && x->requires_grad) {
+        grad_fn *fn = attach(scratch, out, rope_backward, 1, 2);
+        fn->inputs[0] = x;
+        fn->saved_tensors[0] = (tensor *)freqs_cos;
+        fn->saved_tensors[1] = (tensor *)freqs_sin;
+    }
+    return out;
+}
+
+void tensor_rope_freqs_init(struct mem_pool *params, tensor **freqs_cos, tensor **freqs_sin,
+                            int dim, int max_seq_len, float base) {
+    DNN_CHECK(dim > 0 && dim % 2 == 0 && max_seq_len > 0, "tensor_rope_freqs_init: bad dims");
+    if (base == 0.0f) base = 10000.0f;
+    int dh = dim / 2;
+    int shape[2] = {max_seq_len, dh};
+    *freqs_cos = tensor_zeros(params, 2, shape, 0);
+    *freqs_sin = tensor_zeros(params, 2, shape, 0);
+    // Tables are computed on the host with libm, exactly as the reference does
+    // (src/rope.c:163-169), then uploaded: bit-identical tables.
+    std::vector<float> c((size_t)max_seq_len * dh), s((size_t)max_seq_len * dh);
+    for (int k = 0; k < dh; k++) {
+        float theta = powf(base, -2.0f * k / (float)dim);
+        for (int n = 0; n < max_seq_len; n++) {
+            float angle = (float)n * theta;
+            c[(size_t)n * dh + k] = cosf(angle);
+            s[(size_t)n * dh + k] = sinf(angle);
+        }
+    }
+    dnn_cuda_upload(*freqs_cos, c.data(), c.size() * 4);
+    dnn_cuda_upload(*freqs_sin, s.data(), s.size() * 4);
+}
+
+tensor *tensor_split_heads(struct mem_pool *scratch, tensor *t, int H) {
+    DNN_CHECK(t->ndim == 3, "split_heads: input must be 3D [B, N, H*d_k]");
+    DNN_CHECK(t->contiguous, "split_heads: input must be contiguous");
+    int B = t->shape[0], N = t->shape[1], D = t->shape[2];
+    DNN_CHECK(H > 0 && D % H == 0, "split_heads: D must be divisible by H");
+    int dk = D / H;
+    int shape[4] = {B, H, N, dk};
+    tensor *out = tensor_scratch(scratch, 4, shape, 0);
+    permute<0>("split_heads_fwd_kernel", (float *)out->data, (float *)t->data + t->offset, B, H, N, dk, (int64_t)N * D, dk, D);
+    if (dnn_grad_enabled() && t->requires_grad) {
+        grad_fn *fn = attach(scratch, out, split_heads_backward, 1, 1);
+        fn->inputs[0] = t;
+        int *h = host_alloc_t<int>(scratch); *h = H;
+        fn->saved_tensors[0] = (tensor *)h;
+    }
+    return out;
+}
+
+tensor *tensor_merge_heads(struct mem_pool *scratch, tensor *t) {
+    DNN_CHECK(t->ndim == 4, "merge_heads: input must be 4D [B, H, N, d_k]");
+    DNN_CHECK(t->contiguous, "merge_heads: input must be contiguous");
+    int B = t->shape[0], H = t->shape[1], N = t->shape[2], dk = t->shape[3];
+    int shape[3] = {B, N, H * dk};
+    tensor *out = tensor_scratch(scratch, 3, shape, 0);
+    permute<0>("merge_heads_fwd_kernel", (float *)out->data, (float *)t->data + t->offset, B, N, H, dk,
+               (int64_t)H * N * dk, dk, (int64_t)N * dk);
+    if (dnn_grad_enabled() && t->requires_grad) {
+        grad_fn *fn = attach(scratch, out, merge_heads_backward, 1, 0);
+        fn->inputs[0] = t;
+    }
+    return out;
+}
+
+void tensor_split_qkv_heads(struct mem_pool *scratch, tensor *qkv, int H,
+                            tensor **Qh_out, tensor **Kh_out, tensor **Vh_out) {
+    DNN_CHECK(qkv->ndim == 3, "split_qkv_heads: qkv must be 3D [B,N,3*H*d_k]");
+    DNN_CHECK(qkv->contiguous, "split_qkv_heads: qkv must be contiguous");
+    int B = qkv->shape[0], N = qkv->shape[1], D = qkv->shape[2];
+    DNN_CHECK(D % (3 * H) == 0, "split_qkv_heads: D must be 3*H*d_k");
+    int dk = D / (3 * H);
+    int shape[4] = {B, H, N, dk};
+    tensor *outs[3];
+    for (int i = 0; i < 3; i++) outs[i] = tensor_scratch(scratch, 4, shape, 0);
+    for (int i = 0; i < 3; i++)
+        permute<0>("split_qkv_fwd_kernel", (float *)outs[i]->data, (float *)qkv->data + qkv->offset + (int64_t)i * H * dk,
+                   B, H, N, dk, (int64_t)N * D, dk, D);
+    if (dnn_grad_enabled() && qkv->requires_grad) {
+        for (int i = 0; i < 3; i++) {
+            grad_fn *fn = attach(scratch, outs[i], split_qkv_heads_backward, 1, 1);
+            fn->inputs[0] = qkv;
+            int *idx = host_alloc_t<int>(scratch); *idx = i;
+            fn->saved_tensors[0] = (tensor *)idx;
+        }
+    }
+    *Qh_out = outs[0]; *Kh_out = outs[1]; *Vh_out = outs[2];
+}
+
+tensor *tensor_embedding(struct mem_pool *scratch, const tensor *table, const tensor *ids) {
+    DNN_CHECK(table && ids, "embedding: NULL argument");
+    DNN_CHECK(table->ndim == 2, "embedding: table must be 2D");
+    DNN_CHECK(ids->ndim == 1, "embedding: ids must be 1D");
+    DNN_CHECK(table->contiguous, "embedding: table must be contiguous");
+    int vocab = table->shape[0], d = table->shape[1], n = ids->shape[0];
+    int shape[2] = {n, d};
+    tensor *out = tensor_scratch(scratch, 2, shape, 0);
+    if (n > 0) {
+        const float *td = (const float *)table->data;     // the reference ignores table->offset here
+        int vec = d % 4 == 0 && aligned16(td) && aligned16(out->data) && table->strides[1] == 1 && table->strides[0] % 4 == 0;
+        embedding_fwd_kernel<<<n, 128, 0, stream()>>>((float *)out->data, td, (const int *)ids->data, n, d, vocab,
+                                                      table->strides[0], table->strides[1], vec);
+        LAUNCHED("embedding_fwd_kernel");
+    }
+    if (dnn_grad_enabled() && table->requires_grad) {
+        grad_fn *fn = attach(scratch, out, embedding_backward, 1, 1);
+        fn->inputs[0] = (tensor *)table;
+        fn->saved_tensors[0] = (tensor *)ids;
+    }
+    return out;
+}
+
+}  // extern "C"

@@ -1,0 +1,266 @@
+// AdamW, gradient norm / clipping, zero_grad and the LR schedules.
+// replaces src/optim.c:67-316 of the reference.
+//
+// The reference loops over parameter tensors with OpenMP, which is badly
+// balanced (one 24.6 M-element embedding next to 768-element gains).  Here all
+// tensors of one call are described by a small table and ONE launch covers
+// them: a CTA owns a fixed-size chunk of one tensor.  AdamW is HBM-bound at
+// 28 bytes per parameter (read p, g, m, v; write p, m, v).
+#include "common.cuh"
+#include "device_utils.cuh"
+#include <vector>
+#include <algorithm>
+
+namespace dnnb {
+
+constexpr int kChunk = 8192;       // elements per CTA (256 threads x 8 float4)
+
+struct TensorRef { float *p, *g, *m, *v; int64_t n; float lr; int first_chunk; };
+
+__device__ __forceinline__ int find_tensor(const TensorRef *tab, int nt, int chunk) {
+    int lo = 0, hi = nt - 1;
+    while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (tab[mid].first_chunk <= chunk) lo = mid; else hi = mid - 1; }
+    return lo;
+}
+
+struct AdamHyper { float b1, b2, eps, wd, bc1, bc2_sqrt; };
+
+__device__ __forceinline__ void adam1(float &p, float &m, float &v, float g, float lr, float step, const AdamHyper &h) {
+    m = h.b1 * m + (1.0f - h.b1) * g;
+    v = h.b2 * v + (1.0f - h.b2) * g * g;
+    float denom = sqrtf(v) / h.bc2_sqrt + h.eps;
+    p *= 1.0f - lr * h.wd;
+    p -= step * m / denom;
+}
+
+__global__ void __launch_bounds__(256) adamw_kernel(const TensorRef *__restrict__ tab, int nt, AdamHyper h) {
+    int t = find_tensor(tab, nt, blockIdx.x);
+    TensorRef r = tab[t];
+    int64_t start = (int64_t)(blockIdx.x - r.first_chunk) * kChunk;
+    int64_t end = start + kChunk < r.n ? start + kChunk : r.n;
+    float step = r.lr / h.bc1;
+    bool vec = ((((uintptr_t)r.p | (uintptr_t)r.g | (uintptr_t)r.m | (uintptr_t)r.v) & 15) == 0);
+    if (vec) {
+        int64_t e4 = start + ((end - start) & ~(int64_t)3);
+        for (int64_t i = start + threadIdx.x * 4; i < e4; i += 1024) {
+            float4 p = *(float4 *)(r.p + i), g = *(const float4 *)(r.g + i), m = *(float4 *)(r.m + i), v = *(float4 *)(r.v + i);
+            adam1(p.x, m.x, v.x, g.x, r.lr, step, h); adam1(p.y, m.y, v.y, g.y, r.lr, step, h);
+            adam1(p.z, m.z, v.z, g.z, r.lr, step, h); adam1(p.w, m.w, v.w, g.w, r.lr, step, h);
+            *(float4 *)(r.p + i) = p; *(float4 *)(r.m + i) = m; *(float4 *)(r.v + i) = v;
+        }
+        start = e4;
+    }
+    for (int64_t i = start + threadIdx.x; i < end; i += 256) adam1(r.p[i], r.m[i], r.v[i], r.g[i], r.lr, step, h);
+}
+
+// sum of squares per chunk in double (the reference accumulates in double, src/optim.c:194-204)
+__global__ void __launch_bounds__(256) sumsq_kernel(const TensorRef *__restrict__ tab, int nt, double *__restrict__ partial) {
+    __shared__ double sh[8];
+    int t = find_tensor(tab, nt, blockIdx.x);
+    TensorRef r = tab[t];
+    int64_t start = (int64_t)(blockIdx.x - r.first_chunk) * kChunk;
+    int64_t end = start + kChunk < r.n ? start + kChunk : r.n;
+    double s = 0.0;
+    for (int64_t i = start + threadIdx.x; i < end; i += 256) { double g = (double)r.g[i]; s += g * g; }
+    s = warp_sum_d(s);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) { double tt = 0.0; for (int w = 0; w < 8; w++) tt += sh[w]; partial[blockIdx.x] = tt; }
+}
+__global__ void sumsq_final_kernel(const double *__restrict__ partial, int n, float *__restrict__ out_norm, double *__restrict__ out_sq) {
+    __shared__ double sh[32];
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += partial[i];
+    s = warp_sum_d(s);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double tt = 0.0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) tt += sh[w];
+        out_sq[0] = tt;
+        out_norm[0] = sqrtf((float)tt);
+    }
+}
+__global__ void __launch_bounds__(256) scale_kernel(const TensorRef *__restrict__ tab, int nt, float scale) {
+    int t = find_tensor(tab, nt, blockIdx.x);
+    TensorRef r = tab[t];
+    int64_t start = (int64_t)(blockIdx.x - r.first_chunk) * kChunk;
+    int64_t end = start + kChunk < r.n ? start + kChunk : r.n;
+    for (int64_t i = start + threadIdx.x; i < end; i += 256) r.g[i] *= scale;
+}
+
+// Device-resident staging for the tables and reduction partials; grown on demand.
+struct OptScratch { TensorRef *tab = nullptr; size_t tab_cap = 0; double *partial = nullptr; size_t part_cap = 0;
+                    float *norm = nullptr; double *sq = nullptr; };
+static OptScratch g_os;
+
+static int upload_table(std::vector<TensorRef> &tab) {
+    int chunks = 0;
+    for (auto &r : tab) { r.first_chunk = chunks; chunks += (int)((r.n + kChunk - 1) / kChunk); }
+    if (tab.size() > g_os.tab_cap) {
+        CUDA_OK(cudaStreamSynchronize(stream()));
+        if (g_os.tab) CUDA_OK(cudaFree(g_os.tab));
+        g_os.tab_cap = tab.size() * 2 + 64;
+        CUDA_OK(cudaMalloc((void **)&g_os.tab, g_os.tab_cap * sizeof(TensorRef)));
+    }
+    if ((size_t)chunks > g_os.part_cap) {
+        CUDA_OK(cudaStreamSynchronize(stream()));
+        if (g_os.partial) CUDA_OK(cudaFree(g_os.partial));
+        g_os.part_cap = (size_t)chunks * 2 + 1024;
+        CUDA_OK(cudaMalloc((void **)&g_os.partial, g_os.part_cap * sizeof(double)));
+    }
+    if (!g_os.norm) { CUDA_OK(cudaMalloc((void **)&g_os.norm, sizeof(float))); CUDA_OK(cudaMalloc((void **)&g_os.sq, sizeof(double))); }
+    CUDA_OK(cudaMemcpyAsync(g_os.tab, tab.data(), tab.size() * sizeof(TensorRef), cudaMemcpyHostToDevice, stream()));
+    return chunks;
+}
+
+static std::vector<TensorRef> grad_table(tensor **params, int n_params) {
+    std::vector<TensorRef> tab;
+    for (int i = 0; i < n_params; i++) {
+        float *g = params[i]->grad;
+        if (!g) continue;
+        TensorRef r; r.p = nullptr; r.g = g; r.m = r.v = nullptr; r.n = numel_of(params[i]); r.lr = 0.f; r.first_chunk = 0;
+        if (r.n > 0) tab.push_back(r);
+    }
+    return tab;
+}
+
+// Sum of squared gradients -> device scalars; returns false when no grads exist.
+static bool grad_sumsq_device(tensor **params, int n_params, std::vector<TensorRef> &tab, int &chunks) {
+    tab = grad_table(params, n_params);
+    if (tab.empty()) return false;
+    chunks = upload_table(tab);
+    sumsq_kernel<<<chunks, 256, 0, stream()>>>(g_os.tab, (int)tab.size(), g_os.partial);
+    LAUNCHED("grad_sumsq_kernel");
+    sumsq_final_kernel<<<1, 1024, 0, stream()>>>(g_os.partial, chunks, g_os.norm, g_os.sq);
+    LAUNCHED("grad_sumsq_final_kernel");
+    return true;
+}
+
+static float lr_at(const lr_scheduler *s, int t) {
+    // src/optim.c:104-150
+    float base = s->base_lr;
+    if (s->warmup_iters > 0 && t < s->warmup_iters) return base * (float)(t + 1) / (float)s->warmup_iters;
+    int post = t - s->warmup_iters;
+    if (post < 0) post = 0;
+    switch (s->schedule) {
+    case LR_SCHEDULE_COSINE:
+    case LR_SCHEDULE_LINEAR_WARMUP_COSINE: {
+        int decay = s->total_iters - s->warmup_iters;
+        if (decay <= 0) return base;
+        float c = 0.5f * (1.0f + cosf((float)M_PI * post / decay));
+        return s->min_lr + (base - s->min_lr) * c;
+    }
+    case LR_SCHEDULE_STEP:
+        if (s->step_size <= 0) return base;
+        return base * powf(s->gamma, (float)(post / s->step_size));
+    case LR_SCHEDULE_EXPONENTIAL:
+        if (post == 0) return base;
+        return base * powf(s->gamma, (float)post);
+    default:
+        return base;
+    }
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+adamw_opt *adamw_create(struct mem_pool *params_pool, tensor **params, int n_params, float lr,
+                        float beta1, float beta2, float eps, float weight_decay) {
+    adamw_opt *opt = host_alloc_t<adamw_opt>(params_pool);
+    opt->params = params; opt->n_params = n_params; opt->lr = lr;
+    opt->beta1 = beta1; opt->beta2 = beta2; opt->eps = eps; opt->weight_decay = weight_decay; opt->t = 0;
+    opt->m = host_alloc_t<tensor *>(params_pool, n_params);
+    opt->v = host_alloc_t<tensor *>(params_pool, n_params);
+    for (int i = 0; i < n_params; i++) {
+        opt->m[i] = tensor_zeros(params_pool, params[i]->ndim, params[i]->shape, 0);
+        opt->v[i] = tensor_zeros(params_pool, params[i]->ndim, params[i]->shape, 0);
+    }
+    return opt;
+}
+void adamw_free(adamw_opt *opt) { (void)opt; }
+
+// Gradient buffers of the parameters are bump-allocated one after another, so
+// adjacent ones are merged into a single memset.
+void adamw_zero_grad(adamw_opt *opt) {
+    std::vector<std::pair<char *, size_t>> spans;
+    for (int i = 0; i < opt->n_params; i++) {
+        float *g = opt->params[i]->grad;
+        if (g) spans.emplace_back((char *)g, (size_t)numel_of(opt->params[i]) * 4);
+    }
+    std::sort(spans.begin(), spans.end());
+    size_t i = 0;
+    while (i < spans.size()) {
+        char *b = spans[i].first, *e = b + spans[i].second;
+        size_t j = i + 1;
+        // the gap up to the next 256-byte boundary is allocator padding
+        while (j < spans.size() && spans[j].first <= (char *)(((uintptr_t)e + 255) & ~(uintptr_t)255) && spans[j].first >= e) {
+            e = spans[j].first + spans[j].second; j++;
+        }
+        CUDA_OK(cudaMemsetAsync(b, 0, (size_t)(e - b), stream()));
+        i = j;
+    }
+}
+
+float grad_norm(tensor **params, int n_params) {
+    std::vector<TensorRef> tab; int chunks = 0;
+    if (!grad_sumsq_device(params, n_params, tab, chunks)) return 0.0f;
+    float h = 0.f;
+    dnn_cuda_memcpy_d2h(&h, g_os.norm, sizeof h);
+    return h;
+}
+
+float clip_grad_norm(tensor **params, int n_params, float max_norm) {
+    if (max_norm <= 0.0f) return 0.0f;
+    std::vector<TensorRef> tab; int chunks = 0;
+    if (!grad_sumsq_device(params, n_params, tab, chunks)) return 0.0f;
+    float total = 0.f;
+    dnn_cuda_memcpy_d2h(&total, g_os.norm, sizeof total);     // the API returns the norm: one sync per step
+    if (total > max_norm) {
+        float scale = max_norm / total;
+        scale_kernel<<<chunks, 256, 0, stream()>>>(g_os.tab, (int)tab.size(), scale);
+        LAUNCHED("grad_scale_kernel");
+    }
+    return total;
+}
+
+void adamw_step_with_lr_multipliers(adamw_opt *opt, const float *lr_mults) {
+    opt->t++;
+    AdamHyper h;
+    h.b1 = opt->beta1; h.b2 = opt->beta2; h.eps = opt->eps; h.wd = opt->weight_decay;
+    h.bc1 = 1.0f - powf(h.b1, (float)opt->t);
+    h.bc2_sqrt = sqrtf(1.0f - powf(h.b2, (float)opt->t));
+    std::vector<TensorRef> tab;
+    for (int i = 0; i < opt->n_params; i++) {
+        tensor *p = opt->params[i];
+        if (!p->grad) continue;                    // not in the backward graph (src/optim.c:287)
+        TensorRef r;
+        r.p = tensor_data_ptr(p); r.g = p->grad; r.m = tensor_data_ptr(opt->m[i]); r.v = tensor_data_ptr(opt->v[i]);
+        r.n = numel_of(p); r.lr = opt->lr * (lr_mults ? lr_mults[i] : 1.0f); r.first_chunk = 0;
+        if (r.n > 0) tab.push_back(r);
+    }
+    if (tab.empty()) return;
+    int chunks = upload_table(tab);
+    adamw_kernel<<<chunks, 256, 0, stream()>>>(g_os.tab, (int)tab.size(), h);
+    LAUNCHED("adamw_kernel");
+}
+void adamw_step(adamw_opt *opt) { adamw_step_with_lr_multipliers(opt, nullptr); }
+
+lr_scheduler *lr_scheduler_create(struct mem_pool *params_pool, adamw_opt *opt, int schedule, float base_lr,
+                                  int warmup_iters, int total_iters, float min_lr, int step_size, float gamma) {
+    lr_scheduler *s = host_alloc_t<lr_scheduler>(params_pool);
+    s->opt = opt; s->schedule = schedule; s->base_lr = base_lr; s->warmup_iters = warmup_iters;
+    s->total_iters = total_iters; s->step_size = step_size; s->gamma = gamma; s->t = 0;
+    s->min_lr = (min_lr < 0.0f) ? base_lr / 10.0f : min_lr;
+    opt->lr = lr_at(s, 0);
+    return s;
+}
+void  lr_scheduler_step(lr_scheduler *s) { s->t++; s->opt->lr = lr_at(s, s->t); }
+float lr_scheduler_get_lr(const lr_scheduler *s) { return lr_at(s, s->t); }
+void  lr_scheduler_reset(lr_scheduler *s) { s->t = 0; s->opt->lr = lr_at(s, 0); }
+void  lr_scheduler_destroy(lr_scheduler *s) { (void)s; }
+
+}  // extern "C"

@@ -1,0 +1,309 @@
+// Device runtime: the compute stream, the device arenas that shadow each
+// mem_pool, payload transfer and error reporting.
+//
+// Pools: replaces src/pool.c:8-57 and src/context.c:5-35 of the reference.
+// A mem_pool keeps its three public fields; `buffer` is a host mapping that
+// holds structs and saved scalars, and a device arena of the same capacity is
+// created on first payload allocation and found again through `buffer`.
+#include "common.cuh"
+#include <sys/mman.h>
+#include <unordered_map>
+#include <vector>
+#include <mutex>
+#include <string>
+
+namespace dnnb {
+
+struct Arena {
+    char  *base = nullptr;
+    size_t cap = 0, off = 0, peak = 0;
+    std::vector<std::pair<size_t, size_t>> marks;   // (host offset, device offset)
+};
+
+struct Runtime {
+    bool         ready = false;
+    int          device = 0;
+    cudaStream_t compute = nullptr;
+    int          gemm_mode = DNN_CUDA_GEMM_TF32;
+    long long    launches = 0;
+    std::string  last_error;
+    std::unordered_map<const void *, Arena> arenas;   // keyed by mem_pool.buffer
+};
+static Runtime g_rt;
+static std::mutex g_mu;
+
+static void set_error(const std::string &s) { g_rt.last_error = s; }
+
+void cuda_fail(cudaError_t e, const char *what, const char *file, int line) {
+    char buf[512];
+    snprintf(buf, sizeof buf, "CUDA error %d (%s) at %s:%d: %s", (int)e, cudaGetErrorString(e), file, line, what);
+    set_error(buf);
+    fprintf(stderr, "dnn_b200: %s\n", buf);
+    abort();
+}
+
+static int init_device(int device, bool may_abort) {
+    if (g_rt.ready) return 0;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        set_error(std::string("no usable CUDA device: ") + cudaGetErrorString(e));
+        (void)cudaGetLastError();
+        if (may_abort) {
+            fprintf(stderr, "dnn_b200: %s. This library runs on the GPU only; there is no CPU fallback.\n",
+                    g_rt.last_error.c_str());
+            abort();
+        }
+        return -1;
+    }
+    if (device < 0 || device >= n) { set_error("device index out of range"); if (may_abort) abort(); return -2; }
+    CUDA_OK(cudaSetDevice(device));
+    CUDA_OK(cudaStreamCreateWithFlags(&g_rt.compute, cudaStreamNonBlocking));
+    g_rt.device = device;
+    const char *mode = getenv("DNN_CUDA_GEMM");
+    if (mode) {
+        if (!strcmp(mode, "fp32")) g_rt.gemm_mode = DNN_CUDA_GEMM_FP32;
+        else if (!strcmp(mode, "tf32")) g_rt.gemm_mode = DNN_CUDA_GEMM_TF32;
+        else if (!strcmp(mode, "3xtf32")) g_rt.gemm_mode = DNN_CUDA_GEMM_3XTF32;
+    }
+    g_rt.ready = true;
+    return 0;
+}
+
+cudaStream_t stream() {
+    if (!g_rt.ready) init_device(0, true);
+    return g_rt.compute;
+}
+
+void launched(const char *name) {
+    g_rt.launches++;
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        char buf[256];
+        snprintf(buf, sizeof buf, "launch of %s", name);
+        cuda_fail(e, buf, __FILE__, __LINE__);
+    }
+}
+
+int gemm_mode() { return g_rt.gemm_mode; }
+
+static Arena *arena_of(const mem_pool *pool, bool create) {
+    DNN_CHECK(pool && pool->buffer, "pool is NULL or destroyed");
+    auto it = g_rt.arenas.find(pool->buffer);
+    if (it != g_rt.arenas.end()) return &it->second;
+    if (!create) return nullptr;
+    stream();   // make sure the device is initialised (aborts without one)
+    Arena a;
+    a.cap = pool->capacity;
+    cudaError_t e = cudaMalloc((void **)&a.base, a.cap ? a.cap : 256);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "dnn_b200: cannot reserve %zu bytes of device memory for a pool\n", a.cap);
+        cuda_fail(e, "cudaMalloc(pool arena)", __FILE__, __LINE__);
+    }
+    return &(g_rt.arenas[pool->buffer] = a);
+}
+
+void *dev_alloc(struct mem_pool *pool, size_t bytes, bool zero) {
+    Arena *a = arena_of(pool, true);
+    size_t need = (bytes + 255) & ~(size_t)255;
+    if (need == 0) need = 256;
+    if (a->off + need > a->cap) {
+        fprintf(stderr, "dnn_b200: pool out of device memory (capacity %zu, used %zu, wanted %zu)\n",
+                a->cap, a->off, need);
+        abort();
+    }
+    void *p = a->base + a->off;
+    a->off += need;
+    if (a->off > a->peak) a->peak = a->off;
+    if (zero) CUDA_OK(cudaMemsetAsync(p, 0, bytes, stream()));
+    return p;
+}
+
+void *dev_put(struct mem_pool *pool, const void *host, size_t bytes) {
+    void *d = dev_alloc(pool, bytes, false);
+    // pageable source: the runtime stages it before returning, so `host` may die
+    CUDA_OK(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, stream()));
+    return d;
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+// ── pools ───────────────────────────────────────────────────────────────
+mem_pool mem_pool_create(size_t capacity) {
+    mem_pool p;
+    // Host side: address space only; pages are committed when touched.
+    void *m = mmap(nullptr, capacity ? capacity : 4096, PROT_READ | PROT_WRITE,
+                   MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
+    DNN_CHECK(m != MAP_FAILED, "mem_pool_create: cannot map host buffer");
+    p.buffer = (char *)m;
+    p.capacity = capacity;
+    p.offset = 0;
+    return p;
+}
+
+void mem_pool_destroy(mem_pool *pool) {
+    if (!pool || !pool->buffer) return;
+    auto it = g_rt.arenas.find(pool->buffer);
+    if (it != g_rt.arenas.end()) {
+        cudaStreamSynchronize(g_rt.compute);
+        cudaFree(it->second.base);
+        g_rt.arenas.erase(it);
+    }
+    munmap(pool->buffer, pool->capacity ? pool->capacity : 4096);
+    pool->buffer = nullptr;
+    pool->capacity = 0;
+    pool->offset = 0;
+}
+
+void mem_pool_reset(mem_pool *pool) {
+    pool->offset = 0;
+    Arena *a = arena_of(pool, false);
+    if (a) { a->off = 0; a->marks.clear(); }
+}
+
+size_t mem_pool_mark(mem_pool *pool) {
+    Arena *a = arena_of(pool, false);
+    if (a) a->marks.emplace_back(pool->offset, a->off);
+    return pool->offset;
+}
+
+void mem_pool_release(mem_pool *pool, size_t mark) {
+    pool->offset = mark;
+    Arena *a = arena_of(pool, false);
+    if (!a) return;
+    while (!a->marks.empty() && a->marks.back().first > mark) a->marks.pop_back();
+    if (!a->marks.empty() && a->marks.back().first == mark) {
+        a->off = a->marks.back().second;
+        a->marks.pop_back();
+    } else if (mark == 0) {
+        a->off = 0;
+    }
+}
+
+static inline size_t host_round(size_t b) { return (b + 15) & ~(size_t)15; }
+
+void *_mem_pool_alloc(struct mem_pool *pool, size_t bytes, const void *src) {
+    size_t need = host_round(bytes);
+    DNN_CHECK(pool->offset + need <= pool->capacity, "_mem_pool_alloc: out of memory");
+    void *p = pool->buffer + pool->offset;
+    if (src) memcpy(p, src, bytes); else memset(p, 0, bytes);
+    pool->offset += need;
+    return p;
+}
+
+void *_mem_pool_alloc_nz(struct mem_pool *pool, size_t bytes) {
+    size_t need = host_round(bytes);
+    DNN_CHECK(pool->offset + need <= pool->capacity, "_mem_pool_alloc_nz: out of memory");
+    void *p = pool->buffer + pool->offset;
+    pool->offset += need;
+    return p;
+}
+
+int dnn_ctx_init(dnn_ctx *ctx, size_t params_sz, size_t scratch_sz, size_t data_sz) {
+    mem_pool *p = (mem_pool *)malloc(sizeof(mem_pool));
+    mem_pool *s = (mem_pool *)malloc(sizeof(mem_pool));
+    mem_pool *d = (mem_pool *)malloc(sizeof(mem_pool));
+    if (!p || !s || !d) { free(p); free(s); free(d); return -1; }
+    *p = mem_pool_create(params_sz);
+    *s = mem_pool_create(scratch_sz);
+    *d = mem_pool_create(data_sz);
+    ctx->params = p; ctx->scratch = s; ctx->data = d;
+    return 0;
+}
+
+void dnn_ctx_reset_step(dnn_ctx *ctx) {
+    mem_pool_reset(ctx->scratch);
+    mem_pool_reset(ctx->data);
+}
+
+void dnn_ctx_destroy(dnn_ctx *ctx) {
+    mem_pool **ps[3] = {&ctx->params, &ctx->scratch, &ctx->data};
+    for (auto pp : ps) if (*pp) { mem_pool_destroy(*pp); free(*pp); *pp = nullptr; }
+}
+
+// ── dnn_cuda_* ──────────────────────────────────────────────────────────
+int dnn_cuda_init(int device) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_rt.ready) return g_rt.device == device ? 0 : -3;
+    return init_device(device, false);
+}
+
+int dnn_cuda_available(void) {
+    if (g_rt.ready) return 1;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return n > 0;
+}
+
+int dnn_cuda_sync(void) {
+    cudaError_t e = cudaStreamSynchronize(stream());
+    if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return -1; }
+    return 0;
+}
+
+const char *dnn_cuda_last_error(void) { return g_rt.last_error.c_str(); }
+void *dnn_cuda_stream(void) { return (void *)stream(); }
+
+static int xfer(void *dst, const void *src, size_t bytes, cudaMemcpyKind kind, bool wait) {
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, kind, stream());
+    if (e == cudaSuccess && wait) e = cudaStreamSynchronize(stream());
+    if (e != cudaSuccess) { set_error(std::string("copy failed: ") + cudaGetErrorString(e)); return -1; }
+    return 0;
+}
+
+int dnn_cuda_upload(tensor *t, const void *host_src, size_t bytes) {
+    if (!t || !t->data || !t->contiguous) { set_error("upload: tensor must be contiguous with a payload"); return -2; }
+    if (bytes > (size_t)numel_of(t) * 4) { set_error("upload: more bytes than the tensor holds"); return -3; }
+    return xfer((float *)t->data + t->offset, host_src, bytes, cudaMemcpyHostToDevice, false);
+}
+
+int dnn_cuda_download(const tensor *t, void *host_dst, size_t bytes) {
+    if (!t || !t->data || !t->contiguous) { set_error("download: tensor must be contiguous with a payload"); return -2; }
+    if (bytes > (size_t)numel_of(t) * 4) { set_error("download: more bytes than the tensor holds"); return -3; }
+    return xfer(host_dst, (const float *)t->data + t->offset, bytes, cudaMemcpyDeviceToHost, true);
+}
+
+int dnn_cuda_download_grad(const tensor *t, void *host_dst, size_t bytes) {
+    if (!t || !t->grad) { set_error("download_grad: tensor has no grad"); return -2; }
+    if (bytes > (size_t)numel_of(t) * 4) { set_error("download_grad: more bytes than the tensor holds"); return -3; }
+    return xfer(host_dst, t->grad, bytes, cudaMemcpyDeviceToHost, true);
+}
+
+int dnn_cuda_memcpy_h2d(void *dev_dst, const void *host_src, size_t bytes) {
+    return xfer(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, false);
+}
+int dnn_cuda_memcpy_d2h(void *host_dst, const void *dev_src, size_t bytes) {
+    return xfer(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, true);
+}
+
+void *dnn_cuda_host_alloc(size_t bytes) {
+    stream();
+    void *p = nullptr;
+    if (cudaMallocHost(&p, bytes) != cudaSuccess) { set_error("cudaMallocHost failed"); return nullptr; }
+    return p;
+}
+void dnn_cuda_host_free(void *p) { if (p) cudaFreeHost(p); }
+
+int dnn_cuda_set_gemm_mode(int mode) {
+    if (mode < 0 || mode > 2) { set_error("unknown gemm mode"); return -1; }
+    g_rt.gemm_mode = mode;
+    return 0;
+}
+int dnn_cuda_get_gemm_mode(void) { return g_rt.gemm_mode; }
+long long dnn_cuda_launch_count(void) { return g_rt.launches; }
+
+size_t dnn_cuda_pool_device_used(const mem_pool *pool) {
+    Arena *a = arena_of(pool, false);
+    return a ? a->off : 0;
+}
+size_t dnn_cuda_pool_device_peak(const mem_pool *pool) {
+    Arena *a = arena_of(pool, false);
+    return a ? a->peak : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,87 @@
+/* dnn_cuda.h — the device-side additions to the dnn.c C API.
+ *
+ * The reference library (masc-it/dnn.c) is CPU only, so it has no counterpart
+ * for most of these calls; each comment says which host-side idiom of the
+ * reference the call stands in for.  All functions return 0 on success and a
+ * negative value on failure unless stated otherwise; dnn_cuda_last_error()
+ * describes the last failure.  Shape and pool-capacity violations inside the
+ * dnn.c entry points keep the reference's behaviour (message + abort()).
+ */
+#ifndef DNN_CUDA_H
+#define DNN_CUDA_H
+
+#include "dnn_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Select the device this process drives and create its compute stream.
+ * Optional: the first pool or tensor call does dnn_cuda_init(0) itself.
+ * There is no CPU fallback: without a usable CUDA device the library prints a
+ * message and aborts on the first call that needs device memory. */
+int  dnn_cuda_init(int device);
+/* 1 if a CUDA device can be used, 0 otherwise.  Never aborts. */
+int  dnn_cuda_available(void);
+/* Wait for all queued work.  Stands in for "the op has returned" in the
+ * reference, where every op is synchronous. */
+int  dnn_cuda_sync(void);
+const char *dnn_cuda_last_error(void);
+/* cudaStream_t of the compute stream, as an opaque pointer. */
+void *dnn_cuda_stream(void);
+
+/* Payload transfer.  Stand in for the reference idiom of dereferencing
+ * t->data / t->grad on the host (src/gpt.c:165-172 builds batches that way,
+ * examples read ((float*)loss->data)[0]).  `bytes` is counted from the
+ * tensor's first element (data + offset); the tensor must be contiguous.
+ * upload is asynchronous when `host_src` is pinned; download waits. */
+int  dnn_cuda_upload(tensor *t, const void *host_src, size_t bytes);
+int  dnn_cuda_download(const tensor *t, void *host_dst, size_t bytes);
+int  dnn_cuda_download_grad(const tensor *t, void *host_dst, size_t bytes);
+/* Raw copies for callers that hold device pointers (opt->m[i]->data etc.). */
+int  dnn_cuda_memcpy_h2d(void *dev_dst, const void *host_src, size_t bytes);
+int  dnn_cuda_memcpy_d2h(void *host_dst, const void *dev_src, size_t bytes);
+/* Pinned host memory for end-to-end loops (batch staging). */
+void *dnn_cuda_host_alloc(size_t bytes);
+void  dnn_cuda_host_free(void *p);
+
+/* Arithmetic mode of matmul / matmul_add / conv GEMMs and attention.
+ *   DNN_CUDA_GEMM_FP32   fp32 FMA kernels (exact-order-free fp32; parity mode)
+ *   DNN_CUDA_GEMM_TF32   tcgen05 tensor-core GEMM, TF32 inputs, fp32 accumulate
+ *   DNN_CUDA_GEMM_3XTF32 tcgen05 GEMM with the big/small TF32 split (3 MMAs)
+ * Replaces the reference's compile-time HAVE_CBLAS / NO_CBLAS switch
+ * (src/ops_matrix.c:19-25). */
+#define DNN_CUDA_GEMM_FP32   0
+#define DNN_CUDA_GEMM_TF32   1
+#define DNN_CUDA_GEMM_3XTF32 2
+int  dnn_cuda_set_gemm_mode(int mode);
+int  dnn_cuda_get_gemm_mode(void);
+
+/* Kernels launched by this library since process start (for benchmarks). */
+long long dnn_cuda_launch_count(void);
+/* Bytes of the pool's device arena in use / high-water mark since creation. */
+size_t dnn_cuda_pool_device_used(const mem_pool *pool);
+size_t dnn_cuda_pool_device_peak(const mem_pool *pool);
+
+/* Data-parallel gradient exchange (one process per GPU).  The reference has
+ * no multi-process path; these follow the place where a DDP hook would sit in
+ * src/gpt.c:201-206, between dnn_backward() and clip_grad_norm().
+ *   unique_id : fills 128 bytes on rank 0; the caller broadcasts them.
+ *   init      : joins the NCCL communicator.
+ *   allreduce : averages param->grad over ranks, in place, bucketed on a
+ *               second stream; params with grad == NULL are skipped, which
+ *               must be the same set on every rank. */
+int  dnn_cuda_dp_unique_id(void *out_128_bytes);
+int  dnn_cuda_dp_init(int rank, int world_size, const void *id_128_bytes);
+int  dnn_cuda_dp_allreduce_grads(tensor **params, int n_params);
+int  dnn_cuda_dp_world_size(void);
+int  dnn_cuda_dp_finalize(void);
+/* decoder_lm_train_step with the all-reduce between backward and clipping. */
+tensor *dnn_cuda_dp_decoder_lm_train_step(struct mem_pool *scratch_pool, decoder_lm *lm,
+                                          const tensor *input_ids, const tensor *target,
+                                          adamw_opt *opt, float grad_clip, float *grad_norm_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DNN_CUDA_H */

@@ -1,0 +1,5 @@
+/* Compatibility shim: dnn.c callers include "rope.h"; the whole API lives in dnn_b200.h. */
+#ifndef DNN_B200_SHIM_ROPE_H
+#define DNN_B200_SHIM_ROPE_H
+#include "dnn_b200.h"
+#endif

@@ -1,0 +1,5 @@
+/* Compatibility shim: dnn.c callers include "vlm.h"; the whole API lives in dnn_b200.h. */
+#ifndef DNN_B200_SHIM_VLM_H
+#define DNN_B200_SHIM_VLM_H
+#include "dnn_b200.h"
+#endif

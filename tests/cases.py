@@ -1,0 +1,529 @@
+"""Op-level parity cases for the dnn.c hot path.
+
+Every case has three parts that share seeded inputs:
+  make(rng)        -> dict of numpy inputs
+  run(dnn, inp)    -> dict of outputs computed THROUGH THE C API of a loaded
+                      library (the CUDA build or the reference build)
+  oracle(inp)      -> the same dict computed by the numpy restatement
+
+Backward is exercised the way dnn_backward() does it: the tape node of the
+op's output is called with a seeded upstream gradient.
+"""
+import ctypes as C
+
+import numpy as np
+
+from conftest import load_binding
+from oracle import dnn_oracle as O
+
+TensorP = load_binding().TensorP
+
+
+def _r(rng, *shape, scale=1.0):
+    return (rng.standard_normal(shape) * scale).astype(np.float32)
+
+
+class Case:
+    def __init__(self, name, make, run, oracle, tol=2e-5, exact=(), golden_exact=()):
+        self.name, self.make, self.run, self.oracle, self.tol, self.exact = name, make, run, oracle, tol, exact
+        # keys that must equal the REFERENCE's output bit for bit (golden vectors), although
+        # the numpy oracle, whose libm differs, only agrees to rounding
+        self.golden_exact = tuple(golden_exact) + tuple(exact)
+
+    def __repr__(self):
+        return self.name
+
+
+CASES = []
+
+
+def case(name, tol=2e-5, exact=(), golden_exact=()):
+    def deco(cls):
+        CASES.append(Case(name, cls.make, cls.run, cls.oracle, tol, exact, golden_exact))
+        return cls
+    return deco
+
+
+def _grads(dnn, *ts):
+    return [dnn.download_grad(t) for t in ts]
+
+
+# ── rms_norm / layer_norm ─────────────────────────────────────────────────
+def _norm_cases():
+    for rows, d in ((37, 768), (5, 130), (64, 2048), (3, 4100), (1, 7)):
+        @case("rms_norm[%dx%d]" % (rows, d))
+        class _:
+            @staticmethod
+            def make(rng, rows=rows, d=d):
+                return dict(x=_r(rng, rows, d), w=_r(rng, d) * 0.5 + 1, g=_r(rng, rows, d))
+
+            @staticmethod
+            def run(dnn, i):
+                x, w = dnn.tensor(i["x"], dnn.scratch, True), dnn.param(i["w"])
+                y = dnn.lib.tensor_rms_norm(dnn.scratch, x, w, 1e-5)
+                dnn.backward_from(y, i["g"])
+                dx, dw = _grads(dnn, x, w)
+                return dict(y=dnn.download(y), dx=dx, dw=dw)
+
+            @staticmethod
+            def oracle(i):
+                y, dx, dw = O.rms_norm(i["x"], i["w"], 1e-5, i["g"])
+                return dict(y=y, dx=dx, dw=dw)
+
+        @case("layer_norm[%dx%d]" % (rows, d))
+        class _:
+            @staticmethod
+            def make(rng, rows=rows, d=d):
+                return dict(x=_r(rng, rows, d) + 0.3, w=_r(rng, d) * 0.5 + 1, b=_r(rng, d), g=_r(rng, rows, d))
+
+            @staticmethod
+            def run(dnn, i):
+                x, w, b = dnn.tensor(i["x"], dnn.scratch, True), dnn.param(i["w"]), dnn.param(i["b"])
+                y = dnn.lib.tensor_layer_norm(dnn.scratch, x, w, b, 1e-5)
+                dnn.backward_from(y, i["g"])
+                dx, dw, db = _grads(dnn, x, w, b)
+                return dict(y=dnn.download(y), dx=dx, dw=dw, db=db)
+
+            @staticmethod
+            def oracle(i):
+                y, dx, dw, db = O.layer_norm(i["x"], i["w"], i["b"], 1e-5, i["g"])
+                return dict(y=y, dx=dx, dw=dw, db=db)
+
+
+_norm_cases()
+
+
+# ── elementwise ───────────────────────────────────────────────────────────
+def _unary(name, libfn, ofn, shapes):
+    for shape in shapes:
+        @case("%s%s" % (name, list(shape)))
+        class _:
+            @staticmethod
+            def make(rng, shape=shape):
+                return dict(x=_r(rng, *shape, scale=2.0), g=_r(rng, *shape))
+
+            @staticmethod
+            def run(dnn, i):
+                x = dnn.tensor(i["x"], dnn.scratch, True)
+                y = getattr(dnn.lib, libfn)(dnn.scratch, x)
+                dnn.backward_from(y, i["g"])
+                return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+            @staticmethod
+            def oracle(i):
+                y, dx = ofn(i["x"], i["g"])
+                return dict(y=y, dx=dx)
+
+
+_unary("relu", "tensor_relu", O.relu, [(4, 32, 7, 7), (1001,)])
+_unary("silu", "tensor_silu", O.silu, [(33, 129), (8,)])
+
+
+def _binary(name, libfn, ofn, pairs):
+    for sa, sb in pairs:
+        @case("%s%s%s" % (name, list(sa), list(sb)))
+        class _:
+            @staticmethod
+            def make(rng, sa=sa, sb=sb):
+                out = np.broadcast_shapes(sa, sb)
+                return dict(a=_r(rng, *sa), b=_r(rng, *sb), g=_r(rng, *out))
+
+            @staticmethod
+            def run(dnn, i):
+                a, b = dnn.tensor(i["a"], dnn.scratch, True), dnn.tensor(i["b"], dnn.scratch, True)
+                y = getattr(dnn.lib, libfn)(dnn.scratch, a, b)
+                dnn.backward_from(y, i["g"])
+                da, db = _grads(dnn, a, b)
+                return dict(y=dnn.download(y), da=da, db=db)
+
+            @staticmethod
+            def oracle(i):
+                y, da, db = ofn(i["a"], i["b"], i["g"])
+                return dict(y=y, da=da, db=db)
+
+
+_binary("add", "tensor_add", O.add, [((6, 50, 64), (6, 50, 64)), ((3, 7, 33), (33,)), ((33,), (3, 7, 33)),
+                                      ((4, 19, 24), (1, 19, 24)), ((5, 1, 8), (1, 6, 8))])
+_binary("swiglu", "tensor_swiglu", O.swiglu, [((9, 17, 64), (9, 17, 64)), ((3, 5, 31), (3, 5, 31)), ((4, 6, 8), (1, 6, 8))])
+
+for sa, sb, dim in (((3, 19, 16), (3, 5, 16), 1), ((4, 8), (2, 8), 0), ((2, 3, 4), (2, 3, 9), 2)):
+    @case("cat%s%s dim%d" % (list(sa), list(sb), dim))
+    class _:
+        @staticmethod
+        def make(rng, sa=sa, sb=sb, dim=dim):
+            out = list(sa); out[dim] += sb[dim]
+            return dict(a=_r(rng, *sa), b=_r(rng, *sb), g=_r(rng, *out), dim=dim)
+
+        @staticmethod
+        def run(dnn, i):
+            a, b = dnn.tensor(i["a"], dnn.scratch, True), dnn.tensor(i["b"], dnn.scratch, True)
+            y = dnn.lib.tensor_cat(dnn.scratch, a, b, i["dim"])
+            dnn.backward_from(y, i["g"])
+            da, db = _grads(dnn, a, b)
+            return dict(y=dnn.download(y), da=da, db=db)
+
+        @staticmethod
+        def oracle(i):
+            y, da, db = O.cat(i["a"], i["b"], i["dim"], i["g"])
+            return dict(y=y, da=da, db=db)
+
+
+# ── matmul_add / matmul ───────────────────────────────────────────────────
+MM = [  # (a shape, b shape, trans_b)
+    ((4, 37, 64), (64, 96), 0),       # activations x broadcast weight: collapses to one GEMM
+    ((4, 37, 64), (96, 64), 1),       # tied-head form
+    ((70, 33), (33, 10), 0),          # 2-D, pitch not a multiple of 16 bytes
+    ((70, 33), (10, 33), 1),
+    ((3, 2, 17, 8), (3, 2, 8, 5), 0), # true batched
+    ((2, 128, 256), (256, 128), 0),   # tensor-core sized
+    ((2, 128, 256), (128, 256), 1),
+]
+for sa, sb, tb in MM:
+    @case("matmul_add%s%s T%d" % (list(sa), list(sb), tb), tol=3e-5)
+    class _:
+        @staticmethod
+        def make(rng, sa=sa, sb=sb, tb=tb):
+            n = sb[-2] if tb else sb[-1]
+            out = tuple(np.broadcast_shapes(sa[:-2], sb[:-2])) + (sa[-2], n)
+            return dict(a=_r(rng, *sa), b=_r(rng, *sb, scale=0.2), bias=_r(rng, n), g=_r(rng, *out), tb=tb)
+
+        @staticmethod
+        def run(dnn, i):
+            a = dnn.tensor(i["a"], dnn.scratch, True)
+            b, bias = dnn.param(i["b"]), dnn.param(i["bias"])
+            y = dnn.lib.tensor_matmul_add(dnn.scratch, a, b, i["tb"], bias)
+            dnn.backward_from(y, i["g"])
+            da, db, dbias = _grads(dnn, a, b, bias)
+            return dict(y=dnn.download(y), da=da, db=db, dbias=dbias)
+
+        @staticmethod
+        def oracle(i):
+            y, da, db, dbias = O.matmul_add(i["a"], i["b"], i["tb"], i["bias"], i["g"])
+            return dict(y=y, da=da, db=db, dbias=dbias)
+
+for sa, sb in (((5, 21, 16), (16, 12)), ((40, 24), (24, 40)), ((2, 3, 9, 4), (2, 3, 4, 6))):
+    @case("matmul%s%s" % (list(sa), list(sb)), tol=3e-5)
+    class _:
+        @staticmethod
+        def make(rng, sa=sa, sb=sb):
+            out = tuple(np.broadcast_shapes(sa[:-2], sb[:-2])) + (sa[-2], sb[-1])
+            return dict(a=_r(rng, *sa), b=_r(rng, *sb), g=_r(rng, *out))
+
+        @staticmethod
+        def run(dnn, i):
+            a, b = dnn.tensor(i["a"], dnn.scratch, True), dnn.tensor(i["b"], dnn.scratch, True)
+            y = dnn.lib.tensor_matmul(dnn.scratch, a, b)
+            dnn.backward_from(y, i["g"])
+            da, db = _grads(dnn, a, b)
+            return dict(y=dnn.download(y), da=da, db=db)
+
+        @staticmethod
+        def oracle(i):
+            y, da, db, _ = O.matmul_add(i["a"], i["b"], 0, None, i["g"])
+            return dict(y=y, da=da, db=db)
+
+
+# ── attention ─────────────────────────────────────────────────────────────
+ATT = [  # B, H, N, d, mode, prefix, seq_lens
+    (2, 3, 70, 32, 0, 0, None),
+    (1, 2, 1, 64, 0, 0, None),
+    (2, 2, 129, 64, 0, 0, None),
+    (3, 2, 70, 8, 1, 5, (70, 3, 37)),          # N_b < prefix, padded rows
+    (2, 2, 65, 64, 1, 64, (65, 40)),
+    (2, 1, 128, 128, 1, 1, None),
+    (2, 2, 63, 32, 0, 0, (63, 17)),
+]
+for B, H, N, d, mode, prefix, lens in ATT:
+    @case("attention[B%d H%d N%d d%d mode%d P%d lens=%s]" % (B, H, N, d, mode, prefix, lens), tol=3e-5)
+    class _:
+        @staticmethod
+        def make(rng, B=B, H=H, N=N, d=d, mode=mode, prefix=prefix, lens=lens):
+            return dict(q=_r(rng, B, H, N, d), k=_r(rng, B, H, N, d), v=_r(rng, B, H, N, d), g=_r(rng, B, H, N, d),
+                        mode=mode, prefix=prefix, lens=None if lens is None else np.array(lens, np.int32))
+
+        @staticmethod
+        def run(dnn, i):
+            q, k, v = (dnn.tensor(i[n], dnn.scratch, True) for n in "qkv")
+            lens = None if i["lens"] is None else i["lens"].ctypes.data_as(C.POINTER(C.c_int))
+            o = dnn.lib.tensor_attention_ex(dnn.scratch, q, k, v, None, i["mode"], i["prefix"], lens)
+            g = i["g"].copy()
+            if i["lens"] is not None:                     # rows beyond seq_len carry no gradient
+                for b, nb in enumerate(i["lens"]):
+                    g[b, :, nb:] = 0
+            dnn.backward_from(o, g)
+            dq, dk, dv = _grads(dnn, q, k, v)
+            return dict(o=dnn.download(o), dq=dq, dk=dk, dv=dv)
+
+        @staticmethod
+        def oracle(i):
+            o, dq, dk, dv = O.attention(i["q"], i["k"], i["v"], i["mode"], i["prefix"], i["lens"], i["g"])
+            return dict(o=o, dq=dq, dk=dk, dv=dv)
+
+
+# ── rope / head layout / embedding ────────────────────────────────────────
+for shape in ((2, 3, 17, 32), (1, 1, 5, 6), (2, 12, 64, 64)):
+    @case("rope%s" % list(shape))
+    class _:
+        @staticmethod
+        def make(rng, shape=shape):
+            cos, sin = O.rope_tables(shape[-1], shape[-2])
+            return dict(x=_r(rng, *shape), g=_r(rng, *shape), cos=cos, sin=sin)
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            fc, fs = dnn.tensor(i["cos"], dnn.params), dnn.tensor(i["sin"], dnn.params)
+            y = dnn.lib.tensor_rope(dnn.scratch, x, fc, fs)
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.rope(i["x"], i["cos"], i["sin"], i["g"])
+            return dict(y=y, dx=dx)
+
+
+@case("rope_freqs_init", tol=1e-6, golden_exact=("cos", "sin"))
+class _:
+    @staticmethod
+    def make(rng):
+        return dict(dim=64, n=100)
+
+    @staticmethod
+    def run(dnn, i):
+        fc, fs = TensorP(), TensorP()
+        dnn.lib.tensor_rope_freqs_init(dnn.params, C.byref(fc), C.byref(fs), i["dim"], i["n"], 0.0)
+        return dict(cos=dnn.download(fc), sin=dnn.download(fs))
+
+    @staticmethod
+    def oracle(i):
+        c, s = O.rope_tables(i["dim"], i["n"])
+        return dict(cos=c, sin=s)
+
+
+for B, N, H, dk in ((2, 19, 3, 8), (1, 7, 2, 5), (2, 64, 12, 64)):
+    @case("split_qkv_heads[B%d N%d H%d dk%d]" % (B, N, H, dk), exact=("q", "k", "v"))
+    class _:
+        @staticmethod
+        def make(rng, B=B, N=N, H=H, dk=dk):
+            return dict(x=_r(rng, B, N, 3 * H * dk), H=H, gq=_r(rng, B, H, N, dk), gk=_r(rng, B, H, N, dk), gv=_r(rng, B, H, N, dk))
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            q, k, v = TensorP(), TensorP(), TensorP()
+            dnn.lib.tensor_split_qkv_heads(dnn.scratch, x, i["H"], C.byref(q), C.byref(k), C.byref(v))
+            for t, g in ((q, i["gq"]), (k, i["gk"]), (v, i["gv"])):
+                dnn.backward_from(t, g)
+            return dict(q=dnn.download(q), k=dnn.download(k), v=dnn.download(v), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            q, k, v, dx = O.split_qkv_heads(i["x"], i["H"], i["gq"], i["gk"], i["gv"])
+            return dict(q=q, k=k, v=v, dx=dx)
+
+    @case("merge_heads[B%d N%d H%d dk%d]" % (B, N, H, dk), exact=("y", "dx"))
+    class _:
+        @staticmethod
+        def make(rng, B=B, N=N, H=H, dk=dk):
+            return dict(x=_r(rng, B, H, N, dk), g=_r(rng, B, N, H * dk))
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            y = dnn.lib.tensor_merge_heads(dnn.scratch, x)
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.merge_heads(i["x"], i["g"])
+            return dict(y=y, dx=dx)
+
+    @case("split_heads[B%d N%d H%d dk%d]" % (B, N, H, dk), exact=("y", "dx"))
+    class _:
+        @staticmethod
+        def make(rng, B=B, N=N, H=H, dk=dk):
+            return dict(x=_r(rng, B, N, H * dk), H=H, g=_r(rng, B, H, N, dk))
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            y = dnn.lib.tensor_split_heads(dnn.scratch, x, i["H"])
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.split_heads(i["x"], i["H"], i["g"])
+            return dict(y=y, dx=dx)
+
+
+for V, D, n in ((50, 16, 200), (7, 5, 1), (300, 768, 64)):
+    @case("embedding[V%d D%d n%d]" % (V, D, n), exact=("y",))
+    class _:
+        @staticmethod
+        def make(rng, V=V, D=D, n=n):
+            return dict(table=_r(rng, V, D), ids=rng.integers(0, V, size=n).astype(np.int32), g=_r(rng, n, D))
+
+        @staticmethod
+        def run(dnn, i):
+            table = dnn.param(i["table"])
+            ids = dnn.tensor(i["ids"], dnn.data)
+            y = dnn.lib.tensor_embedding(dnn.scratch, table, ids)
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dtable=dnn.download_grad(table))
+
+        @staticmethod
+        def oracle(i):
+            y, dt = O.embedding(i["table"], i["ids"], i["g"])
+            return dict(y=y, dtable=dt)
+
+
+# ── cross entropy ─────────────────────────────────────────────────────────
+def _ce_run(dnn, i):
+    full = dnn.tensor(i["logits_full"], dnn.scratch, True)
+    logits = full
+    if i["slice"] is not None:
+        dim, start, ln = i["slice"]
+        logits = dnn.lib.tensor_slice(dnn.scratch, full, dim, start, ln)
+    target = dnn.tensor(i["target"], dnn.data)
+    if i["mask"] is None:
+        loss = dnn.lib.tensor_cross_entropy(dnn.scratch, logits, target, i["dim"])
+    else:
+        mask = dnn.tensor(i["mask"], dnn.data)
+        loss = dnn.lib.tensor_cross_entropy_masked(dnn.scratch, logits, target, mask, i["dim"])
+    dnn.lib.dnn_backward(dnn.scratch, loss)
+    dnn.sync()
+    return dict(loss=dnn.download(loss), dlogits=dnn.download_grad(full))
+
+
+def _ce_oracle(i):
+    full = i["logits_full"]
+    sl = [slice(None)] * full.ndim
+    if i["slice"] is not None:
+        dim, start, ln = i["slice"]
+        sl[dim] = slice(start, start + ln)
+    loss, d = O.cross_entropy(full[tuple(sl)], i["target"], i["mask"])
+    dfull = np.zeros_like(full)
+    dfull[tuple(sl)] = d
+    return dict(loss=np.array([loss], np.float32), dlogits=dfull)
+
+
+CE = [  # full logits shape, slice (dim,start,len) or None, masked
+    ((64, 10), None, False),                 # 2-D classification path
+    ((4, 33, 257), (1, 0, 32), False),       # GPT path: [B,N,V] sliced to [B,N-1,V]
+    ((3, 20, 1024), (1, 12, 8), True),       # VLM path: text rows of [B,I+T,V], masked
+    ((2, 9, 40), None, True),
+    ((2, 5, 32000), None, False),            # wide rows, float4 path
+]
+for shape, slc, masked in CE:
+    @case("cross_entropy%s slice=%s masked=%d" % (list(shape), slc, masked))
+    class _:
+        @staticmethod
+        def make(rng, shape=shape, slc=slc, masked=masked):
+            full = _r(rng, *shape, scale=2.0)
+            tshape = list(shape[:-1])
+            if slc is not None:
+                tshape[slc[0]] = slc[2]
+            target = rng.integers(0, shape[-1], size=tshape).astype(np.int32)
+            mask = (rng.random(tshape) > 0.3).astype(np.float32) if masked else None
+            return dict(logits_full=full, slice=slc, target=target, mask=mask, dim=len(shape) - 1)
+
+        run = staticmethod(_ce_run)
+        oracle = staticmethod(_ce_oracle)
+
+
+# ── conv2d / avg_pool2d ───────────────────────────────────────────────────
+CONV = [  # N, C, H, W, out_C, k, stride, pad
+    (3, 1, 28, 28, 8, 3, 1, 1),      # reference takes its Winograd path: true NCHW
+    (2, 4, 9, 7, 6, 3, 1, 1),
+    (2, 3, 32, 32, 16, 16, 16, 0),   # patch embed: (M, out_C) memory in an NCHW-shaped tensor
+    (2, 2, 11, 11, 5, 3, 2, 0),
+    (1, 2, 8, 8, 4, 5, 1, 2),
+]
+for N, Cc, H, W, oc, k, s, p in CONV:
+    @case("conv2d[N%d C%d %dx%d oc%d k%d s%d p%d]" % (N, Cc, H, W, oc, k, s, p), tol=3e-5)
+    class _:
+        @staticmethod
+        def make(rng, N=N, Cc=Cc, H=H, W=W, oc=oc, k=k, s=s, p=p):
+            Ho, Wo = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+            return dict(x=_r(rng, N, Cc, H, W), w=_r(rng, oc, Cc, k, k, scale=0.3), b=_r(rng, oc), g=_r(rng, N, oc, Ho, Wo), s=s, p=p)
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            w, b = dnn.param(i["w"]), dnn.param(i["b"])
+            y = dnn.lib.tensor_conv2d(dnn.scratch, x, w, b, i["s"], i["p"])
+            dnn.backward_from(y, i["g"])
+            dx, dw, db = _grads(dnn, x, w, b)
+            return dict(y=dnn.download(y), dx=dx, dw=dw, db=db)
+
+        @staticmethod
+        def oracle(i):
+            y, dx, dw, db = O.conv2d(i["x"], i["w"], i["b"], i["s"], i["p"], i["g"])
+            return dict(y=y, dx=dx, dw=dw, db=db)
+
+for shape, k, s in (((2, 3, 28, 28), 2, 2), ((2, 2, 9, 9), 2, 1), ((1, 2, 11, 10), 3, 2)):
+    @case("avg_pool2d%s k%d s%d" % (list(shape), k, s))
+    class _:
+        @staticmethod
+        def make(rng, shape=shape, k=k, s=s):
+            Ho, Wo = (shape[2] - k) // s + 1, (shape[3] - k) // s + 1
+            return dict(x=_r(rng, *shape), g=_r(rng, shape[0], shape[1], Ho, Wo), k=k, s=s)
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            y = dnn.lib.tensor_avg_pool2d(dnn.scratch, x, i["k"], i["s"])
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.avg_pool2d(i["x"], i["k"], i["s"], i["g"])
+            return dict(y=y, dx=dx)
+
+
+# ── views ─────────────────────────────────────────────────────────────────
+@case("transpose+contiguous+reshape (VLM image-embed path)", exact=("y", "dx"))
+class _:
+    @staticmethod
+    def make(rng):
+        return dict(x=_r(rng, 2, 6, 3, 4), g=_r(rng, 2, 12, 6))
+
+    @staticmethod
+    def run(dnn, i):
+        x = dnn.tensor(i["x"], dnn.scratch, True)
+        t = dnn.lib.tensor_transpose(dnn.scratch, x, 1, 2)
+        t = dnn.lib.tensor_transpose(dnn.scratch, t, 2, 3)
+        c = dnn.lib.tensor_contiguous(dnn.scratch, t)
+        dnn.backward_from(c, i["g"].reshape(2, 3, 4, 6))
+        y = dnn.lib.tensor_reshape(dnn.scratch, c, 3, load_binding().ints([2, 12, 6]))
+        return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+    @staticmethod
+    def oracle(i):
+        y = np.ascontiguousarray(i["x"].transpose(0, 2, 3, 1)).reshape(2, 12, 6)
+        dx = np.ascontiguousarray(i["g"].reshape(2, 3, 4, 6).transpose(0, 3, 1, 2))
+        return dict(y=y, dx=dx)
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    den = np.linalg.norm(b)
+    return float(np.linalg.norm(a - b) / den) if den > 0 else float(np.linalg.norm(a - b))
+
+
+def compare(case, got, want, tol=None, golden=False):
+    tol = case.tol if tol is None else tol
+    exact = case.golden_exact if golden else case.exact
+    assert set(got) == set(want), (sorted(got), sorted(want))
+    for k in sorted(want):
+        assert got[k] is not None, "%s: %s was never written" % (case.name, k)
+        assert got[k].shape == want[k].shape, (case.name, k, got[k].shape, want[k].shape)
+        if k in exact:
+            assert np.array_equal(got[k], want[k]), "%s: %s not bit-exact" % (case.name, k)
+        else:
+            e = rel_l2(got[k], want[k])
+            assert e <= tol, "%s: %s relative L2 error %.3g > %.1g" % (case.name, k, e, tol)

@@ -1,0 +1,165 @@
+"""Model-level runs through the C API (decoder LM, MNIST-shaped CNN, vision LM).
+
+The same functions drive the CUDA library and the reference library: they
+create the model with the library's own constructors, overwrite every
+parameter with seeded values (so both sides start from identical weights),
+run training steps with the library's *_train_step and return losses,
+gradient norms, gradients and updated parameters as numpy arrays.
+"""
+import ctypes as C
+
+import numpy as np
+
+from conftest import load_binding
+from oracle import dnn_oracle as O
+
+B = load_binding()
+
+
+def seeded_weights(dnn, module, names, seed, std=0.02):
+    """N(0, std) for matrices / conv filters / position tables, 0 for biases, 1 for norm gains."""
+    rng = np.random.default_rng(seed)
+    params = dnn.parameters(module)
+    assert len(params) == len(names), (len(params), len(names))
+    vals = {}
+    for t, name in zip(params, names):
+        shape = dnn.shape_of(t)
+        if name.endswith("norm.weight"):
+            v = np.ones(shape, np.float32)
+        elif name.endswith("bias"):
+            v = np.zeros(shape, np.float32)
+        else:
+            v = (rng.standard_normal(shape) * std).astype(np.float32)
+        dnn.upload(t, v)
+        vals[name] = v
+    return params, vals
+
+
+def lm_config(name):
+    return {
+        # BASELINE config 1: tiny decoder LM
+        "c1": dict(V=256, D=128, L=4, H=4, F=512, B=16, N=128, lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, seed=0),
+        # small enough for the float64 numpy oracle and for golden vectors in git
+        "tiny": dict(V=64, D=32, L=2, H=2, F=64, B=2, N=16, lr=1e-3, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, seed=7),
+        "odd": dict(V=50, D=48, L=1, H=3, F=40, B=3, N=33, lr=1e-3, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=0.5, seed=8),
+    }[name]
+
+
+def lm_inputs(cfg):
+    """Token ids from the reference's own generator (xorshift128+, src/rng.c)."""
+    r = O.Rng(cfg["seed"])
+    ids = np.array([r.uniform_int(cfg["V"]) for _ in range(cfg["B"] * cfg["N"])], np.int32).reshape(cfg["B"], cfg["N"])
+    return ids, np.ascontiguousarray(ids[:, 1:])
+
+
+def run_lm(dnn, cfg, steps=1, want_grads=True):
+    lib = dnn.lib
+    lm = lib.decoder_lm_create(dnn.params, cfg["V"], cfg["D"], cfg["L"], cfg["H"], cfg["D"] // cfg["H"], cfg["F"])
+    lib.decoder_lm_enable_rope(dnn.params, lm, cfg["N"], 10000.0)
+    names = O.lm_param_names(cfg["L"])
+    params, w0 = seeded_weights(dnn, lm, names, cfg["seed"] + 100)
+    arr = (B.TensorP * len(params))(*params)
+    opt = lib.adamw_create(dnn.params, arr, len(params), cfg["lr"], cfg["b1"], cfg["b2"], cfg["eps"], cfg["wd"])
+    ids_np, tgt_np = lm_inputs(cfg)
+    out = dict(loss=[], grad_norm=[], names=names, w0=w0, ids=ids_np, targets=tgt_np)
+    for s in range(steps):
+        ids = dnn.tensor(ids_np, dnn.data)
+        tgt = lib.decoder_lm_shift_targets(dnn.data, ids)
+        if s == 0:
+            out["shifted"] = dnn.download(tgt, np.int32)
+        gn = C.c_float(0)
+        loss = lib.decoder_lm_train_step(dnn.scratch, lm, ids, tgt, opt, cfg["clip"], C.byref(gn))
+        out["loss"].append(dnn.scalar(loss))
+        out["grad_norm"].append(float(gn.value))
+        if s == 0 and want_grads:
+            out["grads"] = {n: dnn.download_grad(t) for n, t in zip(names, params)}   # after clipping
+        dnn.reset_step()
+    out["params"] = {n: dnn.download(t) for n, t in zip(names, params)}
+    out["_keep"] = (arr,)
+    return out
+
+
+# ── MNIST-shaped CNN (BASELINE config 3) ──────────────────────────────────
+CNN_NAMES = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
+
+
+def run_cnn(dnn, batch=8, steps=2, seed=2):
+    lib = dnn.lib
+    c1 = lib.conv2d_create(dnn.params, 1, 32, 3, 1, 1)
+    c2 = lib.conv2d_create(dnn.params, 32, 64, 3, 1, 1)
+    f1 = lib.linear_create(dnn.params, 3136, 128)
+    f2 = lib.linear_create(dnn.params, 128, 10)
+    params = []
+    for m in (c1, c2, f1, f2):
+        params += dnn.parameters(m)
+    rng = np.random.default_rng(seed)
+    for t, n in zip(params, CNN_NAMES):
+        shape = dnn.shape_of(t)
+        fan_in = int(np.prod(shape[1:])) if len(shape) == 4 else shape[0]
+        bound = np.sqrt(6.0 / fan_in) if len(shape) == 4 else 1.0 / np.sqrt(3136 if n.startswith("fc1") else 128)
+        v = np.zeros(shape, np.float32) if n.startswith("conv") and n.endswith("bias") else \
+            ((rng.random(shape) * 2 - 1) * bound).astype(np.float32)
+        dnn.upload(t, v)
+    arr = (B.TensorP * len(params))(*params)
+    opt = lib.adamw_create(dnn.params, arr, len(params), 1e-3, 0.9, 0.999, 1e-8, 0.01)
+    x_np = rng.random((batch, 784)).astype(np.float32)
+    y_np = rng.integers(0, 10, size=batch).astype(np.int32)
+    out = dict(loss=[], names=CNN_NAMES)
+    for s in range(steps):
+        x = dnn.tensor(x_np, dnn.data)
+        y = dnn.tensor(y_np, dnn.data)
+        h = lib.tensor_reshape(dnn.scratch, x, 4, B.ints([batch, 1, 28, 28]))
+        h = lib.tensor_avg_pool2d(dnn.scratch, lib.tensor_relu(dnn.scratch, lib.conv2d_forward(dnn.scratch, c1, h)), 2, 2)
+        h = lib.tensor_avg_pool2d(dnn.scratch, lib.tensor_relu(dnn.scratch, lib.conv2d_forward(dnn.scratch, c2, h)), 2, 2)
+        h = lib.tensor_reshape(dnn.scratch, h, 2, B.ints([batch, 3136]))
+        h = lib.tensor_relu(dnn.scratch, lib.linear_forward(dnn.scratch, f1, h))
+        logits = lib.linear_forward(dnn.scratch, f2, h)
+        loss = lib.tensor_cross_entropy(dnn.scratch, logits, y, 1)
+        lib.dnn_backward(dnn.scratch, loss)
+        out["loss"].append(dnn.scalar(loss))
+        if s == 0:
+            out["logits"] = dnn.download(logits)
+            out["grads"] = {n: dnn.download_grad(t) for n, t in zip(CNN_NAMES, params)}
+        lib.adamw_step(opt)
+        lib.adamw_zero_grad(opt)
+        dnn.reset_step()
+    out["params"] = {n: dnn.download(t) for n, t in zip(CNN_NAMES, params)}
+    out["_keep"] = (arr,)
+    return out
+
+
+# ── prefix-LM vision LM (BASELINE config 4, reduced) ──────────────────────
+def vlm_param_names(n_layers):
+    return ["patch_embed.weight", "patch_embed.bias", "img_proj.weight", "img_proj.bias"] + \
+           ["lm." + n for n in O.lm_param_names(n_layers)] + ["image_pos"]
+
+
+def run_vlm(dnn, steps=2, seed=3, Bsz=3, img=32, patch=16, V=40, D=32, L=2, H=2, F=48, Tmax=8):
+    lib = dnn.lib
+    vlm = lib.vision_lm_create(dnn.params, V, D, L, H, D // H, F, 3, img, img, patch, 1)
+    lib.vision_lm_enable_rope(dnn.params, vlm, Tmax, 10000.0)
+    names = vlm_param_names(L)
+    params, _ = seeded_weights(dnn, vlm, names, seed + 100)
+    arr = (B.TensorP * len(params))(*params)
+    opt = lib.adamw_create(dnn.params, arr, len(params), 6e-4, 0.9, 0.95, 1e-8, 0.1)
+    rng = np.random.default_rng(seed)
+    images = rng.standard_normal((Bsz, 3, img, img)).astype(np.float32)
+    lens = rng.integers(2, Tmax + 1, size=Bsz).astype(np.int32)
+    ids = rng.integers(0, V, size=(Bsz, Tmax)).astype(np.int32)
+    tgt = rng.integers(0, V, size=(Bsz, Tmax)).astype(np.int32)
+    mask = (np.arange(Tmax)[None, :] < (lens[:, None] - 1)).astype(np.float32)
+    out = dict(loss=[], grad_norm=[], names=names)
+    for s in range(steps):
+        ti, tt = dnn.tensor(ids, dnn.data), dnn.tensor(tgt, dnn.data)
+        tm, tx = dnn.tensor(mask, dnn.data), dnn.tensor(images, dnn.data)
+        gn = C.c_float(0)
+        loss = lib.vision_lm_train_step_padded(dnn.scratch, vlm, tx, ti, tt, tm, lens.ctypes.data_as(C.POINTER(C.c_int)),
+                                               opt, 1.0, C.byref(gn))
+        out["loss"].append(dnn.scalar(loss))
+        out["grad_norm"].append(float(gn.value))
+        if s == 0:
+            out["grads"] = {n: dnn.download_grad(t) for n, t in zip(names, params)}
+        dnn.reset_step()
+    out["params"] = {n: dnn.download(t) for n, t in zip(names, params)}
+    out["_keep"] = (arr,)
+    return out
