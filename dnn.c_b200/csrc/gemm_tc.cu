@@ -1,6 +1,467 @@
-// placeholder until the tensor-core kernel lands
+// TF32 tensor-core GEMM for sm_100a: tcgen05.mma with TMEM accumulators, fed by TMA.
+//
+//   C[M,N] (=|+=) A[M,K] * B[K,N] (+ bias[N]),  fp32 in memory, TF32 multiply, fp32 accumulate.
+//
+// One persistent CTA per SM walks (tile, k-split) work units.  Warp roles:
+//   warp 0      one elected lane issues the TMA loads (cp.async.bulk.tensor, one
+//               CTA's own tiles, no multicast) into a ring of shared-memory stages;
+//   warp 1      one elected lane issues tcgen05.mma (128 x BN x 8 per instruction)
+//               and commits stage / accumulator completions to mbarriers;
+//   warps 2..5  epilogue: tcgen05.ld the 128 x BN accumulator from TMEM, add bias
+//               or the previous C, store.  TMEM holds two accumulators, so the
+//               epilogue of one tile overlaps the main loop of the next.
+// Operands may be K-major (K contiguous in memory) or MN-major (M resp. N
+// contiguous); both are expressed through the shared-memory matrix descriptor
+// (128-byte swizzle) and the instruction descriptor's major bits, so the same
+// kernel serves A*B, A*B^T, dA and dW without transposing anything in memory.
+// Tails in M, N and K need no special code: TMA zero-fills out-of-bounds boxes.
+//
+// Every mbarrier wait is bounded; a wait that runs out records an error code
+// that dnn_cuda_sync() reports, and the CTA still frees its TMEM and returns.
 #include "common.cuh"
+#include "device_utils.cuh"
+#include <cuda.h>
+
 namespace dnnb {
-bool gemm_tc_supported(const GemmArgs &) { return false; }
-void gemm_tc(const GemmArgs &g, bool) { gemm_simt(g); }
+
+constexpr int BM = 128;            // tile rows = MMA M
+constexpr int BK = 32;             // K per stage: 32 fp32 = one 128-byte swizzle row
+constexpr int UMMA_K = 8;          // K per tcgen05.mma for TF32
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kWaitSpins = 1u << 26;
+
+__device__ int g_gemm_error = 0;   // 0 ok; otherwise (role << 8 | detail) of the first wait that gave up
+
+// ---- PTX wrappers -------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: false when the phase did not complete within kWaitSpins polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < kWaitSpins; it++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (it > 1024) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (Blackwell descriptor version 1), rows of 128 bytes.
+//   K-major : a row holds 32 consecutive k of one m/n; 16-byte chunks swizzled with row%8
+//             (layout type 2); 8-row groups are `sbo` = 1024 B apart.
+//   MN-major: a row holds 32 consecutive m/n of one k.  For 32-bit operands the only
+//             MN-major layout the tensor core takes is the 128-byte swizzle with 32-byte
+//             atoms (layout type 1: 32-byte chunks swizzled with row%4); groups of 4
+//             k-rows are `sbo` = 512 B apart and the next 32 m/n start `lbo` bytes on.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout_type << 61;
+    return d;
+}
+
+struct TcArgs {
+    float *C; int64_t ldc;             // row-major output (or split-K partials, ldc = N)
+    const float *bias;
+    int M, N, K;
+    int accumulate;
+    int a_kmajor, b_kmajor;
+    int splits, kb_per_split;          // split-K: work unit = (tile, split)
+    int tiles_m, tiles_n;
+};
+
+template <int BN> struct TcCfg {
+    static constexpr int kStageA = BM * BK * 4;                   // 16 KiB
+    static constexpr int kStageB = BN * BK * 4;
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kSmem = kStages * (kStageA + kStageB) + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = 2 * BN;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcArgs g) {
+    using Cfg = TcCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sA = smem, *sB = smem + Cfg::kStages * Cfg::kStageA;
+    uint64_t *bars = (uint64_t *)(smem + Cfg::kStages * (Cfg::kStageA + Cfg::kStageB));
+    uint64_t *full = bars, *empty = bars + Cfg::kStages, *acc_full = bars + 2 * Cfg::kStages, *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = (uint32_t *)(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = g.tiles_m * g.tiles_n;
+    const int num_units = num_tiles * g.splits;
+    const int num_kb_total = (g.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                int tile = u / g.splits, split = u - tile * g.splits;
+                int m0 = (tile % g.tiles_m) * BM, n0 = (tile / g.tiles_m) * BN;
+                int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 0x100 | stage); ok = false; break; }
+                    mbar_expect_tx(&full[stage], Cfg::kStageA + Cfg::kStageB);
+                    uint8_t *a = sA + stage * Cfg::kStageA, *b = sB + stage * Cfg::kStageB;
+                    int k = kb * BK;
+                    if (g.a_kmajor) tma_load_2d(a, &tmA, k, m0, &full[stage]);                    // box {32 k, 128 rows}
+                    else for (int c = 0; c < BM / 32; c++) tma_load_2d(a + c * 4096, &tmA, m0 + c * 32, k, &full[stage]);   // box {32 m, 32 k}
+                    if (g.b_kmajor) tma_load_2d(b, &tmB, k, n0, &full[stage]);
+                    else for (int c = 0; c < BN / 32; c++) tma_load_2d(b + c * 4096, &tmB, n0 + c * 32, k, &full[stage]);
+                    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D=f32, A=B=tf32, major bits, N>>3, M>>4
+            uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((g.a_kmajor ? 0u : 1u) << 15) | ((g.b_kmajor ? 0u : 1u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint32_t a_lbo = g.a_kmajor ? 16 : 4096, b_lbo = g.b_kmajor ? 16 : 4096;
+            const uint32_t a_adv = g.a_kmajor ? UMMA_K * 4 : 1024, b_adv = g.b_kmajor ? UMMA_K * 4 : 1024;   // bytes per K=8 step
+            const uint32_t a_sbo = g.a_kmajor ? 1024 : 512, b_sbo = g.b_kmajor ? 1024 : 512;
+            const uint32_t a_lt = g.a_kmajor ? 2 : 1, b_lt = g.b_kmajor ? 2 : 1;
+            int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                int tile = u / g.splits, split = u - tile * g.splits;
+                (void)tile;
+                int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 0x200 | acc); break; }
+                tc_fence_after();
+                uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(&full[stage], phase)) { atomicCAS(&g_gemm_error, 0, 0x300 | stage); ok = false; break; }
+                    tc_fence_after();
+                    uint32_t a_addr = smem_u32(sA + stage * Cfg::kStageA), b_addr = smem_u32(sB + stage * Cfg::kStageB);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        uint64_t ad = make_smem_desc(a_addr + k * a_adv, a_lbo, a_sbo, a_lt);
+                        uint64_t bd = make_smem_desc(b_addr + k * b_adv, b_lbo, b_sbo, b_lt);
+                        tc_mma_tf32(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&empty[stage]);           // frees the stage when these MMAs have read it
+                    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit(&acc_full[acc]);              // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // epilogue warps 2..5: TMEM lanes 32*(warp%4) .. +31  <->  tile rows
+        const int q = warp & 3;
+        int acc = 0; uint32_t acc_phase = 0;
+        for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+            int tile = u / g.splits, split = u - tile * g.splits;
+            int m0 = (tile % g.tiles_m) * BM, n0 = (tile / g.tiles_m) * BN;
+            int kb0 = split * g.kb_per_split;
+            bool has_k = kb0 < num_kb_total;
+            if (!mbar_wait(&acc_full[acc], acc_phase)) { if (lane == 0) atomicCAS(&g_gemm_error, 0, 0x400 | acc); break; }
+            tc_fence_after();
+            int row = m0 + q * 32 + lane;
+            float *crow = g.C + (int64_t)split * g.M * g.ldc + (int64_t)row * g.ldc;
+            bool use_bias = g.bias != nullptr && split == 0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                if (row < g.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        int col = n0 + c0 + j;
+                        if (col >= g.N) break;
+                        float v[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) v[e] = has_k ? __uint_as_float(r[j + e]) : 0.f;
+                        if (col + 3 < g.N) {
+                            if (use_bias) { float4 bb = *reinterpret_cast<const float4 *>(g.bias + col); v[0] += bb.x; v[1] += bb.y; v[2] += bb.z; v[3] += bb.w; }
+                            float4 *dst = reinterpret_cast<float4 *>(crow + col);
+                            if (g.accumulate) { float4 o = *dst; v[0] += o.x; v[1] += o.y; v[2] += o.z; v[3] += o.w; }
+                            *dst = make_float4(v[0], v[1], v[2], v[3]);
+                        } else {
+                            for (int e = 0; e < 4 && col + e < g.N; e++) {
+                                float x = v[e] + (use_bias ? g.bias[col + e] : 0.f);
+                                crow[col + e] = g.accumulate ? crow[col + e] + x : x;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    // teardown: everyone meets here, also after a wait that gave up
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+    }
+}
+
+// C (=|+=) sum_s part[s] (+ bias), fixed order
+__global__ void splitk_reduce_kernel(float *__restrict__ C, int64_t ldc, const float *__restrict__ part, int splits,
+                                     int M, int N, const float *__restrict__ bias, int accumulate) {
+    int64_t total = (int64_t)M * N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int m = (int)(i / N), n = (int)(i - (int64_t)m * N);
+        float s = 0.f;
+        for (int k = 0; k < splits; k++) s += part[(int64_t)k * total + i];
+        if (bias) s += bias[n];
+        float *c = C + (int64_t)m * ldc + n;
+        *c = accumulate ? *c + s : s;
+    }
+}
+
+// big = x with the 13 low mantissa bits cleared (exactly a TF32 value), small = x - big
+__global__ void tf32_split_kernel(const float *__restrict__ x, float *__restrict__ big, float *__restrict__ small,
+                                  int64_t rows, int64_t cols, int64_t pitch) {
+    int64_t total = rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / cols, c = i - r * cols;
+        float v = x[r * pitch + c];
+        float b = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+        big[i] = b; small[i] = v - b;
+    }
+}
+
+// ---- host side ------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        DNN_CHECK(p && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available in this driver");
+        fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D map over a matrix whose contiguous dimension has `inner` elements and whose
+// other dimension has `outer` elements `pitch` floats apart; box = {32, box_outer}.
+static CUtensorMap make_map(const float *base, int64_t inner, int64_t outer, int64_t pitch, int box_outer, bool mn_major) {
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
+    cuuint32_t box[2] = {32, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    // TFLOAT32: the copy engine rounds fp32 to TF32 (nearest even) on the way into shared
+    // memory; the tensor core on its own would truncate, which biases every product low.
+    CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)base, dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r); abort(); }
+    return m;
+}
+
+static bool operand_ok(const float *p, int64_t rs, int64_t cs, int64_t rows, int64_t cols) {
+    if (!aligned16(p)) return false;
+    if (cs == 1) return rs % 4 == 0 && rs >= cols;     // contiguous along the column index
+    if (rs == 1) return cs % 4 == 0 && cs >= rows;     // contiguous along the row index
+    return false;
+}
+
+// Normalised problem: row-major C.  Returns false when the layout cannot be fed to TMA.
+static bool normalise(const GemmArgs &in, GemmArgs &g) {
+    g = in;
+    if (g.batch != 1 || g.M <= 0 || g.N <= 0 || g.K <= 0) return false;
+    if (g.c_cs != 1) {
+        if (g.c_rs != 1 || g.bias) return false;
+        // C^T = B^T A^T : swap the operands so that the output is row-major
+        GemmArgs t = g;
+        t.A = g.B; t.a_rs = g.b_cs; t.a_cs = g.b_rs;
+        t.B = g.A; t.b_rs = g.a_cs; t.b_cs = g.a_rs;
+        t.M = g.N; t.N = g.M; t.c_rs = g.c_cs; t.c_cs = 1;
+        g = t;
+    }
+    if (!aligned16(g.C) || g.c_rs % 4 != 0 || g.c_rs < g.N) return false;
+    if (g.bias && !aligned16(g.bias)) return false;
+    if (!operand_ok(g.A, g.a_rs, g.a_cs, g.M, g.K)) return false;
+    if (!operand_ok(g.B, g.b_rs, g.b_cs, g.K, g.N)) return false;
+    return true;
+}
+
+bool gemm_tc_supported(const GemmArgs &in) {
+    GemmArgs g;
+    if (!normalise(in, g)) return false;
+    // tiny problems are launch-bound either way; keep them on the exact kernel
+    return (int64_t)g.M * g.N * g.K >= (int64_t)64 * 64 * 32;
+}
+
+static float *g_scratch = nullptr;
+static size_t g_scratch_cap = 0;
+static float *scratch(size_t bytes) {
+    if (bytes > g_scratch_cap) {
+        CUDA_OK(cudaStreamSynchronize(stream()));
+        if (g_scratch) CUDA_OK(cudaFree(g_scratch));
+        g_scratch_cap = bytes + (bytes >> 2);
+        CUDA_OK(cudaMalloc((void **)&g_scratch, g_scratch_cap));
+    }
+    return g_scratch;
+}
+
+template <int BN>
+static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
+    using Cfg = TcCfg<BN>;
+    static bool once = false;
+    if (!once) {
+        CUDA_OK(cudaFuncSetAttribute(gemm_tf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        once = true;
+    }
+    // A(m,k): K-major -> matrix [M rows][K contiguous]; MN-major -> [K rows][M contiguous]
+    CUtensorMap tmA = a_kmajor ? make_map(g.A, g.K, g.M, g.a_rs, BM, false) : make_map(g.A, g.M, g.K, g.a_cs, 32, true);
+    CUtensorMap tmB = b_kmajor ? make_map(g.B, g.K, g.N, g.b_cs, BN, false) : make_map(g.B, g.N, g.K, g.b_rs, 32, true);
+    TcArgs t;
+    t.M = g.M; t.N = g.N; t.K = g.K; t.a_kmajor = a_kmajor; t.b_kmajor = b_kmajor;
+    t.tiles_m = (g.M + BM - 1) / BM; t.tiles_n = (g.N + BN - 1) / BN;
+    int tiles = t.tiles_m * t.tiles_n;
+    int num_kb = (g.K + BK - 1) / BK;
+    // split-K when the output has too few tiles to fill the SMs and K is long
+    int splits = 1;
+    if (tiles * 2 <= kNumSMs && num_kb >= 32) {
+        splits = kNumSMs / tiles;
+        int max_splits = num_kb / 8;
+        if (splits > max_splits) splits = max_splits;
+        if (splits > 32) splits = 32;
+        if (splits < 1) splits = 1;
+    }
+    t.kb_per_split = (num_kb + splits - 1) / splits;
+    splits = (num_kb + t.kb_per_split - 1) / t.kb_per_split;
+    t.splits = splits;
+    if (splits == 1) { t.C = g.C; t.ldc = g.c_rs; t.bias = g.bias; t.accumulate = g.accumulate ? 1 : 0; }
+    else { t.C = scratch((size_t)splits * g.M * g.N * 4); t.ldc = g.N; t.bias = nullptr; t.accumulate = 0; }
+    int units = tiles * splits;
+    int grid = units < kNumSMs ? units : kNumSMs;
+    gemm_tf32_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream()>>>(tmA, tmB, t);
+    LAUNCHED("gemm_tf32_kernel");
+    if (splits > 1) {
+        splitk_reduce_kernel<<<grid_for((int64_t)g.M * g.N, 256), 256, 0, stream()>>>(g.C, g.c_rs, t.C, splits, g.M, g.N, g.bias,
+                                                                                     g.accumulate ? 1 : 0);
+        LAUNCHED("splitk_reduce_kernel");
+    }
+}
+
+static void run_tc(const GemmArgs &g) {
+    bool a_k = g.a_cs == 1, b_k = g.b_rs == 1;
+    // a [M,1]-shaped or [1,K]-shaped operand satisfies both; prefer K-major
+    if (g.N > 128) launch_tc<256>(g, a_k, b_k);
+    else launch_tc<128>(g, a_k, b_k);
+}
+
+// Packed copies big/small of an operand, laid out row-major over its contiguous dimension.
+static void split_operand(const float *p, int64_t rs, int64_t cs, int64_t rows, int64_t cols, float *big, float *small,
+                          int64_t &nrs, int64_t &ncs) {
+    int64_t outer, inner, pitch;
+    if (cs == 1) { outer = rows; inner = cols; pitch = rs; nrs = cols; ncs = 1; }
+    else { outer = cols; inner = rows; pitch = cs; nrs = 1; ncs = rows; }
+    tf32_split_kernel<<<grid_for(outer * inner, 256), 256, 0, stream()>>>(p, big, small, outer, inner, pitch);
+    LAUNCHED("tf32_split_kernel");
+}
+
+void gemm_tc(const GemmArgs &in, bool split3) {
+    GemmArgs g;
+    bool ok = normalise(in, g);
+    DNN_CHECK(ok, "gemm_tc called with an unsupported layout");
+    if (!split3) { run_tc(g); return; }
+    // 3xTF32: x = big + small with big exactly TF32; A*B ~= Ab*Bb + Ab*Bs + As*Bb, fp32 accumulation.
+    // Packed rows are padded to a multiple of 4 floats so the copies satisfy the TMA pitch rule.
+    auto pad4 = [](int64_t v) { return (v + 3) & ~(int64_t)3; };
+    int64_t a_inner = g.a_cs == 1 ? g.K : g.M, a_outer = g.a_cs == 1 ? g.M : g.K;
+    int64_t b_inner = g.b_cs == 1 ? g.N : g.K, b_outer = g.b_cs == 1 ? g.K : g.N;
+    if (a_inner % 4 || b_inner % 4) { gemm_simt(in); return; }     // ragged inner extents: exact kernel
+    (void)pad4;
+    size_t na = (size_t)a_inner * a_outer, nb = (size_t)b_inner * b_outer;
+    static float *buf = nullptr; static size_t cap = 0;
+    size_t need = (2 * na + 2 * nb) * 4 + 1024;
+    if (need > cap) {
+        CUDA_OK(cudaStreamSynchronize(stream()));
+        if (buf) CUDA_OK(cudaFree(buf));
+        cap = need + (need >> 2);
+        CUDA_OK(cudaMalloc((void **)&buf, cap));
+    }
+    auto al = [](size_t n) { return (n + 63) & ~(size_t)63; };
+    float *Ab = buf, *As = Ab + al(na), *Bb = As + al(na), *Bs = Bb + al(nb);
+    int64_t ars, acs, brs, bcs;
+    split_operand(g.A, g.a_rs, g.a_cs, g.M, g.K, Ab, As, ars, acs);
+    split_operand(g.B, g.b_rs, g.b_cs, g.K, g.N, Bb, Bs, brs, bcs);
+    GemmArgs t = g;
+    t.a_rs = ars; t.a_cs = acs; t.b_rs = brs; t.b_cs = bcs;
+    // smallest terms first so that they are not lost against a large accumulator
+    t.A = As; t.B = Bb; t.bias = nullptr; run_tc(t);
+    t.accumulate = true;
+    t.A = Ab; t.B = Bs; run_tc(t);
+    t.A = Ab; t.B = Bb; t.bias = g.bias; run_tc(t);
+}
+
+int gemm_tc_error() {
+    int e = 0;
+    cudaMemcpyFromSymbol(&e, g_gemm_error, sizeof e);
+    return e;
+}
+
+}  // namespace dnnb

@@ -243,6 +243,13 @@ int dnn_cuda_available(void) {
 int dnn_cuda_sync(void) {
     cudaError_t e = cudaStreamSynchronize(stream());
     if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return -1; }
+    int ge = gemm_tc_error();
+    if (ge) {
+        char buf[128];
+        snprintf(buf, sizeof buf, "tensor-core GEMM: a bounded barrier wait gave up (code 0x%x)", ge);
+        set_error(buf);
+        return -5;
+    }
     return 0;
 }
 

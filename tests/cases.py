@@ -177,6 +177,10 @@ MM = [  # (a shape, b shape, trans_b)
     ((3, 2, 17, 8), (3, 2, 8, 5), 0), # true batched
     ((2, 128, 256), (256, 128), 0),   # tensor-core sized
     ((2, 128, 256), (128, 256), 1),
+    ((300, 200), (200, 520), 0),      # several 128x256 tiles with ragged edges in M, N and K
+    ((300, 200), (520, 200), 1),
+    ((4096, 136), (136, 96), 0),      # long reduction for dW: split-K path
+    ((3, 1100, 72), (72, 40), 0),
 ]
 for sa, sb, tb in MM:
     @case("matmul_add%s%s T%d" % (list(sa), list(sb), tb), tol=3e-5)

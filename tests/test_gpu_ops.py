@@ -1,0 +1,58 @@
+"""GPU: every op of the hot path, called through the C-ABI of libdnn_b200.so,
+against (a) the numpy oracle on the same seeded inputs and (b) the committed
+vectors produced by the unmodified reference library."""
+import os
+
+import numpy as np
+import pytest
+
+from cases import CASES, compare
+from golden_util import check
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# ops that go through a GEMM or attention kernel: TF32 tensor-core arithmetic,
+# tolerance 1e-3 relative L2 (2e-3 for the conv/attention chains of two GEMMs)
+TENSOR_CORE_OPS = ("matmul", "conv2d", "attention")
+
+
+@pytest.fixture(scope="module")
+def ops_golden():
+    return np.load(os.path.join(GOLDEN, "ops.npz"))
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c.name)
+def test_fp32_mode_matches_oracle_and_reference(gpu, binding, ops_golden, case):
+    gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
+    inp = case.make(np.random.default_rng(1234))
+    got = case.run(gpu, inp)
+    gpu.reset_step()
+    compare(case, got, case.oracle(inp))
+    for k, v in got.items():
+        key = case.name + "/" + k
+        check(key, v, ops_golden[key], ops_golden[key + "#"], max(case.tol, 1e-6), exact=k in case.golden_exact)
+
+
+@pytest.mark.parametrize("mode,tol", [("tf32", 2e-3), ("3xtf32", 3e-5)])
+@pytest.mark.parametrize("case", [c for c in CASES if c.name.startswith(TENSOR_CORE_OPS)], ids=lambda c: c.name)
+def test_tensor_core_modes_match_oracle(gpu, binding, case, mode, tol):
+    gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32 if mode == "tf32" else binding.GEMM_3XTF32)
+    try:
+        inp = case.make(np.random.default_rng(1234))
+        got = case.run(gpu, inp)
+        gpu.reset_step()
+        compare(case, got, case.oracle(inp), tol=tol)
+    finally:
+        gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
+
+
+def test_same_seed_twice_is_bit_identical(gpu, binding):
+    """Determinism on one GPU: no atomics anywhere on the path."""
+    gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
+    for case in [c for c in CASES if c.name.startswith(("rms_norm[37", "embedding[V50", "attention[B2 H3", "matmul_add[4, 37, 64][64"))]:
+        inp = case.make(np.random.default_rng(99))
+        a = case.run(gpu, inp); gpu.reset_step()
+        b = case.run(gpu, inp); gpu.reset_step()
+        for k in a:
+            assert np.array_equal(a[k], b[k]), (case.name, k)
