@@ -188,6 +188,10 @@ CUDA_API = {
     "dnn_cuda_set_gemm_mode": (I, [I]),
     "dnn_cuda_get_gemm_mode": (I, []),
     "dnn_cuda_launch_count": (C.c_longlong, []),
+    "dnn_cuda_timer_start": (I, []),
+    "dnn_cuda_timer_stop_ms": (F, []),
+    "dnn_cuda_profile_enable": (I, [I]),
+    "dnn_cuda_profile_read": (I, [I, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "dnn_cuda_pool_device_used": (C.c_size_t, [PoolP]),
     "dnn_cuda_pool_device_peak": (C.c_size_t, [PoolP]),
     "dnn_cuda_dp_unique_id": (I, [VP]),

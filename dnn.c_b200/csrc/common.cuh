@@ -42,6 +42,9 @@ template <typename T> inline T *host_alloc_t(struct mem_pool *pool, size_t n = 1
 void *dev_put(struct mem_pool *pool, const void *host, size_t bytes);
 
 int gemm_mode();
+// Profiling hooks (no-ops unless dnn_cuda_profile_enable(1)): bracket one launch.
+void prof_begin(int kernel_class);
+void prof_end(int kernel_class, double work);
 
 inline int64_t numel_of(const tensor *t) {
     int64_t n = 1;

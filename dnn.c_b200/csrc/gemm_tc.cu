@@ -397,8 +397,10 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     else { t.C = scratch((size_t)splits * g.M * g.N * 4); t.ldc = g.N; t.bias = nullptr; t.accumulate = 0; }
     int units = tiles * splits;
     int grid = units < kNumSMs ? units : kNumSMs;
+    prof_begin(0);
     gemm_tf32_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream()>>>(tmA, tmB, t);
     LAUNCHED("gemm_tf32_kernel");
+    prof_end(0, 2.0 * g.M * g.N * g.K);
     if (splits > 1) {
         splitk_reduce_kernel<<<grid_for((int64_t)g.M * g.N, 256), 256, 0, stream()>>>(g.C, g.c_rs, t.C, splits, g.M, g.N, g.bias,
                                                                                      g.accumulate ? 1 : 0);

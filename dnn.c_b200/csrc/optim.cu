@@ -244,8 +244,12 @@ void adamw_step_with_lr_multipliers(adamw_opt *opt, const float *lr_mults) {
     }
     if (tab.empty()) return;
     int chunks = upload_table(tab);
+    double bytes = 0;
+    for (auto &r : tab) bytes += 28.0 * (double)r.n;        // read p,g,m,v; write p,m,v
+    prof_begin(1);
     adamw_kernel<<<chunks, 256, 0, stream()>>>(g_os.tab, (int)tab.size(), h);
     LAUNCHED("adamw_kernel");
+    prof_end(1, bytes);
 }
 void adamw_step(adamw_opt *opt) { adamw_step_with_lr_multipliers(opt, nullptr); }
 

@@ -87,6 +87,31 @@ void launched(const char *name) {
 
 int gemm_mode() { return g_rt.gemm_mode; }
 
+// ---- profiling ------------------------------------------------------------------
+struct ProfRec { cudaEvent_t a, b; double work; };
+struct ProfClass { std::vector<ProfRec> recs; cudaEvent_t pending = nullptr; };
+static bool g_prof_on = false;
+static ProfClass g_prof[2];
+static std::vector<cudaEvent_t> g_event_pool;
+static cudaEvent_t g_timer_a = nullptr, g_timer_b = nullptr;
+
+static cudaEvent_t get_event() {
+    if (!g_event_pool.empty()) { cudaEvent_t e = g_event_pool.back(); g_event_pool.pop_back(); return e; }
+    cudaEvent_t e; CUDA_OK(cudaEventCreate(&e)); return e;
+}
+void prof_begin(int c) {
+    if (!g_prof_on) return;
+    g_prof[c].pending = get_event();
+    CUDA_OK(cudaEventRecord(g_prof[c].pending, stream()));
+}
+void prof_end(int c, double work) {
+    if (!g_prof_on || !g_prof[c].pending) return;
+    cudaEvent_t b = get_event();
+    CUDA_OK(cudaEventRecord(b, stream()));
+    g_prof[c].recs.push_back(ProfRec{g_prof[c].pending, b, work});
+    g_prof[c].pending = nullptr;
+}
+
 static Arena *arena_of(const mem_pool *pool, bool create) {
     DNN_CHECK(pool && pool->buffer, "pool is NULL or destroyed");
     auto it = g_rt.arenas.find(pool->buffer);
@@ -295,6 +320,36 @@ void *dnn_cuda_host_alloc(size_t bytes) {
     return p;
 }
 void dnn_cuda_host_free(void *p) { if (p) cudaFreeHost(p); }
+
+int dnn_cuda_timer_start(void) {
+    if (!g_timer_a) { CUDA_OK(cudaEventCreate(&g_timer_a)); CUDA_OK(cudaEventCreate(&g_timer_b)); }
+    CUDA_OK(cudaEventRecord(g_timer_a, stream()));
+    return 0;
+}
+float dnn_cuda_timer_stop_ms(void) {
+    if (!g_timer_a) return -1.0f;
+    CUDA_OK(cudaEventRecord(g_timer_b, stream()));
+    CUDA_OK(cudaEventSynchronize(g_timer_b));
+    float ms = 0.f;
+    CUDA_OK(cudaEventElapsedTime(&ms, g_timer_a, g_timer_b));
+    return ms;
+}
+int dnn_cuda_profile_enable(int on) {
+    CUDA_OK(cudaStreamSynchronize(stream()));
+    for (auto &c : g_prof) { for (auto &r : c.recs) { g_event_pool.push_back(r.a); g_event_pool.push_back(r.b); } c.recs.clear(); c.pending = nullptr; }
+    g_prof_on = on != 0;
+    return 0;
+}
+int dnn_cuda_profile_read(int kernel_class, long long *launches, double *ms, double *work) {
+    if (kernel_class < 0 || kernel_class > 1) return -1;
+    CUDA_OK(cudaStreamSynchronize(stream()));
+    double tms = 0, tw = 0;
+    for (auto &r : g_prof[kernel_class].recs) { float e = 0; CUDA_OK(cudaEventElapsedTime(&e, r.a, r.b)); tms += e; tw += r.work; }
+    if (launches) *launches = (long long)g_prof[kernel_class].recs.size();
+    if (ms) *ms = tms;
+    if (work) *work = tw;
+    return 0;
+}
 
 int dnn_cuda_set_gemm_mode(int mode) {
     if (mode < 0 || mode > 2) { set_error("unknown gemm mode"); return -1; }

@@ -57,6 +57,17 @@ void  dnn_cuda_host_free(void *p);
 int  dnn_cuda_set_gemm_mode(int mode);
 int  dnn_cuda_get_gemm_mode(void);
 
+/* Device-side timing on the compute stream (CUDA events): start records an event,
+ * stop records a second one, waits for it and returns the milliseconds between. */
+int   dnn_cuda_timer_start(void);
+float dnn_cuda_timer_stop_ms(void);
+/* Per-kernel-class profiling for roofline reports.  While enabled, every launch of
+ * the tensor-core GEMM and of AdamW is bracketed by events.  read() waits for the
+ * stream and returns, for class 0 (GEMM) or 1 (AdamW): launches, summed device
+ * milliseconds and summed algorithmic work (FLOP for GEMM, bytes for AdamW). */
+int   dnn_cuda_profile_enable(int on);
+int   dnn_cuda_profile_read(int kernel_class, long long *launches, double *ms, double *work);
+
 /* Kernels launched by this library since process start (for benchmarks). */
 long long dnn_cuda_launch_count(void);
 /* Bytes of the pool's device arena in use / high-water mark since creation. */
