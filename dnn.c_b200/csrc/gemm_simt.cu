@@ -89,8 +89,13 @@ void gemm_simt(const GemmArgs &g) {
 
 void gemm(const GemmArgs &g) {
     int mode = gemm_mode();
-    if (mode != DNN_CUDA_GEMM_FP32 && gemm_tc_supported(g)) gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32);
-    else gemm_simt(g);
+    if (mode == DNN_CUDA_GEMM_FP32 || !gemm_tc_supported(g)) { gemm_simt(g); return; }
+    // Precision policy of TF32 mode: a long reduction into a small output (the filter
+    // gradient of a small convolution: thousands of products of mixed sign per element)
+    // cancels heavily and would lose more than TF32's 1e-3; such GEMMs are tiny, so they
+    // take the 3xTF32 path at no measurable cost.
+    bool small_long = (int64_t)g.M * g.N <= 65536 && g.K >= 1024;
+    gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32 || small_long);
 }
 
 }  // namespace dnnb

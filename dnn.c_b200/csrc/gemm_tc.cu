@@ -431,12 +431,9 @@ void gemm_tc(const GemmArgs &in, bool split3) {
     DNN_CHECK(ok, "gemm_tc called with an unsupported layout");
     if (!split3) { run_tc(g); return; }
     // 3xTF32: x = big + small with big exactly TF32; A*B ~= Ab*Bb + Ab*Bs + As*Bb, fp32 accumulation.
-    // Packed rows are padded to a multiple of 4 floats so the copies satisfy the TMA pitch rule.
-    auto pad4 = [](int64_t v) { return (v + 3) & ~(int64_t)3; };
     int64_t a_inner = g.a_cs == 1 ? g.K : g.M, a_outer = g.a_cs == 1 ? g.M : g.K;
     int64_t b_inner = g.b_cs == 1 ? g.N : g.K, b_outer = g.b_cs == 1 ? g.K : g.N;
     if (a_inner % 4 || b_inner % 4) { gemm_simt(in); return; }     // ragged inner extents: exact kernel
-    (void)pad4;
     size_t na = (size_t)a_inner * a_outer, nb = (size_t)b_inner * b_outer;
     static float *buf = nullptr; static size_t cap = 0;
     size_t need = (2 * na + 2 * nb) * 4 + 1024;
