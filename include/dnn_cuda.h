@@ -68,6 +68,26 @@ float dnn_cuda_timer_stop_ms(void);
 int   dnn_cuda_profile_enable(int on);
 int   dnn_cuda_profile_read(int kernel_class, long long *launches, double *ms, double *work);
 
+/* Column sums without any allocation:  out[c] += sum over r of g[r*cols + c]
+ * (the bias gradient of matmul_add / add).  No counterpart in the reference: this
+ * variant exists for callers that must not allocate device memory at the time of
+ * the call -- programs that have given all of HBM to their own arenas, loops that
+ * cannot afford the device-wide synchronisation an allocation implies, hosts whose
+ * policy forbids allocating after start-up.  The partial sums go to a 4 MiB array
+ * that is compiled into the library and stays resident on every GPU that loads it.
+ *   - `out` (cols floats) and `g` (rows x cols floats, row-major) are device pointers
+ *     supplied by the caller; the work is queued on the library's compute stream.
+ *   - Limit: cols <= 8192 (any number of rows).  Wider inputs return -2 and
+ *     dnn_cuda_colsum_acc_static_error() says why; nothing is launched.
+ *   - The first call on a device resolves the array's device address; make that
+ *     first call before starting any stream capture.
+ *   - All calls share the one array.  Each call rewrites the part it reads, so no
+ *     clearing is needed between calls, but two calls that overlap on the GPU (for
+ *     example from different streams or processes' threads) race on it.
+ * Returns 0 on success, negative on failure. */
+int   dnn_cuda_colsum_acc_static(float *out, const float *g, long long rows, int cols);
+const char *dnn_cuda_colsum_acc_static_error(void);
+
 /* Kernels launched by this library since process start (for benchmarks). */
 long long dnn_cuda_launch_count(void);
 /* Bytes of the pool's device arena in use / high-water mark since creation. */
