@@ -361,6 +361,19 @@ static void attn_bwd_launch(const AttnParams &p) {
     if (p.dq) { attn_bwd_dq_kernel<HD><<<grid, 256, bwd_smem<HD>(), stream()>>>(p); LAUNCHED("attn_bwd_dq_kernel"); }
 }
 
+// tensor-core kernels (attention_tc.cu)
+bool attn_tc_supported(int d, const void *q, const void *k, const void *v);
+void attn_forward_tc(const float *q, const float *k, const float *v, float *o, float *lse, const int *seq_lens,
+                     int B, int H, int N, int d, int prefix, float scale);
+void attn_backward_tc(const float *q, const float *k, const float *v, const float *lse, const float *dout, const float *dvec,
+                      float *dq, float *dk, float *dv, const int *seq_lens, int B, int H, int N, int d, int prefix, float scale);
+
+// TF32 mode runs on the tensor core (head dims 32 and 64); the FP32 and 3xTF32 modes, and
+// other head dims, run the exact kernels of this file.
+static bool use_tc(const AttnParams &p) {
+    return gemm_mode() == DNN_CUDA_GEMM_TF32 && attn_tc_supported(p.d, p.q, p.k, p.v);
+}
+
 void attn_forward_fp32(const AttnParams &p) {
     if (p.d <= 32) attn_fwd_launch<32>(p);
     else if (p.d <= 64) attn_fwd_launch<64>(p);
@@ -392,7 +405,8 @@ static void attention_backward(grad_fn *fn, tensor *go) {
     attn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(p.dout, p.o, dvec, rows, p.d);
     LAUNCHED("attn_bwd_prep_kernel");
     p.dvec = dvec;
-    attn_backward_fp32(p);
+    if (use_tc(p)) attn_backward_tc(p.q, p.k, p.v, p.lse, p.dout, p.dvec, p.dq, p.dk, p.dv, p.seq_lens, p.B, p.H, p.N, p.d, p.prefix, p.scale);
+    else attn_backward_fp32(p);
 }
 
 }  // namespace dnnb
@@ -428,7 +442,8 @@ tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tens
     p.seq_lens = seq_lens ? (const int *)dev_put(scratch, seq_lens, (size_t)B * sizeof(int)) : nullptr;
     p.prefix = mode == ATTENTION_PREFIX_LM ? prefix_len : 0;
     p.scale = 1.0f / sqrtf((float)d);
-    attn_forward_fp32(p);
+    if (use_tc(p)) attn_forward_tc(p.q, p.k, p.v, p.o, p.lse, p.seq_lens, B, H, N, d, p.prefix, p.scale);
+    else attn_forward_fp32(p);
 
     if (needs_grad) {
         grad_fn *fn = attach(scratch, out, attention_backward, 3, 1);

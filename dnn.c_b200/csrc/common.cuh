@@ -98,6 +98,7 @@ void gemm(const GemmArgs &g);          // dispatches on gemm_mode() and layout
 void gemm_simt(const GemmArgs &g);
 bool gemm_tc_supported(const GemmArgs &g);
 void gemm_tc(const GemmArgs &g, bool split3);
+int  attn_tc_error();
 int  gemm_tc_error();            // nonzero when a bounded wait inside the tensor-core kernel gave up
 
 }  // namespace dnnb

@@ -269,9 +269,10 @@ int dnn_cuda_sync(void) {
     cudaError_t e = cudaStreamSynchronize(stream());
     if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return -1; }
     int ge = gemm_tc_error();
-    if (ge) {
-        char buf[128];
-        snprintf(buf, sizeof buf, "tensor-core GEMM: a bounded barrier wait gave up (code 0x%x)", ge);
+    int ae = attn_tc_error();
+    if (ge || ae) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "tensor-core kernel: a bounded barrier wait gave up (gemm code 0x%x, attention code 0x%x)", ge, ae);
         set_error(buf);
         return -5;
     }

@@ -528,6 +528,11 @@ def compare(case, got, want, tol=None, golden=False):
         assert got[k].shape == want[k].shape, (case.name, k, got[k].shape, want[k].shape)
         if k in exact:
             assert np.array_equal(got[k], want[k]), "%s: %s not bit-exact" % (case.name, k)
+        elif np.linalg.norm(want[k]) < 1e-6 * np.sqrt(want[k].size) and tol >= 1e-3:
+            # a gradient that is exactly zero in exact arithmetic (single-key softmax): TF32
+            # leaves rounding-sized residue of the O(1) intermediates; bound it absolutely
+            e = float(np.linalg.norm(got[k])) / np.sqrt(want[k].size)
+            assert e <= tol, "%s: %s should vanish, rms %.3g > %.1g" % (case.name, k, e, tol)
         else:
             e = rel_l2(got[k], want[k])
             assert e <= tol, "%s: %s relative L2 error %.3g > %.1g" % (case.name, k, e, tol)
