@@ -115,6 +115,28 @@ __global__ void colsum_partial_kernel(const float *__restrict__ g, float *__rest
         partial[(int64_t)blockIdx.y * C + c] = t;
     }
 }
+// float4 variant: CTA = 32 x 8 threads covering 128 columns, 16-byte loads.
+__global__ void colsum_partial_v4_kernel(const float *__restrict__ g, float *__restrict__ partial,
+                                         int64_t rows, int C, int rows_per) {
+    __shared__ float4 tile[8][33];
+    int c = (blockIdx.x * 32 + threadIdx.x) * 4;
+    int64_t r0 = (int64_t)blockIdx.y * rows_per;
+    int64_t r1 = r0 + rows_per; if (r1 > rows) r1 = rows;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < C)
+        for (int64_t r = r0 + threadIdx.y; r < r1; r += 8) {
+            float4 v = *reinterpret_cast<const float4 *>(g + r * C + c);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+    tile[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; j++) { float4 v = tile[j][threadIdx.x]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+        *reinterpret_cast<float4 *>(partial + (int64_t)blockIdx.y * C + c) = t;
+    }
+}
 __global__ void colsum_final_kernel(float *__restrict__ out, const float *__restrict__ partial, int nparts, int C) {
     int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -141,9 +163,15 @@ void k_colsum_acc(float *out, const float *g, int64_t rows, int C) {
         g_colsum_cap = need * 2;
         CUDA_OK(cudaMalloc((void **)&g_colsum_scratch, g_colsum_cap));
     }
-    dim3 grid((C + 31) / 32, nparts), block(32, 32);
-    colsum_partial_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per);
-    LAUNCHED("colsum_partial_kernel");
+    if (C % 4 == 0 && aligned16(g)) {
+        dim3 grid((C / 4 + 31) / 32, nparts), block(32, 8);
+        colsum_partial_v4_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per);
+        LAUNCHED("colsum_partial_v4_kernel");
+    } else {
+        dim3 grid((C + 31) / 32, nparts), block(32, 32);
+        colsum_partial_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per);
+        LAUNCHED("colsum_partial_kernel");
+    }
     colsum_final_kernel<<<(C + 127) / 128, 128, 0, stream()>>>(out, g_colsum_scratch, nparts, C);
     LAUNCHED("colsum_final_kernel");
 }

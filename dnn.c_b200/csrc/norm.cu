@@ -169,13 +169,22 @@ __global__ void norm_dw_terms_kernel(const float *__restrict__ x, const float *_
     }
 }
 
-// out[j] += sum_p part[p*d + j], p ascending
+// out[j] += sum_p part[p*d + j].  CTA = 32 columns x 32 row-lanes; lane y sums
+// p = y, y+32, ... and the 32 lane sums are added in lane order (fixed order).
 __global__ void norm_part_reduce_kernel(float *__restrict__ out, const float *__restrict__ part, int nparts, int d) {
-    int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= d) return;
+    __shared__ float tile[32][33];
+    int j = blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
-    for (int p = 0; p < nparts; p++) s += part[(int64_t)p * d + j];
-    out[j] += s;
+    if (j < d)
+        for (int p = threadIdx.y; p < nparts; p += 32) s += part[(int64_t)p * d + j];
+    tile[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && j < d) {
+        float t = 0.f;
+#pragma unroll
+        for (int y = 0; y < 32; y++) t += tile[y][threadIdx.x];
+        out[j] += t;
+    }
 }
 
 template <bool LN>
@@ -217,8 +226,8 @@ static void norm_backward(struct mem_pool *pool, const float *x, const float *w,
         else if (T <= 6) launch_bwd<LN, 6>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
         else if (T <= 8) launch_bwd<LN, 8>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
         else             launch_bwd<LN, 16>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
-        if (dwp) { norm_part_reduce_kernel<<<(d + 127) / 128, 128, 0, stream()>>>(dw, dwp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
-        if (dbp) { norm_part_reduce_kernel<<<(d + 127) / 128, 128, 0, stream()>>>(db, dbp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
+        if (dwp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(dw, dwp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
+        if (dbp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(db, dbp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
         return;
     }
     if (dx) {

@@ -87,6 +87,12 @@ __device__ __forceinline__ float to_tf32(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return __uint_as_float(r);
 }
+// 2^x on the special-function unit (about 2 ulp; used where TF32 rounding dominates anyway)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 // Instruction descriptor: D = f32, A = B = TF32, M = 128, N = n; *_mn selects MN-major.
 __device__ __forceinline__ uint32_t make_idesc_tf32(int n, bool a_mn, bool b_mn) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |

@@ -1,0 +1,192 @@
+"""Op-level forward / backward microbenchmark (BASELINE config 2) through the C-ABI.
+
+    python dnn.c_b200/opbench.py [--op NAME] [--iters 10] [--small]
+
+For every op of the training hot path at the config-2 shapes it reports device
+milliseconds (CUDA events on the library's stream) of the forward and of the
+backward launch set, the algorithmic work (bytes for bandwidth-bound ops, FLOP
+for matmul and attention) and the fraction of the measured peak
+(MEASURED_PEAKS.json: HBM copy bandwidth; TF32 peak taken as half of the
+sustained bf16 figure, there being no measured TF32 number).  Inputs are seeded
+synthetic tensors; an L2-sized buffer is rewritten between timed iterations.
+`--small` shrinks the batch dimension (for profiler captures).
+One JSON line per op.
+"""
+import argparse
+import ctypes as C
+import importlib.util
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def load_binding():
+    name = "dnnc_b200_binding"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(HERE, "binding.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], 0.5 * p["bf16_tflops_sustained"], "measured"
+    return 6650.0, 700.0, "fallback"
+
+
+class Bench:
+    def __init__(self, B, iters, small):
+        self.B, self.iters, self.small = B, iters, small
+        self.d = B.Dnn(B.B200_LIB, params_mb=8192, scratch_mb=24 * 1024, data_mb=256)
+        self.lib = self.d.lib
+        self.rng = np.random.default_rng(1)
+        # 256 MiB rewritten between iterations: twice the 126 MB L2
+        self.flush = self.lib.tensor_zeros(self.d.params, 1, B.ints([64 << 20]), 0)
+        self.hbm, self.tf32, self.src = peaks()
+
+    def dev(self, arr, grad=False):
+        return self.d.tensor(arr, self.d.params, grad)         # params pool: survives reset_step
+
+    def flush_l2(self):
+        """Rewrites the 256 MiB flush tensor on the device (tensor_zero_grad zero-fills
+        t->grad, so grad is pointed at the payload for the duration of the call)."""
+        t = self.flush.contents
+        saved = t.grad
+        t.grad = t.data
+        self.lib.tensor_zero_grad(self.flush)
+        t.grad = saved
+
+    def time(self, fn):
+        self.lib.dnn_cuda_sync()
+        self.lib.dnn_cuda_timer_start()
+        fn()
+        return self.lib.dnn_cuda_timer_stop_ms()
+
+    def run(self, name, build, fwd, gout_shape, work_fwd, work_bwd, bound):
+        """build() -> inputs (made once); fwd(inputs) -> output tensor with a tape node."""
+        inp = build()
+        g = self.dev(self.rng.standard_normal(gout_shape, dtype=np.float32)) if gout_shape else None
+        tf, tb = [], []
+        for it in range(3 + self.iters):
+            self.d.reset_step()
+            self.flush_l2()
+            holder = {}
+            ms_f = self.time(lambda: holder.setdefault("y", fwd(inp)))
+            y = holder["y"]
+            self.flush_l2()
+            if g is not None:
+                fn = C.cast(y.contents.grad_fn, C.POINTER(self.B.GradFn))
+                ms_b = self.time(lambda: fn.contents.backward(fn, g))
+            else:
+                ms_b = self.time(lambda: self.lib.dnn_backward(self.d.scratch, y))
+            for t in inp.get("_zero", []):
+                self.lib.tensor_zero_grad(t)
+            if it >= 3:
+                tf.append(ms_f); tb.append(ms_b)
+        ms_f, ms_b = float(np.median(tf)), float(np.median(tb))
+        peak, unit, scale = (self.hbm, "GB/s", 1e9) if bound == "hbm" else (self.tf32, "TFLOP/s", 1e12)
+        af, ab = work_fwd / (ms_f * 1e-3) / scale, work_bwd / (ms_b * 1e-3) / scale
+        print(json.dumps({"op": name, "bound": bound, "fwd_ms": round(ms_f, 4), "bwd_ms": round(ms_b, 4),
+                          "fwd_achieved": round(af, 1), "bwd_achieved": round(ab, 1), "unit": unit, "peak": round(peak, 1),
+                          "fwd_frac": round(af / peak, 3), "bwd_frac": round(ab / peak, 3), "peak_source": self.src,
+                          "work_fwd": work_fwd, "work_bwd": work_bwd}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--gemm", default="tf32", choices=["tf32", "3xtf32", "fp32"])
+    args = ap.parse_args()
+    B = load_binding()
+    b = Bench(B, args.iters, args.small)
+    lib, d, rng = b.lib, b.d, b.rng
+    lib.dnn_cuda_set_gemm_mode({"fp32": 0, "tf32": 1, "3xtf32": 2}[args.gemm])
+    R = 1024 if args.small else 8192
+    Bt = 2 if args.small else 8
+
+    ops = args.op.split(",")
+
+    def want(n):
+        return "all" in ops or n in ops
+
+    def randn(*shape, scale=1.0):
+        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(scale))
+
+    if want("rms_norm"):
+        b.run("rms_norm", lambda: dict(x=b.dev(randn(R, 768), True), w=b.dev(np.ones(768, np.float32), True)),
+              lambda i: lib.tensor_rms_norm(d.scratch, i["x"], i["w"], 1e-5), (R, 768), 8 * R * 768, 16 * R * 768, "hbm")
+    if want("layer_norm"):
+        b.run("layer_norm", lambda: dict(x=b.dev(randn(R, 768), True), w=b.dev(np.ones(768, np.float32), True),
+                                         bb=b.dev(np.zeros(768, np.float32), True)),
+              lambda i: lib.tensor_layer_norm(d.scratch, i["x"], i["w"], i["bb"], 1e-5), (R, 768), 8 * R * 768, 16 * R * 768, "hbm")
+    if want("swiglu"):
+        n = R * 2048
+        b.run("swiglu", lambda: dict(g=b.dev(randn(R, 2048), True), u=b.dev(randn(R, 2048), True)),
+              lambda i: lib.tensor_swiglu(d.scratch, i["g"], i["u"]), (R, 2048), 12 * n, 28 * n, "hbm")
+    if want("rope"):
+        n = Bt * 12 * 1024 * 64
+        cos = np.cos(np.outer(np.arange(1024), 10000.0 ** (-np.arange(32) / 32.0))).astype(np.float32)
+        sin = np.sin(np.outer(np.arange(1024), 10000.0 ** (-np.arange(32) / 32.0))).astype(np.float32)
+        b.run("rope", lambda: dict(x=b.dev(randn(Bt, 12, 1024, 64), True), c=b.dev(cos), s=b.dev(sin)),
+              lambda i: lib.tensor_rope(d.scratch, i["x"], i["c"], i["s"]), (Bt, 12, 1024, 64), 8 * n, 12 * n, "hbm")
+    if want("cross_entropy_masked"):
+        V = 32000
+        mask = (rng.random((Bt, 1024)) >= 0.1).astype(np.float32)
+        active = float(mask.sum())
+        b.run("cross_entropy_masked",
+              lambda: dict(x=b.dev(randn(Bt, 1024, V, scale=2.0), True), t=b.dev(rng.integers(0, V, size=(Bt, 1024)).astype(np.int32)),
+                           m=b.dev(mask)),
+              lambda i: lib.tensor_cross_entropy_masked(d.scratch, i["x"], i["t"], i["m"], 2), None,
+              4 * active * V, 12 * active * V, "hbm")
+    if want("matmul_add"):
+        M, K, N = R, 768, 3072
+        b.run("matmul_add", lambda: dict(a=b.dev(randn(M, K), True), w=b.dev(randn(K, N, scale=0.02), True),
+                                         bias=b.dev(np.zeros(N, np.float32), True)),
+              lambda i: lib.tensor_matmul_add(d.scratch, i["a"], i["w"], 0, i["bias"]), (M, N), 2.0 * M * N * K, 4.0 * M * N * K, "tensor")
+    for name, mode, prefix in (("attention_causal", 0, 0), ("attention_prefix_lm", 1, 196)):
+        if not want(name) and not want("attention"):
+            continue
+        H, T, D = 12, 1024, 64
+        lens = None if mode == 0 else rng.integers(200, 1025, size=Bt).astype(np.int32)
+        vis = 0
+        for bi in range(Bt):
+            nb = T if lens is None else int(lens[bi])
+            vis += sum(min(nb, (i + 1) if (mode == 0 or i >= prefix) else prefix) for i in range(nb))
+        flop = 4.0 * D * vis * H
+        lp = None if lens is None else lens.ctypes.data_as(C.POINTER(C.c_int))
+        b.run(name, lambda: dict(q=b.dev(randn(Bt, H, T, D), True), k=b.dev(randn(Bt, H, T, D), True), v=b.dev(randn(Bt, H, T, D), True)),
+              lambda i, mode=mode, prefix=prefix, lp=lp: lib.tensor_attention_ex(d.scratch, i["q"], i["k"], i["v"], None, mode, prefix, lp),
+              (Bt, H, T, D), flop, 2 * flop, "tensor")
+    if want("adamw"):
+        P = (16 if args.small else 124) * 1000 * 1000
+        t = lib.tensor_zeros(d.params, 1, B.ints([P]), 1)
+        arr = (B.TensorP * 1)(t)
+        opt = lib.adamw_create(d.params, arr, 1, 6e-4, 0.9, 0.95, 1e-8, 0.1)
+        t.contents.grad = lib.tensor_zeros(d.params, 1, B.ints([P]), 0).contents.data
+        ts = []
+        for it in range(3 + args.iters):
+            b.flush_l2()
+            ms = b.time(lambda: lib.adamw_step(opt))
+            if it >= 3:
+                ts.append(ms)
+        ms = float(np.median(ts))
+        a = 28.0 * P / (ms * 1e-3) / 1e9
+        print(json.dumps({"op": "adamw", "bound": "hbm", "ms": round(ms, 4), "achieved": round(a, 1), "unit": "GB/s", "peak": b.hbm,
+                          "frac": round(a / b.hbm, 3), "params": P, "peak_source": b.src}), flush=True)
+    d.close()
+
+
+if __name__ == "__main__":
+    main()
