@@ -30,6 +30,7 @@ struct AttnParams {
     int B, H, N, d;
     int prefix;                  // 0 for causal
     float scale;
+    int store;                   // bit 0/1/2: dq/dk/dv are written, not added to
 };
 
 __device__ __forceinline__ int visible_len(int i, int prefix, int nb) {
@@ -269,8 +270,8 @@ __global__ void __launch_bounds__(256) attn_bwd_dkv_kernel(AttnParams p) {
             int col = tx + 16 * c;
             if (col >= p.d) continue;
             int64_t at = (slice + row) * p.d + col;
-            if (p.dk) p.dk[at] += dk[jj][c];
-            if (p.dv) p.dv[at] += dv[jj][c];
+            if (p.dk) p.dk[at] = (p.store & 2) ? dk[jj][c] : p.dk[at] + dk[jj][c];
+            if (p.dv) p.dv[at] = (p.store & 4) ? dv[jj][c] : p.dv[at] + dv[jj][c];
         }
     }
 }
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_kernel(AttnParams p) {
 #pragma unroll
         for (int c = 0; c < CC; c++) {
             int col = tx + 16 * c;
-            if (col < p.d) p.dq[(slice + row) * p.d + col] += dq[i][c];
+            if (col < p.d) { int64_t at = (slice + row) * p.d + col; p.dq[at] = (p.store & 1) ? dq[i][c] : p.dq[at] + dq[i][c]; }
         }
     }
 }
@@ -366,7 +367,7 @@ bool attn_tc_supported(int d, const void *q, const void *k, const void *v);
 void attn_forward_tc(const float *q, const float *k, const float *v, float *o, float *lse, const int *seq_lens,
                      int B, int H, int N, int d, int prefix, float scale);
 void attn_backward_tc(const float *q, const float *k, const float *v, const float *lse, const float *dout, const float *dvec,
-                      float *dq, float *dk, float *dv, const int *seq_lens, int B, int H, int N, int d, int prefix, float scale);
+                      float *dq, float *dk, float *dv, const int *seq_lens, int B, int H, int N, int d, int prefix, float scale, int store);
 
 // TF32 mode runs on the tensor core (head dims 32 and 64); the FP32 and 3xTF32 modes, and
 // other head dims, run the exact kernels of this file.
@@ -397,15 +398,21 @@ static void attention_backward(grad_fn *fn, tensor *go) {
     p.o = (float *)sv->out->data; p.lse = sv->lse; p.seq_lens = sv->seq_lens_dev;
     p.prefix = sv->mode == ATTENTION_PREFIX_LM ? sv->prefix : 0; p.scale = sv->scale;
     p.dout = (const float *)go->data;
-    p.dq = wants_grad(q) ? _grad_ensure(q) : nullptr;
-    p.dk = wants_grad(k) ? _grad_ensure(k) : nullptr;
-    p.dv = wants_grad(v) ? _grad_ensure(v) : nullptr;
+    // Without seq_lens the kernels write every row of dq, dk and dv, so a gradient buffer
+    // that nothing has written yet is stored to instead of zero-filled and added to.
+    // Operands that share a buffer, or padded batches, keep the add.
+    bool full = sv->seq_lens_dev == nullptr && q != k && q != v && k != v;
+    bool aq = true, ak = true, av = true;
+    p.dq = wants_grad(q) ? (full ? grad_full(q, &aq) : _grad_ensure(q)) : nullptr;
+    p.dk = wants_grad(k) ? (full ? grad_full(k, &ak) : _grad_ensure(k)) : nullptr;
+    p.dv = wants_grad(v) ? (full ? grad_full(v, &av) : _grad_ensure(v)) : nullptr;
+    p.store = (aq ? 0 : 1) | (ak ? 0 : 2) | (av ? 0 : 4);
     int64_t rows = (int64_t)p.B * p.H * p.N;
     float *dvec = dev_alloc_t<float>(fn->pool, (size_t)rows);
     attn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(p.dout, p.o, dvec, rows, p.d);
     LAUNCHED("attn_bwd_prep_kernel");
     p.dvec = dvec;
-    if (use_tc(p)) attn_backward_tc(p.q, p.k, p.v, p.lse, p.dout, p.dvec, p.dq, p.dk, p.dv, p.seq_lens, p.B, p.H, p.N, p.d, p.prefix, p.scale);
+    if (use_tc(p)) attn_backward_tc(p.q, p.k, p.v, p.lse, p.dout, p.dvec, p.dq, p.dk, p.dv, p.seq_lens, p.B, p.H, p.N, p.d, p.prefix, p.scale, p.store);
     else attn_backward_fp32(p);
 }
 

@@ -41,6 +41,7 @@ struct AttnTcParams {
     int B, H, N;
     int prefix;
     float scale;
+    int store;                           // bit 0/1/2: dq/dk/dv are written, not added to
 };
 
 __device__ __forceinline__ int vis_len(int i, int prefix, int nb) {
@@ -462,14 +463,16 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_co
                 tc_ld32(t_dk + lane_base + c0, c);
                 if (p.dv && key < nb) {
                     float4 *dst = reinterpret_cast<float4 *>(p.dv + (slice + key) * HD + c0);
+                    const bool st = p.store & 4;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) { float4 v = dst[j >> 2];
+                    for (int j = 0; j < 32; j += 4) { float4 v = st ? make_float4(0.f, 0.f, 0.f, 0.f) : dst[j >> 2];
                         v.x += __uint_as_float(a[j]); v.y += __uint_as_float(a[j + 1]); v.z += __uint_as_float(a[j + 2]); v.w += __uint_as_float(a[j + 3]); dst[j >> 2] = v; }
                 }
                 if (p.dk && key < nb) {
                     float4 *dst = reinterpret_cast<float4 *>(p.dk + (slice + key) * HD + c0);
+                    const bool st = p.store & 2;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) { float4 v = dst[j >> 2];
+                    for (int j = 0; j < 32; j += 4) { float4 v = st ? make_float4(0.f, 0.f, 0.f, 0.f) : dst[j >> 2];
                         v.x += __uint_as_float(c[j]); v.y += __uint_as_float(c[j + 1]); v.z += __uint_as_float(c[j + 2]); v.w += __uint_as_float(c[j + 3]); dst[j >> 2] = v; }
                 }
             }
@@ -634,8 +637,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_con
                 tc_ld32(t_dq + lane_base + c0, a);
                 if (live) {
                     float4 *dst = reinterpret_cast<float4 *>(p.dq + (slice + row) * HD + c0);
+                    const bool st = p.store & 1;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) { float4 v = dst[j >> 2];
+                    for (int j = 0; j < 32; j += 4) { float4 v = st ? make_float4(0.f, 0.f, 0.f, 0.f) : dst[j >> 2];
                         v.x += __uint_as_float(a[j]); v.y += __uint_as_float(a[j + 1]); v.z += __uint_as_float(a[j + 2]); v.w += __uint_as_float(a[j + 3]); dst[j >> 2] = v; }
                 }
             }
@@ -682,7 +686,7 @@ bool attn_tc_supported(int d, const void *q, const void *k, const void *v) {
 
 struct AttnParamsHost {           // mirrors the fields of attention.cu's AttnParams that are needed here
     const float *q, *k, *v; float *o, *lse; const float *dout, *dvec; float *dq, *dk, *dv; const int *seq_lens;
-    int B, H, N, d, prefix; float scale;
+    int B, H, N, d, prefix; float scale; int store;
 };
 
 template <int HD>
@@ -704,7 +708,7 @@ static void bwd_launch(const AttnParamsHost &a) {
     int BH = a.B * a.H;
     AttnTcParams p; memset(&p, 0, sizeof p);
     p.lse_in = a.lse; p.dvec = a.dvec; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.seq_lens = a.seq_lens;
-    p.B = a.B; p.H = a.H; p.N = a.N; p.prefix = a.prefix; p.scale = a.scale;
+    p.B = a.B; p.H = a.H; p.N = a.N; p.prefix = a.prefix; p.scale = a.scale; p.store = a.store;
     static bool once = false;
     if (!once) {
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HD>::kSmem));
@@ -739,8 +743,9 @@ void attn_forward_tc(const float *q, const float *k, const float *v, float *o, f
 }
 
 void attn_backward_tc(const float *q, const float *k, const float *v, const float *lse, const float *dout, const float *dvec,
-                      float *dq, float *dk, float *dv, const int *seq_lens, int B, int H, int N, int d, int prefix, float scale) {
+                      float *dq, float *dk, float *dv, const int *seq_lens, int B, int H, int N, int d, int prefix, float scale, int store) {
     AttnParamsHost a; memset(&a, 0, sizeof a);
+    a.store = store;
     a.q = q; a.k = k; a.v = v; a.lse = (float *)lse; a.dout = dout; a.dvec = dvec; a.dq = dq; a.dk = dk; a.dv = dv; a.seq_lens = seq_lens;
     a.B = B; a.H = H; a.N = N; a.d = d; a.prefix = prefix; a.scale = scale;
     if (d == 32) bwd_launch<32>(a); else bwd_launch<64>(a);

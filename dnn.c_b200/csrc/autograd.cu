@@ -7,6 +7,7 @@
 // buffer is device memory, zero-filled with a stream-ordered memset, and each
 // node's `backward` launches kernels instead of looping.
 #include "common.cuh"
+#include "device_utils.cuh"
 #include <vector>
 #include <unordered_set>
 
@@ -39,12 +40,84 @@ float *_grad_ensure(tensor *t) {
         fprintf(stderr, "_grad_ensure: tensor %p has NULL pool (ndim=%d)\n", (void *)base, base->ndim);
         abort();
     }
-    if (!base->grad)
+    if (!base->grad) {
         base->grad = (float *)dev_alloc(base->pool, (size_t)numel_of(base) * sizeof(float), true);
+        base->grad_fresh = 0;
+    } else if (base->grad_fresh) {
+        k_fill(base->grad, numel_of(base), 0.0f);
+        base->grad_fresh = 0;
+    }
     return base->grad;
 }
 
 }  // extern "C"
+
+namespace dnnb {
+
+float *grad_full(tensor *t, bool *accumulate) {
+    tensor *base = t;
+    while (base->parent) base = base->parent;
+    // the caller writes every element of t; that is every element of the root's buffer only
+    // if t spans it (the root itself, or a contiguous reshape of all of it)
+    bool spans = t->contiguous && t->offset == 0 && numel_of(t) == numel_of(base);
+    if (!spans) { *accumulate = true; return _grad_ensure(t); }
+    if (!base->grad) {
+        DNN_CHECK(base->pool, "gradient requested for a tensor without a pool");
+        base->grad = (float *)dev_alloc(base->pool, (size_t)numel_of(base) * sizeof(float), false);
+        base->grad_fresh = 0;
+        *accumulate = false;
+    } else if (base->grad_fresh) {
+        base->grad_fresh = 0;
+        *accumulate = false;
+    } else {
+        *accumulate = true;
+    }
+    return base->grad;
+}
+
+// Zeroes, in each of `blocks` runs of `pitch` floats, the elements outside [lo, hi).
+__global__ void zero_outside_kernel(float *__restrict__ p, int64_t pitch, int64_t blocks, int64_t lo, int64_t hi) {
+    int64_t gap = pitch - (hi - lo);
+    int64_t total = blocks * gap;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t b = i / gap, r = i % gap;
+        p[b * pitch + (r < lo ? r : r - lo + hi)] = 0.0f;
+    }
+}
+
+float *grad_rows(tensor *t, bool *accumulate) {
+    tensor *base = t;
+    while (base->parent) base = base->parent;
+    bool fresh = !base->grad || base->grad_fresh;
+    int nd = t->ndim;
+    if (!fresh || nd < 1 || t == base) return grad_full(t, accumulate);
+    int64_t inner = 1;
+    bool packed = true;
+    for (int d = nd - 1; d >= 1; d--) { if (t->strides[d] != inner) packed = false; inner *= t->shape[d]; }
+    int64_t total = numel_of(base);
+    int64_t pitch = t->shape[0] > 1 ? (int64_t)t->strides[0] : total;
+    int64_t lo = t->offset;
+    bool slab = packed && inner > 0 && pitch >= inner && (int64_t)t->shape[0] * pitch == total && lo >= 0 && lo + inner <= pitch;
+    if (!slab) { *accumulate = true; return _grad_ensure(t); }
+    if (!base->grad) {
+        DNN_CHECK(base->pool, "gradient requested for a tensor without a pool");
+        base->grad = (float *)dev_alloc(base->pool, (size_t)total * sizeof(float), false);
+    }
+    base->grad_fresh = 0;
+    if (pitch > inner) {
+        int64_t gaps = (int64_t)t->shape[0] * (pitch - inner);
+        zero_outside_kernel<<<grid_for(gaps, 256), 256, 0, stream()>>>(base->grad, pitch, t->shape[0], lo, lo + inner);
+        LAUNCHED("zero_outside_kernel");
+    }
+    *accumulate = false;
+    return base->grad;
+}
+
+void grad_settle(tensor *t) {
+    if (t->grad && t->grad_fresh) { k_fill(t->grad, numel_of(t), 0.0f); t->grad_fresh = 0; }
+}
+
+}  // namespace dnnb
 
 namespace {
 
@@ -78,6 +151,7 @@ extern "C" void dnn_backward(struct mem_pool *scratch, tensor *loss) {
         loss->grad = (float *)dev_alloc(loss->pool, (size_t)n * sizeof(float), false);
     }
     k_fill(loss->grad, n, 1.0f);
+    loss->grad_fresh = 0;
 
     for (size_t i = topo.order.size(); i-- > 0;) {
         tensor *t = topo.order[i];

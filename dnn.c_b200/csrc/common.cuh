@@ -71,6 +71,21 @@ inline View view_of(const tensor *t) {
 View bcast_view(const tensor *t, int out_ndim, const int *out_shape);
 int  bcast_shape(int na, const int *sa, int nb, const int *sb, int *out);   // src/broadcast.c
 
+// Gradient destinations.  The reference zero-fills every gradient buffer when it is created
+// and every backward adds to it.  Adding to zeros equals storing, so a buffer that is still
+// "fresh" (allocated, never written) may be overwritten by an op that covers ALL of it; this
+// saves the memset and the read half of the read-modify-write on most activation gradients.
+//   grad_full(t, acc)  for ops that write the whole logical extent of t: returns the root's
+//                      gradient buffer; acc=false means "store, the buffer is fresh".
+//   grad_rows(t, acc)  same, and also for a view that is one packed slab [lo, hi) of every
+//                      leading-dim block of its root (a slice along dim 1): the part of the
+//                      fresh buffer outside the slabs is zeroed, the slabs are stored to.
+//   _grad_ensure(t)    for everything else: the buffer is zero-filled if it was fresh.
+//   grad_settle(t)     before a gradient is READ (norm, clip, AdamW, all-reduce, download).
+float *grad_full(tensor *t, bool *accumulate);
+float *grad_rows(tensor *t, bool *accumulate);
+void   grad_settle(tensor *t);
+
 // Attaches a tape node to `out` (src/autograd.c:29-33 + the per-op boilerplate).
 grad_fn *attach(struct mem_pool *scratch, tensor *out, void (*bw)(grad_fn *, tensor *),
                 int n_inputs, int n_saved);
@@ -83,7 +98,7 @@ void k_copy(float *dst, const float *src, int64_t n);
 void k_gather(float *dst, const float *src, const View &sv, int64_t n);
 void k_scatter(float *dst, const View &dv, const float *src, int64_t n, bool accumulate);
 // column sums: out[c] += sum_r g[r*C + c]
-void k_colsum_acc(float *out, const float *g, int64_t rows, int C);
+void k_colsum_acc(float *out, const float *g, int64_t rows, int C, bool accumulate = true);
 
 // General strided GEMM:  C[m,n] (=|+=) sum_k A[m,k]*B[k,n] (+ bias[n])
 struct GemmArgs {

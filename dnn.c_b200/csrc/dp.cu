@@ -107,10 +107,24 @@ int dnn_cuda_dp_init(int rank, int world_size, const void *id_128_bytes) {
 
 int dnn_cuda_dp_world_size(void) { return g_world; }
 
+// Host-only view of the bucket planner (no device work): given n buffers (address, bytes),
+// writes up to `cap` buckets and returns how many there are.
+int dnn_cuda_dp_plan_buckets(const size_t *addrs, const size_t *bytes, int n, size_t bucket_bytes,
+                             size_t *out_addrs, size_t *out_bytes, int cap) {
+    if (n < 0 || bucket_bytes == 0) return -1;
+    std::vector<Span> grads;
+    for (int i = 0; i < n; i++) grads.push_back(Span{(char *)addrs[i], bytes[i]});
+    std::vector<Span> b = plan_buckets(grads, bucket_bytes);
+    for (int i = 0; i < (int)b.size() && i < cap; i++) { out_addrs[i] = (size_t)b[i].p; out_bytes[i] = b[i].bytes; }
+    return (int)b.size();
+}
+
 int dnn_cuda_dp_allreduce_grads(tensor **params, int n_params) {
     if (g_world == 1) return 0;
     if (!g_comm) { g_dp_error = "dp_allreduce: communicator not initialised"; return -2; }
     std::vector<Span> grads;
+    for (int i = 0; i < n_params; i++)
+        if (params[i]->grad) grad_settle(params[i]);
     for (int i = 0; i < n_params; i++)
         if (params[i]->grad) grads.push_back(Span{(char *)params[i]->grad, (size_t)numel_of(params[i]) * 4});
     if (grads.empty()) return 0;

@@ -137,12 +137,12 @@ __global__ void colsum_partial_v4_kernel(const float *__restrict__ g, float *__r
         *reinterpret_cast<float4 *>(partial + (int64_t)blockIdx.y * C + c) = t;
     }
 }
-__global__ void colsum_final_kernel(float *__restrict__ out, const float *__restrict__ partial, int nparts, int C) {
+__global__ void colsum_final_kernel(float *__restrict__ out, const float *__restrict__ partial, int nparts, int C, int acc) {
     int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     float s = 0.f;
     for (int p = 0; p < nparts; p++) s += partial[(int64_t)p * C + c];
-    out[c] += s;
+    out[c] = acc ? out[c] + s : s;
 }
 
 // Scratch for the partials lives in a small cache owned by this file, grown
@@ -150,7 +150,7 @@ __global__ void colsum_final_kernel(float *__restrict__ out, const float *__rest
 static float *g_colsum_scratch = nullptr;
 static size_t g_colsum_cap = 0;
 
-void k_colsum_acc(float *out, const float *g, int64_t rows, int C) {
+void k_colsum_acc(float *out, const float *g, int64_t rows, int C, bool accumulate) {
     if (rows <= 0 || C <= 0) return;
     int nparts = (int)((rows + 255) / 256);
     if (nparts > 512) nparts = 512;
@@ -172,7 +172,7 @@ void k_colsum_acc(float *out, const float *g, int64_t rows, int C) {
         colsum_partial_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per);
         LAUNCHED("colsum_partial_kernel");
     }
-    colsum_final_kernel<<<(C + 127) / 128, 128, 0, stream()>>>(out, g_colsum_scratch, nparts, C);
+    colsum_final_kernel<<<(C + 127) / 128, 128, 0, stream()>>>(out, g_colsum_scratch, nparts, C, accumulate ? 1 : 0);
     LAUNCHED("colsum_final_kernel");
 }
 

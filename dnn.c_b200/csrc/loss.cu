@@ -114,14 +114,18 @@ __global__ void ce_bwd_kernel(const float *__restrict__ logits, const int *__res
                               const float *__restrict__ mask, SliceMap map,
                               const float *__restrict__ max_in, const float *__restrict__ se_in,
                               const float *__restrict__ gout, const float *__restrict__ inv,
-                              float *__restrict__ dlogits) {
+                              float *__restrict__ dlogits, int acc) {
     int64_t s = blockIdx.x;
     int64_t lo, mo;
     slice_offsets(map, s, lo, mo);
     float m = mask ? mask[mo] : 1.0f;
-    if (mask && m == 0.0f) return;
-    const float *row = logits + lo;
     float *drow = dlogits + lo;
+    if (mask && m == 0.0f) {
+        // a masked-out position has no gradient; a buffer that was not zero-filled gets its zeros here
+        if (!acc) for (int j = threadIdx.x; j < map.C; j += blockDim.x) drow[(int64_t)j * map.cstride] = 0.f;
+        return;
+    }
+    const float *row = logits + lo;
     float mx = max_in[s], se = se_in[s];
     int tgt = target[s];
     float scale = gout[0] * inv[0];
@@ -131,7 +135,7 @@ __global__ void ce_bwd_kernel(const float *__restrict__ logits, const int *__res
         const float4 *r4 = reinterpret_cast<const float4 *>(row);
         float4 *d4 = reinterpret_cast<float4 *>(drow);
         for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
-            float4 v = r4[j], d = d4[j];
+            float4 v = r4[j], d = acc ? d4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
             int c = j * 4;
             d.x += (expf(v.x - mx) / se - (c == tgt ? 1.f : 0.f)) * scale;
             d.y += (expf(v.y - mx) / se - (c + 1 == tgt ? 1.f : 0.f)) * scale;
@@ -142,7 +146,8 @@ __global__ void ce_bwd_kernel(const float *__restrict__ logits, const int *__res
     } else {
         for (int j = threadIdx.x; j < C; j += blockDim.x) {
             int64_t o = (int64_t)j * map.cstride;
-            drow[o] += (expf(row[o] - mx) / se - (j == tgt ? 1.f : 0.f)) * scale;
+            float r = (expf(row[o] - mx) / se - (j == tgt ? 1.f : 0.f)) * scale;
+            drow[o] = acc ? drow[o] + r : r;
         }
     }
 }
@@ -176,12 +181,13 @@ static void ce_backward_common(grad_fn *fn, tensor *go, bool masked) {
     tensor *mask = masked ? fn->saved_tensors[3] : nullptr;
     int dim = *(int *)fn->saved_tensors[masked ? 4 : 3];
     const float *inv = (const float *)fn->saved_tensors[masked ? 5 : 4];
-    float *ag = _grad_ensure(logits);
     SliceMap map = make_map(logits, mask, dim);
     int64_t n_slices = numel_of(logits) / map.C;
     if (n_slices <= 0) return;
+    bool acc = true;
+    float *ag = grad_rows(logits, &acc);
     ce_bwd_kernel<<<(unsigned)n_slices, 256, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
-        mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, ag);
+        mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, ag, acc ? 1 : 0);
     LAUNCHED(masked ? "ce_masked_bwd_kernel" : "ce_bwd_kernel");
 }
 static void cross_entropy_backward(grad_fn *fn, tensor *go) { ce_backward_common(fn, go, false); }

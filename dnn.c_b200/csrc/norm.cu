@@ -74,7 +74,7 @@ template <bool LN, int T>
 __global__ void norm_bwd_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
                                 const float *__restrict__ mean, const float *__restrict__ rstd,
                                 float *__restrict__ dx, float *__restrict__ dw_part, float *__restrict__ db_part,
-                                int64_t rows, int d) {
+                                int64_t rows, int d, int acc_dx) {
     int lane = threadIdx.x & 31;
     int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
@@ -116,7 +116,7 @@ __global__ void norm_bwd_kernel(const float *__restrict__ x, const float *__rest
             for (int t = 0; t < T; t++) {
                 int j = (lane + 32 * t) * 4;
                 if (j < d) {
-                    float4 o = ld4(dxr + j), v = xv[t], dy = dyv[t];
+                    float4 o = acc_dx ? ld4(dxr + j) : make_float4(0.f, 0.f, 0.f, 0.f), v = xv[t], dy = dyv[t];
                     o.x += rs * (dy.x - mdy) - rs * k1 * v.x; o.y += rs * (dy.y - mdy) - rs * k1 * v.y;
                     o.z += rs * (dy.z - mdy) - rs * k1 * v.z; o.w += rs * (dy.w - mdy) - rs * k1 * v.w;
                     st4(dxr + j, o);
@@ -140,7 +140,7 @@ __global__ void norm_bwd_kernel(const float *__restrict__ x, const float *__rest
 template <bool LN>
 __global__ void norm_bwd_dx_scalar_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
                                           const float *__restrict__ mean, const float *__restrict__ rstd,
-                                          float *__restrict__ dx, int d) {
+                                          float *__restrict__ dx, int d, int acc_dx) {
     __shared__ float sh[32];
     int64_t r = blockIdx.x;
     const float *xr = x + r * d, *gr = g + r * d;
@@ -155,7 +155,8 @@ __global__ void norm_bwd_dx_scalar_kernel(const float *__restrict__ x, const flo
     float k1 = rs * rs * inv_d * s1, mdy = LN ? s2 * inv_d : 0.f;
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
         float dy = gr[j] * (w ? w[j] : 1.f), v = xr[j] - mu;
-        dx[r * d + j] += rs * (dy - mdy) - rs * k1 * v;
+        float val = rs * (dy - mdy) - rs * k1 * v;
+        dx[r * d + j] = acc_dx ? dx[r * d + j] + val : val;
     }
 }
 // t[r,j] = g*(x-mu)*rs, to be column-summed
@@ -171,7 +172,7 @@ __global__ void norm_dw_terms_kernel(const float *__restrict__ x, const float *_
 
 // out[j] += sum_p part[p*d + j].  CTA = 32 columns x 32 row-lanes; lane y sums
 // p = y, y+32, ... and the 32 lane sums are added in lane order (fixed order).
-__global__ void norm_part_reduce_kernel(float *__restrict__ out, const float *__restrict__ part, int nparts, int d) {
+__global__ void norm_part_reduce_kernel(float *__restrict__ out, const float *__restrict__ part, int nparts, int d, int acc) {
     __shared__ float tile[32][33];
     int j = blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
@@ -183,7 +184,7 @@ __global__ void norm_part_reduce_kernel(float *__restrict__ out, const float *__
         float t = 0.f;
 #pragma unroll
         for (int y = 0; y < 32; y++) t += tile[y][threadIdx.x];
-        out[j] += t;
+        out[j] = acc ? out[j] + t : t;
     }
 }
 
@@ -202,14 +203,15 @@ static void norm_forward(const float *x, const float *w, const float *b, float *
 
 template <bool LN, int T>
 static void launch_bwd(const float *x, const float *w, const float *g, const float *mean, const float *rstd,
-                       float *dx, float *dwp, float *dbp, int64_t rows, int d, int grid) {
-    norm_bwd_kernel<LN, T><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d);
+                       float *dx, float *dwp, float *dbp, int64_t rows, int d, int grid, int acc_dx) {
+    norm_bwd_kernel<LN, T><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, acc_dx);
     LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
 }
 
 template <bool LN>
 static void norm_backward(struct mem_pool *pool, const float *x, const float *w, const float *g, const float *mean,
-                          const float *rstd, float *dx, float *dw, float *db, int64_t rows, int d) {
+                          const float *rstd, float *dx, float *dw, float *db, int64_t rows, int d,
+                          bool acc_dx, bool acc_dw, bool acc_db) {
     if (rows <= 0) return;
     bool vec = d % 4 == 0 && d <= 2048 && aligned16(x) && aligned16(g) && (!w || aligned16(w)) && (!dx || aligned16(dx));
     if (vec) {
@@ -220,27 +222,27 @@ static void norm_backward(struct mem_pool *pool, const float *x, const float *w,
         float *dwp = dw ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
         float *dbp = (LN && db) ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
         int T = (d + 127) / 128;
-        if (T <= 1)      launch_bwd<LN, 1>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
-        else if (T <= 2) launch_bwd<LN, 2>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
-        else if (T <= 4) launch_bwd<LN, 4>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
-        else if (T <= 6) launch_bwd<LN, 6>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
-        else if (T <= 8) launch_bwd<LN, 8>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
-        else             launch_bwd<LN, 16>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid);
-        if (dwp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(dw, dwp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
-        if (dbp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(db, dbp, nparts, d); LAUNCHED("norm_part_reduce_kernel"); }
+        if (T <= 1)      launch_bwd<LN, 1>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
+        else if (T <= 2) launch_bwd<LN, 2>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
+        else if (T <= 4) launch_bwd<LN, 4>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
+        else if (T <= 6) launch_bwd<LN, 6>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
+        else if (T <= 8) launch_bwd<LN, 8>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
+        else             launch_bwd<LN, 16>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
+        if (dwp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(dw, dwp, nparts, d, acc_dw); LAUNCHED("norm_part_reduce_kernel"); }
+        if (dbp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(db, dbp, nparts, d, acc_db); LAUNCHED("norm_part_reduce_kernel"); }
         return;
     }
     if (dx) {
-        norm_bwd_dx_scalar_kernel<LN><<<(unsigned)rows, 256, 0, stream()>>>(x, w, g, mean, rstd, dx, d);
+        norm_bwd_dx_scalar_kernel<LN><<<(unsigned)rows, 256, 0, stream()>>>(x, w, g, mean, rstd, dx, d, acc_dx);
         LAUNCHED("norm_bwd_dx_scalar_kernel");
     }
     if (dw) {
         float *t = dev_alloc_t<float>(pool, (size_t)rows * d);
         norm_dw_terms_kernel<LN><<<grid_for(rows * d, 256), 256, 0, stream()>>>(x, g, mean, rstd, t, rows, d);
         LAUNCHED("norm_dw_terms_kernel");
-        k_colsum_acc(dw, t, rows, d);
+        k_colsum_acc(dw, t, rows, d, acc_dw);
     }
-    if (LN && db) k_colsum_acc(db, g, rows, d);
+    if (LN && db) k_colsum_acc(db, g, rows, d, acc_db);
 }
 
 static void rms_backward(grad_fn *fn, tensor *go) {
@@ -252,9 +254,10 @@ static void rms_backward(grad_fn *fn, tensor *go) {
     const float *xd = (const float *)x->data + x->offset;
     const float *gd = (const float *)go->data;
     const float *wd = weight ? (const float *)weight->data + weight->offset : nullptr;
-    float *dw = (weight && weight->requires_grad) ? _grad_ensure(weight) : nullptr;
-    float *dx = x->requires_grad ? _grad_ensure(x) : nullptr;   // the reference indexes dx from 0 (src/norm.c:339)
-    norm_backward<false>(fn->pool, xd, wd, gd, nullptr, rstd, dx, dw, nullptr, rows, d);
+    bool acc_w = true, acc_x = true;
+    float *dw = (weight && weight->requires_grad) ? grad_full(weight, &acc_w) : nullptr;
+    float *dx = x->requires_grad ? grad_full(x, &acc_x) : nullptr;   // the reference indexes dx from 0 (src/norm.c:339)
+    norm_backward<false>(fn->pool, xd, wd, gd, nullptr, rstd, dx, dw, nullptr, rows, d, acc_x, acc_w, true);
 }
 
 static void ln_backward(grad_fn *fn, tensor *go) {
@@ -266,10 +269,11 @@ static void ln_backward(grad_fn *fn, tensor *go) {
     const float *xd = (const float *)x->data + x->offset;
     const float *gd = (const float *)go->data;
     const float *wd = weight ? (const float *)weight->data + weight->offset : nullptr;
-    float *dw = (weight && weight->requires_grad) ? _grad_ensure(weight) : nullptr;
-    float *db = (bias && bias->requires_grad) ? _grad_ensure(bias) : nullptr;
-    float *dx = x->requires_grad ? _grad_ensure(x) : nullptr;
-    norm_backward<true>(fn->pool, xd, wd, gd, mean, rstd, dx, dw, db, rows, d);
+    bool acc_w = true, acc_b = true, acc_x = true;
+    float *dw = (weight && weight->requires_grad) ? grad_full(weight, &acc_w) : nullptr;
+    float *db = (bias && bias->requires_grad) ? grad_full(bias, &acc_b) : nullptr;
+    float *dx = x->requires_grad ? grad_full(x, &acc_x) : nullptr;
+    norm_backward<true>(fn->pool, xd, wd, gd, mean, rstd, dx, dw, db, rows, d, acc_x, acc_w, acc_b);
 }
 
 }  // namespace dnnb

@@ -57,7 +57,7 @@ struct AddBcast {
 // the result is deterministic (the reference scatters serially,
 // src/ops_elem.c:83-105).
 struct BcastReduce {
-    float *dst; const float *g; View dv; int out_ndim; int out_shape[DNN_MAX_DIMS];
+    float *dst; const float *g; View dv; int out_ndim; int out_shape[DNN_MAX_DIMS]; int acc;
     int64_t n_dst;     // logical elements of the operand
     int t_ndim; int t_shape[DNN_MAX_DIMS]; int t_strides[DNN_MAX_DIMS]; int t_offset;
     __device__ void operator()(int64_t e) const {
@@ -80,7 +80,7 @@ struct BcastReduce {
             }
             s += g[flat];
         }
-        dst[toff] += s;
+        dst[toff] = acc ? dst[toff] + s : s;
     }
 };
 
@@ -98,8 +98,9 @@ static bool lastdim_bias(const tensor *bias, const tensor *out) {
     return bias->ndim == 1 && out->ndim >= 2 && bias->shape[0] == out->shape[out->ndim - 1];
 }
 
-static void bcast_reduce_into(tensor *t, float *tg, const tensor *g) {
+static void bcast_reduce_into(tensor *t, float *tg, const tensor *g, bool acc = true) {
     BcastReduce f;
+    f.acc = acc ? 1 : 0;
     f.dst = tg; f.g = (const float *)g->data + g->offset; f.out_ndim = g->ndim;
     for (int d = 0; d < DNN_MAX_DIMS; d++) {
         f.out_shape[d] = d < g->ndim ? g->shape[d] : 1;
@@ -117,10 +118,11 @@ static void add_backward(grad_fn *fn, tensor *g) {
     tensor *ops[2] = {a, b};
     for (tensor *t : ops) {
         if (!wants_grad(t)) continue;
-        float *tg = _grad_ensure(t);
-        if (grad_contig(t, g)) k_axpy_acc(tg + t->offset, gd, n);
-        else if (lastdim_bias(t, g)) k_colsum_acc(tg + t->offset, gd, n / t->shape[0], t->shape[0]);
-        else bcast_reduce_into(t, tg, g);
+        bool acc = true;
+        float *tg = grad_full(t, &acc);        // each branch writes every element of t
+        if (grad_contig(t, g)) { if (acc) k_axpy_acc(tg + t->offset, gd, n); else k_copy(tg + t->offset, gd, n); }
+        else if (lastdim_bias(t, g)) k_colsum_acc(tg + t->offset, gd, n / t->shape[0], t->shape[0], acc);
+        else bcast_reduce_into(t, tg, g, acc);
     }
 }
 
@@ -165,14 +167,15 @@ static void cat_backward(grad_fn *fn, tensor *g) {
 struct ReluF  { float *o; const float *x; __device__ void operator()(int64_t i) const { float v = x[i]; o[i] = v > 0.f ? v : 0.f; } };
 struct ReluF4 { float4 *o; const float4 *x; __device__ void operator()(int64_t i) const {
     float4 v = x[i]; o[i] = make_float4(v.x > 0.f ? v.x : 0.f, v.y > 0.f ? v.y : 0.f, v.z > 0.f ? v.z : 0.f, v.w > 0.f ? v.w : 0.f); } };
-struct ReluB  { float *dx; const float *x, *g; __device__ void operator()(int64_t i) const { if (x[i] > 0.f) dx[i] += g[i]; } };
-struct ReluB4 { float4 *dx; const float4 *x, *g; __device__ void operator()(int64_t i) const {
-    float4 v = x[i], gg = g[i], d = dx[i];
+struct ReluB  { float *dx; const float *x, *g; int acc; __device__ void operator()(int64_t i) const {
+    float d = acc ? dx[i] : 0.f; if (x[i] > 0.f) d += g[i]; dx[i] = d; } };
+struct ReluB4 { float4 *dx; const float4 *x, *g; int acc; __device__ void operator()(int64_t i) const {
+    float4 v = x[i], gg = g[i], d = acc ? dx[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     if (v.x > 0.f) d.x += gg.x; if (v.y > 0.f) d.y += gg.y; if (v.z > 0.f) d.z += gg.z; if (v.w > 0.f) d.w += gg.w; dx[i] = d; } };
 
 struct SiluF { float *o; const float *x; __device__ void operator()(int64_t i) const { float v = x[i]; o[i] = v / (1.0f + expf(-v)); } };
-struct SiluB { float *dx; const float *x, *g; __device__ void operator()(int64_t i) const {
-    float v = x[i], s = sigmoidf_(v); dx[i] += s * (1.0f + v - v * s) * g[i]; } };
+struct SiluB { float *dx; const float *x, *g; int acc; __device__ void operator()(int64_t i) const {
+    float v = x[i], s = sigmoidf_(v), r = s * (1.0f + v - v * s) * g[i]; dx[i] = acc ? dx[i] + r : r; } };
 
 __device__ __forceinline__ float swiglu1(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 struct SwigluF  { float *o; const float *g, *u; __device__ void operator()(int64_t i) const { o[i] = swiglu1(g[i], u[i]); } };
@@ -183,11 +186,12 @@ __device__ __forceinline__ void swiglu_b1(float gate, float up, float go, float 
     dg += go * (s * (1.0f + gate - gate * s)) * up;
     du += go * (gate * s);
 }
-struct SwigluB  { float *dg, *du; const float *g, *u, *go; __device__ void operator()(int64_t i) const {
+struct SwigluB  { float *dg, *du; const float *g, *u, *go; int acc_g, acc_u; __device__ void operator()(int64_t i) const {
     float a = 0.f, b = 0.f; swiglu_b1(g[i], u[i], go[i], a, b);
-    if (dg) dg[i] += a; if (du) du[i] += b; } };
-struct SwigluB4 { float4 *dg, *du; const float4 *g, *u, *go; __device__ void operator()(int64_t i) const {
-    float4 a = g[i], b = u[i], o = go[i], x = dg[i], y = du[i];
+    if (dg) dg[i] = acc_g ? dg[i] + a : a; if (du) du[i] = acc_u ? du[i] + b : b; } };
+struct SwigluB4 { float4 *dg, *du; const float4 *g, *u, *go; int acc_g, acc_u; __device__ void operator()(int64_t i) const {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 a = g[i], b = u[i], o = go[i], x = acc_g ? dg[i] : z, y = acc_u ? du[i] : z;
     swiglu_b1(a.x, b.x, o.x, x.x, y.x); swiglu_b1(a.y, b.y, o.y, x.y, y.y);
     swiglu_b1(a.z, b.z, o.z, x.z, y.z); swiglu_b1(a.w, b.w, o.w, x.w, y.w);
     dg[i] = x; du[i] = y; } };
@@ -204,16 +208,17 @@ static void relu_backward(grad_fn *fn, tensor *g) {
     tensor *a = fn->inputs[0];
     if (!wants_grad(a)) return;
     int64_t n = numel_of(a);
-    float *ag = _grad_ensure(a);
+    bool acc = true;
+    float *ag = grad_full(a, &acc);
     const float *gd = (const float *)g->data;
     if (a->contiguous) {
         float *dx = ag + a->offset; const float *x = (const float *)a->data + a->offset;
-        if (v4ok(n, {dx, x, gd})) ew_launch("relu_bwd_kernel", n / 4, ReluB4{(float4 *)dx, (const float4 *)x, (const float4 *)gd});
-        else ew_launch("relu_bwd_kernel", n, ReluB{dx, x, gd});
+        if (v4ok(n, {dx, x, gd})) ew_launch("relu_bwd_kernel", n / 4, ReluB4{(float4 *)dx, (const float4 *)x, (const float4 *)gd, acc});
+        else ew_launch("relu_bwd_kernel", n, ReluB{dx, x, gd, acc});
     } else {
-        float *xt = dev_alloc_t<float>(fn->pool, (size_t)n), *dt = dev_alloc_t<float>(fn->pool, (size_t)n, true);
+        float *xt = dev_alloc_t<float>(fn->pool, (size_t)n), *dt = dev_alloc_t<float>(fn->pool, (size_t)n);
         k_gather(xt, (const float *)a->data, view_of(a), n);
-        ew_launch("relu_bwd_kernel", n, ReluB{dt, xt, gd});
+        ew_launch("relu_bwd_kernel", n, ReluB{dt, xt, gd, 0});
         k_scatter(ag, view_of(a), dt, n, true);
     }
 }
@@ -222,14 +227,15 @@ static void silu_backward(grad_fn *fn, tensor *g) {
     tensor *a = fn->inputs[0];
     if (!wants_grad(a)) return;
     int64_t n = numel_of(a);
-    float *ag = _grad_ensure(a);
+    bool acc = true;
+    float *ag = grad_full(a, &acc);
     const float *gd = (const float *)g->data;
     if (a->contiguous) {
-        ew_launch("silu_bwd_kernel", n, SiluB{ag + a->offset, (const float *)a->data + a->offset, gd});
+        ew_launch("silu_bwd_kernel", n, SiluB{ag + a->offset, (const float *)a->data + a->offset, gd, acc});
     } else {
-        float *xt = dev_alloc_t<float>(fn->pool, (size_t)n), *dt = dev_alloc_t<float>(fn->pool, (size_t)n, true);
+        float *xt = dev_alloc_t<float>(fn->pool, (size_t)n), *dt = dev_alloc_t<float>(fn->pool, (size_t)n);
         k_gather(xt, (const float *)a->data, view_of(a), n);
-        ew_launch("silu_bwd_kernel", n, SiluB{dt, xt, gd});
+        ew_launch("silu_bwd_kernel", n, SiluB{dt, xt, gd, 0});
         k_scatter(ag, view_of(a), dt, n, true);
     }
 }
@@ -239,14 +245,16 @@ static void swiglu_backward(grad_fn *fn, tensor *go) {
     int64_t n = numel_of(go);
     const float *god = (const float *)go->data + go->offset;
     bool ng = wants_grad(gate), nu = wants_grad(up);
-    float *ag = ng ? _grad_ensure(gate) : nullptr, *bg = nu ? _grad_ensure(up) : nullptr;
+    bool acc_g = true, acc_u = true;
+    float *ag = ng ? grad_full(gate, &acc_g) : nullptr, *bg = nu ? grad_full(up, &acc_u) : nullptr;
+    if (gate == up) acc_u = true;            // same buffer: the second write must add
     if (grad_contig(gate, go) && grad_contig(up, go)) {
         float *dg = ag ? ag + gate->offset : nullptr, *du = bg ? bg + up->offset : nullptr;
         const float *g = (const float *)gate->data + gate->offset, *u = (const float *)up->data + up->offset;
-        if (dg && du && v4ok(n, {dg, du, g, u, god}))
-            ew_launch("swiglu_bwd_kernel", n / 4, SwigluB4{(float4 *)dg, (float4 *)du, (const float4 *)g, (const float4 *)u, (const float4 *)god});
+        if (dg && du && dg != du && v4ok(n, {dg, du, g, u, god}))
+            ew_launch("swiglu_bwd_kernel", n / 4, SwigluB4{(float4 *)dg, (float4 *)du, (const float4 *)g, (const float4 *)u, (const float4 *)god, acc_g, acc_u});
         else
-            ew_launch("swiglu_bwd_kernel", n, SwigluB{dg, du, g, u, god});
+            ew_launch("swiglu_bwd_kernel", n, SwigluB{dg, du, g, u, god, acc_g, acc_u});
         return;
     }
     // Broadcast operands: expand to the output shape, differentiate there, then
@@ -255,10 +263,10 @@ static void swiglu_backward(grad_fn *fn, tensor *go) {
     float *dge = dev_alloc_t<float>(fn->pool, (size_t)n, true), *due = dev_alloc_t<float>(fn->pool, (size_t)n, true);
     k_gather(ge, (const float *)gate->data, bcast_view(gate, go->ndim, go->shape), n);
     k_gather(ue, (const float *)up->data, bcast_view(up, go->ndim, go->shape), n);
-    ew_launch("swiglu_bwd_kernel", n, SwigluB{dge, due, ge, ue, god});
+    ew_launch("swiglu_bwd_kernel", n, SwigluB{dge, due, ge, ue, god, 1, 1});
     tensor tmp = *go;
-    if (ag) { tmp.data = dge; tmp.offset = 0; bcast_reduce_into(gate, ag, &tmp); }
-    if (bg) { tmp.data = due; tmp.offset = 0; bcast_reduce_into(up, bg, &tmp); }
+    if (ag) { tmp.data = dge; tmp.offset = 0; bcast_reduce_into(gate, ag, &tmp, acc_g); }
+    if (bg) { tmp.data = due; tmp.offset = 0; bcast_reduce_into(up, bg, &tmp, acc_u); }
 }
 
 }  // namespace dnnb

@@ -14,7 +14,7 @@ namespace dnnb {
 template <bool BWD>
 __global__ void rope_kernel(float *__restrict__ dst, const float *__restrict__ g,
                             const float *__restrict__ fc, const float *__restrict__ fs,
-                            int64_t total4, int N, int d) {
+                            int64_t total4, int N, int d, int acc) {
     int d4 = d >> 2, dh = d >> 1;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
         int q = (int)(i % d4);
@@ -29,7 +29,7 @@ __global__ void rope_kernel(float *__restrict__ dst, const float *__restrict__ g
             reinterpret_cast<float4 *>(dst)[i] = o;
         } else {
             float4 v = reinterpret_cast<const float4 *>(g)[i];
-            float4 o = reinterpret_cast<float4 *>(dst)[i];
+            float4 o = acc ? reinterpret_cast<float4 *>(dst)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
             o.x += v.x * c.x + v.y * s.x;  o.y += -v.x * s.x + v.y * c.x;
             o.z += v.z * c.y + v.w * s.y;  o.w += -v.z * s.y + v.w * c.y;
             reinterpret_cast<float4 *>(dst)[i] = o;
@@ -39,7 +39,7 @@ __global__ void rope_kernel(float *__restrict__ dst, const float *__restrict__ g
 template <bool BWD>
 __global__ void rope_pair_kernel(float *__restrict__ dst, const float *__restrict__ g,
                                  const float *__restrict__ fc, const float *__restrict__ fs,
-                                 int64_t pairs, int N, int d) {
+                                 int64_t pairs, int N, int d, int acc) {
     int dh = d >> 1;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += (int64_t)gridDim.x * blockDim.x) {
         int k = (int)(i % dh);
@@ -50,22 +50,24 @@ __global__ void rope_pair_kernel(float *__restrict__ dst, const float *__restric
             dst[2 * i] = a * c - b * s; dst[2 * i + 1] = a * s + b * c;
         } else {
             float a = g[2 * i], b = g[2 * i + 1];
-            dst[2 * i] += a * c + b * s; dst[2 * i + 1] += -a * s + b * c;
+            float r0 = a * c + b * s, r1 = -a * s + b * c;
+            if (acc) { r0 += dst[2 * i]; r1 += dst[2 * i + 1]; }
+            dst[2 * i] = r0; dst[2 * i + 1] = r1;
         }
     }
 }
 
-static void rope_run(bool bwd, float *dst, const float *g, const float *fc, const float *fs, int64_t numel, int N, int d) {
+static void rope_run(bool bwd, float *dst, const float *g, const float *fc, const float *fs, int64_t numel, int N, int d, int acc = 1) {
     if (numel <= 0) return;
     bool vec = d % 4 == 0 && aligned16(dst) && (!g || aligned16(g)) && (((uintptr_t)fc | (uintptr_t)fs) & 7) == 0;
     if (vec) {
         int64_t n4 = numel / 4;
-        if (bwd) rope_kernel<true><<<grid_for(n4, 256), 256, 0, stream()>>>(dst, g, fc, fs, n4, N, d);
-        else     rope_kernel<false><<<grid_for(n4, 256), 256, 0, stream()>>>(dst, g, fc, fs, n4, N, d);
+        if (bwd) rope_kernel<true><<<grid_for(n4, 256), 256, 0, stream()>>>(dst, g, fc, fs, n4, N, d, acc);
+        else     rope_kernel<false><<<grid_for(n4, 256), 256, 0, stream()>>>(dst, g, fc, fs, n4, N, d, acc);
     } else {
         int64_t np = numel / 2;
-        if (bwd) rope_pair_kernel<true><<<grid_for(np, 256), 256, 0, stream()>>>(dst, g, fc, fs, np, N, d);
-        else     rope_pair_kernel<false><<<grid_for(np, 256), 256, 0, stream()>>>(dst, g, fc, fs, np, N, d);
+        if (bwd) rope_pair_kernel<true><<<grid_for(np, 256), 256, 0, stream()>>>(dst, g, fc, fs, np, N, d, acc);
+        else     rope_pair_kernel<false><<<grid_for(np, 256), 256, 0, stream()>>>(dst, g, fc, fs, np, N, d, acc);
     }
     LAUNCHED(bwd ? "rope_bwd_kernel" : "rope_fwd_kernel");
 }
@@ -75,9 +77,10 @@ static void rope_backward(grad_fn *fn, tensor *go) {
     tensor *fc = fn->saved_tensors[0], *fs = fn->saved_tensors[1];
     if (!wants_grad(x)) return;
     int d = x->shape[x->ndim - 1], N = x->shape[x->ndim - 2];
-    float *grad = _grad_ensure(x);
+    bool acc = true;
+    float *grad = x->contiguous ? grad_full(x, &acc) : _grad_ensure(x);
     rope_run(true, grad + x->offset, (const float *)go->data + go->offset,
-             (const float *)fc->data + fc->offset, (const float *)fs->data + fs->offset, numel_of(x), N, d);
+             (const float *)fc->data + fc->offset, (const float *)fs->data + fs->offset, numel_of(x), N, d, acc);
 }
 
 // ---- [B,P,Q,dk] <-> strided permutations ---------------------------------------

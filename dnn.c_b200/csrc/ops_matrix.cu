@@ -123,8 +123,12 @@ static void mm_backward(const MM &p, tensor *a, tensor *b, int trans_b, const fl
     int64_t bk = trans_b ? p.b.cs : p.b.rs, bn = trans_b ? p.b.rs : p.b.cs;
     bool need_a = wants_grad(a), need_b = wants_grad(b);
     bool self = (a == b);
-    float *ag = need_a ? _grad_ensure(a) : nullptr;
-    float *bg = need_b ? _grad_ensure(b) : nullptr;
+    // dA and dW each write the whole of their operand's gradient, so a fresh buffer is
+    // stored into rather than added to (grad_full); a broadcast operand is summed over
+    // batches and run_batched turns that into store-then-add on its own.
+    bool acc_a = true, acc_b = true;
+    float *ag = need_a ? grad_full(a, &acc_a) : nullptr;
+    float *bg = (need_b && !self) ? grad_full(b, &acc_b) : nullptr;
 
     if (need_a) {
         // dA[m,k] += sum_n G[m,n] * Bop[k,n]   ->  X = G (M x N), Y = Bop^T (N x K)
@@ -133,26 +137,27 @@ static void mm_backward(const MM &p, tensor *a, tensor *b, int trans_b, const fl
             g.A = gd; g.a_rs = p.N; g.a_cs = 1; g.a_bs = 0;
             g.B = bd + p.b.off[0]; g.b_rs = bn; g.b_cs = bk; g.b_bs = 0;
             g.C = ag + p.a.off[0]; g.c_rs = p.a.rs; g.c_cs = p.a.cs; g.c_bs = 0;
-            g.bias = nullptr; g.M = p.M * p.batch; g.N = p.K; g.K = p.N; g.batch = 1; g.accumulate = true;
+            g.bias = nullptr; g.M = p.M * p.batch; g.N = p.K; g.K = p.N; g.batch = 1; g.accumulate = acc_a;
             gemm(g);
         } else {
             run_batched(Side{gd, &p.c, p.N, 1}, Side{bd, &p.b, bn, bk}, ag, &p.a, p.a.rs, p.a.cs,
-                        p.M, p.K, p.N, p.batch, nullptr, true);
+                        p.M, p.K, p.N, p.batch, nullptr, acc_a);
         }
     }
     if ((need_b && !self) || (self && need_a)) {
         float *dst = self ? ag : bg;
+        bool acc = self ? true : acc_b;
         // dBop[k,n] += sum_m A[m,k] * G[m,n]  ->  X = A^T (K x M), Y = G (M x N); C strides follow B's layout
         if (p.collapse) {
             GemmArgs g;
             g.A = ad + p.a.off[0]; g.a_rs = p.a.cs; g.a_cs = p.a.rs; g.a_bs = 0;
             g.B = gd; g.b_rs = p.N; g.b_cs = 1; g.b_bs = 0;
             g.C = dst + p.b.off[0]; g.c_rs = bk; g.c_cs = bn; g.c_bs = 0;
-            g.bias = nullptr; g.M = p.K; g.N = p.N; g.K = p.M * p.batch; g.batch = 1; g.accumulate = true;
+            g.bias = nullptr; g.M = p.K; g.N = p.N; g.K = p.M * p.batch; g.batch = 1; g.accumulate = acc;
             gemm(g);
         } else {
             run_batched(Side{ad, &p.a, p.a.cs, p.a.rs}, Side{gd, &p.c, p.N, 1}, dst, &p.b, bk, bn,
-                        p.K, p.N, p.M, p.batch, nullptr, true);
+                        p.K, p.N, p.M, p.batch, nullptr, acc);
         }
     }
 }
@@ -169,9 +174,10 @@ static void matmul_add_backward(grad_fn *fn, tensor *go) {
     MM p = plan(a, b, trans_b);
     mm_backward(p, a, b, trans_b, (const float *)go->data);
     if (wants_grad(bias)) {
-        float *bg = _grad_ensure(bias);
+        bool acc = true;
+        float *bg = grad_full(bias, &acc);
         int nbias = bias->shape[0];
-        k_colsum_acc(bg + bias->offset, (const float *)go->data, numel_of(go) / nbias, nbias);
+        k_colsum_acc(bg + bias->offset, (const float *)go->data, numel_of(go) / nbias, nbias, acc);
     }
 }
 

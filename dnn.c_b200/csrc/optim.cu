@@ -119,6 +119,7 @@ static std::vector<TensorRef> grad_table(tensor **params, int n_params) {
     for (int i = 0; i < n_params; i++) {
         float *g = params[i]->grad;
         if (!g) continue;
+        grad_settle(params[i]);
         TensorRef r; r.p = nullptr; r.g = g; r.m = r.v = nullptr; r.n = numel_of(params[i]); r.lr = 0.f; r.first_chunk = 0;
         if (r.n > 0) tab.push_back(r);
     }
@@ -183,26 +184,13 @@ adamw_opt *adamw_create(struct mem_pool *params_pool, tensor **params, int n_par
 }
 void adamw_free(adamw_opt *opt) { (void)opt; }
 
-// Gradient buffers of the parameters are bump-allocated one after another, so
-// adjacent ones are merged into a single memset.
+// The reference memsets every parameter gradient here (src/optim.c:93-100).  The buffers are
+// only marked fresh: the first backward contribution of the step (a dW GEMM that covers the
+// whole tensor) stores instead of adding, and whatever is still fresh when gradients are
+// read (grad norm, clipping, AdamW, all-reduce, download) is zero-filled then.
 void adamw_zero_grad(adamw_opt *opt) {
-    std::vector<std::pair<char *, size_t>> spans;
-    for (int i = 0; i < opt->n_params; i++) {
-        float *g = opt->params[i]->grad;
-        if (g) spans.emplace_back((char *)g, (size_t)numel_of(opt->params[i]) * 4);
-    }
-    std::sort(spans.begin(), spans.end());
-    size_t i = 0;
-    while (i < spans.size()) {
-        char *b = spans[i].first, *e = b + spans[i].second;
-        size_t j = i + 1;
-        // the gap up to the next 256-byte boundary is allocator padding
-        while (j < spans.size() && spans[j].first <= (char *)(((uintptr_t)e + 255) & ~(uintptr_t)255) && spans[j].first >= e) {
-            e = spans[j].first + spans[j].second; j++;
-        }
-        CUDA_OK(cudaMemsetAsync(b, 0, (size_t)(e - b), stream()));
-        i = j;
-    }
+    for (int i = 0; i < opt->n_params; i++)
+        if (opt->params[i]->grad) opt->params[i]->grad_fresh = 1;
 }
 
 float grad_norm(tensor **params, int n_params) {
@@ -237,6 +225,7 @@ void adamw_step_with_lr_multipliers(adamw_opt *opt, const float *lr_mults) {
     for (int i = 0; i < opt->n_params; i++) {
         tensor *p = opt->params[i];
         if (!p->grad) continue;                    // not in the backward graph (src/optim.c:287)
+        grad_settle(p);
         TensorRef r;
         r.p = tensor_data_ptr(p); r.g = p->grad; r.m = tensor_data_ptr(opt->m[i]); r.v = tensor_data_ptr(opt->v[i]);
         r.n = numel_of(p); r.lr = opt->lr * (lr_mults ? lr_mults[i] : 1.0f); r.first_chunk = 0;

@@ -303,6 +303,7 @@ int dnn_cuda_download(const tensor *t, void *host_dst, size_t bytes) {
 
 int dnn_cuda_download_grad(const tensor *t, void *host_dst, size_t bytes) {
     if (!t || !t->grad) { set_error("download_grad: tensor has no grad"); return -2; }
+    grad_settle((tensor *)t);
     if (bytes > (size_t)numel_of(t) * 4) { set_error("download_grad: more bytes than the tensor holds"); return -3; }
     return xfer(host_dst, t->grad, bytes, cudaMemcpyDeviceToHost, true);
 }

@@ -256,7 +256,7 @@ int tensor_is_leaf(const tensor *t) { return t->requires_grad && t->grad_fn == n
 int tensor_is_contiguous(const tensor *t) { return t->contiguous; }
 int tensor_requires_grad(const tensor *t) { return t->requires_grad; }
 void tensor_set_requires_grad(tensor *t, int req) { t->requires_grad = req ? 1 : 0; }
-float *tensor_grad(const tensor *t) { return t->grad; }
+float *tensor_grad(const tensor *t) { grad_settle((tensor *)t); return t->grad; }
 tensor *tensor_root(tensor *t) { while (t->parent) t = t->parent; return t; }
 
 void tensor_retain_grad(tensor *t) {
@@ -265,7 +265,7 @@ void tensor_retain_grad(tensor *t) {
     t->grad = (float *)dev_alloc(base->pool, (size_t)numel_of(t) * 4, true);
 }
 void tensor_zero_grad(tensor *t) {
-    if (t->grad) k_fill(t->grad, numel_of(t), 0.0f);
+    if (t->grad) { k_fill(t->grad, numel_of(t), 0.0f); t->grad_fresh = 0; }
 }
 
 void tensor_print(const tensor *t) {

@@ -76,6 +76,8 @@ typedef struct tensor {
     int      ndim;
     unsigned int requires_grad : 1;
     unsigned int contiguous    : 1;
+    unsigned int grad_fresh    : 1;     /* library-internal, in the same 32-bit unit as the two flags
+                                           above: grad is allocated but not yet written (see _grad_ensure) */
     int      offset;                    /* in elements, from data */
     struct tensor *parent;              /* non-NULL for views */
     grad_fn *grad_fn;

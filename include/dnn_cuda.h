@@ -106,6 +106,10 @@ int  dnn_cuda_dp_unique_id(void *out_128_bytes);
 int  dnn_cuda_dp_init(int rank, int world_size, const void *id_128_bytes);
 int  dnn_cuda_dp_allreduce_grads(tensor **params, int n_params);
 int  dnn_cuda_dp_world_size(void);
+/* Host-only: how dnn_cuda_dp_allreduce_grads would cut n gradient buffers (address, bytes)
+ * into all-reduce buckets; returns the bucket count and fills up to `cap` of them. */
+int  dnn_cuda_dp_plan_buckets(const size_t *addrs, const size_t *bytes, int n, size_t bucket_bytes,
+                              size_t *out_addrs, size_t *out_bytes, int cap);
 int  dnn_cuda_dp_finalize(void);
 /* decoder_lm_train_step with the all-reduce between backward and clipping. */
 tensor *dnn_cuda_dp_decoder_lm_train_step(struct mem_pool *scratch_pool, decoder_lm *lm,

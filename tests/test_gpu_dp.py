@@ -1,0 +1,90 @@
+"""GPU (needs 2 devices, otherwise skipped): two data-parallel ranks, each on its own
+GPU with half of the batch, against one rank with the whole batch.  After
+dnn_cuda_dp_decoder_lm_train_step the averaged gradients, the gradient norm and the
+updated parameters must agree with the single-process step, and both ranks must hold
+bit-identical parameters (no parameter broadcast is ever needed)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r"""
+import ctypes as C, os, sys, time
+import numpy as np
+sys.path.insert(0, {root!r}); sys.path.insert(0, os.path.join({root!r}, "tests"))
+from conftest import load_binding
+import models
+from oracle import dnn_oracle as O
+B = load_binding()
+rank, world, out = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+d = B.Dnn(B.B200_LIB, params_mb=256, scratch_mb=1024, data_mb=16, device=rank if world > 1 else 0)
+lib = d.lib
+lib.dnn_cuda_set_gemm_mode(B.GEMM_FP32)
+if world > 1:
+    idfile = os.path.join(out, "nccl_id.bin")
+    buf = (C.c_ubyte * 128)()
+    if rank == 0:
+        assert lib.dnn_cuda_dp_unique_id(buf) == 0
+        open(idfile + ".tmp", "wb").write(bytes(buf)); os.rename(idfile + ".tmp", idfile)
+    else:
+        for _ in range(600):
+            if os.path.exists(idfile): break
+            time.sleep(0.1)
+        buf = (C.c_ubyte * 128)(*open(idfile, "rb").read())
+    assert lib.dnn_cuda_dp_init(rank, world, buf) == 0
+cfg = dict(models.lm_config("tiny"), B=4)
+ids_all, _ = models.lm_inputs(cfg)
+per = cfg["B"] // world
+ids_np = ids_all[rank * per:(rank + 1) * per]
+lm = lib.decoder_lm_create(d.params, cfg["V"], cfg["D"], cfg["L"], cfg["H"], cfg["D"] // cfg["H"], cfg["F"])
+lib.decoder_lm_enable_rope(d.params, lm, cfg["N"], 10000.0)
+names = O.lm_param_names(cfg["L"])
+params, _ = models.seeded_weights(d, lm, names, 123)
+arr = (B.TensorP * len(params))(*params)
+opt = lib.adamw_create(d.params, arr, len(params), cfg["lr"], cfg["b1"], cfg["b2"], cfg["eps"], cfg["wd"])
+res = dict()
+for step in range(2):
+    ids = d.tensor(ids_np, d.data)
+    tgt = lib.decoder_lm_shift_targets(d.data, ids)
+    gn = C.c_float(0)
+    loss = lib.dnn_cuda_dp_decoder_lm_train_step(d.scratch, lm, ids, tgt, opt, cfg["clip"], C.byref(gn))
+    res["loss%d" % step] = np.float32(d.scalar(loss)); res["gn%d" % step] = np.float32(gn.value)
+    if step == 0:
+        for n, t in zip(names, params): res["g/" + n] = d.download_grad(t)
+    d.reset_step()
+for n, t in zip(names, params): res["p/" + n] = d.download(t)
+np.savez(os.path.join(out, "rank%d_of%d.npz" % (rank, world)), **res)
+if world > 1: lib.dnn_cuda_dp_finalize()
+d.close()
+"""
+
+
+def test_two_ranks_match_one_rank_with_the_whole_batch(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "dp_worker.py"
+    script.write_text(WORKER.format(root=ROOT))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    single = subprocess.run([sys.executable, str(script), "0", "1", str(tmp_path)], env=env, capture_output=True, text=True, timeout=600)
+    assert single.returncode == 0, single.stdout + single.stderr
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", str(tmp_path)], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    one = np.load(tmp_path / "rank0_of1.npz")
+    r0, r1 = np.load(tmp_path / "rank0_of2.npz"), np.load(tmp_path / "rank1_of2.npz")
+    # mean of the per-rank mean losses is the full-batch loss
+    assert abs(0.5 * (r0["loss0"] + r1["loss0"]) - one["loss0"]) <= 1e-6 * abs(one["loss0"])
+    assert abs(r0["gn0"] - one["gn0"]) <= 1e-5 * one["gn0"] and r0["gn0"] == r1["gn0"]
+    for k in one.files:
+        if k.startswith(("g/", "p/")):
+            a, b = r0[k].astype(np.float64), one[k].astype(np.float64)
+            assert np.linalg.norm(a - b) <= 2e-5 * np.linalg.norm(b) + 1e-9, k
+            assert np.array_equal(r0[k], r1[k]), "ranks diverged on " + k

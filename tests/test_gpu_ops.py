@@ -56,3 +56,55 @@ def test_same_seed_twice_is_bit_identical(gpu, binding):
         b = case.run(gpu, inp); gpu.reset_step()
         for k in a:
             assert np.array_equal(a[k], b[k]), (case.name, k)
+
+
+class _TwiceBackward:
+    """Proxy of the binding whose backward_from() runs the tape node twice, so the second
+    run finds gradient buffers that already hold a value and must add to them."""
+
+    def __init__(self, dnn, binding):
+        self._dnn, self._binding = dnn, binding
+
+    class _Lib:
+        def __init__(self, lib):
+            self._lib = lib
+
+        def __getattr__(self, name):
+            return getattr(self._lib, name)
+
+        def dnn_backward(self, scratch, loss):
+            self._lib.dnn_backward(scratch, loss)
+            self._lib.dnn_backward(scratch, loss)
+
+    @property
+    def lib(self):
+        return self._Lib(self._dnn.lib)
+
+    def __getattr__(self, name):
+        return getattr(self._dnn, name)
+
+    def backward_from(self, out, gout):
+        import ctypes as C
+        fn = C.cast(out.contents.grad_fn, C.POINTER(self._binding.GradFn))
+        g = self._dnn.tensor(np.asarray(gout, dtype=np.float32).reshape(self._dnn.shape_of(out)), pool=self._dnn.scratch)
+        fn.contents.backward(fn, g)
+        fn.contents.backward(fn, g)
+        self._dnn.sync()
+
+
+OVERWRITING = ("merge_heads", "split_heads")     # their backward stores (src/multihead.c:92,177)
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if not c.name.startswith(("rope_freqs_init", "transpose+"))],
+                         ids=lambda c: c.name)
+def test_second_backward_accumulates(gpu, binding, case):
+    """The first gradient written to a buffer may be a plain store; every later one must add.
+    Running each tape node twice has to give exactly twice the oracle's gradients."""
+    gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
+    inp = case.make(np.random.default_rng(4321))
+    got = case.run(_TwiceBackward(gpu, binding), inp)
+    gpu.reset_step()
+    want = case.oracle(inp)
+    factor = 1.0 if case.name.startswith(OVERWRITING) else 2.0
+    want = {k: (v * factor if k.startswith("d") else v) for k, v in want.items()}
+    compare(case, got, want)
