@@ -7,8 +7,10 @@
 //               CTA's own tiles, no multicast) into a ring of shared-memory stages;
 //   warp 1      one elected lane issues tcgen05.mma (128 x BN x 8 per instruction)
 //               and commits stage / accumulator completions to mbarriers;
-//   warps 2..5  epilogue: tcgen05.ld the 128 x BN accumulator from TMEM, add bias
-//               or the previous C, store.  TMEM holds two accumulators, so the
+//   warps 2..5  epilogue: tcgen05.ld the 128 x BN accumulator from TMEM, add the bias,
+//               write 32 x 32 pieces into swizzled staging tiles and hand them to the
+//               copy engine (tile store, or tile add for C +=), so every global write
+//               is a full 128-byte row segment.  TMEM holds two accumulators, so the
 //               epilogue of one tile overlaps the main loop of the next.
 // Operands may be K-major (K contiguous in memory) or MN-major (M resp. N
 // contiguous); both are expressed through the shared-memory matrix descriptor
@@ -45,18 +47,21 @@ template <int BN> struct TcCfg {
     static constexpr int kStageA = BM * BK * 4;                   // 16 KiB
     static constexpr int kStageB = BN * BK * 4;
     static constexpr int kStages = BN == 256 ? 4 : 6;
-    static constexpr int kSmem = kStages * (kStageA + kStageB) + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int kStore = 4 * 2 * 4096;                   // per epilogue warp: two 32x32 fp32 staging tiles
+    static constexpr int kSmem = kStages * (kStageA + kStageB) + kStore + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int kTmemCols = 2 * BN;
 };
 
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcArgs g) {
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, TcArgs g) {
     using Cfg = TcCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem, *sB = smem + Cfg::kStages * Cfg::kStageA;
-    uint64_t *bars = (uint64_t *)(smem + Cfg::kStages * (Cfg::kStageA + Cfg::kStageB));
+    uint8_t *sC = smem + Cfg::kStages * (Cfg::kStageA + Cfg::kStageB);
+    uint64_t *bars = (uint64_t *)(sC + Cfg::kStore);
     uint64_t *full = bars, *empty = bars + Cfg::kStages, *acc_full = bars + 2 * Cfg::kStages, *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = (uint32_t *)(acc_empty + 2);
 
@@ -140,6 +145,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // epilogue warps 2..5: TMEM lanes 32*(warp%4) .. +31  <->  tile rows
         const int q = warp & 3;
         int acc = 0; uint32_t acc_phase = 0;
+        uint32_t chunk = 0;
         for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
             int tile = u / g.splits, split = u - tile * g.splits;
             int m0 = (tile % g.tiles_m) * BM, n0 = (tile / g.tiles_m) * BN;
@@ -147,40 +153,49 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool has_k = kb0 < num_kb_total;
             if (!mbar_wait(&acc_full[acc], acc_phase)) { if (lane == 0) atomicCAS(&g_gemm_error, 0, 0x400 | acc); break; }
             tc_fence_after();
-            int row = m0 + q * 32 + lane;
-            float *crow = g.C + (int64_t)split * g.M * g.ldc + (int64_t)row * g.ldc;
-            bool use_bias = g.bias != nullptr && split == 0;
+            const int row0 = m0 + q * 32;
+            const bool use_bias = g.bias != nullptr && split == 0;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                if (row < g.M) {
+                const int col0 = n0 + c0;
+                float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        int col = n0 + c0 + j;
-                        if (col >= g.N) break;
-                        float v[4];
+                for (int j = 0; j < 32; j++) v[j] = has_k ? __uint_as_float(r[j]) : 0.f;
+                if (use_bias) {
+                    if (col0 + 32 <= g.N) {
 #pragma unroll
-                        for (int e = 0; e < 4; e++) v[e] = has_k ? __uint_as_float(r[j + e]) : 0.f;
-                        if (col + 3 < g.N) {
-                            if (use_bias) { float4 bb = *reinterpret_cast<const float4 *>(g.bias + col); v[0] += bb.x; v[1] += bb.y; v[2] += bb.z; v[3] += bb.w; }
-                            float4 *dst = reinterpret_cast<float4 *>(crow + col);
-                            if (g.accumulate) { float4 o = *dst; v[0] += o.x; v[1] += o.y; v[2] += o.z; v[3] += o.w; }
-                            *dst = make_float4(v[0], v[1], v[2], v[3]);
-                        } else {
-                            for (int e = 0; e < 4 && col + e < g.N; e++) {
-                                float x = v[e] + (use_bias ? g.bias[col + e] : 0.f);
-                                crow[col + e] = g.accumulate ? crow[col + e] + x : x;
-                            }
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 bb = __ldg(reinterpret_cast<const float4 *>(g.bias + col0 + j));
+                            v[j] += bb.x; v[j + 1] += bb.y; v[j + 2] += bb.z; v[j + 3] += bb.w;
                         }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (col0 + j < g.N) v[j] += g.bias[col0 + j];
                     }
                 }
+                // the staging tile about to be written was handed to the copy engine two chunks ago
+                if (lane == 0) bulk_wait_read<1>();
+                __syncwarp();
+                uint8_t *buf = sC + (q * 2 + (chunk & 1)) * 4096;
+#pragma unroll
+                for (int j = 0; j < 8; j++)       // 128-byte swizzle: 16-byte piece j of row `lane` lands at piece j ^ (lane & 7)
+                    *reinterpret_cast<float4 *>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (col0 < g.N && row0 < g.M) tma_store_3d(&tmC, buf, col0, row0, split, g.accumulate != 0);
+                    bulk_commit();
+                }
+                chunk++;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        if (lane == 0) bulk_wait<0>();      // the staging tiles must outlive the copies that read them
     }
     // teardown: everyone meets here, also after a wait that gave up
     tc_fence_before();
@@ -248,6 +263,20 @@ static CUtensorMap make_map(const float *base, int64_t inner, int64_t outer, int
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r); abort(); }
+    return m;
+}
+
+// 3-D map {N, M, splits} over the output (or over the split-K partials); box = one 32 x 32 staging tile.
+static CUtensorMap make_out_map(float *base, int64_t N, int64_t M, int64_t ldc, int splits) {
+    CUtensorMap m;
+    cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)splits};
+    cuuint64_t strides[2] = {(cuuint64_t)ldc * 4, (cuuint64_t)M * (cuuint64_t)ldc * 4};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled (output) failed (%d)\n", (int)r); abort(); }
     return m;
 }
 
@@ -329,8 +358,9 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     else { t.C = scratch((size_t)splits * g.M * g.N * 4); t.ldc = g.N; t.bias = nullptr; t.accumulate = 0; }
     int units = tiles * splits;
     int grid = units < kNumSMs ? units : kNumSMs;
+    CUtensorMap tmC = make_out_map(t.C, g.N, g.M, t.ldc, splits);
     prof_begin(0);
-    gemm_tf32_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream()>>>(tmA, tmB, t);
+    gemm_tf32_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream()>>>(tmA, tmB, tmC, t);
     LAUNCHED("gemm_tf32_kernel");
     prof_end(0, 2.0 * g.M * g.N * g.K);
     if (splits > 1) {

@@ -155,6 +155,13 @@ def main():
         b.run("matmul_add", lambda: dict(a=b.dev(randn(M, K), True), w=b.dev(randn(K, N, scale=0.02), True),
                                          bias=b.dev(np.zeros(N, np.float32), True)),
               lambda i: lib.tensor_matmul_add(d.scratch, i["a"], i["w"], 0, i["bias"]), (M, N), 2.0 * M * N * K, 4.0 * M * N * K, "tensor")
+    if "matmul_shapes" in ops:
+        # the linear layers of the 124M training step (BASELINE config 5): 16384 tokens
+        M = 2048 if args.small else 16384
+        for K, N in ((768, 2304), (768, 768), (768, 2048), (2048, 768), (768, 32000)):
+            b.run("matmul_add[%dx%dx%d]" % (M, K, N),
+                  lambda: dict(a=b.dev(randn(M, K), True), w=b.dev(randn(K, N, scale=0.02), True), bias=b.dev(np.zeros(N, np.float32), True)),
+                  lambda i: lib.tensor_matmul_add(d.scratch, i["a"], i["w"], 0, i["bias"]), (M, N), 2.0 * M * N * K, 4.0 * M * N * K, "tensor")
     for name, mode, prefix in (("attention_causal", 0, 0), ("attention_prefix_lm", 1, 196)):
         if not want(name) and not want("attention"):
             continue
