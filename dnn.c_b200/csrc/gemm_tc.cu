@@ -43,20 +43,28 @@ struct TcArgs {
     int tiles_m, tiles_n;
 };
 
-template <int BN> struct TcCfg {
+template <int BN, bool PAIR> struct TcCfg {
+    static constexpr int kRowsB = PAIR ? BN / 2 : BN;             // B rows (n) this CTA loads per stage
     static constexpr int kStageA = BM * BK * 4;                   // 16 KiB
-    static constexpr int kStageB = BN * BK * 4;
-    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kStageB = kRowsB * BK * 4;
+    static constexpr int kStages = (kStageA + kStageB) == 49152 ? 4 : 6;
     static constexpr int kStore = 4 * 2 * 4096;                   // per epilogue warp: two 32x32 fp32 staging tiles
     static constexpr int kSmem = kStages * (kStageA + kStageB) + kStore + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int kTmemCols = 2 * BN;
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, TcArgs g) {
-    using Cfg = TcCfg<BN>;
+    using Cfg = TcCfg<BN, PAIR>;
+    static_assert(!PAIR || BN == 256, "a CTA pair computes 256 x 256 tiles");
+    // PAIR: the grid is made of clusters of two CTAs; a pair walks the work units together,
+    // rank 0 (the leader) issues the MMAs for both.
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;
+    const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    constexpr int kTileM = PAIR ? 2 * BM : BM;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem, *sB = smem + Cfg::kStages * Cfg::kStageA;
@@ -68,15 +76,21 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 8 : 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {     // one warp of each CTA of the pair, collectively: the same columns in both CTAs
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anything is sent to them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -88,35 +102,42 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+            for (int u = walker; u < num_units && ok; u += walkers) {
                 int tile = u / g.splits, split = u - tile * g.splits;
-                int m0 = (tile % g.tiles_m) * BM, n0 = (tile / g.tiles_m) * BN;
+                int m0 = (tile % g.tiles_m) * kTileM + (int)rank * BM;
+                int n0 = (tile / g.tiles_m) * BN + (int)rank * Cfg::kRowsB;      // a pair splits B's columns between its CTAs
                 int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&empty[stage], phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 0x100 | stage); ok = false; break; }
-                    mbar_expect_tx(&full[stage], Cfg::kStageA + Cfg::kStageB);
+                    // both CTAs' bytes are counted on the leader's barrier, which alone is armed
+                    if (rank == 0) mbar_expect_tx(&full[stage], (PAIR ? 2 : 1) * (Cfg::kStageA + Cfg::kStageB));
+                    const uint32_t bar = PAIR ? map_to_rank(smem_u32(&full[stage]), 0) : smem_u32(&full[stage]);
+                    auto load = [&](void *dst, const CUtensorMap *map, int x, int y) {
+                        if (PAIR) tma_load_2d_pair(dst, map, x, y, bar);
+                        else tma_load_2d(dst, map, x, y, &full[stage]);
+                    };
                     uint8_t *a = sA + stage * Cfg::kStageA, *b = sB + stage * Cfg::kStageB;
                     int k = kb * BK;
-                    if (g.a_kmajor) tma_load_2d(a, &tmA, k, m0, &full[stage]);                    // box {32 k, 128 rows}
-                    else for (int c = 0; c < BM / 32; c++) tma_load_2d(a + c * 4096, &tmA, m0 + c * 32, k, &full[stage]);   // box {32 m, 32 k}
-                    if (g.b_kmajor) tma_load_2d(b, &tmB, k, n0, &full[stage]);
-                    else for (int c = 0; c < BN / 32; c++) tma_load_2d(b + c * 4096, &tmB, n0 + c * 32, k, &full[stage]);
+                    if (g.a_kmajor) load(a, &tmA, k, m0);                                          // box {32 k, 128 rows}
+                    else for (int c = 0; c < BM / 32; c++) load(a + c * 4096, &tmA, m0 + c * 32, k);   // box {32 m, 32 k}
+                    if (g.b_kmajor) load(b, &tmB, k, n0);
+                    else for (int c = 0; c < Cfg::kRowsB / 32; c++) load(b + c * 4096, &tmB, n0 + c * 32, k);
                     if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // instruction descriptor: D=f32, A=B=tf32, major bits, N>>3, M>>4
+        if (lane == 0 && rank == 0) {
+            // instruction descriptor: D=f32, A=B=tf32, major bits, N>>3, M>>4 (M = 256 across a pair)
             uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((g.a_kmajor ? 0u : 1u) << 15) | ((g.b_kmajor ? 0u : 1u) << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             const uint32_t a_lbo = g.a_kmajor ? 16 : 4096, b_lbo = g.b_kmajor ? 16 : 4096;
             const uint32_t a_adv = g.a_kmajor ? UMMA_K * 4 : 1024, b_adv = g.b_kmajor ? UMMA_K * 4 : 1024;   // bytes per K=8 step
             const uint32_t a_sbo = g.a_kmajor ? 1024 : 512, b_sbo = g.b_kmajor ? 1024 : 512;
             const uint32_t a_lt = g.a_kmajor ? 2 : 1, b_lt = g.b_kmajor ? 2 : 1;
             int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+            for (int u = walker; u < num_units && ok; u += walkers) {
                 int tile = u / g.splits, split = u - tile * g.splits;
                 (void)tile;
                 int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
@@ -131,13 +152,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     for (int k = 0; k < BK / UMMA_K; k++) {
                         uint64_t ad = make_smem_desc(a_addr + k * a_adv, a_lbo, a_sbo, a_lt);
                         uint64_t bd = make_smem_desc(b_addr + k * b_adv, b_lbo, b_sbo, b_lt);
-                        tc_mma_tf32(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if (PAIR) tc_mma_tf32_pair(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        else tc_mma_tf32(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
-                    tc_commit(&empty[stage]);           // frees the stage when these MMAs have read it
+                    // frees the stage (in both CTAs of a pair) when these MMAs have read it
+                    if (PAIR) tc_commit_pair(&empty[stage], 3); else tc_commit(&empty[stage]);
                     if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                tc_commit(&acc_full[acc]);              // accumulator complete
+                if (PAIR) tc_commit_pair(&acc_full[acc], 3); else tc_commit(&acc_full[acc]);      // accumulator complete
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
@@ -146,9 +169,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int q = warp & 3;
         int acc = 0; uint32_t acc_phase = 0;
         uint32_t chunk = 0;
-        for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+        for (int u = walker; u < num_units; u += walkers) {
             int tile = u / g.splits, split = u - tile * g.splits;
-            int m0 = (tile % g.tiles_m) * BM, n0 = (tile / g.tiles_m) * BN;
+            int m0 = (tile % g.tiles_m) * kTileM + (int)rank * BM, n0 = (tile / g.tiles_m) * BN;
             int kb0 = split * g.kb_per_split;
             bool has_k = kb0 < num_kb_total;
             if (!mbar_wait(&acc_full[acc], acc_phase)) { if (lane == 0) atomicCAS(&g_gemm_error, 0, 0x400 | acc); break; }
@@ -192,7 +215,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            if (lane == 0) {       // the leader's MMA warp waits for the epilogue warps of both CTAs
+                if (PAIR) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[acc]), 0));
+                else mbar_arrive(&acc_empty[acc]);
+            }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
         if (lane == 0) bulk_wait<0>();      // the staging tiles must outlive the copies that read them
@@ -200,9 +226,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // teardown: everyone meets here, also after a wait that gave up
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();      // neither CTA leaves while the other may still touch its shared memory or TMEM
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
     }
 }
 
@@ -326,41 +354,66 @@ static float *scratch(size_t bytes) {
     return g_scratch;
 }
 
-template <int BN>
+// Split-K factor.  Cost model in units of one k-block of one tile: every wave of work units
+// pays its k-blocks plus a fixed fill-and-drain share, and every split pays for writing and
+// re-reading one partial copy of the output.
+static int choose_splits(int tiles, int slots, int num_kb, int64_t M, int64_t N) {
+    if (tiles >= slots || num_kb < 32) return 1;
+    const double drain = 8.0;
+    const double partial = (double)M * N * 8.0 / 6.0e12 / 0.5e-6;      // ~0.5 us per k-block, ~6 TB/s
+    int best = 1; double best_cost = 1e30;
+    int max_splits = num_kb / 8 < 32 ? num_kb / 8 : 32;
+    for (int s = 1; s <= max_splits; s++) {
+        int kbs = (num_kb + s - 1) / s;
+        int eff = (num_kb + kbs - 1) / kbs;                            // splits that really get work
+        if (eff != s) continue;
+        int waves = (tiles * s + slots - 1) / slots;
+        double cost = waves * (kbs + drain) + (s > 1 ? partial * s : 0.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+template <int BN, bool PAIR>
 static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
-    using Cfg = TcCfg<BN>;
+    using Cfg = TcCfg<BN, PAIR>;
+    constexpr int kTileM = PAIR ? 2 * BM : BM;
     static bool once = false;
     if (!once) {
-        CUDA_OK(cudaFuncSetAttribute(gemm_tf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        CUDA_OK(cudaFuncSetAttribute(gemm_tf32_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
         once = true;
     }
     // A(m,k): K-major -> matrix [M rows][K contiguous]; MN-major -> [K rows][M contiguous]
     CUtensorMap tmA = a_kmajor ? make_map(g.A, g.K, g.M, g.a_rs, BM, false) : make_map(g.A, g.M, g.K, g.a_cs, 32, true);
-    CUtensorMap tmB = b_kmajor ? make_map(g.B, g.K, g.N, g.b_cs, BN, false) : make_map(g.B, g.N, g.K, g.b_rs, 32, true);
+    CUtensorMap tmB = b_kmajor ? make_map(g.B, g.K, g.N, g.b_cs, Cfg::kRowsB, false) : make_map(g.B, g.N, g.K, g.b_rs, 32, true);
     TcArgs t;
     t.M = g.M; t.N = g.N; t.K = g.K; t.a_kmajor = a_kmajor; t.b_kmajor = b_kmajor;
-    t.tiles_m = (g.M + BM - 1) / BM; t.tiles_n = (g.N + BN - 1) / BN;
+    t.tiles_m = (g.M + kTileM - 1) / kTileM; t.tiles_n = (g.N + BN - 1) / BN;
     int tiles = t.tiles_m * t.tiles_n;
     int num_kb = (g.K + BK - 1) / BK;
+    const int slots = PAIR ? kNumSMs / 2 : kNumSMs;      // work units in flight: one per CTA, or per CTA pair
     // split-K when the output has too few tiles to fill the SMs and K is long
-    int splits = 1;
-    if (tiles * 2 <= kNumSMs && num_kb >= 32) {
-        splits = kNumSMs / tiles;
-        int max_splits = num_kb / 8;
-        if (splits > max_splits) splits = max_splits;
-        if (splits > 32) splits = 32;
-        if (splits < 1) splits = 1;
-    }
+    int splits = choose_splits(tiles, slots, num_kb, g.M, g.N);
     t.kb_per_split = (num_kb + splits - 1) / splits;
     splits = (num_kb + t.kb_per_split - 1) / t.kb_per_split;
     t.splits = splits;
     if (splits == 1) { t.C = g.C; t.ldc = g.c_rs; t.bias = g.bias; t.accumulate = g.accumulate ? 1 : 0; }
     else { t.C = scratch((size_t)splits * g.M * g.N * 4); t.ldc = g.N; t.bias = nullptr; t.accumulate = 0; }
     int units = tiles * splits;
-    int grid = units < kNumSMs ? units : kNumSMs;
+    int walkers = units < slots ? units : slots;
     CUtensorMap tmC = make_out_map(t.C, g.N, g.M, t.ldc, splits);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(PAIR ? 2 * walkers : walkers);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = PAIR ? 2 : 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
     prof_begin(0);
-    gemm_tf32_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, stream()>>>(tmA, tmB, tmC, t);
+    CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<BN, PAIR>, tmA, tmB, tmC, t));
     LAUNCHED("gemm_tf32_kernel");
     prof_end(0, 2.0 * g.M * g.N * g.K);
     if (splits > 1) {
@@ -373,8 +426,11 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
 static void run_tc(const GemmArgs &g) {
     bool a_k = g.a_cs == 1, b_k = g.b_rs == 1;
     // a [M,1]-shaped or [1,K]-shaped operand satisfies both; prefer K-major
-    if (g.N > 128) launch_tc<256>(g, a_k, b_k);
-    else launch_tc<128>(g, a_k, b_k);
+    static int pair_ok = -1;
+    if (pair_ok < 0) { const char *e = getenv("DNN_CUDA_GEMM_PAIR"); pair_ok = (e && e[0] == '0') ? 0 : 1; }
+    if (g.N > 128 && g.M > 128 && pair_ok) launch_tc<256, true>(g, a_k, b_k);
+    else if (g.N > 128) launch_tc<256, false>(g, a_k, b_k);
+    else launch_tc<128, false>(g, a_k, b_k);
 }
 
 // Packed copies big/small of an operand, laid out row-major over its contiguous dimension.
