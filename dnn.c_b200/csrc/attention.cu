@@ -363,16 +363,18 @@ static void attn_bwd_launch(const AttnParams &p) {
 }
 
 // tensor-core kernels (attention_tc.cu)
-bool attn_tc_supported(int d, const void *q, const void *k, const void *v);
-void attn_forward_tc(const float *q, const float *k, const float *v, float *o, float *lse, const int *seq_lens,
+bool attn_tc_supported(int d, const HeadView &q, const HeadView &k, const HeadView &v);
+void attn_forward_tc(const HeadView &q, const HeadView &k, const HeadView &v, const HeadView &o, float *lse, const int *seq_lens,
                      int B, int H, int N, int d, int prefix, float scale);
-void attn_backward_tc(const float *q, const float *k, const float *v, const float *lse, const float *dout, const float *dvec,
-                      float *dq, float *dk, float *dv, const int *seq_lens, int B, int H, int N, int d, int prefix, float scale, int store);
+void attn_backward_tc(const HeadView &q, const HeadView &k, const HeadView &v, const float *lse, const HeadView &dout, const float *dvec,
+                      const HeadView &dq, const HeadView &dk, const HeadView &dv, const int *seq_lens,
+                      int B, int H, int N, int d, int prefix, float scale, int store);
 
 // TF32 mode runs on the tensor core (head dims 32 and 64); the FP32 and 3xTF32 modes, and
 // other head dims, run the exact kernels of this file.
 static bool use_tc(const AttnParams &p) {
-    return gemm_mode() == DNN_CUDA_GEMM_TF32 && attn_tc_supported(p.d, p.q, p.k, p.v);
+    return gemm_mode() == DNN_CUDA_GEMM_TF32 &&
+           attn_tc_supported(p.d, packed_heads(p.q, p.H, p.N, p.d), packed_heads(p.k, p.H, p.N, p.d), packed_heads(p.v, p.H, p.N, p.d));
 }
 
 void attn_forward_fp32(const AttnParams &p) {
@@ -412,8 +414,152 @@ static void attention_backward(grad_fn *fn, tensor *go) {
     attn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(p.dout, p.o, dvec, rows, p.d);
     LAUNCHED("attn_bwd_prep_kernel");
     p.dvec = dvec;
-    if (use_tc(p)) attn_backward_tc(p.q, p.k, p.v, p.lse, p.dout, p.dvec, p.dq, p.dk, p.dv, p.seq_lens, p.B, p.H, p.N, p.d, p.prefix, p.scale, p.store);
+    auto pk = [&](const float *x) { return packed_heads(x, p.H, p.N, p.d); };
+    if (use_tc(p)) attn_backward_tc(pk(p.q), pk(p.k), pk(p.v), p.lse, pk(p.dout), p.dvec, pk(p.dq), pk(p.dk), pk(p.dv), p.seq_lens,
+                                    p.B, p.H, p.N, p.d, p.prefix, p.scale, p.store);
     else attn_backward_fp32(p);
+}
+
+
+// ---- attention straight from a fused QKV projection ---------------------------------------
+// qkv is the [B,N,3*H*d] output of the QKV linear layer, i.e. [B,N,3,H,d].  The tensor-core
+// kernels read Q, K and V through strided tensor maps and write the output token-major
+// [B,N,H*d], so split_qkv_heads, merge_heads and their backward copies disappear; RoPE is
+// applied to the Q and K slices of qkv in place (nothing else reads qkv: the backward of the
+// projection needs its inputs, not its output).  Backward writes dQ, dK, dV straight into the
+// gradient of qkv and undoes the rotation there.  Same arithmetic as the unfused op sequence
+// (src/transformer.c:143-170), element for element.
+
+// rows = B*N tokens; each token row holds 3*H*d floats; pairs of the first 2*H*d are rotated.
+template <bool BWD>
+__global__ void rope_qkv_kernel(float *__restrict__ qkv, const float *__restrict__ fc, const float *__restrict__ fs,
+                                int64_t total2, int N, int H, int d) {
+    // one thread per float4 = two adjacent pairs of q or k
+    const int d4 = d >> 2, dh = d >> 1, per_tok = 2 * H * d4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total2; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t tok = i / per_tok;
+        int rem = (int)(i - tok * per_tok);         // (which, h, quad)
+        int quad = rem % d4;
+        int n = (int)(tok % N);
+        float4 *ptr = reinterpret_cast<float4 *>(qkv + tok * (int64_t)(3 * H * d)) + rem;
+        float2 c = *reinterpret_cast<const float2 *>(fc + (int64_t)n * dh + 2 * quad);
+        float2 sn = *reinterpret_cast<const float2 *>(fs + (int64_t)n * dh + 2 * quad);
+        float4 v = *ptr, o;
+        if (!BWD) {
+            o.x = v.x * c.x - v.y * sn.x; o.y = v.x * sn.x + v.y * c.x;
+            o.z = v.z * c.y - v.w * sn.y; o.w = v.z * sn.y + v.w * c.y;
+        } else {
+            o.x = v.x * c.x + v.y * sn.x;  o.y = -v.x * sn.x + v.y * c.x;
+            o.z = v.z * c.y + v.w * sn.y;  o.w = -v.z * sn.y + v.w * c.y;
+        }
+        *ptr = o;
+    }
+}
+
+// D_i for token-major dO and O: row (b,n,h) of [B,N,H,d] -> dvec[(b*H + h)*N + n]
+__global__ void attn_bwd_prep_tokmajor_kernel(const float *__restrict__ dout, const float *__restrict__ o,
+                                              float *__restrict__ dvec, int B, int N, int H, int d) {
+    int lane = threadIdx.x & 31;
+    int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // (b, n, h)
+    if (r >= (int64_t)B * N * H) return;
+    int h = (int)(r % H);
+    int64_t bn = r / H;
+    int n = (int)(bn % N), b = (int)(bn / N);
+    float s = 0.f;
+    for (int c = lane; c < d; c += 32) s += dout[r * d + c] * o[r * d + c];
+    s = warp_sum(s);
+    if (lane == 0) dvec[((int64_t)b * H + h) * N + n] = s;
+}
+
+static int g_fused_attention = -1;      // -1: not decided yet (environment DNN_CUDA_FUSED_QKV, default on)
+static bool fused_attention_enabled() {
+    if (g_fused_attention < 0) { const char *e = getenv("DNN_CUDA_FUSED_QKV"); g_fused_attention = (e && e[0] == '0') ? 0 : 1; }
+    return g_fused_attention != 0;
+}
+
+struct FusedSaved { float *lse; const int *seq_lens_dev; int mode, prefix, H; float scale; tensor *out; const float *fc, *fs; };
+
+static HeadView qkv_slice(float *base, int which, int N, int H, int d) {
+    HeadView v; v.p = base + (int64_t)which * H * d; v.sb = (int64_t)N * 3 * H * d; v.sh = d; v.sn = (int64_t)3 * H * d; return v;
+}
+static HeadView token_major(float *base, int N, int H, int d) {
+    HeadView v; v.p = base; v.sb = (int64_t)N * H * d; v.sh = d; v.sn = (int64_t)H * d; return v;
+}
+static void rope_qkv(bool bwd, float *qkv, const float *fc, const float *fs, int B, int N, int H, int d) {
+    int64_t total = (int64_t)B * N * 2 * H * (d / 4);
+    if (total <= 0) return;
+    if (bwd) rope_qkv_kernel<true><<<grid_for(total, 256), 256, 0, stream()>>>(qkv, fc, fs, total, N, H, d);
+    else     rope_qkv_kernel<false><<<grid_for(total, 256), 256, 0, stream()>>>(qkv, fc, fs, total, N, H, d);
+    LAUNCHED(bwd ? "rope_qkv_bwd_kernel" : "rope_qkv_fwd_kernel");
+}
+
+static void attention_qkv_backward(grad_fn *fn, tensor *go) {
+    tensor *qkv = fn->inputs[0];
+    if (!wants_grad(qkv)) return;
+    FusedSaved *sv = (FusedSaved *)fn->saved_tensors[0];
+    const int B = qkv->shape[0], N = qkv->shape[1], H = sv->H, d = qkv->shape[2] / (3 * H);
+    float *qd = (float *)qkv->data;
+    const float *gd = (const float *)go->data;
+    int64_t rows = (int64_t)B * N * H;
+    float *dvec = dev_alloc_t<float>(fn->pool, (size_t)rows);
+    attn_bwd_prep_tokmajor_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(gd, (const float *)sv->out->data, dvec, B, N, H, d);
+    LAUNCHED("attn_bwd_prep_kernel");
+    // The kernels store every row when no per-batch lengths are given.  The rotation is undone
+    // in place, which is only right on a buffer that holds nothing but this op's gradient: a
+    // gradient buffer that already has content gets the result through a temporary.
+    bool acc = true;
+    float *g_qkv = grad_full(qkv, &acc);
+    int64_t numel = (int64_t)B * N * 3 * H * d;
+    float *dst = acc ? dev_alloc_t<float>(fn->pool, (size_t)numel) : g_qkv;
+    int store = 7;
+    if (sv->seq_lens_dev) { k_fill(dst, numel, 0.0f); store = 0; }       // rows beyond a sequence's length are never written
+    attn_backward_tc(qkv_slice(qd, 0, N, H, d), qkv_slice(qd, 1, N, H, d), qkv_slice(qd, 2, N, H, d), sv->lse,
+                     token_major(const_cast<float *>(gd), N, H, d), dvec,
+                     qkv_slice(dst, 0, N, H, d), qkv_slice(dst, 1, N, H, d), qkv_slice(dst, 2, N, H, d), sv->seq_lens_dev,
+                     B, H, N, d, sv->mode == ATTENTION_PREFIX_LM ? sv->prefix : 0, sv->scale, store);
+    if (sv->fc) rope_qkv(true, dst, sv->fc, sv->fs, B, N, H, d);
+    if (acc) k_axpy_acc(g_qkv, dst, numel);
+}
+
+// Returns nullptr when the tensor-core path does not apply (mode, head size, layout); the
+// caller then runs the unfused op sequence.
+tensor *attention_from_qkv(struct mem_pool *scratch, tensor *qkv, int H, tensor *fc, tensor *fs,
+                           attention_mode mode, int prefix_len, const int *seq_lens) {
+    if (!fused_attention_enabled() || gemm_mode() != DNN_CUDA_GEMM_TF32) return nullptr;
+    if (!qkv || qkv->ndim != 3 || !qkv->contiguous || qkv->offset != 0 || qkv->parent) return nullptr;
+    const int B = qkv->shape[0], N = qkv->shape[1], D3 = qkv->shape[2];
+    if (H <= 0 || D3 % (3 * H) != 0) return nullptr;
+    const int d = D3 / (3 * H);
+    float *qd = (float *)qkv->data;
+    if (!attn_tc_supported(d, qkv_slice(qd, 0, N, H, d), qkv_slice(qd, 1, N, H, d), qkv_slice(qd, 2, N, H, d))) return nullptr;
+    const float *fcd = nullptr, *fsd = nullptr;
+    if (fc && fs) {
+        if (!fc->contiguous || !fs->contiguous || fc->shape[0] < N) return nullptr;
+        fcd = (const float *)fc->data + fc->offset; fsd = (const float *)fs->data + fs->offset;
+        if ((((uintptr_t)fcd | (uintptr_t)fsd) & 7) != 0) return nullptr;
+    }
+    if (mode == ATTENTION_PREFIX_LM) DNN_CHECK(prefix_len > 0 && prefix_len <= N, "tensor_attention: prefix_len out of range");
+    if (mode == ATTENTION_CAUSAL) DNN_CHECK(prefix_len == 0, "tensor_attention: prefix_len must be 0 in causal mode");
+
+    int shape[3] = {B, N, H * d};
+    tensor *out = tensor_scratch(scratch, 3, shape, 0);
+    bool needs_grad = dnn_grad_enabled() && qkv->requires_grad;
+    float *lse = needs_grad ? dev_alloc_t<float>(scratch, (size_t)B * H * N) : nullptr;
+    const int *lens = seq_lens ? (const int *)dev_put(scratch, seq_lens, (size_t)B * sizeof(int)) : nullptr;
+    const float scale = 1.0f / sqrtf((float)d);
+    if (fcd) rope_qkv(false, qd, fcd, fsd, B, N, H, d);
+    attn_forward_tc(qkv_slice(qd, 0, N, H, d), qkv_slice(qd, 1, N, H, d), qkv_slice(qd, 2, N, H, d),
+                    token_major((float *)out->data, N, H, d), lse, lens, B, H, N, d,
+                    mode == ATTENTION_PREFIX_LM ? prefix_len : 0, scale);
+    if (needs_grad) {
+        grad_fn *fn = attach(scratch, out, attention_qkv_backward, 1, 1);
+        fn->inputs[0] = qkv;
+        FusedSaved *sv = host_alloc_t<FusedSaved>(scratch);
+        sv->lse = lse; sv->seq_lens_dev = lens; sv->mode = (int)mode; sv->prefix = prefix_len; sv->H = H;
+        sv->scale = scale; sv->out = out; sv->fc = fcd; sv->fs = fsd;
+        fn->saved_tensors[0] = (tensor *)sv;
+    }
+    return out;
 }
 
 }  // namespace dnnb
@@ -449,7 +595,8 @@ tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tens
     p.seq_lens = seq_lens ? (const int *)dev_put(scratch, seq_lens, (size_t)B * sizeof(int)) : nullptr;
     p.prefix = mode == ATTENTION_PREFIX_LM ? prefix_len : 0;
     p.scale = 1.0f / sqrtf((float)d);
-    if (use_tc(p)) attn_forward_tc(p.q, p.k, p.v, p.o, p.lse, p.seq_lens, B, H, N, d, p.prefix, p.scale);
+    if (use_tc(p)) attn_forward_tc(packed_heads(p.q, H, N, d), packed_heads(p.k, H, N, d), packed_heads(p.v, H, N, d),
+                                   packed_heads(p.o, H, N, d), p.lse, p.seq_lens, B, H, N, d, p.prefix, p.scale);
     else attn_forward_fp32(p);
 
     if (needs_grad) {
@@ -462,6 +609,9 @@ tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tens
     }
     return out;
 }
+
+void dnn_cuda_set_fused_attention(int on) { g_fused_attention = on ? 1 : 0; }
+int dnn_cuda_get_fused_attention(void) { return fused_attention_enabled() ? 1 : 0; }
 
 tensor *tensor_attention(struct mem_pool *scratch, tensor *q, tensor *k, tensor *v, tensor *mask) {
     return tensor_attention_ex(scratch, q, k, v, mask, ATTENTION_CAUSAL, 0, nullptr);

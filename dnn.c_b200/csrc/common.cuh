@@ -71,6 +71,22 @@ inline View view_of(const tensor *t) {
 View bcast_view(const tensor *t, int out_ndim, const int *out_shape);
 int  bcast_shape(int na, const int *sa, int nb, const int *sb, int *out);   // src/broadcast.c
 
+// A [B,H,N,d] operand of attention addressed through strides (in floats): element (b,h,n,c)
+// lives at p[b*sb + h*sh + n*sn + c].  Packed heads and the [B,N,3,H,d] output of a fused
+// QKV projection are both of this form.
+struct HeadView {
+    float *p;
+    int64_t sb, sh, sn;
+};
+inline HeadView packed_heads(const float *p, int H, int N, int d) {
+    HeadView v; v.p = const_cast<float *>(p); v.sb = (int64_t)H * N * d; v.sh = (int64_t)N * d; v.sn = d; return v;
+}
+
+// Attention computed straight from the [B,N,3*H*d] output of a fused QKV projection (attention.cu).
+// Returns nullptr when the tensor-core path does not apply.
+tensor *attention_from_qkv(struct mem_pool *scratch, tensor *qkv, int H, tensor *fc, tensor *fs,
+                           attention_mode mode, int prefix_len, const int *seq_lens);
+
 // Gradient destinations.  The reference zero-fills every gradient buffer when it is created
 // and every backward adds to it.  Adding to zeros equals storing, so a buffer that is still
 // "fresh" (allocated, never written) may be overwritten by an op that covers ALL of it; this

@@ -131,10 +131,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // instruction descriptor: D=f32, A=B=tf32, major bits, N>>3, M>>4 (M = 256 across a pair)
             uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((g.a_kmajor ? 0u : 1u) << 15) | ((g.b_kmajor ? 0u : 1u) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            // Descriptors are built once; inside the loops only the 16-byte-granular address field
+            // moves (by stage and by K=8 step), so issuing an MMA costs a few integer adds.  The
+            // tensor core needs 128 cycles per instruction at N = 256 and the issuing thread has to
+            // stay well under that.
             const uint32_t a_lbo = g.a_kmajor ? 16 : 4096, b_lbo = g.b_kmajor ? 16 : 4096;
-            const uint32_t a_adv = g.a_kmajor ? UMMA_K * 4 : 1024, b_adv = g.b_kmajor ? UMMA_K * 4 : 1024;   // bytes per K=8 step
             const uint32_t a_sbo = g.a_kmajor ? 1024 : 512, b_sbo = g.b_kmajor ? 1024 : 512;
             const uint32_t a_lt = g.a_kmajor ? 2 : 1, b_lt = g.b_kmajor ? 2 : 1;
+            const uint64_t a_desc0 = make_smem_desc(smem_u32(sA), a_lbo, a_sbo, a_lt), b_desc0 = make_smem_desc(smem_u32(sB), b_lbo, b_sbo, b_lt);
+            const uint64_t a_adv = (g.a_kmajor ? UMMA_K * 4 : 1024) >> 4, b_adv = (g.b_kmajor ? UMMA_K * 4 : 1024) >> 4;   // per K=8 step
             int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
             for (int u = walker; u < num_units && ok; u += walkers) {
@@ -147,11 +152,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&full[stage], phase)) { atomicCAS(&g_gemm_error, 0, 0x300 | stage); ok = false; break; }
                     tc_fence_after();
-                    uint32_t a_addr = smem_u32(sA + stage * Cfg::kStageA), b_addr = smem_u32(sB + stage * Cfg::kStageB);
+                    const uint64_t a_st = a_desc0 + (uint64_t)(stage * (Cfg::kStageA >> 4)), b_st = b_desc0 + (uint64_t)(stage * (Cfg::kStageB >> 4));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) {
-                        uint64_t ad = make_smem_desc(a_addr + k * a_adv, a_lbo, a_sbo, a_lt);
-                        uint64_t bd = make_smem_desc(b_addr + k * b_adv, b_lbo, b_sbo, b_lt);
+                        const uint64_t ad = a_st + k * a_adv, bd = b_st + k * b_adv;
                         if (PAIR) tc_mma_tf32_pair(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                         else tc_mma_tf32(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }

@@ -98,17 +98,24 @@ tensor *transformer_block_forward_ex(struct mem_pool *scratch, transformer_block
     // attention sub-layer, pre-norm
     tensor *h = rms_norm_forward(scratch, block->attn_norm, x);
     tensor *qkv = linear_forward(scratch, block->qkv_proj, h);
-    tensor *q, *k, *v;
-    tensor_split_qkv_heads(scratch, qkv, block->n_heads, &q, &k, &v);
-    if (block->freqs_cos && block->freqs_sin) {
-        int N = q->shape[2];
-        tensor *fc = tensor_slice(scratch, block->freqs_cos, 0, 0, N);
-        tensor *fs = tensor_slice(scratch, block->freqs_sin, 0, 0, N);
-        q = tensor_rope(scratch, q, fc, fs);
-        k = tensor_rope(scratch, k, fc, fs);
+    // Tensor-core path: attention reads Q, K, V in place from qkv and writes token-major output.
+    bool rope = block->freqs_cos && block->freqs_sin;
+    tensor *merged = qkv->ndim == 3 ? attention_from_qkv(scratch, qkv, block->n_heads, rope ? block->freqs_cos : nullptr,
+                                                         rope ? block->freqs_sin : nullptr, mode, prefix_len, seq_lens)
+                                    : nullptr;
+    if (!merged) {
+        tensor *q, *k, *v;
+        tensor_split_qkv_heads(scratch, qkv, block->n_heads, &q, &k, &v);
+        if (rope) {
+            int N = q->shape[2];
+            tensor *fc = tensor_slice(scratch, block->freqs_cos, 0, 0, N);
+            tensor *fs = tensor_slice(scratch, block->freqs_sin, 0, 0, N);
+            q = tensor_rope(scratch, q, fc, fs);
+            k = tensor_rope(scratch, k, fc, fs);
+        }
+        tensor *att = tensor_attention_ex(scratch, q, k, v, nullptr, mode, prefix_len, seq_lens);
+        merged = tensor_merge_heads(scratch, att);
     }
-    tensor *att = tensor_attention_ex(scratch, q, k, v, nullptr, mode, prefix_len, seq_lens);
-    tensor *merged = tensor_merge_heads(scratch, att);
     tensor *proj = linear_forward(scratch, block->out_proj, merged);
     tensor *x1 = tensor_add(scratch, x, proj);
     // feed-forward sub-layer, pre-norm

@@ -21,9 +21,19 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Non-blocking probe of a phase.  A try_wait costs about 170 cycles even when the phase is
+// already complete (it is a potentially suspending instruction); test_wait costs about 5, so
+// every wait probes first and only then falls back to the suspending form.
+__device__ __forceinline__ bool mbar_test(uint32_t bar_addr, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar_addr), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: false when the phase did not complete within kWaitSpins polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     uint32_t addr = smem_u32(bar);
+    if (mbar_test(addr, parity)) return true;
     for (uint32_t it = 0; it < kWaitSpins; it++) {
         uint32_t ok;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
@@ -59,6 +69,24 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 32 consecutive TMEM columns of this thread's lane <- 32 registers (the inverse of tc_ld32)
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// MMA whose A operand is read from TMEM (128 lanes x K columns, 8 columns per K=8 step); B from shared memory
+__device__ __forceinline__ void tc_mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // Shared-memory matrix descriptor (Blackwell descriptor version 1), rows of 128 bytes.
 //   K-major : a row holds 32 consecutive k of one m/n; 16-byte chunks swizzled with row%8
 //             (layout type 2); 8-row groups are `sbo` = 1024 B apart.
@@ -79,6 +107,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *map, int x, int y, int z, int w, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
 }
 // Tile stores shared -> global through the copy engine (bulk async-group completion).  Parts of
 // the box beyond the tensor's extents are clipped.  `add` turns the store into a float add.
@@ -113,6 +145,11 @@ __device__ __forceinline__ uint32_t make_idesc_tf32(int n, bool a_mn, bool b_mn)
     return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
+// Address-field increments (units of 16 bytes) of the kk-th K=8 step relative to the descriptor
+// of step 0: issue loops build one descriptor per operand buffer and add these constants, which
+// keeps the single issuing thread far below the tensor core's time per instruction.
+__device__ __forceinline__ constexpr uint64_t kmajor_step(int rows, int kk) { return (uint64_t)(((kk >> 2) * rows * 128 + (kk & 3) * 32) >> 4); }
+__device__ __forceinline__ constexpr uint64_t mnmajor_step(int kk) { return (uint64_t)(kk * 64); }
 // K-major tile [k-blocks of 32][rows][32 floats], 128-byte swizzle: descriptor of the kk-th K=8 step.
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t base, int rows, int kk) {
     return make_smem_desc(base + (uint32_t)((kk >> 2) * rows * 128 + (kk & 3) * 32), 16, 1024, 2);

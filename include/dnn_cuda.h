@@ -57,6 +57,15 @@ void  dnn_cuda_host_free(void *p);
 int  dnn_cuda_set_gemm_mode(int mode);
 int  dnn_cuda_get_gemm_mode(void);
 
+/* Transformer blocks in TF32 mode with head size 32 or 64 run attention straight from the
+ * fused QKV projection: Q, K and V are read in place from its [B,N,3,H,d] output, RoPE is
+ * applied there, and the result is written token-major, which removes the head split / merge
+ * copies of the reference's block (src/transformer.c:143-170) without changing any value.
+ * `on` = 0 forces the reference's op-by-op sequence (default 1; environment
+ * DNN_CUDA_FUSED_QKV=0 does the same).  No counterpart in the reference. */
+void dnn_cuda_set_fused_attention(int on);
+int  dnn_cuda_get_fused_attention(void);
+
 /* Device-side timing on the compute stream (CUDA events): start records an event,
  * stop records a second one, waits for it and returns the milliseconds between. */
 int   dnn_cuda_timer_start(void);

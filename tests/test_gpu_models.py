@@ -126,3 +126,50 @@ def test_config1_against_live_reference(binding):
         a, b = got["grads"][n], want["grads"][n]
         err = np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b.astype(np.float64))
         assert err <= 3e-5, (n, err)
+
+
+@pytest.mark.parametrize("shape", [dict(D=128, H=4, N=128, B=4), dict(D=128, H=2, N=200, B=3), dict(D=192, H=3, N=77, B=2)],
+                         ids=["d32", "d64-ragged", "d64-short"])
+def test_attention_from_fused_qkv_equals_op_sequence(binding, shape):
+    """Transformer blocks in TF32 mode read Q, K, V in place from the QKV projection and write
+    token-major output.  That path must reproduce the reference's op-by-op sequence (split heads,
+    RoPE, attention, merge heads) bit for bit: same kernels, same values, only the addressing
+    differs.  Head sizes 32 and 64, sequence lengths that are not multiples of the tiles."""
+    cfg = dict(models.lm_config("c1"))
+    cfg.update(V=96, L=2, F=256, **shape)
+    outs = []
+    for fused in (1, 0):
+        d = fresh(binding, binding.GEMM_TF32)
+        d.lib.dnn_cuda_set_fused_attention(fused)
+        try:
+            outs.append(models.run_lm(d, cfg, steps=2))
+        finally:
+            d.lib.dnn_cuda_set_fused_attention(1)
+            d.close()
+    a, b = outs
+    assert a["loss"] == b["loss"], (a["loss"], b["loss"])
+    assert a["grad_norm"] == b["grad_norm"]
+    for n in a["grads"]:
+        assert np.array_equal(a["grads"][n], b["grads"][n]), n
+    for n in a["params"]:
+        assert np.array_equal(a["params"][n], b["params"][n]), n
+
+
+def test_vision_lm_fused_qkv_equals_op_sequence(binding):
+    """Prefix-LM attention with per-batch lengths (padded rows) through both block paths."""
+    outs = []
+    for fused in (1, 0):
+        d = fresh(binding, binding.GEMM_TF32)
+        d.lib.dnn_cuda_set_fused_attention(fused)
+        try:
+            outs.append(models.run_vlm(d, D=64, H=2, steps=2))
+        finally:
+            d.lib.dnn_cuda_set_fused_attention(1)
+            d.close()
+    a, b = outs
+    assert a["loss"] == b["loss"], (a["loss"], b["loss"])
+    for n in a["grads"]:
+        if a["grads"][n] is None:
+            assert b["grads"][n] is None
+            continue
+        assert np.array_equal(a["grads"][n], b["grads"][n]), n
