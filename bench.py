@@ -35,6 +35,13 @@ CFG = dict(V=32000, D=768, L=12, H=12, F=2048, B=16, N=1024, lr=6e-4, b1=0.9, b2
 CPU_SAMPLE = dict(CFG, B=1, N=16)
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libdnn_ref.so")
 METRIC = "train tokens/s (fwd+bwd+AdamW), 12L-768d GPT"
+# DRAM bytes (read + write) the GEMM kernel moves per training step of CFG in TF32 mode, from an
+# ncu capture of every linear-layer shape at full size, forward, dA and dW (summary:
+# profiles/gemm_tf32_kernel_linear_shapes.txt): 2.603 GB per transformer block; the three launches
+# of the vocabulary projection (6.7 GB working set, not captured) are taken at their algorithmic
+# bytes.  183 GEMM launches per step; `roofline.traffic` is the per-launch average.
+GEMM_DRAM_BYTES_PER_STEP = 12 * 2.603e9 + 6.73e9
+GEMM_LAUNCHES_PER_STEP = 183
 
 
 def param_names(L):
@@ -297,7 +304,9 @@ def main():
                        "seq_len": cfg["N"], "global_batch_tokens": world * tokens, "params": n_params,
                        "parallelism": "dp%d" % world, "l2_flush": "inputs larger than L2 (activations ~30 GB per step)"},
             "roofline": {"bound": "tensor", "kernel": "gemm_tf32_kernel", "achieved": round(achieved, 1), "peak": round(tf32_peak, 1),
-                         "unit": "TFLOP/s", "frac": round(achieved / tf32_peak, 4), "traffic": None,
+                         "unit": "TFLOP/s", "frac": round(achieved / tf32_peak, 4),
+                         "traffic": round(GEMM_DRAM_BYTES_PER_STEP / GEMM_LAUNCHES_PER_STEP) if args.gemm == "tf32" and cfg == CFG else None,
+                         "traffic_unit": "bytes per launch (DRAM read + write, ncu)",
                          "launches": nl.value, "kernel_ms_per_step": round(gms.value / args.steps, 3),
                          "flop_per_step": gwork.value / args.steps,
                          "peak_source": "0.5 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s); no TF32 figure is measured there" % src,

@@ -41,6 +41,7 @@ struct TcArgs {
     int a_kmajor, b_kmajor;
     int splits, kb_per_split;          // split-K: work unit = (tile, split)
     int tiles_m, tiles_n;
+    int n_fastest;                     // tile order: consecutive work units walk along N (1) or along M (0)
 };
 
 template <int BN, bool PAIR> struct TcCfg {
@@ -52,6 +53,14 @@ template <int BN, bool PAIR> struct TcCfg {
     static constexpr int kSmem = kStages * (kStageA + kStageB) + kStore + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int kTmemCols = 2 * BN;
 };
+
+// Work unit -> tile coordinates.  Units that run at the same time should share the operand that
+// does not fit in L2: walking along M re-reads the A rows once per N tile, walking along N
+// re-reads B once per M tile; the host picks the order whose re-read operand stays in L2.
+__device__ __forceinline__ void tile_of(const TcArgs &g, int tile, int &tm, int &tn) {
+    if (g.n_fastest) { tm = tile / g.tiles_n; tn = tile - tm * g.tiles_n; }
+    else { tn = tile / g.tiles_m; tm = tile - tn * g.tiles_m; }
+}
 
 template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -104,8 +113,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool ok = true;
             for (int u = walker; u < num_units && ok; u += walkers) {
                 int tile = u / g.splits, split = u - tile * g.splits;
-                int m0 = (tile % g.tiles_m) * kTileM + (int)rank * BM;
-                int n0 = (tile / g.tiles_m) * BN + (int)rank * Cfg::kRowsB;      // a pair splits B's columns between its CTAs
+                int tm, tn;
+                tile_of(g, tile, tm, tn);
+                int m0 = tm * kTileM + (int)rank * BM;
+                int n0 = tn * BN + (int)rank * Cfg::kRowsB;      // a pair splits B's columns between its CTAs
                 int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&empty[stage], phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 0x100 | stage); ok = false; break; }
@@ -175,7 +186,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t chunk = 0;
         for (int u = walker; u < num_units; u += walkers) {
             int tile = u / g.splits, split = u - tile * g.splits;
-            int m0 = (tile % g.tiles_m) * kTileM + (int)rank * BM, n0 = (tile / g.tiles_m) * BN;
+            int tm, tn;
+            tile_of(g, tile, tm, tn);
+            int m0 = tm * kTileM + (int)rank * BM, n0 = tn * BN;
             int kb0 = split * g.kb_per_split;
             bool has_k = kb0 < num_kb_total;
             if (!mbar_wait(&acc_full[acc], acc_phase)) { if (lane == 0) atomicCAS(&g_gemm_error, 0, 0x400 | acc); break; }
@@ -395,6 +408,11 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     t.tiles_m = (g.M + kTileM - 1) / kTileM; t.tiles_n = (g.N + BN - 1) / BN;
     int tiles = t.tiles_m * t.tiles_n;
     int num_kb = (g.K + BK - 1) / BK;
+    // Tile order.  Walking along M streams all of A once per N tile; that is free while A stays
+    // in L2 (about half of the 126 MB is a safe share) and otherwise costs tiles_n passes over
+    // A from HBM.  When A is too large and B is not, walk along N instead.
+    const double a_bytes = 4.0 * g.M * g.K, b_bytes = 4.0 * g.K * g.N, l2_share = 48e6;
+    t.n_fastest = (t.tiles_n > 1 && a_bytes > l2_share && b_bytes <= l2_share) ? 1 : 0;
     const int slots = PAIR ? kNumSMs / 2 : kNumSMs;      // work units in flight: one per CTA, or per CTA pair
     // split-K when the output has too few tiles to fill the SMs and K is long
     int splits = choose_splits(tiles, slots, num_kb, g.M, g.N);

@@ -45,9 +45,9 @@ def peaks():
 
 
 class Bench:
-    def __init__(self, B, iters, small):
+    def __init__(self, B, iters, small, params_mb=8192, scratch_mb=24 * 1024):
         self.B, self.iters, self.small = B, iters, small
-        self.d = B.Dnn(B.B200_LIB, params_mb=8192, scratch_mb=24 * 1024, data_mb=256)
+        self.d = B.Dnn(B.B200_LIB, params_mb=params_mb, scratch_mb=scratch_mb, data_mb=256)
         self.lib = self.d.lib
         self.rng = np.random.default_rng(1)
         # 256 MiB rewritten between iterations: twice the 126 MB L2
@@ -108,9 +108,12 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--gemm", default="tf32", choices=["tf32", "3xtf32", "fp32"])
+    ap.add_argument("--pools-mb", default="8192,24576", help="params,scratch arena sizes (small arenas keep profiler captures fast)")
+    ap.add_argument("--shapes", default="", help="matmul_shapes only: indices of the shapes to run, e.g. 0,1,2,3")
     args = ap.parse_args()
     B = load_binding()
-    b = Bench(B, args.iters, args.small)
+    pm, sm = (int(x) for x in args.pools_mb.split(","))
+    b = Bench(B, args.iters, args.small, pm, sm)
     lib, d, rng = b.lib, b.d, b.rng
     lib.dnn_cuda_set_gemm_mode({"fp32": 0, "tf32": 1, "3xtf32": 2}[args.gemm])
     R = 1024 if args.small else 8192
@@ -158,7 +161,9 @@ def main():
     if "matmul_shapes" in ops:
         # the linear layers of the 124M training step (BASELINE config 5): 16384 tokens
         M = 2048 if args.small else 16384
-        for K, N in ((768, 2304), (768, 768), (768, 2048), (2048, 768), (768, 32000)):
+        shapes = ((768, 2304), (768, 768), (768, 2048), (2048, 768), (768, 32000))
+        pick = [int(x) for x in args.shapes.split(",")] if args.shapes else range(len(shapes))
+        for K, N in [shapes[i] for i in pick]:
             b.run("matmul_add[%dx%dx%d]" % (M, K, N),
                   lambda: dict(a=b.dev(randn(M, K), True), w=b.dev(randn(K, N, scale=0.02), True), bias=b.dev(np.zeros(N, np.float32), True)),
                   lambda i: lib.tensor_matmul_add(d.scratch, i["a"], i["w"], 0, i["bias"]), (M, N), 2.0 * M * N * K, 4.0 * M * N * K, "tensor")
