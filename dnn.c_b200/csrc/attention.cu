@@ -388,6 +388,44 @@ void attn_backward_fp32(const AttnParams &p) {
     else attn_bwd_launch<128>(p);
 }
 
+// D_i for token-major dO and O: row (b,n,h) of [B,N,H,d] -> dvec[(b*H + h)*N + n].
+// d/4 lanes share a row (one float4 each), so a warp covers 128/d rows with 128-bit loads.
+template <int D, bool TOKMAJOR>
+__global__ void attn_bwd_prep_v4_kernel(const float4 *__restrict__ dout, const float4 *__restrict__ o,
+                                        float *__restrict__ dvec, int B, int N, int H) {
+    constexpr int LPR = D / 4, RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31, sub = lane % LPR;
+    const int64_t rows = (int64_t)B * N * H;
+    int64_t r = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + lane / LPR;     // (b, n, h)
+    float s = 0.f;
+    if (r < rows) {
+        float4 a = dout[r * LPR + sub], b = o[r * LPR + sub];
+        s = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    }
+#pragma unroll
+    for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (r < rows && sub == 0) {
+        if (TOKMAJOR) {
+            int h = (int)(r % H);
+            int64_t bn = r / H;
+            int n = (int)(bn % N), b = (int)(bn / N);
+            dvec[((int64_t)b * H + h) * N + n] = s;
+        } else {
+            dvec[r] = s;              // rows are already (b, h, n)
+        }
+    }
+}
+// Both layouts go through the same arithmetic (same partial sums, same reduction tree), so the
+// packed and the token-major path give identical D_i.
+template <bool TOKMAJOR>
+static void launch_prep_v4(const float *dout, const float *o, float *dvec, int B, int N, int H, int d) {
+    const float4 *g4 = reinterpret_cast<const float4 *>(dout), *o4 = reinterpret_cast<const float4 *>(o);
+    int64_t rows = (int64_t)B * N * H;
+    if (d == 64) attn_bwd_prep_v4_kernel<64, TOKMAJOR><<<(unsigned)((rows + 15) / 16), 256, 0, stream()>>>(g4, o4, dvec, B, N, H);
+    else         attn_bwd_prep_v4_kernel<32, TOKMAJOR><<<(unsigned)((rows + 31) / 32), 256, 0, stream()>>>(g4, o4, dvec, B, N, H);
+    LAUNCHED("attn_bwd_prep_kernel");
+}
+
 struct AttnSaved { float *lse; const int *seq_lens_dev; int mode, prefix; float scale; tensor *out; };
 
 static void attention_backward(grad_fn *fn, tensor *go) {
@@ -411,8 +449,12 @@ static void attention_backward(grad_fn *fn, tensor *go) {
     p.store = (aq ? 0 : 1) | (ak ? 0 : 2) | (av ? 0 : 4);
     int64_t rows = (int64_t)p.B * p.H * p.N;
     float *dvec = dev_alloc_t<float>(fn->pool, (size_t)rows);
-    attn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(p.dout, p.o, dvec, rows, p.d);
-    LAUNCHED("attn_bwd_prep_kernel");
+    if ((p.d == 32 || p.d == 64) && aligned16(p.dout) && aligned16(p.o)) {
+        launch_prep_v4<false>(p.dout, p.o, dvec, p.B, p.N, p.H, p.d);
+    } else {
+        attn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(p.dout, p.o, dvec, rows, p.d);
+        LAUNCHED("attn_bwd_prep_kernel");
+    }
     p.dvec = dvec;
     auto pk = [&](const float *x) { return packed_heads(x, p.H, p.N, p.d); };
     if (use_tc(p)) attn_backward_tc(pk(p.q), pk(p.k), pk(p.v), p.lse, pk(p.dout), p.dvec, pk(p.dq), pk(p.dk), pk(p.dv), p.seq_lens,
@@ -456,21 +498,6 @@ __global__ void rope_qkv_kernel(float *__restrict__ qkv, const float *__restrict
     }
 }
 
-// D_i for token-major dO and O: row (b,n,h) of [B,N,H,d] -> dvec[(b*H + h)*N + n]
-__global__ void attn_bwd_prep_tokmajor_kernel(const float *__restrict__ dout, const float *__restrict__ o,
-                                              float *__restrict__ dvec, int B, int N, int H, int d) {
-    int lane = threadIdx.x & 31;
-    int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // (b, n, h)
-    if (r >= (int64_t)B * N * H) return;
-    int h = (int)(r % H);
-    int64_t bn = r / H;
-    int n = (int)(bn % N), b = (int)(bn / N);
-    float s = 0.f;
-    for (int c = lane; c < d; c += 32) s += dout[r * d + c] * o[r * d + c];
-    s = warp_sum(s);
-    if (lane == 0) dvec[((int64_t)b * H + h) * N + n] = s;
-}
-
 static int g_fused_attention = -1;      // -1: not decided yet (environment DNN_CUDA_FUSED_QKV, default on)
 static bool fused_attention_enabled() {
     if (g_fused_attention < 0) { const char *e = getenv("DNN_CUDA_FUSED_QKV"); g_fused_attention = (e && e[0] == '0') ? 0 : 1; }
@@ -502,8 +529,7 @@ static void attention_qkv_backward(grad_fn *fn, tensor *go) {
     const float *gd = (const float *)go->data;
     int64_t rows = (int64_t)B * N * H;
     float *dvec = dev_alloc_t<float>(fn->pool, (size_t)rows);
-    attn_bwd_prep_tokmajor_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(gd, (const float *)sv->out->data, dvec, B, N, H, d);
-    LAUNCHED("attn_bwd_prep_kernel");
+    launch_prep_v4<true>(gd, (const float *)sv->out->data, dvec, B, N, H, d);
     // The kernels store every row when no per-batch lengths are given.  The rotation is undone
     // in place, which is only right on a buffer that holds nothing but this op's gradient: a
     // gradient buffer that already has content gets the result through a temporary.

@@ -116,9 +116,18 @@ __global__ void colsum_partial_kernel(const float *__restrict__ g, float *__rest
     }
 }
 // float4 variant: CTA = 32 x 8 threads covering 128 columns, 16-byte loads.
+// Arrival counters of the fused column sum, one per group of 128 columns.  The last CTA of a
+// group to finish resets its counter, so the array is all zero between launches.
+constexpr int kColsumGroups = 2048;
+__device__ unsigned int g_colsum_arrivals[kColsumGroups];
+
+// out != nullptr: the CTA that finishes last in its column group adds the partials of all row
+// slabs in slab order (fixed order: the result does not depend on which CTA is last) and
+// writes `out`, which saves the second launch.
 __global__ void colsum_partial_v4_kernel(const float *__restrict__ g, float *__restrict__ partial,
-                                         int64_t rows, int C, int rows_per) {
+                                         int64_t rows, int C, int rows_per, float *__restrict__ out, int acc) {
     __shared__ float4 tile[8][33];
+    __shared__ int is_last;
     int c = (blockIdx.x * 32 + threadIdx.x) * 4;
     int64_t r0 = (int64_t)blockIdx.y * rows_per;
     int64_t r1 = r0 + rows_per; if (r1 > rows) r1 = rows;
@@ -135,6 +144,35 @@ __global__ void colsum_partial_v4_kernel(const float *__restrict__ g, float *__r
 #pragma unroll
         for (int j = 0; j < 8; j++) { float4 v = tile[j][threadIdx.x]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
         *reinterpret_cast<float4 *>(partial + (int64_t)blockIdx.y * C + c) = t;
+    }
+    if (out == nullptr) return;
+    __threadfence();                         // this CTA's partials are visible before its arrival
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+        unsigned prev = atomicAdd(&g_colsum_arrivals[blockIdx.x], 1u);
+        is_last = (prev == gridDim.y - 1);
+        if (is_last) g_colsum_arrivals[blockIdx.x] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // 256 threads over the 128 columns of this group: threadIdx.y picks one of 8 slab lanes
+    // (p = y, y+8, ...), lane sums are combined in lane order
+    float4 s2 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < C)
+        for (int p = threadIdx.y; p < (int)gridDim.y; p += 8) {
+            float4 v = __ldcg(reinterpret_cast<const float4 *>(partial + (int64_t)p * C + c));      // L2: written by other CTAs
+            s2.x += v.x; s2.y += v.y; s2.z += v.z; s2.w += v.w;
+        }
+    tile[threadIdx.y][threadIdx.x] = s2;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; j++) { float4 v = tile[j][threadIdx.x]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+        float4 *o4 = reinterpret_cast<float4 *>(out + c);
+        if (acc) { float4 o = *o4; t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w; }
+        *o4 = t;
     }
 }
 __global__ void colsum_final_kernel(float *__restrict__ out, const float *__restrict__ partial, int nparts, int C, int acc) {
@@ -165,8 +203,11 @@ void k_colsum_acc(float *out, const float *g, int64_t rows, int C, bool accumula
     }
     if (C % 4 == 0 && aligned16(g)) {
         dim3 grid((C / 4 + 31) / 32, nparts), block(32, 8);
-        colsum_partial_v4_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per);
+        bool fused = (int)grid.x <= kColsumGroups && aligned16(out);
+        colsum_partial_v4_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per, fused ? out : nullptr,
+                                                               accumulate ? 1 : 0);
         LAUNCHED("colsum_partial_v4_kernel");
+        if (fused) return;
     } else {
         dim3 grid((C + 31) / 32, nparts), block(32, 32);
         colsum_partial_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per);

@@ -169,31 +169,78 @@ __global__ void embedding_fwd_kernel(float *__restrict__ out, const float *__res
     }
 }
 
-// Scatter-add with duplicate ids, deterministic: the CTA of the FIRST
-// occurrence of an id adds the rows of all its occurrences in ascending order
-// (the order of the reference's serial loop, src/embedding.c:37-43).
-__global__ void embedding_bwd_kernel(float *__restrict__ tg, const float *__restrict__ g, const int *__restrict__ ids,
-                                     int n_ids, int d, int vocab, int64_t g_s0, int64_t t_s0, int64_t t_s1) {
-    __shared__ int flags[256];
-    int i = blockIdx.x;
+// Scatter-add with duplicate ids, deterministic and in the order of the reference's serial loop
+// (src/embedding.c:37-43): the occurrences of every id are bucketed (count, scan, fill), and one
+// CTA per id adds the rows of its occurrences in ascending position.  The only atomics are integer
+// counters whose final values do not depend on the order of arrival.
+__global__ void emb_count_kernel(const int *__restrict__ ids, int n, int vocab, int *__restrict__ count) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
     int id = ids[i];
-    if (id < 0 || id >= vocab) return;
-    int dup = 0;
-    for (int j = threadIdx.x; j < i; j += blockDim.x) dup |= (ids[j] == id);
-    if (__syncthreads_or(dup)) return;
-    for (int j0 = i; j0 < n_ids; j0 += blockDim.x) {
-        int j = j0 + threadIdx.x;
-        int f = (j < n_ids) && (ids[j] == id);
-        flags[threadIdx.x] = f;
-        if (__syncthreads_or(f)) {
-            for (int t = 0; t < blockDim.x; t++) {
-                if (!flags[t]) continue;
-                const float *gr = g + (int64_t)(j0 + t) * g_s0;
-                for (int c = threadIdx.x; c < d; c += blockDim.x)
-                    tg[(int64_t)id * t_s0 + (int64_t)c * t_s1] += gr[c];
-            }
-        }
+    if (id >= 0 && id < vocab) atomicAdd(&count[id], 1);
+}
+// start[v] = sum of count[0..v); one CTA walks the vocabulary in chunks of its size
+__global__ void emb_scan_kernel(const int *__restrict__ count, int vocab, int *__restrict__ start) {
+    __shared__ int sh[1024];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int v0 = 0; v0 < vocab; v0 += blockDim.x) {
+        int v = v0 + threadIdx.x;
+        int c = v < vocab ? count[v] : 0;
+        sh[threadIdx.x] = c;
         __syncthreads();
+        for (int off = 1; off < (int)blockDim.x; off <<= 1) {
+            int t = threadIdx.x >= off ? sh[threadIdx.x - off] : 0;
+            __syncthreads();
+            sh[threadIdx.x] += t;
+            __syncthreads();
+        }
+        if (v < vocab) start[v] = carry + sh[threadIdx.x] - c;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry += sh[threadIdx.x];
+        __syncthreads();
+    }
+}
+__global__ void emb_fill_kernel(const int *__restrict__ ids, int n, int vocab, const int *__restrict__ start,
+                                int *__restrict__ cursor, int *__restrict__ list) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int id = ids[i];
+    if (id >= 0 && id < vocab) list[start[id] + atomicAdd(&cursor[id], 1)] = i;
+}
+// One CTA per id.  The bucket is in arrival order; the next position to add is the smallest one
+// above the last (block-wide minimum), so rows are added in ascending position.
+__global__ void embedding_bwd_kernel(float *__restrict__ tg, const float *__restrict__ g, const int *__restrict__ count,
+                                     const int *__restrict__ start, const int *__restrict__ list,
+                                     int d, int64_t g_s0, int64_t t_s0, int64_t t_s1, int vec) {
+    __shared__ int sh[32];
+    const int id = blockIdx.x, k = count[id];
+    if (k == 0) return;
+    const int *mine = list + start[id];
+    float *row = tg + (int64_t)id * t_s0;
+    int last = -1;
+    for (int it = 0; it < k; it++) {
+        int best = 0x7fffffff;
+        for (int j = threadIdx.x; j < k; j += blockDim.x) { int p = mine[j]; if (p > last && p < best) best = p; }
+        for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+        if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = best;
+        __syncthreads();
+        best = sh[0];
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) best = min(best, sh[w]);
+        __syncthreads();
+        last = best;
+        const float *gr = g + (int64_t)last * g_s0;
+        if (vec) {
+            const float4 *g4 = reinterpret_cast<const float4 *>(gr);
+            float4 *r4 = reinterpret_cast<float4 *>(row);
+            for (int c = threadIdx.x; c < d / 4; c += blockDim.x) {
+                float4 a = r4[c], x = g4[c];
+                r4[c] = make_float4(a.x + x.x, a.y + x.y, a.z + x.z, a.w + x.w);
+            }
+        } else {
+            for (int c = threadIdx.x; c < d; c += blockDim.x) row[(int64_t)c * t_s1] += gr[c];
+        }
     }
 }
 
@@ -201,11 +248,25 @@ static void embedding_backward(grad_fn *fn, tensor *go) {
     tensor *table = fn->inputs[0];
     tensor *ids = fn->saved_tensors[0];
     if (!wants_grad(table)) return;
-    int n = ids->shape[0], d = table->shape[1];
-    if (n <= 0) return;
+    int n = ids->shape[0], d = table->shape[1], vocab = table->shape[0];
+    if (n <= 0 || vocab <= 0) return;
     float *tg = _grad_ensure(table);
-    embedding_bwd_kernel<<<n, 256, 0, stream()>>>(tg, (const float *)go->data, (const int *)ids->data, n, d,
-                                                  table->shape[0], go->strides[0], table->strides[0], table->strides[1]);
+    const int *idp = (const int *)ids->data;
+    int *count = (int *)dev_alloc(fn->pool, (size_t)vocab * 2 * sizeof(int), true);      // count | cursor, zeroed
+    int *cursor = count + vocab;
+    int *start = (int *)dev_alloc(fn->pool, (size_t)vocab * sizeof(int), false);
+    int *list = (int *)dev_alloc(fn->pool, (size_t)n * sizeof(int), false);
+    emb_count_kernel<<<(n + 255) / 256, 256, 0, stream()>>>(idp, n, vocab, count);
+    LAUNCHED("emb_count_kernel");
+    emb_scan_kernel<<<1, 1024, 0, stream()>>>(count, vocab, start);
+    LAUNCHED("emb_scan_kernel");
+    emb_fill_kernel<<<(n + 255) / 256, 256, 0, stream()>>>(idp, n, vocab, start, cursor, list);
+    LAUNCHED("emb_fill_kernel");
+    const float *gd = (const float *)go->data;
+    int vec = table->strides[1] == 1 && d % 4 == 0 && table->strides[0] % 4 == 0 && go->strides[0] % 4 == 0 &&
+              aligned16(tg) && aligned16(gd);
+    embedding_bwd_kernel<<<vocab, 128, 0, stream()>>>(tg, gd, count, start, list, d, go->strides[0], table->strides[0],
+                                                      table->strides[1], vec);
     LAUNCHED("embedding_bwd_kernel");
 }
 
