@@ -42,6 +42,7 @@ struct TcArgs {
     int splits, kb_per_split;          // split-K: work unit = (tile, split)
     int tiles_m, tiles_n;
     int n_fastest;                     // tile order: consecutive work units walk along N (1) or along M (0)
+    int a_chunked, b_chunked;          // MN-major operand described as {32, K, extent/32}: one TMA copy per stage
 };
 
 template <int BN, bool PAIR> struct TcCfg {
@@ -129,9 +130,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     };
                     uint8_t *a = sA + stage * Cfg::kStageA, *b = sB + stage * Cfg::kStageB;
                     int k = kb * BK;
+                    auto load3 = [&](void *dst, const CUtensorMap *map, int y, int z) {
+                        if (PAIR) tma_load_3d_pair(dst, map, 0, y, z, bar);
+                        else tma_load_3d(dst, map, 0, y, z, &full[stage]);
+                    };
                     if (g.a_kmajor) load(a, &tmA, k, m0);                                          // box {32 k, 128 rows}
+                    else if (g.a_chunked) load3(a, &tmA, k, m0 >> 5);                              // box {32 m, 32 k, 4 chunks of m}
                     else for (int c = 0; c < BM / 32; c++) load(a + c * 4096, &tmA, m0 + c * 32, k);   // box {32 m, 32 k}
                     if (g.b_kmajor) load(b, &tmB, k, n0);
+                    else if (g.b_chunked) load3(b, &tmB, k, n0 >> 5);
                     else for (int c = 0; c < Cfg::kRowsB / 32; c++) load(b + c * 4096, &tmB, n0 + c * 32, k);
                     if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
                 }
@@ -325,6 +332,24 @@ static CUtensorMap make_out_map(float *base, int64_t N, int64_t M, int64_t ldc, 
     return m;
 }
 
+// MN-major operand whose contiguous extent is a multiple of 32: 3-D map {32, outer, inner/32} with
+// box {32, 32, chunks}, which lands in shared memory as [chunk][k row][32 floats] -- the layout the
+// per-chunk 2-D copies produce -- with one copy instead of `chunks`.  (The split dimension cannot be
+// clipped by the copy engine, hence the multiple-of-32 condition; a chunk index beyond the last
+// chunk is out of bounds in the third dimension and reads zeros.)
+static CUtensorMap make_chunked_map(const float *base, int64_t inner, int64_t outer, int64_t pitch, int chunks) {
+    CUtensorMap m;
+    cuuint64_t dims[3] = {32, (cuuint64_t)outer, (cuuint64_t)(inner / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)pitch * 4, 128};
+    cuuint32_t box[3] = {32, 32, (cuuint32_t)chunks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, (void *)base, dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled (chunked) failed (%d)\n", (int)r); abort(); }
+    return m;
+}
+
 static bool operand_ok(const float *p, int64_t rs, int64_t cs, int64_t rows, int64_t cols) {
     if (!aligned16(p)) return false;
     if (cs == 1) return rs % 4 == 0 && rs >= cols;     // contiguous along the column index
@@ -401,9 +426,13 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
         once = true;
     }
     // A(m,k): K-major -> matrix [M rows][K contiguous]; MN-major -> [K rows][M contiguous]
-    CUtensorMap tmA = a_kmajor ? make_map(g.A, g.K, g.M, g.a_rs, BM, false) : make_map(g.A, g.M, g.K, g.a_cs, 32, true);
-    CUtensorMap tmB = b_kmajor ? make_map(g.B, g.K, g.N, g.b_cs, Cfg::kRowsB, false) : make_map(g.B, g.N, g.K, g.b_rs, 32, true);
+    const bool a_chunked = !a_kmajor && g.M % 32 == 0, b_chunked = !b_kmajor && g.N % 32 == 0;
+    CUtensorMap tmA = a_kmajor ? make_map(g.A, g.K, g.M, g.a_rs, BM, false)
+                    : a_chunked ? make_chunked_map(g.A, g.M, g.K, g.a_cs, BM / 32) : make_map(g.A, g.M, g.K, g.a_cs, 32, true);
+    CUtensorMap tmB = b_kmajor ? make_map(g.B, g.K, g.N, g.b_cs, Cfg::kRowsB, false)
+                    : b_chunked ? make_chunked_map(g.B, g.N, g.K, g.b_rs, Cfg::kRowsB / 32) : make_map(g.B, g.N, g.K, g.b_rs, 32, true);
     TcArgs t;
+    t.a_chunked = a_chunked ? 1 : 0; t.b_chunked = b_chunked ? 1 : 0;
     t.M = g.M; t.N = g.N; t.K = g.K; t.a_kmajor = a_kmajor; t.b_kmajor = b_kmajor;
     t.tiles_m = (g.M + kTileM - 1) / kTileM; t.tiles_n = (g.N + BN - 1) / BN;
     int tiles = t.tiles_m * t.tiles_n;
