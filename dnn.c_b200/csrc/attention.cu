@@ -368,7 +368,8 @@ void attn_forward_tc(const HeadView &q, const HeadView &k, const HeadView &v, co
                      int B, int H, int N, int d, int prefix, float scale);
 void attn_backward_tc(const HeadView &q, const HeadView &k, const HeadView &v, const float *lse, const HeadView &dout, const float *dvec,
                       const HeadView &dq, const HeadView &dk, const HeadView &dv, const int *seq_lens,
-                      int B, int H, int N, int d, int prefix, float scale, int store);
+                      int B, int H, int N, int d, int prefix, float scale, int store,
+                      const float *rope_c = nullptr, const float *rope_s = nullptr);
 
 // TF32 mode runs on the tensor core (head dims 32 and 64); the FP32 and 3xTF32 modes, and
 // other head dims, run the exact kernels of this file.
@@ -491,8 +492,8 @@ __global__ void rope_qkv_kernel(float *__restrict__ qkv, const float *__restrict
             o.x = v.x * c.x - v.y * sn.x; o.y = v.x * sn.x + v.y * c.x;
             o.z = v.z * c.y - v.w * sn.y; o.w = v.z * sn.y + v.w * c.y;
         } else {
-            o.x = v.x * c.x + v.y * sn.x;  o.y = -v.x * sn.x + v.y * c.x;
-            o.z = v.z * c.y + v.w * sn.y;  o.w = -v.z * sn.y + v.w * c.y;
+            rope_inv_pair(v.x, v.y, c.x, sn.x, o.x, o.y);
+            rope_inv_pair(v.z, v.w, c.y, sn.y, o.z, o.w);
         }
         *ptr = o;
     }
@@ -539,11 +540,14 @@ static void attention_qkv_backward(grad_fn *fn, tensor *go) {
     float *dst = acc ? dev_alloc_t<float>(fn->pool, (size_t)numel) : g_qkv;
     int store = 7;
     if (sv->seq_lens_dev) { k_fill(dst, numel, 0.0f); store = 0; }       // rows beyond a sequence's length are never written
+    // In store mode the kernels rotate dQ and dK back in their epilogues; otherwise a pass over dst does it.
+    const bool rot_in_kernel = sv->fc && store == 7 && (((uintptr_t)sv->fc | (uintptr_t)sv->fs) & 15) == 0;
     attn_backward_tc(qkv_slice(qd, 0, N, H, d), qkv_slice(qd, 1, N, H, d), qkv_slice(qd, 2, N, H, d), sv->lse,
                      token_major(const_cast<float *>(gd), N, H, d), dvec,
                      qkv_slice(dst, 0, N, H, d), qkv_slice(dst, 1, N, H, d), qkv_slice(dst, 2, N, H, d), sv->seq_lens_dev,
-                     B, H, N, d, sv->mode == ATTENTION_PREFIX_LM ? sv->prefix : 0, sv->scale, store);
-    if (sv->fc) rope_qkv(true, dst, sv->fc, sv->fs, B, N, H, d);
+                     B, H, N, d, sv->mode == ATTENTION_PREFIX_LM ? sv->prefix : 0, sv->scale, store,
+                     rot_in_kernel ? sv->fc : nullptr, rot_in_kernel ? sv->fs : nullptr);
+    if (sv->fc && !rot_in_kernel) rope_qkv(true, dst, sv->fc, sv->fs, B, N, H, d);
     if (acc) k_axpy_acc(g_qkv, dst, numel);
 }
 

@@ -49,6 +49,8 @@ struct AttnTcParams {
     int prefix;
     float scale;
     int store;                           // bit 0/1/2: dq/dk/dv are written, not added to
+    const float *rope_c, *rope_s;        // backward: [N, d/2] tables; when set, dQ and dK leave the kernel rotated back
+                                         // (the gradient of the RoPE that produced Q and K), which needs store mode
 };
 
 __device__ __forceinline__ int vis_len(int i, int prefix, int nb) {
@@ -89,6 +91,25 @@ __device__ __forceinline__ uint32_t use_parity(int t) { return (uint32_t)(t >> 1
 // products of tile t+1 never wait for the tensor core to finish reading tile t-1.
 __device__ __forceinline__ int buf3(int t) { return t % 3; }
 __device__ __forceinline__ uint32_t use_parity3(int t) { return (uint32_t)(t / 3) & 1u; }
+
+// Undoes the rotary embedding on 32 consecutive gradient columns [c0, c0+32) of position `pos`.
+template <int HD>
+__device__ __forceinline__ void unrotate32(uint32_t (&a)[32], const float *__restrict__ fc, const float *__restrict__ fs, int pos, int c0) {
+    const float4 *c4 = reinterpret_cast<const float4 *>(fc + (int64_t)pos * (HD / 2) + c0 / 2);
+    const float4 *s4 = reinterpret_cast<const float4 *>(fs + (int64_t)pos * (HD / 2) + c0 / 2);
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const float4 c = __ldg(c4 + q), s = __ldg(s4 + q);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int j = 8 * q + 2 * e;
+            float ox, oy;
+            rope_inv_pair(__uint_as_float(a[j]), __uint_as_float(a[j + 1]), cc[e], ss[e], ox, oy);
+            a[j] = __float_as_uint(ox); a[j + 1] = __float_as_uint(oy);
+        }
+    }
+}
 
 // Adds (or stores) 32 consecutive floats held in registers to a row in global memory.
 __device__ __forceinline__ void emit_row32(float *dst, const uint32_t (&a)[32], bool store) {
@@ -495,6 +516,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_co
                 tc_ld32(t_dk + lane_base + c0, c);
                 if (p.dv.p && key < nb)
                     emit_row32(p.dv.p + (int64_t)b * p.dv.sb + (int64_t)h * p.dv.sh + (int64_t)key * p.dv.sn + c0, a, (p.store & 4) != 0);
+                if (p.dk.p && key < nb && p.rope_c) unrotate32<HD>(c, p.rope_c, p.rope_s, key, c0);
                 if (p.dk.p && key < nb)
                     emit_row32(p.dk.p + (int64_t)b * p.dk.sb + (int64_t)h * p.dk.sh + (int64_t)key * p.dk.sn + c0, c, (p.store & 2) != 0);
             }
@@ -666,6 +688,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_con
             if (ok && c0 < HD) {
                 uint32_t a[32];
                 tc_ld32(t_dq + lane_base + c0, a);
+                if (live && p.rope_c) unrotate32<HD>(a, p.rope_c, p.rope_s, row, c0);
                 if (live) emit_row32(p.dq.p + (int64_t)b * p.dq.sb + (int64_t)h * p.dq.sh + (int64_t)row * p.dq.sn + c0, a, (p.store & 1) != 0);
             }
         }
@@ -717,6 +740,7 @@ struct AttnHost {
     HeadView q, k, v, o, dout, dq, dk, dv;
     float *lse; const float *dvec; const int *seq_lens;
     int B, H, N, d, prefix; float scale; int store;
+    const float *rope_c, *rope_s;
 };
 
 template <int HD>
@@ -738,6 +762,7 @@ static void bwd_launch(const AttnHost &a) {
     AttnTcParams p; memset(&p, 0, sizeof p);
     p.lse_in = a.lse; p.dvec = a.dvec; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.seq_lens = a.seq_lens;
     p.B = a.B; p.H = a.H; p.N = a.N; p.prefix = a.prefix; p.scale = a.scale; p.store = a.store;
+    p.rope_c = a.rope_c; p.rope_s = a.rope_s;
     static bool once = false;
     if (!once) {
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HD>::kSmem));
@@ -773,9 +798,11 @@ void attn_forward_tc(const HeadView &q, const HeadView &k, const HeadView &v, co
 
 void attn_backward_tc(const HeadView &q, const HeadView &k, const HeadView &v, const float *lse, const HeadView &dout, const float *dvec,
                       const HeadView &dq, const HeadView &dk, const HeadView &dv, const int *seq_lens,
-                      int B, int H, int N, int d, int prefix, float scale, int store) {
+                      int B, int H, int N, int d, int prefix, float scale, int store, const float *rope_c, const float *rope_s) {
     AttnHost a; memset(&a, 0, sizeof a);
     a.store = store;
+    DNN_CHECK(!rope_c || (store & 3) == 3, "attention backward: the fused rotation needs dQ and dK in store mode");
+    a.rope_c = rope_c; a.rope_s = rope_s;
     a.q = q; a.k = k; a.v = v; a.lse = (float *)lse; a.dout = dout; a.dvec = dvec; a.dq = dq; a.dk = dk; a.dv = dv; a.seq_lens = seq_lens;
     a.B = B; a.H = H; a.N = N; a.d = d; a.prefix = prefix; a.scale = scale;
     if (d == 32) bwd_launch<32>(a); else bwd_launch<64>(a);

@@ -30,8 +30,10 @@ __global__ void rope_kernel(float *__restrict__ dst, const float *__restrict__ g
         } else {
             float4 v = reinterpret_cast<const float4 *>(g)[i];
             float4 o = acc ? reinterpret_cast<float4 *>(dst)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-            o.x += v.x * c.x + v.y * s.x;  o.y += -v.x * s.x + v.y * c.x;
-            o.z += v.z * c.y + v.w * s.y;  o.w += -v.z * s.y + v.w * c.y;
+            float rx, ry, rz, rw;
+            rope_inv_pair(v.x, v.y, c.x, s.x, rx, ry);
+            rope_inv_pair(v.z, v.w, c.y, s.y, rz, rw);
+            o.x += rx; o.y += ry; o.z += rz; o.w += rw;
             reinterpret_cast<float4 *>(dst)[i] = o;
         }
     }
@@ -50,7 +52,8 @@ __global__ void rope_pair_kernel(float *__restrict__ dst, const float *__restric
             dst[2 * i] = a * c - b * s; dst[2 * i + 1] = a * s + b * c;
         } else {
             float a = g[2 * i], b = g[2 * i + 1];
-            float r0 = a * c + b * s, r1 = -a * s + b * c;
+            float r0, r1;
+            rope_inv_pair(a, b, c, s, r0, r1);
             if (acc) { r0 += dst[2 * i]; r1 += dst[2 * i + 1]; }
             dst[2 * i] = r0; dst[2 * i + 1] = r1;
         }
