@@ -489,8 +489,8 @@ __global__ void rope_qkv_kernel(float *__restrict__ qkv, const float *__restrict
         float2 sn = *reinterpret_cast<const float2 *>(fs + (int64_t)n * dh + 2 * quad);
         float4 v = *ptr, o;
         if (!BWD) {
-            o.x = v.x * c.x - v.y * sn.x; o.y = v.x * sn.x + v.y * c.x;
-            o.z = v.z * c.y - v.w * sn.y; o.w = v.z * sn.y + v.w * c.y;
+            rope_fwd_pair(v.x, v.y, c.x, sn.x, o.x, o.y);
+            rope_fwd_pair(v.z, v.w, c.y, sn.y, o.z, o.w);
         } else {
             rope_inv_pair(v.x, v.y, c.x, sn.x, o.x, o.y);
             rope_inv_pair(v.z, v.w, c.y, sn.y, o.z, o.w);
@@ -551,10 +551,24 @@ static void attention_qkv_backward(grad_fn *fn, tensor *go) {
     if (acc) k_axpy_acc(g_qkv, dst, numel);
 }
 
+// Whether a block with these sizes will take the fused path (asked before the QKV projection
+// runs, so that the projection's epilogue can apply the rotation).
+bool attention_from_qkv_applicable(const tensor *x, int H, int d, const tensor *fc, const tensor *fs) {
+    if (!fused_attention_enabled() || gemm_mode() != DNN_CUDA_GEMM_TF32) return false;
+    if (!x || x->ndim != 3 || H <= 0 || (d != 32 && d != 64)) return false;
+    if (fc && fs) {
+        if (!fc->contiguous || !fs->contiguous || fc->shape[0] < x->shape[1]) return false;
+        const float *a = (const float *)fc->data + fc->offset, *b = (const float *)fs->data + fs->offset;
+        if ((((uintptr_t)a | (uintptr_t)b) & 15) != 0) return false;
+    }
+    return true;
+}
+
 // Returns nullptr when the tensor-core path does not apply (mode, head size, layout); the
-// caller then runs the unfused op sequence.
+// caller then runs the unfused op sequence.  `rotated`: the projection that produced qkv has
+// already applied RoPE to its Q and K columns.
 tensor *attention_from_qkv(struct mem_pool *scratch, tensor *qkv, int H, tensor *fc, tensor *fs,
-                           attention_mode mode, int prefix_len, const int *seq_lens) {
+                           attention_mode mode, int prefix_len, const int *seq_lens, bool rotated) {
     if (!fused_attention_enabled() || gemm_mode() != DNN_CUDA_GEMM_TF32) return nullptr;
     if (!qkv || qkv->ndim != 3 || !qkv->contiguous || qkv->offset != 0 || qkv->parent) return nullptr;
     const int B = qkv->shape[0], N = qkv->shape[1], D3 = qkv->shape[2];
@@ -577,7 +591,7 @@ tensor *attention_from_qkv(struct mem_pool *scratch, tensor *qkv, int H, tensor 
     float *lse = needs_grad ? dev_alloc_t<float>(scratch, (size_t)B * H * N) : nullptr;
     const int *lens = seq_lens ? (const int *)dev_put(scratch, seq_lens, (size_t)B * sizeof(int)) : nullptr;
     const float scale = 1.0f / sqrtf((float)d);
-    if (fcd) rope_qkv(false, qd, fcd, fsd, B, N, H, d);
+    if (fcd && !rotated) rope_qkv(false, qd, fcd, fsd, B, N, H, d);
     attn_forward_tc(qkv_slice(qd, 0, N, H, d), qkv_slice(qd, 1, N, H, d), qkv_slice(qd, 2, N, H, d),
                     token_major((float *)out->data, N, H, d), lse, lens, B, H, N, d,
                     mode == ATTENTION_PREFIX_LM ? prefix_len : 0, scale);

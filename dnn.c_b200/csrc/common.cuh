@@ -85,7 +85,8 @@ inline HeadView packed_heads(const float *p, int H, int N, int d) {
 // Attention computed straight from the [B,N,3*H*d] output of a fused QKV projection (attention.cu).
 // Returns nullptr when the tensor-core path does not apply.
 tensor *attention_from_qkv(struct mem_pool *scratch, tensor *qkv, int H, tensor *fc, tensor *fs,
-                           attention_mode mode, int prefix_len, const int *seq_lens);
+                           attention_mode mode, int prefix_len, const int *seq_lens, bool rotated);
+bool attention_from_qkv_applicable(const tensor *x, int H, int d, const tensor *fc, const tensor *fs);
 
 // Gradient destinations.  The reference zero-fills every gradient buffer when it is created
 // and every backward adds to it.  Adding to zeros equals storing, so a buffer that is still
@@ -126,6 +127,13 @@ struct GemmArgs {
     bool accumulate;
 };
 void gemm(const GemmArgs &g);          // dispatches on gemm_mode() and layout
+
+// One-shot epilogue request for the next tensor-core GEMM on this thread: rotate (RoPE) the
+// pairs of the first `cols` output columns, which are heads of size d; row r is position r % N.
+// The GEMM that honours it clears it; gemm_rope_epilogue_take() tells whether that happened
+// (and clears a request nobody honoured, so that the caller can run the rotation itself).
+void gemm_rope_epilogue_request(const float *fc, const float *fs, int N, int d, int cols);
+bool gemm_rope_epilogue_take();
 void gemm_simt(const GemmArgs &g);
 bool gemm_tc_supported(const GemmArgs &g);
 void gemm_tc(const GemmArgs &g, bool split3);

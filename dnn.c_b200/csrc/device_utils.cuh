@@ -57,6 +57,11 @@ __device__ __forceinline__ float block_max(float v, float *sh) {
 }
 
 
+// Rotation of one RoPE pair (src/rope.c:60-112), roundings spelled out for the same reason as below.
+__device__ __forceinline__ void rope_fwd_pair(float x, float y, float c, float s, float &ox, float &oy) {
+    ox = __fmaf_rn(x, c, -__fmul_rn(y, s));
+    oy = __fmaf_rn(x, s, __fmul_rn(y, c));
+}
 // Inverse rotation of one RoPE pair (the gradient of src/rope.c:60-112).  Roundings are spelled
 // out so that every kernel that applies it -- the stand-alone RoPE backward, the in-place version
 // on a fused QKV gradient and the attention backward epilogues -- produces the same bits.

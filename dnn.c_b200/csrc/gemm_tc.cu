@@ -43,6 +43,8 @@ struct TcArgs {
     int tiles_m, tiles_n;
     int n_fastest;                     // tile order: consecutive work units walk along N (1) or along M (0)
     int a_chunked, b_chunked;          // MN-major operand described as {32, K, extent/32}: one TMA copy per stage
+    const float *rope_c, *rope_s;      // epilogue rotation of the first rope_cols columns (heads of rope_d, position = row % rope_N)
+    int rope_N, rope_d, rope_cols;
 };
 
 template <int BN, bool PAIR> struct TcCfg {
@@ -222,6 +224,23 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         for (int j = 0; j < 32; j++) if (col0 + j < g.N) v[j] += g.bias[col0 + j];
                     }
                 }
+                if (g.rope_c && col0 < g.rope_cols) {         // rope_cols, rope_d are multiples of 32: the chunk lies in one head
+                    const int pos = (row0 + lane) % g.rope_N, hc = col0 % g.rope_d;
+                    const float4 *c4 = reinterpret_cast<const float4 *>(g.rope_c + (int64_t)pos * (g.rope_d >> 1) + (hc >> 1));
+                    const float4 *s4 = reinterpret_cast<const float4 *>(g.rope_s + (int64_t)pos * (g.rope_d >> 1) + (hc >> 1));
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; q4++) {
+                        const float4 c = __ldg(c4 + q4), sn = __ldg(s4 + q4);
+                        const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int j = 8 * q4 + 2 * e;
+                            float ox, oy;
+                            rope_fwd_pair(v[j], v[j + 1], cc[e], ss[e], ox, oy);
+                            v[j] = ox; v[j + 1] = oy;
+                        }
+                    }
+                }
                 // the staging tile about to be written was handed to the copy engine two chunks ago
                 if (lane == 0) bulk_wait_read<1>();
                 __syncwarp();
@@ -384,6 +403,17 @@ bool gemm_tc_supported(const GemmArgs &in) {
     return (int64_t)g.M * g.N * g.K >= (int64_t)64 * 64 * 32;
 }
 
+struct RopeEpilogue { const float *fc, *fs; int N, d, cols; bool pending, honoured; };
+static thread_local RopeEpilogue g_rope = {nullptr, nullptr, 0, 0, 0, false, false};
+void gemm_rope_epilogue_request(const float *fc, const float *fs, int N, int d, int cols) {
+    g_rope.fc = fc; g_rope.fs = fs; g_rope.N = N; g_rope.d = d; g_rope.cols = cols; g_rope.pending = true; g_rope.honoured = false;
+}
+bool gemm_rope_epilogue_take() {
+    bool h = g_rope.honoured;
+    g_rope.pending = false; g_rope.honoured = false;
+    return h;
+}
+
 static float *g_scratch = nullptr;
 static size_t g_scratch_cap = 0;
 static float *scratch(size_t bytes) {
@@ -448,6 +478,12 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     t.kb_per_split = (num_kb + splits - 1) / splits;
     splits = (num_kb + t.kb_per_split - 1) / t.kb_per_split;
     t.splits = splits;
+    t.rope_c = t.rope_s = nullptr; t.rope_N = t.rope_d = t.rope_cols = 0;
+    if (g_rope.pending && splits == 1 && !g.accumulate && g.M % g_rope.N == 0 && g_rope.cols <= g.N &&
+        g_rope.cols % 32 == 0 && g_rope.d % 32 == 0 && (((uintptr_t)g_rope.fc | (uintptr_t)g_rope.fs) & 15) == 0) {
+        t.rope_c = g_rope.fc; t.rope_s = g_rope.fs; t.rope_N = g_rope.N; t.rope_d = g_rope.d; t.rope_cols = g_rope.cols;
+        g_rope.pending = false; g_rope.honoured = true;
+    }
     if (splits == 1) { t.C = g.C; t.ldc = g.c_rs; t.bias = g.bias; t.accumulate = g.accumulate ? 1 : 0; }
     else { t.C = scratch((size_t)splits * g.M * g.N * 4); t.ldc = g.N; t.bias = nullptr; t.accumulate = 0; }
     int units = tiles * splits;
@@ -499,6 +535,7 @@ void gemm_tc(const GemmArgs &in, bool split3) {
     bool ok = normalise(in, g);
     DNN_CHECK(ok, "gemm_tc called with an unsupported layout");
     if (!split3) { run_tc(g); return; }
+    g_rope.pending = false;            // an epilogue rotation cannot be split over the three partial products
     // 3xTF32: x = big + small with big exactly TF32; A*B ~= Ab*Bb + Ab*Bs + As*Bb, fp32 accumulation.
     int64_t a_inner = g.a_cs == 1 ? g.K : g.M, a_outer = g.a_cs == 1 ? g.M : g.K;
     int64_t b_inner = g.b_cs == 1 ? g.N : g.K, b_outer = g.b_cs == 1 ? g.K : g.N;

@@ -97,12 +97,21 @@ tensor *transformer_block_forward_ex(struct mem_pool *scratch, transformer_block
     DNN_CHECK(x->shape[x->ndim - 1] == block->d_model, "transformer_block_forward: last dim must be d_model");
     // attention sub-layer, pre-norm
     tensor *h = rms_norm_forward(scratch, block->attn_norm, x);
-    tensor *qkv = linear_forward(scratch, block->qkv_proj, h);
-    // Tensor-core path: attention reads Q, K, V in place from qkv and writes token-major output.
+    // Tensor-core path: attention reads Q, K, V in place from qkv and writes token-major output;
+    // the QKV projection applies RoPE to its Q and K columns in its epilogue.
     bool rope = block->freqs_cos && block->freqs_sin;
-    tensor *merged = qkv->ndim == 3 ? attention_from_qkv(scratch, qkv, block->n_heads, rope ? block->freqs_cos : nullptr,
-                                                         rope ? block->freqs_sin : nullptr, mode, prefix_len, seq_lens)
-                                    : nullptr;
+    bool fused = attention_from_qkv_applicable(h, block->n_heads, block->d_k, rope ? block->freqs_cos : nullptr,
+                                               rope ? block->freqs_sin : nullptr);
+    if (fused && rope)
+        gemm_rope_epilogue_request((const float *)block->freqs_cos->data + block->freqs_cos->offset,
+                                   (const float *)block->freqs_sin->data + block->freqs_sin->offset,
+                                   h->shape[1], block->d_k, 2 * block->n_heads * block->d_k);
+    tensor *qkv = linear_forward(scratch, block->qkv_proj, h);
+    bool rotated = gemm_rope_epilogue_take();
+    tensor *merged = fused ? attention_from_qkv(scratch, qkv, block->n_heads, rope ? block->freqs_cos : nullptr,
+                                                rope ? block->freqs_sin : nullptr, mode, prefix_len, seq_lens, rotated)
+                           : nullptr;
+    DNN_CHECK(merged || !rotated, "transformer_block_forward: the projection rotated Q and K but the fused attention path refused");
     if (!merged) {
         tensor *q, *k, *v;
         tensor_split_qkv_heads(scratch, qkv, block->n_heads, &q, &k, &v);

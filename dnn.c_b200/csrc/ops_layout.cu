@@ -24,8 +24,8 @@ __global__ void rope_kernel(float *__restrict__ dst, const float *__restrict__ g
         if (!BWD) {
             float4 v = reinterpret_cast<float4 *>(dst)[i];
             float4 o;
-            o.x = v.x * c.x - v.y * s.x; o.y = v.x * s.x + v.y * c.x;
-            o.z = v.z * c.y - v.w * s.y; o.w = v.z * s.y + v.w * c.y;
+            rope_fwd_pair(v.x, v.y, c.x, s.x, o.x, o.y);
+            rope_fwd_pair(v.z, v.w, c.y, s.y, o.z, o.w);
             reinterpret_cast<float4 *>(dst)[i] = o;
         } else {
             float4 v = reinterpret_cast<const float4 *>(g)[i];
@@ -49,7 +49,7 @@ __global__ void rope_pair_kernel(float *__restrict__ dst, const float *__restric
         float c = fc[(int64_t)n * dh + k], s = fs[(int64_t)n * dh + k];
         if (!BWD) {
             float a = dst[2 * i], b = dst[2 * i + 1];
-            dst[2 * i] = a * c - b * s; dst[2 * i + 1] = a * s + b * c;
+            rope_fwd_pair(a, b, c, s, dst[2 * i], dst[2 * i + 1]);
         } else {
             float a = g[2 * i], b = g[2 * i + 1];
             float r0, r1;

@@ -7,6 +7,8 @@
 // them: a CTA owns a fixed-size chunk of one tensor.  AdamW is HBM-bound at
 // 28 bytes per parameter (read p, g, m, v; write p, m, v).
 #include "common.cuh"
+#include <cstdio>
+#include <cstring>
 #include "device_utils.cuh"
 #include <vector>
 #include <algorithm>
@@ -183,6 +185,58 @@ adamw_opt *adamw_create(struct mem_pool *params_pool, tensor **params, int n_par
     return opt;
 }
 void adamw_free(adamw_opt *opt) { (void)opt; }
+
+// ── optimiser state files ────────────────────────────────────────────────
+// The reference saves weights only (module_save, src/module.c:208-268), so a run cannot be
+// resumed.  This file holds what is missing: magic "DNNO", u32 version = 1, u32 n_params,
+// i32 t, f32 lr, beta1, beta2, eps, weight_decay, then per parameter u32 numel, float m[numel],
+// float v[numel], in the optimiser's parameter order.  Together with module_save it restores a
+// run bit for bit (the kernels are deterministic).
+int dnn_cuda_optimizer_save(const adamw_opt *opt, const char *path) {
+    if (!opt || !path) return -1;
+    FILE *f = fopen(path, "wb");
+    if (!f) return -2;
+    uint32_t version = 1, n = (uint32_t)opt->n_params;
+    int32_t t = opt->t;
+    float hyper[5] = {opt->lr, opt->beta1, opt->beta2, opt->eps, opt->weight_decay};
+    bool ok = fwrite("DNNO", 1, 4, f) == 4 && fwrite(&version, 4, 1, f) == 1 && fwrite(&n, 4, 1, f) == 1 &&
+              fwrite(&t, 4, 1, f) == 1 && fwrite(hyper, 4, 5, f) == 5;
+    std::vector<float> host;
+    for (int i = 0; ok && i < opt->n_params; i++) {
+        uint32_t numel = (uint32_t)numel_of(opt->params[i]);
+        host.resize(numel);
+        ok = fwrite(&numel, 4, 1, f) == 1;
+        for (tensor *s : {opt->m[i], opt->v[i]}) {
+            ok = ok && dnn_cuda_download(s, host.data(), (size_t)numel * 4) == 0 && fwrite(host.data(), 4, numel, f) == numel;
+        }
+    }
+    ok = (fclose(f) == 0) && ok;
+    return ok ? 0 : -3;
+}
+
+// Loads into an optimiser created for the same parameters (count and sizes are checked).
+// Hyper-parameters come from the file as well, t included.
+int dnn_cuda_optimizer_load(adamw_opt *opt, const char *path) {
+    if (!opt || !path) return -1;
+    FILE *f = fopen(path, "rb");
+    if (!f) return -2;
+    char magic[4]; uint32_t version = 0, n = 0; int32_t t = 0; float hyper[5];
+    bool ok = fread(magic, 1, 4, f) == 4 && memcmp(magic, "DNNO", 4) == 0 && fread(&version, 4, 1, f) == 1 && version == 1 &&
+              fread(&n, 4, 1, f) == 1 && (int)n == opt->n_params && fread(&t, 4, 1, f) == 1 && fread(hyper, 4, 5, f) == 5;
+    std::vector<float> host;
+    for (int i = 0; ok && i < opt->n_params; i++) {
+        uint32_t numel = 0;
+        ok = fread(&numel, 4, 1, f) == 1 && (int64_t)numel == numel_of(opt->params[i]);
+        if (!ok) break;
+        host.resize(numel);
+        for (tensor *s : {opt->m[i], opt->v[i]})
+            ok = ok && fread(host.data(), 4, numel, f) == numel && dnn_cuda_upload(s, host.data(), (size_t)numel * 4) == 0;
+    }
+    fclose(f);
+    if (!ok) return -3;
+    opt->t = t; opt->lr = hyper[0]; opt->beta1 = hyper[1]; opt->beta2 = hyper[2]; opt->eps = hyper[3]; opt->weight_decay = hyper[4];
+    return 0;
+}
 
 // The reference memsets every parameter gradient here (src/optim.c:93-100).  The buffers are
 // only marked fresh: the first backward contribution of the step (a dW GEMM that covers the

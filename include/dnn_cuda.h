@@ -66,6 +66,15 @@ int  dnn_cuda_get_gemm_mode(void);
 void dnn_cuda_set_fused_attention(int on);
 int  dnn_cuda_get_fused_attention(void);
 
+/* Optimiser state on disk (AdamW moments m and v, step counter t, hyper-parameters).  The
+ * reference's state files hold weights only (module_save / module_load, src/module.c:208-339),
+ * so its runs cannot be resumed; module_save + dnn_cuda_optimizer_save written at the same step
+ * and loaded into a freshly created model and optimiser continue the run bit for bit.
+ * 0 on success; -1 bad argument, -2 cannot open, -3 I/O error or mismatch with `opt`.
+ * No counterpart in the reference. */
+int  dnn_cuda_optimizer_save(const adamw_opt *opt, const char *path);
+int  dnn_cuda_optimizer_load(adamw_opt *opt, const char *path);
+
 /* Device-side timing on the compute stream (CUDA events): start records an event,
  * stop records a second one, waits for it and returns the milliseconds between. */
 int   dnn_cuda_timer_start(void);
