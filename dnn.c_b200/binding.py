@@ -187,6 +187,9 @@ CUDA_API = {
     "dnn_cuda_host_free": (None, [VP]),
     "dnn_cuda_set_gemm_mode": (I, [I]),
     "dnn_cuda_get_gemm_mode": (I, []),
+    "dnn_cuda_graph_capture_decoder_lm_step": (VP, [PoolP, VP, TensorP, TensorP, C.POINTER(AdamW), F]),
+    "dnn_cuda_graph_replay": (I, [VP, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "dnn_cuda_graph_destroy": (None, [VP]),
     "dnn_cuda_optimizer_save": (I, [C.POINTER(AdamW), C.c_char_p]),
     "dnn_cuda_optimizer_load": (I, [C.POINTER(AdamW), C.c_char_p]),
     "dnn_cuda_set_fused_attention": (None, [I]),

@@ -25,6 +25,7 @@ void cuda_fail(cudaError_t e, const char *what, const char *file, int line);
 cudaStream_t stream();
 // Counts one kernel launch and checks the launch error.
 void launched(const char *name);
+void add_launches(long long n);
 #define LAUNCHED(name) ::dnnb::launched(name)
 
 // Device allocation from the arena attached to `pool` (256-byte aligned).
@@ -87,6 +88,14 @@ inline HeadView packed_heads(const float *p, int H, int N, int d) {
 tensor *attention_from_qkv(struct mem_pool *scratch, tensor *qkv, int H, tensor *fc, tensor *fs,
                            attention_mode mode, int prefix_len, const int *seq_lens, bool rotated);
 bool attention_from_qkv_applicable(const tensor *x, int H, int d, const tensor *fc, const tensor *fs);
+
+// Optimiser tail of a captured training step (optim.cu).
+struct OptGraph;
+OptGraph *opt_graph_prepare(adamw_opt *opt, float grad_clip);
+void opt_graph_launch(OptGraph *og, adamw_opt *opt);
+void opt_graph_advance(OptGraph *og, adamw_opt *opt);
+const float *opt_graph_norm(const OptGraph *og);
+void opt_graph_destroy(OptGraph *og);
 
 // Gradient destinations.  The reference zero-fills every gradient buffer when it is created
 // and every backward adds to it.  Adding to zeros equals storing, so a buffer that is still

@@ -221,6 +221,73 @@ tensor *dnn_cuda_dp_decoder_lm_train_step(struct mem_pool *scratch, decoder_lm *
     return lm_step(scratch, lm, input_ids, target, opt, grad_clip, grad_norm_out, dnn_cuda_dp_world_size() > 1);
 }
 
+// ── whole-step CUDA graph ────────────────────────────────────────────────
+// The step's kernels, memsets and copies are recorded once with stream capture and replayed as
+// one graph launch.  That works because nothing in a step depends on host values that change:
+// the pools hand out the same addresses every time, the tape is only needed while recording, and
+// the optimiser tail reads learning rate and bias corrections from device memory (optim.cu).
+struct dnn_cuda_step_graph {
+    cudaGraph_t graph; cudaGraphExec_t exec;
+    OptGraph *og; adamw_opt *opt; tensor *loss;
+    long long kernels;          // kernel launches recorded in the graph
+};
+
+dnn_cuda_step_graph *dnn_cuda_graph_capture_decoder_lm_step(struct mem_pool *scratch, decoder_lm *lm, const tensor *input_ids,
+                                                            const tensor *target, adamw_opt *opt, float grad_clip) {
+    DNN_CHECK(lm && input_ids && target && opt, "graph capture: NULL argument");
+    DNN_CHECK(input_ids->ndim == 2 && input_ids->contiguous && input_ids->shape[1] >= 2, "graph capture: input_ids must be contiguous [B, N >= 2]");
+    DNN_CHECK(dnn_cuda_dp_world_size() <= 1, "graph capture: not available with data parallelism");
+    CUDA_OK(cudaStreamSynchronize(stream()));
+    dnn_cuda_step_graph *sg = new dnn_cuda_step_graph();
+    sg->opt = opt;
+    sg->og = opt_graph_prepare(opt, grad_clip);
+    const int N = input_ids->shape[1];
+    const long long launches_before = dnn_cuda_launch_count();
+    cudaError_t e = cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal);
+    DNN_CHECK(e == cudaSuccess, "graph capture: cudaStreamBeginCapture failed");
+    adamw_zero_grad(opt);
+    tensor *logits = decoder_lm_forward(scratch, lm, input_ids);
+    tensor *shifted = tensor_slice(scratch, logits, 1, 0, N - 1);
+    sg->loss = tensor_cross_entropy(scratch, shifted, target, 2);
+    dnn_backward(scratch, sg->loss);
+    opt_graph_launch(sg->og, opt);
+    e = cudaStreamEndCapture(stream(), &sg->graph);
+    sg->kernels = dnn_cuda_launch_count() - launches_before;
+    add_launches(-sg->kernels);                      // recorded, not run
+    if (e != cudaSuccess || !sg->graph) {
+        // typically a buffer that had to grow while recording: one eager step of the same shapes first
+        fprintf(stderr, "dnn_b200: step graph capture failed (%s); run one eager training step of the same shapes before capturing\n",
+                cudaGetErrorString(e));
+        cudaGetLastError();
+        opt_graph_destroy(sg->og);
+        delete sg;
+        return nullptr;
+    }
+    e = cudaGraphInstantiate(&sg->exec, sg->graph, 0);
+    DNN_CHECK(e == cudaSuccess, "graph capture: cudaGraphInstantiate failed");
+    return sg;
+}
+
+int dnn_cuda_graph_replay(dnn_cuda_step_graph *sg, float *loss_out, float *grad_norm_out) {
+    if (!sg) return -1;
+    opt_graph_advance(sg->og, sg->opt);
+    if (cudaGraphLaunch(sg->exec, stream()) != cudaSuccess) return -2;
+    add_launches(sg->kernels);
+    int rc = 0;
+    if (loss_out) rc |= dnn_cuda_memcpy_d2h(loss_out, (const float *)sg->loss->data + sg->loss->offset, sizeof(float));
+    if (grad_norm_out) rc |= dnn_cuda_memcpy_d2h(grad_norm_out, opt_graph_norm(sg->og), sizeof(float));
+    return rc;
+}
+
+void dnn_cuda_graph_destroy(dnn_cuda_step_graph *sg) {
+    if (!sg) return;
+    cudaStreamSynchronize(stream());
+    if (sg->exec) cudaGraphExecDestroy(sg->exec);
+    if (sg->graph) cudaGraphDestroy(sg->graph);
+    opt_graph_destroy(sg->og);
+    delete sg;
+}
+
 void decoder_lm_enable_rope(struct mem_pool *pool, decoder_lm *lm, int max_seq_len, float base) {
     DNN_CHECK(lm && max_seq_len > 0, "enable_rope: bad argument");
     int d_k = lm->blocks[0]->d_k;

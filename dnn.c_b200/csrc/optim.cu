@@ -96,6 +96,48 @@ struct OptScratch { TensorRef *tab = nullptr; size_t tab_cap = 0; double *partia
                     float *norm = nullptr; double *sq = nullptr; };
 static OptScratch g_os;
 
+// ── variants for a captured step ─────────────────────────────────────────
+// A CUDA graph bakes kernel arguments in, so what changes from step to step (learning rate,
+// bias corrections) is read from a small device struct that the graph refreshes from pinned
+// host memory, and the clipping decision is taken on the device from the norm just computed.
+struct StepState { float lr, bc1, bc2_sqrt, max_norm; };
+
+__global__ void __launch_bounds__(256) scale_dev_kernel(const TensorRef *__restrict__ tab, int nt, const float *__restrict__ norm,
+                                                        const StepState *__restrict__ st) {
+    const float total = norm[0], max_norm = st->max_norm;
+    if (!(max_norm > 0.0f) || !(total > max_norm)) return;          // same rule as clip_grad_norm: no scaling at or below the bound
+    const float scale = max_norm / total;
+    int t = find_tensor(tab, nt, blockIdx.x);
+    TensorRef r = tab[t];
+    int64_t start = (int64_t)(blockIdx.x - r.first_chunk) * kChunk;
+    int64_t end = start + kChunk < r.n ? start + kChunk : r.n;
+    for (int64_t i = start + threadIdx.x; i < end; i += 256) r.g[i] *= scale;
+}
+// TensorRef.lr holds the per-tensor multiplier here; the step's learning rate comes from the state
+__global__ void __launch_bounds__(256) adamw_dev_kernel(const TensorRef *__restrict__ tab, int nt, AdamHyper h0,
+                                                        const StepState *__restrict__ st) {
+    AdamHyper h = h0;
+    h.bc1 = st->bc1; h.bc2_sqrt = st->bc2_sqrt;
+    int t = find_tensor(tab, nt, blockIdx.x);
+    TensorRef r = tab[t];
+    r.lr = st->lr * r.lr;
+    int64_t start = (int64_t)(blockIdx.x - r.first_chunk) * kChunk;
+    int64_t end = start + kChunk < r.n ? start + kChunk : r.n;
+    float step = r.lr / h.bc1;
+    bool vec = ((((uintptr_t)r.p | (uintptr_t)r.g | (uintptr_t)r.m | (uintptr_t)r.v) & 15) == 0);
+    if (vec) {
+        int64_t e4 = start + ((end - start) & ~(int64_t)3);
+        for (int64_t i = start + threadIdx.x * 4; i < e4; i += 1024) {
+            float4 p = *(float4 *)(r.p + i), g = *(const float4 *)(r.g + i), m = *(float4 *)(r.m + i), v = *(float4 *)(r.v + i);
+            adam1(p.x, m.x, v.x, g.x, r.lr, step, h); adam1(p.y, m.y, v.y, g.y, r.lr, step, h);
+            adam1(p.z, m.z, v.z, g.z, r.lr, step, h); adam1(p.w, m.w, v.w, g.w, r.lr, step, h);
+            *(float4 *)(r.p + i) = p; *(float4 *)(r.m + i) = m; *(float4 *)(r.v + i) = v;
+        }
+        start = e4;
+    }
+    for (int64_t i = start + threadIdx.x; i < end; i += 256) adam1(r.p[i], r.m[i], r.v[i], r.g[i], r.lr, step, h);
+}
+
 static int upload_table(std::vector<TensorRef> &tab) {
     int chunks = 0;
     for (auto &r : tab) { r.first_chunk = chunks; chunks += (int)((r.n + kChunk - 1) / kChunk); }
@@ -295,6 +337,79 @@ void adamw_step_with_lr_multipliers(adamw_opt *opt, const float *lr_mults) {
     prof_end(1, bytes);
 }
 void adamw_step(adamw_opt *opt) { adamw_step_with_lr_multipliers(opt, nullptr); }
+
+}  // extern "C"
+
+namespace dnnb {
+
+// Optimiser tail of a captured step: its own tables and reduction buffers (the eager path's are
+// re-uploaded on every call, which a graph cannot replay), a device StepState and its pinned
+// host copy.
+struct OptGraph {
+    TensorRef *tab = nullptr; int nt = 0, chunks = 0;
+    double *partial = nullptr, *sq = nullptr; float *norm = nullptr;
+    StepState *state_dev = nullptr, *state_host = nullptr;
+    AdamHyper h;
+};
+
+// Outside capture.  Every parameter must already own a gradient buffer (one eager step has run).
+OptGraph *opt_graph_prepare(adamw_opt *opt, float grad_clip) {
+    OptGraph *og = new OptGraph();
+    std::vector<TensorRef> tab;
+    int chunks = 0;
+    for (int i = 0; i < opt->n_params; i++) {
+        tensor *p = opt->params[i];
+        if (!p->grad) continue;
+        TensorRef r;
+        r.p = tensor_data_ptr(p); r.g = p->grad; r.m = tensor_data_ptr(opt->m[i]); r.v = tensor_data_ptr(opt->v[i]);
+        r.n = numel_of(p); r.lr = 1.0f; r.first_chunk = chunks;
+        if (r.n <= 0) continue;
+        chunks += (int)((r.n + kChunk - 1) / kChunk);
+        tab.push_back(r);
+    }
+    DNN_CHECK(!tab.empty(), "step graph: no parameter has a gradient yet; run one eager step first");
+    og->nt = (int)tab.size(); og->chunks = chunks;
+    CUDA_OK(cudaMalloc((void **)&og->tab, tab.size() * sizeof(TensorRef)));
+    CUDA_OK(cudaMemcpy(og->tab, tab.data(), tab.size() * sizeof(TensorRef), cudaMemcpyHostToDevice));
+    CUDA_OK(cudaMalloc((void **)&og->partial, (size_t)chunks * sizeof(double)));
+    CUDA_OK(cudaMalloc((void **)&og->sq, sizeof(double)));
+    CUDA_OK(cudaMalloc((void **)&og->norm, sizeof(float)));
+    CUDA_OK(cudaMalloc((void **)&og->state_dev, sizeof(StepState)));
+    CUDA_OK(cudaMallocHost((void **)&og->state_host, sizeof(StepState)));
+    og->h.b1 = opt->beta1; og->h.b2 = opt->beta2; og->h.eps = opt->eps; og->h.wd = opt->weight_decay; og->h.bc1 = og->h.bc2_sqrt = 1.0f;
+    og->state_host->max_norm = grad_clip;
+    return og;
+}
+// Inside capture, after backward: norm, clip, AdamW.
+void opt_graph_launch(OptGraph *og, adamw_opt *opt) {
+    for (int i = 0; i < opt->n_params; i++) if (opt->params[i]->grad) grad_settle(opt->params[i]);
+    CUDA_OK(cudaMemcpyAsync(og->state_dev, og->state_host, sizeof(StepState), cudaMemcpyHostToDevice, stream()));
+    sumsq_kernel<<<og->chunks, 256, 0, stream()>>>(og->tab, og->nt, og->partial);
+    LAUNCHED("grad_sumsq_kernel");
+    sumsq_final_kernel<<<1, 1024, 0, stream()>>>(og->partial, og->chunks, og->norm, og->sq);
+    LAUNCHED("grad_sumsq_final_kernel");
+    scale_dev_kernel<<<og->chunks, 256, 0, stream()>>>(og->tab, og->nt, og->norm, og->state_dev);
+    LAUNCHED("grad_scale_kernel");
+    adamw_dev_kernel<<<og->chunks, 256, 0, stream()>>>(og->tab, og->nt, og->h, og->state_dev);
+    LAUNCHED("adamw_kernel");
+}
+// Before every replay: the step counter moves on the host, the graph reads the derived numbers.
+void opt_graph_advance(OptGraph *og, adamw_opt *opt) {
+    opt->t++;
+    og->state_host->lr = opt->lr;
+    og->state_host->bc1 = 1.0f - powf(opt->beta1, (float)opt->t);
+    og->state_host->bc2_sqrt = sqrtf(1.0f - powf(opt->beta2, (float)opt->t));
+}
+const float *opt_graph_norm(const OptGraph *og) { return og->norm; }
+void opt_graph_destroy(OptGraph *og) {
+    if (!og) return;
+    cudaFree(og->tab); cudaFree(og->partial); cudaFree(og->sq); cudaFree(og->norm); cudaFree(og->state_dev); cudaFreeHost(og->state_host);
+    delete og;
+}
+
+}  // namespace dnnb
+
+extern "C" {
 
 lr_scheduler *lr_scheduler_create(struct mem_pool *params_pool, adamw_opt *opt, int schedule, float base_lr,
                                   int warmup_iters, int total_iters, float min_lr, int step_size, float gamma) {

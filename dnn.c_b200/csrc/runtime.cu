@@ -85,6 +85,9 @@ void launched(const char *name) {
     }
 }
 
+// kernels that ran (or, negative, were only recorded) without passing through launched()
+void add_launches(long long n) { g_rt.launches += n; }
+
 int gemm_mode() { return g_rt.gemm_mode; }
 
 // ---- profiling ------------------------------------------------------------------

@@ -75,6 +75,24 @@ int  dnn_cuda_get_fused_attention(void);
 int  dnn_cuda_optimizer_save(const adamw_opt *opt, const char *path);
 int  dnn_cuda_optimizer_load(adamw_opt *opt, const char *path);
 
+/* Whole training step as one CUDA graph.  capture records zero_grad + forward + cross entropy +
+ * backward + gradient clipping + AdamW of decoder_lm_train_step (src/gpt.c:178-216) on the
+ * given tensors WITHOUT running it; replay runs the recorded step: it advances opt->t, uses the
+ * current opt->lr (so lr_scheduler_step between replays works), and, where asked, copies the loss
+ * and the pre-clip gradient norm back (that copy waits for the step).
+ * Rules: run at least one eager decoder_lm_train_step of the same shapes first (buffers that grow
+ * on demand must have their final size, parameters must own gradient buffers); new batches are
+ * written into the SAME input_ids / target tensors with dnn_cuda_upload; the scratch pool may be
+ * reset and used between replays, but not while a replay is in flight; data-parallel runs are not
+ * captured.  capture returns NULL with a message when recording fails.  Results equal the eager
+ * step bit for bit.  No counterpart in the reference (whose ops run synchronously on the host). */
+typedef struct dnn_cuda_step_graph dnn_cuda_step_graph;
+dnn_cuda_step_graph *dnn_cuda_graph_capture_decoder_lm_step(struct mem_pool *scratch_pool, decoder_lm *lm,
+                                                            const tensor *input_ids, const tensor *target,
+                                                            adamw_opt *opt, float grad_clip);
+int  dnn_cuda_graph_replay(dnn_cuda_step_graph *g, float *loss_out, float *grad_norm_out);
+void dnn_cuda_graph_destroy(dnn_cuda_step_graph *g);
+
 /* Device-side timing on the compute stream (CUDA events): start records an event,
  * stop records a second one, waits for it and returns the milliseconds between. */
 int   dnn_cuda_timer_start(void);
