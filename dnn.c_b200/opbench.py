@@ -181,6 +181,46 @@ def main():
         b.run(name, lambda: dict(q=b.dev(randn(Bt, H, T, D), True), k=b.dev(randn(Bt, H, T, D), True), v=b.dev(randn(Bt, H, T, D), True)),
               lambda i, mode=mode, prefix=prefix, lp=lp: lib.tensor_attention_ex(d.scratch, i["q"], i["k"], i["v"], None, mode, prefix, lp),
               (Bt, H, T, D), flop, 2 * flop, "tensor")
+    if "step_graph" in ops:
+        # BASELINE config 1 (V 256, d 128, 4 blocks, 4 heads, FFN 512, batch 16 x 128): kernels of a
+        # few microseconds, so the step is bound by launch overhead; eager steps against replays of
+        # the recorded step, wall time per step including the loss read-back
+        import time
+        V, D, L, H, F, Bsz, N = 256, 128, 4, 4, 512, 16, 128
+        lm = lib.decoder_lm_create(d.params, V, D, L, H, D // H, F)
+        lib.decoder_lm_enable_rope(d.params, lm, N, 10000.0)
+        lib.dnn_seed(4); lib.decoder_lm_init_weights(lm)
+        params = d.parameters(lm)
+        arr = (B.TensorP * len(params))(*params)
+        opt = lib.adamw_create(d.params, arr, len(params), 3e-4, 0.9, 0.95, 1e-8, 0.1)
+        ids = d.tensor(rng.integers(0, V, size=(Bsz, N)).astype(np.int32), d.params)
+        tgt = lib.decoder_lm_shift_targets(d.params, ids)
+        gn = C.c_float(0)
+
+        def eager():
+            loss = lib.decoder_lm_train_step(d.scratch, lm, ids, tgt, opt, 1.0, C.byref(gn))
+            v = d.scalar(loss); d.reset_step(); return v
+        for _ in range(5):
+            eager()
+        before = lib.dnn_cuda_launch_count()
+        t0 = time.perf_counter()
+        for _ in range(50):
+            eager()
+        ms_eager = (time.perf_counter() - t0) * 1e3 / 50
+        per_step = (lib.dnn_cuda_launch_count() - before) // 50
+        g = lib.dnn_cuda_graph_capture_decoder_lm_step(d.scratch, lm, ids, tgt, opt, 1.0)
+        loss = C.c_float(0)
+        for _ in range(5):
+            lib.dnn_cuda_graph_replay(g, C.byref(loss), None)
+        t0 = time.perf_counter()
+        for _ in range(50):
+            lib.dnn_cuda_graph_replay(g, C.byref(loss), None)
+        ms_graph = (time.perf_counter() - t0) * 1e3 / 50
+        lib.dnn_cuda_graph_destroy(g)
+        print(json.dumps({"op": "step_graph", "workload": "decoder LM config 1 (V256 d128 L4 H4 F512, 16x128 tokens)",
+                          "kernels_per_step": int(per_step), "eager_ms_per_step": round(ms_eager, 3), "graph_ms_per_step": round(ms_graph, 3),
+                          "eager_tokens_per_s": round(Bsz * N / ms_eager * 1e3), "graph_tokens_per_s": round(Bsz * N / ms_graph * 1e3),
+                          "speedup": round(ms_eager / ms_graph, 2)}), flush=True)
     if want("adamw"):
         P = (16 if args.small else 124) * 1000 * 1000
         t = lib.tensor_zeros(d.params, 1, B.ints([P]), 1)
