@@ -118,6 +118,18 @@ API = {
     "tensor_relu": (TensorP, [PoolP, TensorP]),
     "tensor_silu": (TensorP, [PoolP, TensorP]),
     "tensor_swiglu": (TensorP, [PoolP, TensorP, TensorP]),
+    "tensor_sub": (TensorP, [PoolP, TensorP, TensorP]),
+    "tensor_mul": (TensorP, [PoolP, TensorP, TensorP]),
+    "tensor_div": (TensorP, [PoolP, TensorP, TensorP]),
+    "tensor_neg": (TensorP, [PoolP, TensorP]),
+    "tensor_pow": (TensorP, [PoolP, TensorP, F]),
+    "tensor_triu": (TensorP, [PoolP, I, I]),
+    "tensor_sigmoid": (TensorP, [PoolP, TensorP]),
+    "tensor_softmax": (TensorP, [PoolP, TensorP, I]),
+    "tensor_causal_softmax": (TensorP, [PoolP, TensorP]),
+    "tensor_dropout": (TensorP, [PoolP, TensorP, F]),
+    "tensor_sum": (TensorP, [PoolP, TensorP, I]),
+    "tensor_mean": (TensorP, [PoolP, TensorP, I]),
     "tensor_cross_entropy": (TensorP, [PoolP, TensorP, TensorP, I]),
     "tensor_cross_entropy_masked": (TensorP, [PoolP, TensorP, TensorP, TensorP, I]),
     "tensor_embedding": (TensorP, [PoolP, TensorP, TensorP]),

@@ -4,6 +4,8 @@
 // replaces src/ops_elem.c:18-175,660-945 and src/ops_activation.c:14-333.
 #include "common.cuh"
 #include "device_utils.cuh"
+#include <vector>
+#include <cstdio>
 
 namespace dnnb {
 
@@ -269,6 +271,231 @@ static void swiglu_backward(grad_fn *fn, tensor *go) {
     if (bg) { tmp.data = due; tmp.offset = 0; bcast_reduce_into(up, bg, &tmp, acc_u); }
 }
 
+
+// ══════════ the rest of the element-wise / reduction surface of ops.h ══════════
+// sub, mul, div (broadcasting), neg, pow, sigmoid, sum, mean, softmax, causal_softmax, dropout,
+// triu.  None of them is on the training path of the models; they are simple, correct, HBM-bound
+// kernels that keep the reference's semantics (src/ops_elem.c:178-680, src/ops_reduce.c,
+// src/ops_activation.c:70-130,300-800,1410-1500).
+
+enum { BIN_SUB = 0, BIN_MUL = 1, BIN_DIV = 2 };
+struct BinF {
+    float *o; const float *a, *b; View va, vb; int op;
+    __device__ void operator()(int64_t i) const {
+        float x = a[voff(va, i)], y = b[voff(vb, i)];
+        o[i] = op == BIN_SUB ? x - y : op == BIN_MUL ? x * y : x / y;
+    }
+};
+// per-element operand gradients in the OUTPUT shape (reduced over broadcast dims afterwards)
+struct BinB {
+    float *da, *db; const float *a, *b, *g; View va, vb; int op;
+    __device__ void operator()(int64_t i) const {
+        float x = a[voff(va, i)], y = b[voff(vb, i)], gg = g[i];
+        if (op == BIN_SUB) { if (da) da[i] = gg; if (db) db[i] = -gg; }
+        else if (op == BIN_MUL) { if (da) da[i] = y * gg; if (db) db[i] = x * gg; }
+        else { if (da) da[i] = (1.0f / y) * gg; if (db) db[i] = (-x / (y * y)) * gg; }
+    }
+};
+
+template <int OP>
+static void binary_backward(grad_fn *fn, tensor *go) {
+    tensor *a = fn->inputs[0], *b = fn->inputs[1];
+    if ((OP == BIN_SUB || OP == BIN_DIV) && a == b) {          // d(a-a) = d(a/a) = 0 (src/ops_elem.c:183-188,395-399)
+        if (a->requires_grad && !a->grad_fn) _grad_ensure(a);
+        return;
+    }
+    int64_t n = numel_of(go);
+    const float *gd = (const float *)go->data + go->offset;
+    bool na = wants_grad(a), nb = wants_grad(b);
+    if (!na && !nb) return;
+    float *dae = na ? dev_alloc_t<float>(fn->pool, (size_t)n) : nullptr, *dbe = nb ? dev_alloc_t<float>(fn->pool, (size_t)n) : nullptr;
+    ew_launch("binary_bwd_kernel", n, BinB{dae, dbe, (const float *)a->data, (const float *)b->data, gd,
+                                           bcast_view(a, go->ndim, go->shape), bcast_view(b, go->ndim, go->shape), OP});
+    tensor tmp = *go;
+    tmp.offset = 0;
+    tensor *ops[2] = {a, b}; float *parts[2] = {dae, dbe};
+    for (int k = 0; k < 2; k++) {
+        if (!parts[k]) continue;
+        tensor *t = ops[k];
+        float *tg = _grad_ensure(t);
+        tmp.data = parts[k];
+        if (grad_contig(t, go)) k_axpy_acc(tg + t->offset, parts[k], n);
+        else bcast_reduce_into(t, tg, &tmp, true);
+    }
+}
+
+template <int OP>
+static tensor *binary_forward(struct mem_pool *scratch, const tensor *a, const tensor *b, const char *name) {
+    DNN_CHECK(a && b, "binary op: NULL operand");
+    int shape[DNN_MAX_DIMS];
+    int nd = bcast_shape(a->ndim, a->shape, b->ndim, b->shape, shape);
+    if (nd <= 0) { fprintf(stderr, "%s: incompatible shapes\n", name); abort(); }
+    tensor *out = tensor_scratch(scratch, nd, shape, 0);
+    ew_launch("binary_fwd_kernel", numel_of(out), BinF{(float *)out->data, (const float *)a->data, (const float *)b->data,
+                                                       bcast_view(a, nd, shape), bcast_view(b, nd, shape), OP});
+    if (dnn_grad_enabled() && (a->requires_grad || b->requires_grad)) {
+        grad_fn *fn = attach(scratch, out, binary_backward<OP>, 2, 0);
+        fn->inputs[0] = (tensor *)a; fn->inputs[1] = (tensor *)b;
+    }
+    return out;
+}
+
+// ---- unary: neg, pow, sigmoid ----
+enum { UN_NEG = 0, UN_POW = 1, UN_SIGMOID = 2 };
+struct UnF { float *o; const float *x; View vx; int op; float e;
+    __device__ void operator()(int64_t i) const {
+        float v = x[voff(vx, i)];
+        o[i] = op == UN_NEG ? -v : op == UN_POW ? powf(v, e) : 1.0f / (1.0f + expf(-v));
+    } };
+// dx[view(i)] += f'(.) * g[i]; `y` is the saved output for sigmoid
+struct UnB { float *dx; const float *x, *y, *g; View vx; int op; float e;
+    __device__ void operator()(int64_t i) const {
+        int64_t o = voff(vx, i);
+        float d;
+        if (op == UN_NEG) d = -g[i];
+        else if (op == UN_POW) d = e * powf(x[o], e - 1.0f) * g[i];
+        else { float sg = y[i]; d = sg * (1.0f - sg) * g[i]; }
+        dx[o] += d;
+    } };
+struct UnSaved { int op; float e; tensor *out; };
+static void unary_backward(grad_fn *fn, tensor *go) {
+    tensor *a = fn->inputs[0];
+    if (!wants_grad(a)) return;
+    UnSaved *sv = (UnSaved *)fn->saved_tensors[0];
+    float *ag = _grad_ensure(a);
+    // a view whose elements alias (broadcast strides) would race on +=; views of this library never do
+    ew_launch("unary_bwd_kernel", numel_of(a), UnB{ag, (const float *)a->data, sv->out ? (const float *)sv->out->data : nullptr,
+                                                   (const float *)go->data + go->offset, view_of(a), sv->op, sv->e});
+}
+static tensor *unary_forward(struct mem_pool *scratch, const tensor *t, int op, float e) {
+    DNN_CHECK(t, "unary op: NULL input");
+    tensor *out = tensor_scratch(scratch, t->ndim, t->shape, 0);
+    ew_launch("unary_fwd_kernel", numel_of(t), UnF{(float *)out->data, (const float *)t->data, view_of(t), op, e});
+    if (dnn_grad_enabled() && t->requires_grad) {
+        grad_fn *fn = attach(scratch, out, unary_backward, 1, 1);
+        fn->inputs[0] = (tensor *)t;
+        UnSaved *sv = host_alloc_t<UnSaved>(scratch);
+        sv->op = op; sv->e = e; sv->out = op == UN_SIGMOID ? out : nullptr;
+        fn->saved_tensors[0] = (tensor *)sv;
+    }
+    return out;
+}
+
+// ---- sum over one dim (keepdim) ----
+// input viewed as [outer, D, inner] (through the view for non-contiguous inputs); one thread per output
+struct SumF { float *o; const float *x; View vx; int D; int64_t inner;
+    __device__ void operator()(int64_t i) const {
+        int64_t oi = i / inner, in = i - oi * inner;
+        float s = 0.f;
+        for (int k = 0; k < D; k++) s += x[voff(vx, (oi * D + k) * inner + in)];
+        o[i] = s;
+    } };
+struct SumB { float *dx; const float *g; View vx; int D; int64_t inner;
+    __device__ void operator()(int64_t i) const {          // i over the INPUT elements
+        int64_t oi = i / (D * inner), in = i % inner;
+        dx[voff(vx, i)] += g[oi * inner + in];
+    } };
+static void sum_backward(grad_fn *fn, tensor *go) {
+    tensor *t = fn->inputs[0];
+    if (!wants_grad(t)) return;
+    int dim = *(int *)fn->saved_tensors[0];
+    int64_t inner = 1;
+    for (int d = dim + 1; d < t->ndim; d++) inner *= t->shape[d];
+    float *tg = _grad_ensure(t);
+    ew_launch("sum_bwd_kernel", numel_of(t), SumB{tg, (const float *)go->data + go->offset, view_of(t), t->shape[dim], inner});
+}
+
+// ---- softmax over one dim / causal softmax over the last dim ----
+// one warp per slice; a slice is D elements `inner` apart in the packed [outer, D, inner] input
+__global__ void softmax_fwd_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t slices, int D, int64_t inner, int causal_n) {
+    int lane = threadIdx.x & 31;
+    int64_t s = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (s >= slices) return;
+    int64_t oi = s / inner, in = s - oi * inner;
+    const float *xs = x + oi * D * inner + in;
+    float *ys = y + oi * D * inner + in;
+    int len = causal_n ? (int)(s % causal_n) + 1 : D;          // causal: row i sees columns 0..i
+    float m = -INFINITY;
+    for (int k = lane; k < len; k += 32) m = fmaxf(m, xs[k * inner]);
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int k = lane; k < len; k += 32) sum += expf(xs[k * inner] - m);
+    sum = warp_sum(sum);
+    for (int k = lane; k < D; k += 32) ys[k * inner] = k < len ? expf(xs[k * inner] - m) / sum : 0.f;
+}
+// dx = y * (g - sum(y*g)) over the slice
+__global__ void softmax_bwd_kernel(const float *__restrict__ y, const float *__restrict__ g, float *__restrict__ d,
+                                   int64_t slices, int D, int64_t inner, int causal_n) {
+    int lane = threadIdx.x & 31;
+    int64_t s = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (s >= slices) return;
+    int64_t oi = s / inner, in = s - oi * inner, base = oi * D * inner + in;
+    int len = causal_n ? (int)(s % causal_n) + 1 : D;
+    float dot = 0.f;
+    for (int k = lane; k < len; k += 32) dot += y[base + k * inner] * g[base + k * inner];
+    dot = warp_sum(dot);
+    for (int k = lane; k < D; k += 32) d[base + k * inner] = k < len ? y[base + k * inner] * (g[base + k * inner] - dot) : 0.f;
+}
+struct SoftSaved { tensor *out; int dim; int causal_n; };
+static void softmax_backward(grad_fn *fn, tensor *go) {
+    tensor *a = fn->inputs[0];
+    if (!wants_grad(a)) return;
+    SoftSaved *sv = (SoftSaved *)fn->saved_tensors[0];
+    int64_t n = numel_of(a), inner = 1;
+    for (int d = sv->dim + 1; d < a->ndim; d++) inner *= a->shape[d];
+    int D = a->shape[sv->dim];
+    int64_t slices = n / D;
+    float *d = dev_alloc_t<float>(fn->pool, (size_t)n);
+    softmax_bwd_kernel<<<(unsigned)((slices + 7) / 8), 256, 0, stream()>>>((const float *)sv->out->data, (const float *)go->data + go->offset, d,
+                                                                          slices, D, inner, sv->causal_n);
+    LAUNCHED("softmax_bwd_kernel");
+    float *ag = _grad_ensure(a);
+    if (a->contiguous) k_axpy_acc(ag + a->offset, d, n);
+    else k_scatter(ag, view_of(a), d, n, true);
+}
+static tensor *softmax_forward(struct mem_pool *scratch, const tensor *t, int dim, int causal_n) {
+    tensor *out = tensor_scratch(scratch, t->ndim, t->shape, 0);
+    int64_t n = numel_of(t), inner = 1;
+    for (int d = dim + 1; d < t->ndim; d++) inner *= t->shape[d];
+    int D = t->shape[dim];
+    int64_t slices = D > 0 ? n / D : 0;
+    const float *x = (const float *)t->data + t->offset;
+    if (!t->contiguous) {
+        float *tmp = dev_alloc_t<float>(scratch, (size_t)n);
+        k_gather(tmp, (const float *)t->data, view_of(t), n);
+        x = tmp;
+    }
+    if (slices > 0) {
+        softmax_fwd_kernel<<<(unsigned)((slices + 7) / 8), 256, 0, stream()>>>(x, (float *)out->data, slices, D, inner, causal_n);
+        LAUNCHED("softmax_fwd_kernel");
+    }
+    if (dnn_grad_enabled() && t->requires_grad) {
+        grad_fn *fn = attach(scratch, out, softmax_backward, 1, 1);
+        fn->inputs[0] = (tensor *)t;
+        SoftSaved *sv = host_alloc_t<SoftSaved>(scratch);
+        sv->out = out; sv->dim = dim; sv->causal_n = causal_n;
+        fn->saved_tensors[0] = (tensor *)sv;
+    }
+    return out;
+}
+
+// ---- dropout: the keep mask comes from the host generator in element order, as in the reference ----
+struct DropF { float *o; const float *x, *mask; View vx; float scale;
+    __device__ void operator()(int64_t i) const { o[i] = mask[i] * x[voff(vx, i)] * scale; } };
+struct DropB { float *dx; const float *g, *mask; View vx; float scale;
+    __device__ void operator()(int64_t i) const { dx[voff(vx, i)] += g[i] * mask[i] * scale; } };
+struct DropSaved { const float *mask; float scale; };
+static void dropout_backward(grad_fn *fn, tensor *go) {
+    tensor *a = fn->inputs[0];
+    if (!a->requires_grad) return;
+    DropSaved *sv = (DropSaved *)fn->saved_tensors[0];
+    float *ag = _grad_ensure(a);
+    ew_launch("dropout_bwd_kernel", numel_of(a), DropB{ag, (const float *)go->data + go->offset, sv->mask, view_of(a), sv->scale});
+}
+
+struct TriuF { float *o; int N, diag;
+    __device__ void operator()(int64_t i) const { int r = (int)(i / N), c = (int)(i - (int64_t)r * N); o[i] = c >= r + diag ? -INFINITY : 0.0f; } };
+
 }  // namespace dnnb
 
 using namespace dnnb;
@@ -398,6 +625,93 @@ tensor *tensor_swiglu(struct mem_pool *scratch, const tensor *gate, const tensor
         grad_fn *fn = attach(scratch, out, swiglu_backward, 2, 0);
         fn->inputs[0] = (tensor *)gate; fn->inputs[1] = (tensor *)up;
     }
+    return out;
+}
+
+tensor *tensor_sub(struct mem_pool *scratch, const tensor *a, const tensor *b) { return binary_forward<BIN_SUB>(scratch, a, b, "tensor_sub"); }
+tensor *tensor_mul(struct mem_pool *scratch, const tensor *a, const tensor *b) { return binary_forward<BIN_MUL>(scratch, a, b, "tensor_mul"); }
+tensor *tensor_div(struct mem_pool *scratch, const tensor *a, const tensor *b) { return binary_forward<BIN_DIV>(scratch, a, b, "tensor_div"); }
+tensor *tensor_neg(struct mem_pool *scratch, const tensor *t) { return unary_forward(scratch, t, UN_NEG, 0.f); }
+tensor *tensor_pow(struct mem_pool *scratch, const tensor *t, float exp) { return unary_forward(scratch, t, UN_POW, exp); }
+tensor *tensor_sigmoid(struct mem_pool *scratch, const tensor *t) { return unary_forward(scratch, t, UN_SIGMOID, 0.f); }
+
+tensor *tensor_sum(struct mem_pool *scratch, const tensor *t, int dim) {
+    DNN_CHECK(t, "tensor_sum: NULL input");
+    int nd = t->ndim;
+    if (dim < 0) dim += nd;
+    DNN_CHECK(dim >= 0 && dim < nd, "tensor_sum: dim out of range");
+    int shape[DNN_MAX_DIMS];
+    for (int d = 0; d < nd; d++) shape[d] = t->shape[d];
+    shape[dim] = 1;                                           // keepdim
+    tensor *out = tensor_scratch(scratch, nd, shape, 0);
+    int64_t inner = 1;
+    for (int d = dim + 1; d < nd; d++) inner *= t->shape[d];
+    ew_launch("sum_fwd_kernel", numel_of(out), SumF{(float *)out->data, (const float *)t->data, view_of(t), t->shape[dim], inner});
+    if (dnn_grad_enabled() && t->requires_grad) {
+        grad_fn *fn = attach(scratch, out, sum_backward, 1, 1);
+        fn->inputs[0] = (tensor *)t;
+        int *sd = host_alloc_t<int>(scratch); *sd = dim;
+        fn->saved_tensors[0] = (tensor *)sd;
+    }
+    return out;
+}
+
+// mean = sum * (1/n) through tensor_mul with a one-element tensor, like the reference (src/ops_reduce.c:138-153)
+tensor *tensor_mean(struct mem_pool *scratch, const tensor *t, int dim) {
+    DNN_CHECK(t, "tensor_mean: NULL input");
+    int d = dim < 0 ? dim + t->ndim : dim;
+    DNN_CHECK(d >= 0 && d < t->ndim, "tensor_mean: dim out of range");
+    tensor *s = tensor_sum(scratch, t, dim);
+    int one = 1;
+    tensor *scale = tensor_scratch(scratch, 1, &one, 0);
+    k_fill((float *)scale->data, 1, 1.0f / (float)t->shape[d]);
+    return tensor_mul(scratch, s, scale);
+}
+
+tensor *tensor_softmax(struct mem_pool *scratch, const tensor *t, int dim) {
+    DNN_CHECK(t, "tensor_softmax: NULL input");
+    if (dim < 0) dim += t->ndim;
+    DNN_CHECK(dim >= 0 && dim < t->ndim, "tensor_softmax: dim out of range");
+    return softmax_forward(scratch, t, dim, 0);
+}
+
+tensor *tensor_causal_softmax(struct mem_pool *scratch, const tensor *t) {
+    DNN_CHECK(t && t->ndim >= 2, "tensor_causal_softmax: need at least 2 dims");
+    DNN_CHECK(t->shape[t->ndim - 2] == t->shape[t->ndim - 1], "tensor_causal_softmax: last two dims must be equal");
+    return softmax_forward(scratch, t, t->ndim - 1, t->shape[t->ndim - 1]);
+}
+
+tensor *tensor_dropout(struct mem_pool *scratch, const tensor *t, float p) {
+    DNN_CHECK(t, "tensor_dropout: NULL input");
+    DNN_CHECK(p >= 0.0f && p < 1.0f, "tensor_dropout: p must be in [0, 1)");
+    if (!dnn_grad_enabled()) return (tensor *)t;              // evaluation: identity (src/ops_activation.c:1449)
+    int64_t n = numel_of(t);
+    float scale = 1.0f / (1.0f - p);
+    tensor *out = tensor_scratch(scratch, t->ndim, t->shape, 0);
+    // same draws, same order as the reference's serial loop (src/ops_activation.c:1460-1463)
+    std::vector<float> keep((size_t)n);
+    for (int64_t i = 0; i < n; i++) keep[(size_t)i] = dnn_rng_uniform(dnn_get_rng()) >= p ? 1.0f : 0.0f;
+    float *mask = dev_alloc_t<float>(scratch, (size_t)n);
+    if (n > 0) {
+        CUDA_OK(cudaMemcpyAsync(mask, keep.data(), (size_t)n * 4, cudaMemcpyHostToDevice, stream()));
+        CUDA_OK(cudaStreamSynchronize(stream()));             // `keep` is pageable and about to go away
+    }
+    ew_launch("dropout_fwd_kernel", n, DropF{(float *)out->data, (const float *)t->data, mask, view_of(t), scale});
+    if (t->requires_grad) {
+        grad_fn *fn = attach(scratch, out, dropout_backward, 1, 1);
+        fn->inputs[0] = (tensor *)t;
+        DropSaved *sv = host_alloc_t<DropSaved>(scratch);
+        sv->mask = mask; sv->scale = scale;
+        fn->saved_tensors[0] = (tensor *)sv;
+    }
+    return out;
+}
+
+tensor *tensor_triu(struct mem_pool *scratch, int N, int diagonal) {
+    DNN_CHECK(N > 0, "tensor_triu: N must be positive");
+    int shape[2] = {N, N};
+    tensor *out = tensor_scratch(scratch, 2, shape, 0);
+    ew_launch("triu_kernel", (int64_t)N * N, TriuF{(float *)out->data, N, diagonal});
     return out;
 }
 

@@ -141,6 +141,21 @@ tensor *tensor_matmul_add(struct mem_pool *scratch, const tensor *a, const tenso
 tensor *tensor_relu(struct mem_pool *scratch, const tensor *t);                              /* src/ops_activation.c:37-69 */
 tensor *tensor_silu(struct mem_pool *scratch, const tensor *t);                              /* src/ops_activation.c:165-199 */
 tensor *tensor_swiglu(struct mem_pool *scratch, const tensor *gate, const tensor *up);       /* src/ops_activation.c:283-333 */
+
+/* The rest of include/ops.h: not used by the training path of the models, provided so that
+ * programs written against the reference link unchanged.  Broadcasting as tensor_add. */
+tensor *tensor_sub(struct mem_pool *scratch, const tensor *a, const tensor *b);              /* src/ops_elem.c:234-285 */
+tensor *tensor_mul(struct mem_pool *scratch, const tensor *a, const tensor *b);              /* src/ops_elem.c:340-391 */
+tensor *tensor_div(struct mem_pool *scratch, const tensor *a, const tensor *b);              /* src/ops_elem.c:452-500 */
+tensor *tensor_neg(struct mem_pool *scratch, const tensor *t);                               /* src/ops_elem.c:588-625 */
+tensor *tensor_pow(struct mem_pool *scratch, const tensor *t, float exp);                    /* src/ops_elem.c:526-570 */
+tensor *tensor_triu(struct mem_pool *scratch, int N, int diagonal);                          /* src/ops_elem.c:643-658; 0 / -inf mask */
+tensor *tensor_sigmoid(struct mem_pool *scratch, const tensor *t);                           /* src/ops_activation.c:94-125 */
+tensor *tensor_softmax(struct mem_pool *scratch, const tensor *t, int dim);                  /* src/ops_activation.c:434-560 */
+tensor *tensor_causal_softmax(struct mem_pool *scratch, const tensor *t);                    /* src/ops_activation.c:683-800 */
+tensor *tensor_dropout(struct mem_pool *scratch, const tensor *t, float p);                  /* src/ops_activation.c:1446-1500; identity when gradients are off */
+tensor *tensor_sum(struct mem_pool *scratch, const tensor *t, int dim);                      /* src/ops_reduce.c:57-136; keeps the reduced dim as 1 */
+tensor *tensor_mean(struct mem_pool *scratch, const tensor *t, int dim);                     /* src/ops_reduce.c:138-153 */
 tensor *tensor_cross_entropy(struct mem_pool *scratch, const tensor *logits,
                              const tensor *target, int dim);                                  /* src/ops_activation.c:948-1145 */
 tensor *tensor_cross_entropy_masked(struct mem_pool *scratch, const tensor *logits,

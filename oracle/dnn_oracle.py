@@ -41,6 +41,80 @@ def add(a, b, gout):
     return _f32(y), _f32(_unbroadcast(g, a.shape)), _f32(_unbroadcast(g, b.shape))
 
 
+# ── the rest of ops.h (src/ops_elem.c:178-680, src/ops_reduce.c:12-153, src/ops_activation.c:70-130,300-800,1410-1500)
+def sub(a, b, gout):
+    g = gout.astype(F64)
+    return _f32(a.astype(F64) - b.astype(F64)), _f32(_unbroadcast(g, a.shape)), _f32(_unbroadcast(-g, b.shape))
+
+
+def mul(a, b, gout):
+    a64, b64, g = a.astype(F64), b.astype(F64), gout.astype(F64)
+    return _f32(a64 * b64), _f32(_unbroadcast(g * b64, a.shape)), _f32(_unbroadcast(g * a64, b.shape))
+
+
+def div(a, b, gout):
+    a64, b64, g = a.astype(F64), b.astype(F64), gout.astype(F64)
+    return _f32(a64 / b64), _f32(_unbroadcast(g / b64, a.shape)), _f32(_unbroadcast(-g * a64 / (b64 * b64), b.shape))
+
+
+def neg(x, gout):
+    return _f32(-x), _f32(-gout)
+
+
+def power(x, e, gout):
+    x64 = x.astype(F64)
+    return _f32(x64 ** e), _f32(e * x64 ** (e - 1.0) * gout.astype(F64))
+
+
+def sigmoid(x, gout):
+    s = 1.0 / (1.0 + np.exp(-x.astype(F64)))
+    return _f32(s), _f32(s * (1.0 - s) * gout.astype(F64))
+
+
+def sum_dim(x, dim, gout):
+    """keepdim sum; gout has the output shape (size 1 along dim)."""
+    y = x.astype(F64).sum(axis=dim, keepdims=True)
+    return _f32(y), _f32(np.broadcast_to(gout.astype(F64), x.shape))
+
+
+def mean_dim(x, dim, gout):
+    y = x.astype(F64).mean(axis=dim, keepdims=True)
+    return _f32(y), _f32(np.broadcast_to(gout.astype(F64), x.shape) / x.shape[dim])
+
+
+def softmax(x, dim, gout):
+    x64 = x.astype(F64)
+    e = np.exp(x64 - x64.max(axis=dim, keepdims=True))
+    y = e / e.sum(axis=dim, keepdims=True)
+    g = gout.astype(F64)
+    return _f32(y), _f32(y * (g - (y * g).sum(axis=dim, keepdims=True)))
+
+
+def causal_softmax(x, gout):
+    """softmax over the last dim of (..., N, N) with columns j > i of row i masked out (exact zeros)."""
+    x64 = x.astype(F64)
+    n = x.shape[-1]
+    keep = np.tril(np.ones((n, n), bool))
+    xm = np.where(keep, x64, -np.inf)
+    e = np.exp(xm - xm.max(axis=-1, keepdims=True))
+    y = e / e.sum(axis=-1, keepdims=True)
+    g = gout.astype(F64)
+    return _f32(y), _f32(np.where(keep, y * (g - (y * g).sum(axis=-1, keepdims=True)), 0.0))
+
+
+def dropout(x, p, seed, gout):
+    """keep mask from the reference generator in element order: uniform() >= p (src/ops_activation.c:1460)."""
+    r = Rng(seed)
+    keep = np.array([1.0 if r.uniform() >= p else 0.0 for _ in range(x.size)], F64).reshape(x.shape)
+    scale = 1.0 / (1.0 - p)
+    return _f32(keep * x.astype(F64) * scale), _f32(keep * gout.astype(F64) * scale)
+
+
+def triu(n, diagonal):
+    i, j = np.indices((n, n))
+    return np.where(j >= i + diagonal, -np.inf, 0.0).astype(np.float32)
+
+
 def cat(a, b, dim, gout):
     y = np.concatenate([a, b], axis=dim)
     ga, gb = np.split(gout, [a.shape[dim]], axis=dim)

@@ -146,6 +146,152 @@ _binary("add", "tensor_add", O.add, [((6, 50, 64), (6, 50, 64)), ((3, 7, 33), (3
                                       ((4, 19, 24), (1, 19, 24)), ((5, 1, 8), (1, 6, 8))])
 _binary("swiglu", "tensor_swiglu", O.swiglu, [((9, 17, 64), (9, 17, 64)), ((3, 5, 31), (3, 5, 31)), ((4, 6, 8), (1, 6, 8))])
 
+# ── the rest of ops.h: sub, mul, div, neg, pow, sigmoid, sum, mean, softmax, causal softmax, dropout, triu ──
+_binary("sub", "tensor_sub", O.sub, [((5, 9, 32), (5, 9, 32)), ((3, 7, 33), (33,)), ((4, 1, 8), (1, 6, 8))])
+_binary("mul", "tensor_mul", O.mul, [((5, 9, 32), (5, 9, 32)), ((33,), (3, 7, 33)), ((4, 1, 8), (1, 6, 8)), ((6, 5), (1,))])
+_unary("neg", "tensor_neg", O.neg, [(7, 33), (5,)])
+_unary("sigmoid", "tensor_sigmoid", O.sigmoid, [(9, 65), (12,)])
+
+for sa, sb in (((6, 40), (6, 40)), ((3, 5, 16), (16,)), ((4, 1, 8), (1, 6, 8))):
+    @case("div%s%s" % (list(sa), list(sb)))
+    class _:
+        @staticmethod
+        def make(rng, sa=sa, sb=sb):
+            out = np.broadcast_shapes(sa, sb)
+            b = (1.5 + 0.3 * _r(rng, *sb)) * np.where(_r(rng, *sb) > 0, 1, -1)       # away from zero, both signs
+            return dict(a=_r(rng, *sa), b=b.astype(np.float32), g=_r(rng, *out))
+
+        @staticmethod
+        def run(dnn, i):
+            a, b = dnn.tensor(i["a"], dnn.scratch, True), dnn.tensor(i["b"], dnn.scratch, True)
+            y = dnn.lib.tensor_div(dnn.scratch, a, b)
+            dnn.backward_from(y, i["g"])
+            da, db = _grads(dnn, a, b)
+            return dict(y=dnn.download(y), da=da, db=db)
+
+        @staticmethod
+        def oracle(i):
+            y, da, db = O.div(i["a"], i["b"], i["g"])
+            return dict(y=y, da=da, db=db)
+
+for shape, e in (((8, 33), 2.0), ((5, 7), 2.5), ((64,), -1.0)):
+    @case("pow%s^%g" % (list(shape), e))
+    class _:
+        @staticmethod
+        def make(rng, shape=shape, e=e):
+            return dict(x=(0.5 + np.abs(_r(rng, *shape))).astype(np.float32), g=_r(rng, *shape), e=e)
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            y = dnn.lib.tensor_pow(dnn.scratch, x, i["e"])
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.power(i["x"], i["e"], i["g"])
+            return dict(y=y, dx=dx)
+
+for opname, libfn, ofn in (("sum", "tensor_sum", O.sum_dim), ("mean", "tensor_mean", O.mean_dim)):
+    for shape, dim in (((5, 17, 9), 1), ((5, 17, 9), -1), ((6, 33), 0), ((40,), 0)):
+        @case("%s%s dim%d" % (opname, list(shape), dim))
+        class _:
+            @staticmethod
+            def make(rng, shape=shape, dim=dim):
+                out = list(shape); out[dim] = 1
+                return dict(x=_r(rng, *shape), g=_r(rng, *out), dim=dim)
+
+            @staticmethod
+            def run(dnn, i, libfn=libfn, opname=opname):
+                x = dnn.tensor(i["x"], dnn.scratch, True)
+                y = getattr(dnn.lib, libfn)(dnn.scratch, x, i["dim"])
+                dnn.backward_from(y, i["g"])
+                if opname == "mean":
+                    # mean = mul(sum(x), 1/n): y's node is the mul; hand its gradient on to the sum node
+                    fn = C.cast(y.contents.grad_fn, C.POINTER(load_binding().GradFn))
+                    s_ = fn.contents.inputs[0]
+                    dnn.backward_from(s_, dnn.download_grad(s_))
+                return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+            @staticmethod
+            def oracle(i, ofn=ofn):
+                y, dx = ofn(i["x"], i["dim"], i["g"])
+                return dict(y=y, dx=dx)
+
+for shape, dim in (((7, 50), 1), ((7, 50), 0), ((3, 9, 20), 1), ((4, 5, 33), -1)):
+    @case("softmax%s dim%d" % (list(shape), dim))
+    class _:
+        @staticmethod
+        def make(rng, shape=shape, dim=dim):
+            return dict(x=_r(rng, *shape, scale=2.0), g=_r(rng, *shape), dim=dim)
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            y = dnn.lib.tensor_softmax(dnn.scratch, x, i["dim"])
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.softmax(i["x"], i["dim"], i["g"])
+            return dict(y=y, dx=dx)
+
+for shape in ((13, 13), (2, 3, 40, 40)):
+    @case("causal_softmax%s" % (list(shape),))
+    class _:
+        @staticmethod
+        def make(rng, shape=shape):
+            return dict(x=_r(rng, *shape, scale=2.0), g=_r(rng, *shape))
+
+        @staticmethod
+        def run(dnn, i):
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            y = dnn.lib.tensor_causal_softmax(dnn.scratch, x)
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.causal_softmax(i["x"], i["g"])
+            return dict(y=y, dx=dx)
+
+for shape, p in (((6, 37), 0.25), ((200,), 0.5)):
+    @case("dropout%s p%g" % (list(shape), p))
+    class _:
+        @staticmethod
+        def make(rng, shape=shape, p=p):
+            return dict(x=_r(rng, *shape), g=_r(rng, *shape), p=p, seed=1234)
+
+        @staticmethod
+        def run(dnn, i):
+            dnn.lib.dnn_seed(i["seed"])                       # the mask comes from the host generator, element by element
+            x = dnn.tensor(i["x"], dnn.scratch, True)
+            y = dnn.lib.tensor_dropout(dnn.scratch, x, i["p"])
+            dnn.backward_from(y, i["g"])
+            return dict(y=dnn.download(y), dx=dnn.download_grad(x))
+
+        @staticmethod
+        def oracle(i):
+            y, dx = O.dropout(i["x"], i["p"], i["seed"], i["g"])
+            return dict(y=y, dx=dx)
+
+for n, diag in ((9, 1), (6, 0), (5, -2)):
+    @case("triu[%d] diag%d" % (n, diag), exact=("y",))
+    class _:
+        @staticmethod
+        def make(rng, n=n, diag=diag):
+            return dict(n=n, diag=diag)
+
+        @staticmethod
+        def run(dnn, i):
+            return dict(y=dnn.download(dnn.lib.tensor_triu(dnn.scratch, i["n"], i["diag"])))
+
+        @staticmethod
+        def oracle(i):
+            return dict(y=O.triu(i["n"], i["diag"]))
+
 for sa, sb, dim in (((3, 19, 16), (3, 5, 16), 1), ((4, 8), (2, 8), 0), ((2, 3, 4), (2, 3, 9), 2)):
     @case("cat%s%s dim%d" % (list(sa), list(sb), dim))
     class _:
