@@ -141,12 +141,19 @@ void gemm(const GemmArgs &g);          // dispatches on gemm_mode() and layout
 // pairs of the first `cols` output columns, which are heads of size d; row r is position r % N.
 // The GEMM that honours it clears it; gemm_rope_epilogue_take() tells whether that happened
 // (and clears a request nobody honoured, so that the caller can run the rotation itself).
+// Same protocol for a residual: the next tensor-core GEMM computes C = A*B + bias + resid.
+void gemm_residual_request(const float *resid, int64_t ld);
+bool gemm_residual_take();
+// x + (a*b + bias) with the addition done in the GEMM epilogue when possible (ops_matrix.cu);
+// equal to tensor_add(scratch, x, tensor_matmul_add(scratch, a, b, trans_b, bias)) bit for bit.
+tensor *matmul_add_residual(struct mem_pool *scratch, const tensor *a, const tensor *b, int trans_b, const tensor *bias, const tensor *x);
 void gemm_rope_epilogue_request(const float *fc, const float *fs, int N, int d, int cols);
 bool gemm_rope_epilogue_take();
 void gemm_simt(const GemmArgs &g);
 bool gemm_tc_supported(const GemmArgs &g);
 void gemm_tc(const GemmArgs &g, bool split3);
 int  attn_tc_error();
+int  norm_error();               // nonzero when a staged row copy of the norm backward never landed
 int  gemm_tc_error();            // nonzero when a bounded wait inside the tensor-core kernel gave up
 
 }  // namespace dnnb

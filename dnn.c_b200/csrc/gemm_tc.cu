@@ -43,6 +43,7 @@ struct TcArgs {
     int tiles_m, tiles_n;
     int n_fastest;                     // tile order: consecutive work units walk along N (1) or along M (0)
     int a_chunked, b_chunked;          // MN-major operand described as {32, K, extent/32}: one TMA copy per stage
+    const float *resid; int64_t resid_ld;     // epilogue: C = A*B + bias + resid (row-major, same shape as C)
     const float *rope_c, *rope_s;      // epilogue rotation of the first rope_cols columns (heads of rope_d, position = row % rope_N)
     int rope_N, rope_d, rope_cols;
 };
@@ -224,6 +225,19 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         for (int j = 0; j < 32; j++) if (col0 + j < g.N) v[j] += g.bias[col0 + j];
                     }
                 }
+                if (g.resid && row0 + lane < g.M) {
+                    const float *rr = g.resid + (int64_t)(row0 + lane) * g.resid_ld + col0;
+                    if (col0 + 32 <= g.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 x = *reinterpret_cast<const float4 *>(rr + j);
+                            v[j] += x.x; v[j + 1] += x.y; v[j + 2] += x.z; v[j + 3] += x.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (col0 + j < g.N) v[j] += rr[j];
+                    }
+                }
                 if (g.rope_c && col0 < g.rope_cols) {         // rope_cols, rope_d are multiples of 32: the chunk lies in one head
                     const int pos = (row0 + lane) % g.rope_N, hc = col0 % g.rope_d;
                     const float4 *c4 = reinterpret_cast<const float4 *>(g.rope_c + (int64_t)pos * (g.rope_d >> 1) + (hc >> 1));
@@ -403,6 +417,15 @@ bool gemm_tc_supported(const GemmArgs &in) {
     return (int64_t)g.M * g.N * g.K >= (int64_t)64 * 64 * 32;
 }
 
+struct ResidEpilogue { const float *r; int64_t ld; bool pending, honoured; };
+static thread_local ResidEpilogue g_resid = {nullptr, 0, false, false};
+void gemm_residual_request(const float *resid, int64_t ld) { g_resid.r = resid; g_resid.ld = ld; g_resid.pending = true; g_resid.honoured = false; }
+bool gemm_residual_take() {
+    bool h = g_resid.honoured;
+    g_resid.pending = false; g_resid.honoured = false;
+    return h;
+}
+
 struct RopeEpilogue { const float *fc, *fs; int N, d, cols; bool pending, honoured; };
 static thread_local RopeEpilogue g_rope = {nullptr, nullptr, 0, 0, 0, false, false};
 void gemm_rope_epilogue_request(const float *fc, const float *fs, int N, int d, int cols) {
@@ -478,6 +501,11 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     t.kb_per_split = (num_kb + splits - 1) / splits;
     splits = (num_kb + t.kb_per_split - 1) / t.kb_per_split;
     t.splits = splits;
+    t.resid = nullptr; t.resid_ld = 0;
+    if (g_resid.pending && splits == 1 && !g.accumulate && aligned16(g_resid.r) && g_resid.ld % 4 == 0) {
+        t.resid = g_resid.r; t.resid_ld = g_resid.ld;
+        g_resid.pending = false; g_resid.honoured = true;
+    }
     t.rope_c = t.rope_s = nullptr; t.rope_N = t.rope_d = t.rope_cols = 0;
     if (g_rope.pending && splits == 1 && !g.accumulate && g.M % g_rope.N == 0 && g_rope.cols <= g.N &&
         g_rope.cols % 32 == 0 && g_rope.d % 32 == 0 && (((uintptr_t)g_rope.fc | (uintptr_t)g_rope.fs) & 15) == 0) {
@@ -536,6 +564,7 @@ void gemm_tc(const GemmArgs &in, bool split3) {
     DNN_CHECK(ok, "gemm_tc called with an unsupported layout");
     if (!split3) { run_tc(g); return; }
     g_rope.pending = false;            // an epilogue rotation cannot be split over the three partial products
+    g_resid.pending = false;           // nor can a residual be added three times
     // 3xTF32: x = big + small with big exactly TF32; A*B ~= Ab*Bb + Ab*Bs + As*Bb, fp32 accumulation.
     int64_t a_inner = g.a_cs == 1 ? g.K : g.M, a_outer = g.a_cs == 1 ? g.M : g.K;
     int64_t b_inner = g.b_cs == 1 ? g.N : g.K, b_outer = g.b_cs == 1 ? g.K : g.N;

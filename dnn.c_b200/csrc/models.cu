@@ -125,12 +125,27 @@ tensor *transformer_block_forward_ex(struct mem_pool *scratch, transformer_block
         tensor *att = tensor_attention_ex(scratch, q, k, v, nullptr, mode, prefix_len, seq_lens);
         merged = tensor_merge_heads(scratch, att);
     }
-    tensor *proj = linear_forward(scratch, block->out_proj, merged);
-    tensor *x1 = tensor_add(scratch, x, proj);
+    // The two residual additions run in the epilogue of the projection that feeds them
+    // (x + (a W + b), same roundings as the separate add) unless the op-by-op block is asked for.
+    const bool fuse_residual = dnn_cuda_get_fused_attention() != 0;
+    tensor *x1;
+    if (fuse_residual) {
+        x1 = matmul_add_residual(scratch, merged, block->out_proj->weight, 0, block->out_proj->bias, x);
+    } else {
+        tensor *proj = linear_forward(scratch, block->out_proj, merged);
+        x1 = tensor_add(scratch, x, proj);
+    }
     // feed-forward sub-layer, pre-norm
     h = rms_norm_forward(scratch, block->ffn_norm, x1);
-    tensor *ffn = swiglu_ffn_forward(scratch, block->ffn, h);
-    return tensor_add(scratch, x1, ffn);
+    if (!fuse_residual) {
+        tensor *ffn = swiglu_ffn_forward(scratch, block->ffn, h);
+        return tensor_add(scratch, x1, ffn);
+    }
+    swiglu_ffn *f = block->ffn;
+    tensor *gate = linear_forward(scratch, f->gate_proj, h);
+    tensor *up = linear_forward(scratch, f->up_proj, h);
+    tensor *hidden = tensor_swiglu(scratch, gate, up);
+    return matmul_add_residual(scratch, hidden, f->down_proj->weight, 0, f->down_proj->bias, x1);
 }
 
 tensor *transformer_block_forward(struct mem_pool *scratch, transformer_block *block, const tensor *x) {

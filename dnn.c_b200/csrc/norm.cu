@@ -135,6 +135,119 @@ __global__ void norm_bwd_kernel(const float *__restrict__ x, const float *__rest
     }
 }
 
+// Same computation with the rows staged through shared memory by the copy engine: every warp
+// owns two row buffers (x row and g row each) and two mbarriers; while it works on one row, a
+// bulk copy (cp.async.bulk, 1-D) of its next row is in flight.  The loads cost no registers and
+// never stop, which the register version cannot do: it has nothing in flight while it reduces
+// and stores.  Used when two buffers per warp fit (d <= 768 with 8 warps and 2 CTAs per SM).
+__device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src), "r"(bytes),
+                   "r"((uint32_t)__cvta_generic_to_shared(bar)) : "memory");
+}
+__device__ __forceinline__ void bar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_expect(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(bytes) : "memory");
+}
+// bounded: a copy that never lands must not hang the GPU; the caller flags the error
+__device__ __forceinline__ bool bar_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(bar);
+    for (uint32_t it = 0; it < (1u << 24); it++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ int g_norm_error = 0;
+
+template <bool LN, int T>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
+norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
+                       const float *__restrict__ mean, const float *__restrict__ rstd,
+                       float *__restrict__ dx, float *__restrict__ dw_part, float *__restrict__ db_part,
+                       int64_t rows, int d, int acc_dx) {
+    extern __shared__ __align__(128) uint8_t norm_smem[];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + wid;
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+    const uint32_t row_bytes = (uint32_t)d * 4;
+    // per warp: [2 buffers][x row | g row], then the CTA's barriers
+    float *buf = reinterpret_cast<float *>(norm_smem) + (size_t)wid * 4 * d;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(norm_smem + (size_t)kWarpsPerCta * 4 * row_bytes) + wid * 2;
+    if (lane == 0) { bar_init(&bars[0], 1); bar_init(&bars[1], 1); asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    __syncwarp();
+    const float inv_d = 1.0f / (float)d;
+    float4 aw[T], ab[LN ? T : 1];
+#pragma unroll
+    for (int t = 0; t < T; t++) { aw[t] = make_float4(0.f, 0.f, 0.f, 0.f); if (LN) ab[t] = aw[t]; }
+    auto fetch = [&](int64_t r, int b) {
+        if (lane == 0) {
+            bar_expect(&bars[b], 2 * row_bytes);
+            bulk_load_1d(buf + (size_t)b * 2 * d, x + r * d, row_bytes, &bars[b]);
+            bulk_load_1d(buf + (size_t)b * 2 * d + d, g + r * d, row_bytes, &bars[b]);
+        }
+    };
+    if (warp < rows) fetch(warp, 0);
+    int it = 0;
+    for (int64_t r = warp; r < rows; r += nwarps, it++) {
+        const int b = it & 1;
+        if (r + nwarps < rows) fetch(r + nwarps, b ^ 1);       // the other buffer was consumed in the previous trip
+        const float rs = rstd[r], mu = LN ? mean[r] : 0.f;
+        bool ok = bar_wait(&bars[b], (uint32_t)(it >> 1) & 1u);
+        if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) atomicCAS(&g_norm_error, 0, 1); break; }
+        const float *xs = buf + (size_t)b * 2 * d, *gs = xs + d;
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int t = 0; t < T; t++) {
+            int j = (lane + 32 * t) * 4;
+            if (j < d) {
+                float4 v = ld4(xs + j), gg = ld4(gs + j);
+                float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+                v.x -= mu; v.y -= mu; v.z -= mu; v.w -= mu;
+                s1 += gg.x * ww.x * v.x + gg.y * ww.y * v.y + gg.z * ww.z * v.z + gg.w * ww.w * v.w;
+                if (LN) s2 += gg.x * ww.x + gg.y * ww.y + gg.z * ww.z + gg.w * ww.w;
+                if (dw_part) {
+                    aw[t].x += gg.x * v.x * rs; aw[t].y += gg.y * v.y * rs;
+                    aw[t].z += gg.z * v.z * rs; aw[t].w += gg.w * v.w * rs;
+                }
+                if (LN && db_part) { ab[t].x += gg.x; ab[t].y += gg.y; ab[t].z += gg.z; ab[t].w += gg.w; }
+            }
+        }
+        s1 = warp_sum(s1);
+        if (LN) s2 = warp_sum(s2);
+        if (dx) {
+            float *dxr = dx + r * d;
+            const float k1 = rs * rs * inv_d * s1, mdy = LN ? s2 * inv_d : 0.f;
+#pragma unroll
+            for (int t = 0; t < T; t++) {
+                int j = (lane + 32 * t) * 4;
+                if (j < d) {
+                    float4 v = ld4(xs + j), gg = ld4(gs + j);
+                    float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+                    float4 o = acc_dx ? ld4(dxr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v.x -= mu; v.y -= mu; v.z -= mu; v.w -= mu;
+                    o.x += rs * (gg.x * ww.x - mdy) - rs * k1 * v.x; o.y += rs * (gg.y * ww.y - mdy) - rs * k1 * v.y;
+                    o.z += rs * (gg.z * ww.z - mdy) - rs * k1 * v.z; o.w += rs * (gg.w * ww.w - mdy) - rs * k1 * v.w;
+                    st4(dxr + j, o);
+                }
+            }
+        }
+        __syncwarp();          // every lane is done with this buffer before lane 0 refills it two trips on
+    }
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+        int j = (lane + 32 * t) * 4;
+        if (j < d) {
+            if (dw_part) st4(dw_part + warp * d + j, aw[t]);
+            if (LN && db_part) st4(db_part + warp * d + j, ab[t]);
+        }
+    }
+}
+
 // Scalar fallback for d not a multiple of 4, unaligned rows or d > 2048:
 // one CTA per row for dx, column sums done by separate kernels.
 template <bool LN>
@@ -188,6 +301,12 @@ __global__ void norm_part_reduce_kernel(float *__restrict__ out, const float *__
     }
 }
 
+int norm_error() {
+    int e = 0;
+    cudaMemcpyFromSymbol(&e, g_norm_error, sizeof e);
+    return e;
+}
+
 template <bool LN>
 static void norm_forward(const float *x, const float *w, const float *b, float *y, float *mean, float *rstd,
                          int64_t rows, int d, float eps) {
@@ -204,6 +323,15 @@ static void norm_forward(const float *x, const float *w, const float *b, float *
 template <bool LN, int T>
 static void launch_bwd(const float *x, const float *w, const float *g, const float *mean, const float *rstd,
                        float *dx, float *dwp, float *dbp, int64_t rows, int d, int grid, int acc_dx) {
+    // rows staged through shared memory when two CTAs of 8 warps with two row pairs each fit on an SM
+    const size_t smem = (size_t)kWarpsPerCta * 4 * d * sizeof(float) + kWarpsPerCta * 2 * sizeof(uint64_t);
+    if (smem <= 100 * 1024 && d % 4 == 0 && T <= 6) {
+        static bool once = false;
+        if (!once) { CUDA_OK(cudaFuncSetAttribute(norm_bwd_staged_kernel<LN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)); once = true; }
+        norm_bwd_staged_kernel<LN, T><<<grid, kWarpsPerCta * 32, smem, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, acc_dx);
+        LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
+        return;
+    }
     norm_bwd_kernel<LN, T><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, acc_dx);
     LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
 }

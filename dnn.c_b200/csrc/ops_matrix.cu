@@ -181,11 +181,50 @@ static void matmul_add_backward(grad_fn *fn, tensor *go) {
     }
 }
 
+// inputs: a, b, bias, x (the residual).  d(out)/dx = identity; the rest is matmul_add's backward.
+static void matmul_add_residual_backward(grad_fn *fn, tensor *go) {
+    tensor *x = fn->inputs[3];
+    if (wants_grad(x)) {
+        bool acc = true;
+        float *xg = grad_full(x, &acc);
+        int64_t n = numel_of(go);
+        if (acc) k_axpy_acc(xg + x->offset, (const float *)go->data, n);
+        else k_copy(xg + x->offset, (const float *)go->data, n);
+    }
+    matmul_add_backward(fn, go);
+}
+
 static tensor *mm_out(struct mem_pool *scratch, const MM &p) {
     int shape[DNN_MAX_DIMS];
     for (int i = 0; i < p.batch_ndim; i++) shape[i] = p.batch_shape[i];
     shape[p.batch_ndim] = p.M; shape[p.batch_ndim + 1] = p.N;
     return tensor_scratch(scratch, p.batch_ndim + 2, shape, 0);
+}
+
+tensor *matmul_add_residual(struct mem_pool *scratch, const tensor *a, const tensor *b, int trans_b, const tensor *bias, const tensor *x) {
+    // the fused form needs x to have exactly the output's shape, packed
+    bool fits = gemm_mode() == DNN_CUDA_GEMM_TF32 && x && x->contiguous && a->ndim >= 2 && b->ndim == 2 && bias && bias->ndim == 1;
+    if (fits) {
+        int64_t rows = numel_of(a) / a->shape[a->ndim - 1];
+        int ncols = trans_b ? b->shape[0] : b->shape[1];
+        fits = x->ndim == a->ndim && numel_of(x) == rows * ncols && x->shape[x->ndim - 1] == ncols && ncols % 4 == 0;
+        for (int d = 0; fits && d < a->ndim - 1; d++) fits = x->shape[d] == a->shape[d];
+    }
+    if (!fits) return tensor_add(scratch, x, tensor_matmul_add(scratch, a, b, trans_b, bias));
+    MM p = plan(a, b, trans_b);
+    DNN_CHECK(bias->shape[0] == p.N, "matmul_add_residual: bias size != out cols");
+    tensor *out = mm_out(scratch, p);
+    const float *xd = (const float *)x->data + x->offset;
+    gemm_residual_request(xd, p.N);
+    mm_forward(p, a, b, trans_b, (const float *)bias->data + bias->offset, (float *)out->data);
+    if (!gemm_residual_take()) k_axpy_acc((float *)out->data, xd, numel_of(out));        // the GEMM took another route
+    if (dnn_grad_enabled() && (a->requires_grad || b->requires_grad || bias->requires_grad || x->requires_grad)) {
+        grad_fn *fn = attach(scratch, out, matmul_add_residual_backward, 4, 1);
+        fn->inputs[0] = (tensor *)a; fn->inputs[1] = (tensor *)b; fn->inputs[2] = (tensor *)bias; fn->inputs[3] = (tensor *)x;
+        int *st = host_alloc_t<int>(scratch); *st = trans_b;
+        fn->saved_tensors[0] = (tensor *)st;
+    }
+    return out;
 }
 
 }  // namespace dnnb

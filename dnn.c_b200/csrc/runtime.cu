@@ -273,9 +273,10 @@ int dnn_cuda_sync(void) {
     if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return -1; }
     int ge = gemm_tc_error();
     int ae = attn_tc_error();
-    if (ge || ae) {
-        char buf[160];
-        snprintf(buf, sizeof buf, "tensor-core kernel: a bounded barrier wait gave up (gemm code 0x%x, attention code 0x%x)", ge, ae);
+    int ne = norm_error();
+    if (ge || ae || ne) {
+        char buf[200];
+        snprintf(buf, sizeof buf, "a bounded barrier wait gave up (gemm code 0x%x, attention code 0x%x, norm backward %d)", ge, ae, ne);
         set_error(buf);
         return -5;
     }

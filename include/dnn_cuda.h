@@ -61,6 +61,8 @@ int  dnn_cuda_get_gemm_mode(void);
  * fused QKV projection: Q, K and V are read in place from its [B,N,3,H,d] output, RoPE is
  * applied there, and the result is written token-major, which removes the head split / merge
  * copies of the reference's block (src/transformer.c:143-170) without changing any value.
+ * The same switch covers the block's two residual additions, which then run in the epilogue of
+ * the output / down projection instead of as separate passes.
  * `on` = 0 forces the reference's op-by-op sequence (default 1; environment
  * DNN_CUDA_FUSED_QKV=0 does the same).  No counterpart in the reference. */
 void dnn_cuda_set_fused_attention(int on);
