@@ -187,6 +187,8 @@ def main():
         # the recorded step, wall time per step including the loss read-back
         import time
         V, D, L, H, F, Bsz, N = 256, 128, 4, 4, 512, 16, 128
+        if args.shapes == "gpt124m":                      # BASELINE config 5 instead: GPU-bound, shows what launch gaps cost
+            V, D, L, H, F, Bsz, N = 32000, 768, 12, 12, 2048, 16, 1024
         lm = lib.decoder_lm_create(d.params, V, D, L, H, D // H, F)
         lib.decoder_lm_enable_rope(d.params, lm, N, 10000.0)
         lib.dnn_seed(4); lib.decoder_lm_init_weights(lm)
@@ -204,20 +206,21 @@ def main():
             eager()
         before = lib.dnn_cuda_launch_count()
         t0 = time.perf_counter()
-        for _ in range(50):
+        reps = 50 if D < 512 else 10
+        for _ in range(reps):
             eager()
-        ms_eager = (time.perf_counter() - t0) * 1e3 / 50
-        per_step = (lib.dnn_cuda_launch_count() - before) // 50
+        ms_eager = (time.perf_counter() - t0) * 1e3 / reps
+        per_step = (lib.dnn_cuda_launch_count() - before) // reps
         g = lib.dnn_cuda_graph_capture_decoder_lm_step(d.scratch, lm, ids, tgt, opt, 1.0)
         loss = C.c_float(0)
         for _ in range(5):
             lib.dnn_cuda_graph_replay(g, C.byref(loss), None)
         t0 = time.perf_counter()
-        for _ in range(50):
+        for _ in range(reps):
             lib.dnn_cuda_graph_replay(g, C.byref(loss), None)
-        ms_graph = (time.perf_counter() - t0) * 1e3 / 50
+        ms_graph = (time.perf_counter() - t0) * 1e3 / reps
         lib.dnn_cuda_graph_destroy(g)
-        print(json.dumps({"op": "step_graph", "workload": "decoder LM config 1 (V256 d128 L4 H4 F512, 16x128 tokens)",
+        print(json.dumps({"op": "step_graph", "workload": "decoder LM V%d d%d L%d H%d F%d, %dx%d tokens" % (V, D, L, H, F, Bsz, N),
                           "kernels_per_step": int(per_step), "eager_ms_per_step": round(ms_eager, 3), "graph_ms_per_step": round(ms_graph, 3),
                           "eager_tokens_per_s": round(Bsz * N / ms_eager * 1e3), "graph_tokens_per_s": round(Bsz * N / ms_graph * 1e3),
                           "speedup": round(ms_eager / ms_graph, 2)}), flush=True)
