@@ -78,11 +78,16 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 // single-thread roles (loader, MMA issuer)
 #define CTRL_WAIT(bar, parity, code)                                                     \
     if (ok && !wait_or_abort((bar), (parity), abort_flag)) { atomicCAS(&g_attn_error, 0, (code)); *abort_flag = 1; ok = false; }
-// compute warps (all 32 lanes, result made warp-uniform so aligned TMEM accesses stay converged)
+// compute warps: lane 0 polls the barrier and the warp takes its verdict (one poller per warp
+// keeps 256 threads from hammering a shared-memory barrier that the tensor core's operand reads
+// share a port with); every lane then passes the tcgen05 fence that follows the wait
 #define WARP_WAIT(bar, parity, code)                                                     \
-    do { bool mine_ = ok && wait_or_abort((bar), (parity), abort_flag);                  \
-         if (ok && !mine_) { atomicCAS(&g_attn_error, 0, (code)); *abort_flag = 1; }     \
-         ok = __all_sync(0xffffffffu, mine_); } while (0)
+    do { int mine_ = 1;                                                                  \
+         if (lane == 0) {                                                                \
+             mine_ = ok && wait_or_abort((bar), (parity), abort_flag);                   \
+             if (ok && !mine_) { atomicCAS(&g_attn_error, 0, (code)); *abort_flag = 1; } \
+         }                                                                               \
+         ok = __shfl_sync(0xffffffffu, mine_, 0) != 0; } while (0)
 
 // Tile t of a two-slot ring uses slot t & 1; the barrier of that slot completes once per
 // use, so the completion that belongs to tile t has parity (t >> 1) & 1.
