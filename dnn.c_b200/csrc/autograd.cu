@@ -10,6 +10,7 @@
 #include "device_utils.cuh"
 #include <vector>
 #include <unordered_set>
+#include <unordered_map>
 
 using namespace dnnb;
 
@@ -119,7 +120,17 @@ void grad_settle(tensor *t) {
 
 }  // namespace dnnb
 
+namespace dnnb {
+// Told, during dnn_backward, when the gradient of a leaf (a root tensor without a tape node that
+// requires grad) has received its last contribution.  Used to start the data-parallel exchange of
+// a gradient bucket while backward is still running.
+static void (*g_leaf_ready)(tensor *leaf) = nullptr;
+void set_leaf_ready_observer(void (*fn)(tensor *leaf)) { g_leaf_ready = fn; }
+}  // namespace dnnb
+
 namespace {
+
+inline tensor *root_of(tensor *t) { while (t->parent) t = t->parent; return t; }
 
 struct Topo {
     std::vector<tensor *> order;
@@ -153,17 +164,36 @@ extern "C" void dnn_backward(struct mem_pool *scratch, tensor *loss) {
     k_fill(loss->grad, n, 1.0f);
     loss->grad_fresh = 0;
 
+    // number of tape nodes that still owe each leaf a contribution
+    std::unordered_map<tensor *, int> owed;
+    if (g_leaf_ready)
+        for (tensor *t : topo.order) {
+            grad_fn *fn = t->grad_fn;
+            for (int i = 0; i < fn->n_inputs; i++) {
+                tensor *r = root_of(fn->inputs[i]);
+                if (!r->grad_fn && r->requires_grad) owed[r]++;
+            }
+        }
+
     for (size_t i = topo.order.size(); i-- > 0;) {
         tensor *t = topo.order[i];
         grad_fn *fn = t->grad_fn;
-        if (!fn || !t->grad) continue;
-        tensor gv;
-        memset(&gv, 0, sizeof gv);
-        gv.data = (void *)t->grad;
-        gv.ndim = t->ndim;
-        int s = 1;
-        for (int d = t->ndim - 1; d >= 0; d--) { gv.shape[d] = t->shape[d]; gv.strides[d] = s; s *= t->shape[d]; }
-        gv.contiguous = 1;
-        fn->backward(fn, &gv);
+        if (!fn) continue;
+        if (t->grad) {                       // a node whose output never received a gradient is skipped
+            tensor gv;
+            memset(&gv, 0, sizeof gv);
+            gv.data = (void *)t->grad;
+            gv.ndim = t->ndim;
+            int s = 1;
+            for (int d = t->ndim - 1; d >= 0; d--) { gv.shape[d] = t->shape[d]; gv.strides[d] = s; s *= t->shape[d]; }
+            gv.contiguous = 1;
+            fn->backward(fn, &gv);
+        }
+        if (g_leaf_ready)                    // run or skipped, this node owes its leaves nothing more
+            for (int k = 0; k < fn->n_inputs; k++) {
+                tensor *r = root_of(fn->inputs[k]);
+                auto it = owed.find(r);
+                if (it != owed.end() && --it->second == 0) g_leaf_ready(r);
+            }
     }
 }

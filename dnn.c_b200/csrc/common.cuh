@@ -89,6 +89,12 @@ tensor *attention_from_qkv(struct mem_pool *scratch, tensor *qkv, int H, tensor 
                            attention_mode mode, int prefix_len, const int *seq_lens, bool rotated);
 bool attention_from_qkv_applicable(const tensor *x, int H, int d, const tensor *fc, const tensor *fs);
 
+// dnn_backward tells `fn` when a leaf's gradient has received its last contribution (autograd.cu).
+void set_leaf_ready_observer(void (*fn)(tensor *leaf));
+// Data-parallel exchange overlapped with backward (dp.cu): begin before dnn_backward, finish after.
+bool dp_overlap_begin(tensor **params, int n_params);
+int  dp_overlap_finish();
+
 // Optimiser tail of a captured training step (optim.cu).
 struct OptGraph;
 OptGraph *opt_graph_prepare(adamw_opt *opt, float grad_clip);

@@ -40,9 +40,12 @@ struct StepTail { float gn; };
 
 // backward -> [all-reduce] -> clip / norm -> AdamW; shared by every *_train_step
 float finish_step(struct mem_pool *scratch, tensor *loss, adamw_opt *opt, float grad_clip, bool dp) {
+    // data parallel: from the second step on the buckets of the gradient exchange are sent while
+    // backward still runs; the first step (gradient buffers not allocated yet) exchanges afterwards
+    bool overlapped = dp && dp_overlap_begin(opt->params, opt->n_params);
     dnn_backward(scratch, loss);
     if (dp) {
-        int rc = dnn_cuda_dp_allreduce_grads(opt->params, opt->n_params);
+        int rc = overlapped ? dp_overlap_finish() : dnn_cuda_dp_allreduce_grads(opt->params, opt->n_params);
         DNN_CHECK(rc == 0, "data-parallel gradient all-reduce failed");
     }
     float gn = grad_clip > 0.0f ? clip_grad_norm(opt->params, opt->n_params, grad_clip)

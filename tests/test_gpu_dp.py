@@ -65,13 +65,15 @@ d.close()
 """
 
 
-def test_two_ranks_match_one_rank_with_the_whole_batch(tmp_path):
+@pytest.mark.parametrize("overlap", ["0", "1"], ids=["exchange-after-backward", "exchange-during-backward"])
+def test_two_ranks_match_one_rank_with_the_whole_batch(tmp_path, overlap):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "dp_worker.py"
     script.write_text(WORKER.format(root=ROOT))
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    # small buckets: the exchange of the second step is split into many all-reduces that start during backward
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", DNN_CUDA_BUCKET_BYTES="16384", DNN_CUDA_DP_OVERLAP=overlap)
     single = subprocess.run([sys.executable, str(script), "0", "1", str(tmp_path)], env=env, capture_output=True, text=True, timeout=600)
     assert single.returncode == 0, single.stdout + single.stderr
     procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", str(tmp_path)], env=env, stdout=subprocess.PIPE,
