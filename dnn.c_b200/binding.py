@@ -174,6 +174,11 @@ API = {
     "decoder_lm_init_weights": (None, [VP]),
     "decoder_lm_forward": (TensorP, [PoolP, VP, TensorP]),
     "decoder_lm_shift_targets": (TensorP, [PoolP, TensorP]),
+    "decoder_lm_generate": (C.POINTER(C.c_int), [PoolP, PoolP, VP, TensorP, I, F, I, C.POINTER(C.c_int)]),
+    "decoder_lm_argmax_token": (I, [C.POINTER(C.c_float), I]),
+    "decoder_lm_sample_with_temp": (I, [C.POINTER(C.c_float), I, F]),
+    "kv_cache_create": (VP, [PoolP, I, I, I, I]),
+    "transformer_block_forward_cached": (TensorP, [PoolP, VP, TensorP, VP]),
     "decoder_lm_train_step": (TensorP, [PoolP, VP, TensorP, TensorP, C.POINTER(AdamW), F, C.POINTER(C.c_float)]),
     "vision_lm_create": (VP, [PoolP, I, I, I, I, I, I, I, I, I, I, I]),
     "vision_lm_enable_rope": (None, [PoolP, VP, I, F]),

@@ -1,0 +1,249 @@
+// Evaluation-only generation for the decoder LM: KV cache, cached transformer block, sampling
+// helpers and decoder_lm_generate.  replaces src/transformer.c:28-112,211-416 and
+// src/gpt.c:220-421 of the reference.
+//
+// No tape is built (generation runs with gradients off).  The cache lives in device memory as
+// [B,H,max_seq,d]; a step projects the new tokens, rotates Q and K at their absolute positions,
+// appends K and V to the cache with one strided device copy each, and runs attention of the new
+// queries against everything cached.  That attention has N_new queries (usually one) against S
+// keys, so it is a small bandwidth-bound kernel of its own: one CTA per query row, scores in
+// shared memory.  Differences from the reference that do not change a token: the prompt is
+// pre-filled in one pass instead of token by token; logits travel to the host once per token for
+// the reference's own sampling arithmetic and random stream.
+#include "common.cuh"
+#include "device_utils.cuh"
+#include <vector>
+
+namespace dnnb {
+
+constexpr int kEosId = 258;      // TOKENIZER_EOS_ID of the reference (include/tokenizer.h:24)
+
+// One CTA per (query i, head, batch).  visible(i) = first index the query may NOT see.
+// q: [B,H,Nn,d] packed; k,v: cache with row stride d and head/batch strides; out: [B,H,Nn,d] packed.
+__global__ void attn_cached_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                   float *__restrict__ out, int H, int Nn, int S, int d, int64_t k_sb, int64_t k_sh,
+                                   int old_seq, int prefix, float scale) {
+    extern __shared__ float sc[];                 // S scores, then 32 floats of reduction scratch
+    float *red = sc + S;
+    const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int gq = old_seq + i;
+    int vis = (prefix > 0 && gq < prefix) ? prefix : gq + 1;
+    if (vis > S) vis = S;
+    const float *qr = q + (((int64_t)b * H + h) * Nn + i) * d;
+    const float *kb = k + (int64_t)b * k_sb + (int64_t)h * k_sh;
+    const float *vb = v + (int64_t)b * k_sb + (int64_t)h * k_sh;
+    float mx = -INFINITY;
+    for (int j = threadIdx.x; j < vis; j += blockDim.x) {
+        const float *kr = kb + (int64_t)j * d;
+        float s = 0.f;
+        for (int c = 0; c < d; c++) s += qr[c] * kr[c];
+        s *= scale;
+        sc[j] = s;
+        mx = fmaxf(mx, s);
+    }
+    mx = block_max(mx, red);
+    float se = 0.f;
+    for (int j = threadIdx.x; j < vis; j += blockDim.x) { float e = expf(sc[j] - mx); sc[j] = e; se += e; }
+    se = block_sum(se, red);
+    __syncthreads();
+    const float inv = 1.0f / se;
+    float *orow = out + (((int64_t)b * H + h) * Nn + i) * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < vis; j++) acc += sc[j] * vb[(int64_t)j * d + c];
+        orow[c] = acc * inv;
+    }
+}
+
+}  // namespace dnnb
+
+using namespace dnnb;
+
+extern "C" {
+
+kv_cache *kv_cache_create(struct mem_pool *params_pool, int B, int H, int max_seq, int d_k) {
+    DNN_CHECK(B > 0 && H > 0 && max_seq > 0 && d_k > 0, "kv_cache_create: sizes must be positive");
+    kv_cache *kvc = host_alloc_t<kv_cache>(params_pool);
+    int shape[4] = {B, H, max_seq, d_k};
+    kvc->k_cache = tensor_zeros(params_pool, 4, shape, 0);
+    kvc->v_cache = tensor_zeros(params_pool, 4, shape, 0);
+    kvc->seq_len = 0;
+    kvc->max_seq = max_seq;
+    return kvc;
+}
+
+void kv_cache_append(kv_cache *kvc, const tensor *K_new, const tensor *V_new) {
+    DNN_CHECK(kvc && K_new && V_new, "kv_cache_append: NULL argument");
+    DNN_CHECK(K_new->ndim == 4 && V_new->ndim == 4, "kv_cache_append: inputs must be 4D [B, H, N, d_k]");
+    DNN_CHECK(K_new->contiguous && V_new->contiguous, "kv_cache_append: inputs must be contiguous");
+    int B = K_new->shape[0], H = K_new->shape[1], Nn = K_new->shape[2], D = K_new->shape[3];
+    DNN_CHECK(B == kvc->k_cache->shape[0] && H == kvc->k_cache->shape[1] && D == kvc->k_cache->shape[3], "kv_cache_append: shape mismatch");
+    DNN_CHECK(Nn == V_new->shape[2], "kv_cache_append: K/V seq len mismatch");
+    DNN_CHECK(kvc->seq_len + Nn <= kvc->max_seq, "kv_cache_append: cache full");
+    size_t row = (size_t)Nn * D * 4, pitch = (size_t)kvc->max_seq * D * 4;
+    const tensor *src[2] = {K_new, V_new};
+    tensor *dst[2] = {kvc->k_cache, kvc->v_cache};
+    for (int t = 0; t < 2; t++)
+        CUDA_OK(cudaMemcpy2DAsync((float *)dst[t]->data + dst[t]->offset + (size_t)kvc->seq_len * D, pitch,
+                                  (const float *)src[t]->data + src[t]->offset, row, row, (size_t)B * H,
+                                  cudaMemcpyDeviceToDevice, stream()));
+    kvc->seq_len += Nn;
+}
+
+tensor *kv_cache_get_K(struct mem_pool *scratch, kv_cache *kvc) {
+    DNN_CHECK(kvc && kvc->seq_len > 0, "kv_cache_get_K: empty cache");
+    return tensor_slice(scratch, kvc->k_cache, 2, 0, kvc->seq_len);
+}
+tensor *kv_cache_get_V(struct mem_pool *scratch, kv_cache *kvc) {
+    DNN_CHECK(kvc && kvc->seq_len > 0, "kv_cache_get_V: empty cache");
+    return tensor_slice(scratch, kvc->v_cache, 2, 0, kvc->seq_len);
+}
+
+tensor *transformer_block_forward_cached_ex(struct mem_pool *scratch, transformer_block *block, const tensor *x, kv_cache *cache,
+                                            attention_mode mode, int prefix_len) {
+    DNN_CHECK(block && x && cache, "cached forward: NULL argument");
+    DNN_CHECK(x->contiguous && x->ndim >= 2 && x->shape[x->ndim - 1] == block->d_model, "cached forward: x must be contiguous [.., N, d_model]");
+    DNN_CHECK(!dnn_grad_enabled() || !x->requires_grad, "cached forward is evaluation-only: enter dnn_no_grad first");
+    const int B = x->shape[0], Nn = x->shape[x->ndim - 2], H = block->n_heads, d = block->d_k;
+    if (mode == ATTENTION_PREFIX_LM) DNN_CHECK(cache->seq_len == 0, "prefix-LM prefill requires an empty cache");
+    DNN_CHECK(d <= 1024, "cached forward: head size too large");
+
+    tensor *h = rms_norm_forward(scratch, block->attn_norm, x);
+    tensor *qkv = linear_forward(scratch, block->qkv_proj, h);
+    tensor *q, *k, *v;
+    tensor_split_qkv_heads(scratch, qkv, H, &q, &k, &v);
+    if (block->freqs_cos && block->freqs_sin) {          // new tokens sit at positions [seq_len, seq_len + Nn)
+        tensor *fc = tensor_slice(scratch, block->freqs_cos, 0, cache->seq_len, Nn);
+        tensor *fs = tensor_slice(scratch, block->freqs_sin, 0, cache->seq_len, Nn);
+        q = tensor_rope(scratch, q, fc, fs);
+        k = tensor_rope(scratch, k, fc, fs);
+    }
+    kv_cache_append(cache, k, v);
+    const int S = cache->seq_len, old_seq = S - Nn;
+    int shape[4] = {B, H, Nn, d};
+    tensor *att = tensor_scratch(scratch, 4, shape, 0);
+    size_t smem = ((size_t)S + 32) * sizeof(float);
+    DNN_CHECK(smem <= 200 * 1024, "cached forward: sequence too long for the score buffer");
+    static size_t smem_set = 0;
+    if (smem > 48 * 1024 && smem > smem_set) {
+        CUDA_OK(cudaFuncSetAttribute(attn_cached_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        smem_set = 200 * 1024;
+    }
+    const tensor *kc = cache->k_cache, *vc = cache->v_cache;
+    attn_cached_kernel<<<dim3(Nn, H, B), 128, smem, stream()>>>(
+        (const float *)q->data + q->offset, (const float *)kc->data + kc->offset, (const float *)vc->data + vc->offset,
+        (float *)att->data, H, Nn, S, d, kc->strides[0], kc->strides[1], old_seq,
+        mode == ATTENTION_PREFIX_LM ? prefix_len : 0, 1.0f / sqrtf((float)d));
+    LAUNCHED("attn_cached_kernel");
+    tensor *merged = tensor_merge_heads(scratch, att);
+    tensor *proj = linear_forward(scratch, block->out_proj, merged);
+    tensor *x1 = tensor_add(scratch, x, proj);
+    h = rms_norm_forward(scratch, block->ffn_norm, x1);
+    tensor *ffn = swiglu_ffn_forward(scratch, block->ffn, h);
+    return tensor_add(scratch, x1, ffn);
+}
+
+tensor *transformer_block_forward_cached(struct mem_pool *scratch, transformer_block *block, const tensor *x, kv_cache *cache) {
+    return transformer_block_forward_cached_ex(scratch, block, x, cache, ATTENTION_CAUSAL, 0);
+}
+
+// ── sampling on host logits, the reference's arithmetic and random stream (src/gpt.c:220-256) ──
+int decoder_lm_argmax_token(const float *logits, int vocab_size) {
+    int best = 0;
+    float best_val = logits[0];
+    for (int i = 1; i < vocab_size; i++)
+        if (logits[i] > best_val) { best_val = logits[i]; best = i; }
+    return best;
+}
+
+int decoder_lm_sample_with_temp(const float *logits, int vocab_size, float temp) {
+    float inv_temp = 1.0f / temp, mx = -INFINITY;
+    for (int i = 0; i < vocab_size; i++) { float v = logits[i] * inv_temp; if (v > mx) mx = v; }
+    float sum = 0.0f;
+    for (int i = 0; i < vocab_size; i++) sum += expf(logits[i] * inv_temp - mx);
+    float r = dnn_rng_uniform(dnn_get_rng()), cum = 0.0f;
+    for (int i = 0; i < vocab_size; i++) {
+        cum += expf(logits[i] * inv_temp - mx) / sum;
+        if (r < cum) return i;
+    }
+    return vocab_size - 1;
+}
+
+int *decoder_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_pool, decoder_lm *lm, const tensor *prompt_ids,
+                         int max_new_tokens, float temperature, int use_cache, int *n_out) {
+    DNN_CHECK(lm && prompt_ids && n_out, "generate: NULL argument");
+    DNN_CHECK(prompt_ids->ndim == 2 && prompt_ids->shape[0] == 1 && prompt_ids->contiguous, "generate: prompt_ids must be contiguous [1, N]");
+    DNN_CHECK(max_new_tokens > 0 && temperature >= 0.0f, "generate: bad max_new_tokens / temperature");
+    const int prompt_len = prompt_ids->shape[1], max_len = prompt_len + max_new_tokens, V = lm->vocab_size, D = lm->d_model;
+    int *output = host_alloc_t<int>(data_pool, (size_t)max_len);                    // host ids, as in the reference
+    DNN_CHECK(dnn_cuda_download(prompt_ids, output, (size_t)prompt_len * sizeof(int)) == 0, "generate: cannot read the prompt");
+    int cur = prompt_len;
+    std::vector<float> logits_host((size_t)V);
+    dnn_grad_ctx ng = dnn_no_grad_enter();
+
+    auto pick = [&](const tensor *logits, int row) {                               // logits [1, rows, V]
+        const float *src = (const float *)logits->data + logits->offset + (size_t)row * V;
+        DNN_CHECK(dnn_cuda_memcpy_d2h(logits_host.data(), src, (size_t)V * sizeof(float)) == 0, "generate: cannot read logits");
+        return temperature == 0.0f ? decoder_lm_argmax_token(logits_host.data(), V)
+                                   : decoder_lm_sample_with_temp(logits_host.data(), V, temperature);
+    };
+
+    if (use_cache && lm->n_layers > 0) {
+        const int d_k = lm->blocks[0]->d_k, H = lm->blocks[0]->n_heads;
+        size_t mark = mem_pool_mark(data_pool);                                     // caches are released at the end, output stays
+        std::vector<kv_cache *> caches((size_t)lm->n_layers);
+        for (int i = 0; i < lm->n_layers; i++) caches[(size_t)i] = kv_cache_create(data_pool, 1, H, max_len, d_k);
+        int one_shape[1] = {1};
+        tensor *single = tensor_zeros_data(data_pool, 1, one_shape);
+        // prefill: the whole prompt in one pass (the reference feeds it token by token; same keys, same logits)
+        {
+            int pshape[1] = {prompt_len};
+            tensor *pid = tensor_zeros_data(data_pool, 1, pshape);
+            DNN_CHECK(dnn_cuda_upload(pid, output, (size_t)prompt_len * sizeof(int)) == 0, "generate: upload failed");
+            tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, pid);
+            int hs[3] = {1, prompt_len, D};
+            tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
+            for (int i = 0; i < lm->n_layers; i++) h = transformer_block_forward_cached(scratch_pool, lm->blocks[i], h, caches[(size_t)i]);
+            tensor *last = tensor_slice(scratch_pool, h, 1, prompt_len - 1, 1);
+            tensor *lastc = tensor_contiguous(scratch_pool, last);
+            tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, lastc));
+            int next = pick(logits, 0);
+            mem_pool_reset(scratch_pool);
+            output[cur++] = next;
+            if (next == kEosId) goto done_cached;
+        }
+        while (cur < max_len) {
+            DNN_CHECK(dnn_cuda_upload(single, &output[cur - 1], sizeof(int)) == 0, "generate: upload failed");
+            tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, single);
+            int hs[3] = {1, 1, D};
+            tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
+            for (int i = 0; i < lm->n_layers; i++) h = transformer_block_forward_cached(scratch_pool, lm->blocks[i], h, caches[(size_t)i]);
+            tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, h));
+            int next = pick(logits, 0);
+            mem_pool_reset(scratch_pool);
+            output[cur++] = next;
+            if (next == kEosId) break;
+        }
+done_cached:
+        dnn_cuda_sync();
+        mem_pool_release(data_pool, mark);
+    } else {
+        while (cur < max_len) {
+            size_t mark = mem_pool_mark(data_pool);
+            int ishape[2] = {1, cur};
+            tensor *ids = tensor_zeros_data(data_pool, 2, ishape);
+            DNN_CHECK(dnn_cuda_upload(ids, output, (size_t)cur * sizeof(int)) == 0, "generate: upload failed");
+            tensor *logits = decoder_lm_forward(scratch_pool, lm, ids);
+            int next = pick(logits, cur - 1);
+            mem_pool_reset(scratch_pool);
+            mem_pool_release(data_pool, mark);
+            output[cur++] = next;
+            if (next == kEosId) break;
+        }
+    }
+    dnn_no_grad_exit(ng);
+    *n_out = cur;
+    return output;
+}
+
+}  // extern "C"

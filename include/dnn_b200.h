@@ -323,6 +323,24 @@ tensor *transformer_block_forward_ex(struct mem_pool *scratch, transformer_block
                                      attention_mode mode, int prefix_len, const int *seq_lens);
 tensor *transformer_block_forward(struct mem_pool *scratch, transformer_block *block, const tensor *x);
 
+/* KV cache and cached block forward for generation (evaluation only, no tape).
+ * replaces include/transformer.h:26-128 (src/transformer.c:28-112,211-416).
+ * k_cache / v_cache are [B, H, max_seq, d_k] device tensors. */
+typedef struct {
+    tensor *k_cache;
+    tensor *v_cache;
+    int     seq_len;
+    int     max_seq;
+} kv_cache;
+kv_cache *kv_cache_create(struct mem_pool *params_pool, int B, int H, int max_seq, int d_k);
+void      kv_cache_append(kv_cache *kvc, const tensor *K_new, const tensor *V_new);
+tensor   *kv_cache_get_K(struct mem_pool *scratch, kv_cache *kvc);
+tensor   *kv_cache_get_V(struct mem_pool *scratch, kv_cache *kvc);
+tensor *transformer_block_forward_cached_ex(struct mem_pool *scratch, transformer_block *block, const tensor *x,
+                                            kv_cache *cache, attention_mode mode, int prefix_len);
+tensor *transformer_block_forward_cached(struct mem_pool *scratch, transformer_block *block, const tensor *x,
+                                         kv_cache *cache);
+
 typedef struct {
     module              base;
     embedding          *embed;
@@ -348,6 +366,13 @@ tensor *decoder_lm_forward(struct mem_pool *scratch, decoder_lm *lm, const tenso
 tensor *decoder_lm_shift_targets(struct mem_pool *pool, const tensor *input_ids);
 tensor *decoder_lm_train_step(struct mem_pool *scratch_pool, decoder_lm *lm, const tensor *input_ids,
                               const tensor *target, adamw_opt *opt, float grad_clip, float *grad_norm_out);
+/* Generation (src/gpt.c:220-421): sampling helpers work on HOST logits with the reference's
+ * arithmetic and random stream; decoder_lm_generate returns host token ids (prompt + new) allocated
+ * from data_pool, batch 1, stops at token 258 (the reference tokenizer's end-of-sequence id). */
+int  decoder_lm_argmax_token(const float *logits, int vocab_size);
+int  decoder_lm_sample_with_temp(const float *logits, int vocab_size, float temp);
+int *decoder_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_pool, decoder_lm *lm,
+                         const tensor *prompt_ids, int max_new_tokens, float temperature, int use_cache, int *n_out);
 void    decoder_lm_enable_rope(struct mem_pool *params_pool, decoder_lm *lm, int max_seq_len, float base);
 void    decoder_lm_init_weights(decoder_lm *lm);
 long long decoder_lm_num_parameters(decoder_lm *lm);

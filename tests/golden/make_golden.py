@@ -44,6 +44,15 @@ def main():
     ref.close()
     np.savez_compressed(os.path.join(HERE, "ops.npz"), **ops)
 
+    gen = {}
+    for name, over, prompt, max_new, temp, use_cache in models.GEN_CASES:
+        d = B.Dnn(REF_LIB, params_mb=64, scratch_mb=512, data_mb=64)
+        cfg = dict(models.lm_config("tiny")); cfg.update(over)
+        gen[name] = np.array(models.run_generate(d, cfg, prompt, max_new, temp, use_cache, seed=77), np.int32)
+        d.close()
+        print("generate", name, gen[name].tolist())
+    np.savez_compressed(os.path.join(HERE, "generate.npz"), **gen)
+
     mdl = {}
 
     def model(tag, fn, **kw):

@@ -79,6 +79,30 @@ def run_lm(dnn, cfg, steps=1, want_grads=True):
     return out
 
 
+def run_generate(dnn, cfg, prompt, max_new, temperature, use_cache, seed=0):
+    """decoder_lm_generate on a seeded model; returns the token list (prompt + new)."""
+    lib = dnn.lib
+    lm = lib.decoder_lm_create(dnn.params, cfg["V"], cfg["D"], cfg["L"], cfg["H"], cfg["D"] // cfg["H"], cfg["F"])
+    lib.decoder_lm_enable_rope(dnn.params, lm, len(prompt) + max_new, 10000.0)
+    names = O.lm_param_names(cfg["L"])
+    seeded_weights(dnn, lm, names, cfg["seed"] + 100, std=0.3)       # large weights: peaked logits, argmax far from ties
+    lib.dnn_seed(seed)
+    ids = dnn.tensor(np.asarray(prompt, np.int32).reshape(1, -1), dnn.data)
+    n = C.c_int(0)
+    out = lib.decoder_lm_generate(dnn.scratch, dnn.data, lm, ids, max_new, temperature, use_cache, C.byref(n))
+    toks = [int(out[i]) for i in range(n.value)]
+    dnn.reset_step()
+    return toks
+
+
+GEN_CASES = [   # name, config overrides, prompt, max_new, temperature, use_cache
+    ("greedy-cache", dict(V=64, D=32, L=2, H=2, F=64), [3, 17, 42, 5, 9], 12, 0.0, 1),
+    ("greedy-nocache", dict(V=64, D=32, L=2, H=2, F=64), [3, 17, 42, 5, 9], 12, 0.0, 0),
+    ("sampled-cache", dict(V=64, D=32, L=2, H=2, F=64), [1, 2, 3], 10, 0.8, 1),
+    ("greedy-cache-d32", dict(V=96, D=128, L=2, H=4, F=256), [7, 90, 33, 2, 11, 64, 5], 9, 0.0, 1),
+]
+
+
 # ── MNIST-shaped CNN (BASELINE config 3) ──────────────────────────────────
 CNN_NAMES = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
 
