@@ -48,6 +48,7 @@ float *_grad_ensure(tensor *t) {
         k_fill(base->grad, numel_of(base), 0.0f);
         base->grad_fresh = 0;
     }
+    dnnb::colsum_cache_forget(base->grad);        // the caller is about to write this buffer
     return base->grad;
 }
 
@@ -73,6 +74,7 @@ float *grad_full(tensor *t, bool *accumulate) {
     } else {
         *accumulate = true;
     }
+    colsum_cache_forget(base->grad);
     return base->grad;
 }
 
@@ -105,6 +107,7 @@ float *grad_rows(tensor *t, bool *accumulate) {
         base->grad = (float *)dev_alloc(base->pool, (size_t)total * sizeof(float), false);
     }
     base->grad_fresh = 0;
+    colsum_cache_forget(base->grad);
     if (pitch > inner) {
         int64_t gaps = (int64_t)t->shape[0] * (pitch - inner);
         zero_outside_kernel<<<grid_for(gaps, 256), 256, 0, stream()>>>(base->grad, pitch, t->shape[0], lo, lo + inner);
@@ -155,6 +158,7 @@ extern "C" void dnn_backward(struct mem_pool *scratch, tensor *loss) {
     DNN_CHECK(loss, "dnn_backward: loss is NULL");
     Topo topo;
     topo.visit(loss);
+    colsum_cache_forget(nullptr);                // cached column sums never outlive one backward pass
 
     int64_t n = numel_of(loss);
     if (!loss->grad) {
@@ -196,4 +200,5 @@ extern "C" void dnn_backward(struct mem_pool *scratch, tensor *loss) {
                 if (it != owed.end() && --it->second == 0) g_leaf_ready(r);
             }
     }
+    colsum_cache_forget(nullptr);
 }

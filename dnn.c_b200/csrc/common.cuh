@@ -123,6 +123,11 @@ grad_fn *attach(struct mem_pool *scratch, tensor *out, void (*bw)(grad_fn *, ten
                 int n_inputs, int n_saved);
 
 // ---- kernel-side entry points used across files -------------------------
+// column sums left behind by the kernel that wrote a gradient buffer (kernels_common.cu)
+float *colsum_cache_reserve(int C);
+void colsum_cache_publish(const float *src, int64_t rows, int C);
+void colsum_cache_forget(const void *buffer);          // nullptr: forget whatever is cached
+void k_colsum_finish(float *sums, const float *partial, int nparts, int C);
 void k_fill(float *p, int64_t n, float v);
 void k_axpy_acc(float *dst, const float *src, int64_t n);                 // dst += src
 void k_copy(float *dst, const float *src, int64_t n);

@@ -183,6 +183,38 @@ __global__ void colsum_final_kernel(float *__restrict__ out, const float *__rest
     out[c] = acc ? out[c] + s : s;
 }
 
+// ── column sums a producer has already computed ──────────────────────────────
+// A backward kernel that writes a whole gradient buffer can sum its columns on the way (the
+// bias gradient of the layer that consumes the buffer needs exactly that) and leave the sums
+// here.  k_colsum_acc uses them when it is asked for the same buffer, rows and width, which saves
+// a pass over the buffer.  The entry dies with any later write to the buffer (the gradient
+// helpers call colsum_cache_forget) and at both ends of dnn_backward.
+struct ColsumCache { const float *src = nullptr; int64_t rows = 0; int C = 0; float *sums = nullptr; size_t cap = 0; bool valid = false; };
+static ColsumCache g_cc;
+float *colsum_cache_reserve(int C) {
+    if ((size_t)C > g_cc.cap) {
+        CUDA_OK(cudaStreamSynchronize(stream()));
+        if (g_cc.sums) CUDA_OK(cudaFree(g_cc.sums));
+        g_cc.cap = (size_t)C * 2;
+        CUDA_OK(cudaMalloc((void **)&g_cc.sums, g_cc.cap * sizeof(float)));
+    }
+    g_cc.valid = false;
+    return g_cc.sums;
+}
+void colsum_cache_publish(const float *src, int64_t rows, int C) { g_cc.src = src; g_cc.rows = rows; g_cc.C = C; g_cc.valid = true; }
+void colsum_cache_forget(const void *buffer) { if (buffer == nullptr || buffer == (const void *)g_cc.src) g_cc.valid = false; }
+
+__global__ void colsum_apply_kernel(float *__restrict__ out, const float *__restrict__ sums, int C, int acc) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < C) out[c] = acc ? out[c] + sums[c] : sums[c];
+}
+
+// Partials [nparts, C] -> sums[C] in slab order (deterministic); used by producers that leave sums in the cache.
+void k_colsum_finish(float *sums, const float *partial, int nparts, int C) {
+    colsum_final_kernel<<<(C + 127) / 128, 128, 0, stream()>>>(sums, partial, nparts, C, 0);
+    LAUNCHED("colsum_final_kernel");
+}
+
 // Scratch for the partials lives in a small cache owned by this file, grown
 // on demand (never shrinks; one per process).
 static float *g_colsum_scratch = nullptr;
@@ -190,6 +222,11 @@ static size_t g_colsum_cap = 0;
 
 void k_colsum_acc(float *out, const float *g, int64_t rows, int C, bool accumulate) {
     if (rows <= 0 || C <= 0) return;
+    if (g_cc.valid && g_cc.src == g && g_cc.rows == rows && g_cc.C == C) {          // the producer of g left its column sums
+        colsum_apply_kernel<<<(C + 255) / 256, 256, 0, stream()>>>(out, g_cc.sums, C, accumulate ? 1 : 0);
+        LAUNCHED("colsum_apply_kernel");
+        return;
+    }
     int nparts = (int)((rows + 255) / 256);
     if (nparts > 512) nparts = 512;
     int rows_per = (int)((rows + nparts - 1) / nparts);

@@ -152,6 +152,51 @@ __global__ void ce_bwd_kernel(const float *__restrict__ logits, const int *__res
     }
 }
 
+// The same gradient, tiled so that the column sums of what is written come for free: CTA
+// (32 x 8 threads) = 128 classes x one slab of slices; a thread walks its slab 8 slices at a
+// time with one float4 of classes, stores the gradient and keeps the running column sums, which
+// end up in partial[slab][C].  The consumer of d(logits) is normally a linear layer whose bias
+// gradient is exactly these sums.  Only for stores into a fresh buffer (acc = 0) with packed
+// classes; one CTA per slice (above) serves everything else.
+__global__ void __launch_bounds__(256)
+ce_bwd_colsum_kernel(const float *__restrict__ logits, const int *__restrict__ target, const float *__restrict__ mask, SliceMap map,
+                     const float *__restrict__ max_in, const float *__restrict__ se_in, const float *__restrict__ gout,
+                     const float *__restrict__ inv, float *__restrict__ dlogits, float *__restrict__ partial,
+                     int64_t n_slices, int slices_per) {
+    __shared__ float4 tile[8][33];
+    const int C = map.C, c = (blockIdx.x * 32 + threadIdx.x) * 4;
+    const int64_t s0 = (int64_t)blockIdx.y * slices_per;
+    int64_t s1 = s0 + slices_per; if (s1 > n_slices) s1 = n_slices;
+    const float base_scale = gout[0] * inv[0];
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < C)
+        for (int64_t s = s0 + threadIdx.y; s < s1; s += 8) {
+            int64_t lo, mo;
+            slice_offsets(map, s, lo, mo);
+            const float m = mask ? mask[mo] : 1.0f;
+            float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!(mask && m == 0.0f)) {
+                const float4 v = *reinterpret_cast<const float4 *>(logits + lo + c);
+                const float mx = max_in[s], se = se_in[s], scale = mask ? base_scale * m : base_scale;
+                const int tgt = target[s];
+                d.x = (expf(v.x - mx) / se - (c == tgt ? 1.f : 0.f)) * scale;
+                d.y = (expf(v.y - mx) / se - (c + 1 == tgt ? 1.f : 0.f)) * scale;
+                d.z = (expf(v.z - mx) / se - (c + 2 == tgt ? 1.f : 0.f)) * scale;
+                d.w = (expf(v.w - mx) / se - (c + 3 == tgt ? 1.f : 0.f)) * scale;
+            }
+            *reinterpret_cast<float4 *>(dlogits + lo + c) = d;
+            sum.x += d.x; sum.y += d.y; sum.z += d.z; sum.w += d.w;
+        }
+    tile[threadIdx.y][threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; j++) { float4 v = tile[j][threadIdx.x]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+        *reinterpret_cast<float4 *>(partial + (int64_t)blockIdx.y * C + c) = t;
+    }
+}
+
 static SliceMap make_map(const tensor *logits, const tensor *mask, int dim) {
     SliceMap m;
     memset(&m, 0, sizeof m);
@@ -186,6 +231,28 @@ static void ce_backward_common(grad_fn *fn, tensor *go, bool masked) {
     if (n_slices <= 0) return;
     bool acc = true;
     float *ag = grad_rows(logits, &acc);
+    // Fresh buffer, packed classes, every slice 16-byte aligned: tiled kernel that also leaves the
+    // column sums of d(logits) for the layer that consumes it.
+    tensor *root = logits; while (root->parent) root = root->parent;
+    bool aligned = aligned16(logits->data) && aligned16(ag) && (logits->offset % 4 == 0);
+    for (int k = 0; k < map.nd && aligned; k++) aligned = map.lstride[k] % 4 == 0;
+    if (!acc && map.cstride == 1 && map.C % 4 == 0 && aligned && root->ndim >= 2 && root->contiguous &&
+        root->shape[root->ndim - 1] == map.C && n_slices >= 64) {
+        int nslabs = (int)((n_slices + 255) / 256);
+        if (nslabs > 256) nslabs = 256;
+        int per = (int)((n_slices + nslabs - 1) / nslabs);
+        nslabs = (int)((n_slices + per - 1) / per);
+        float *partial = dev_alloc_t<float>(fn->pool, (size_t)nslabs * map.C);
+        float *sums = colsum_cache_reserve(map.C);
+        dim3 grid((map.C / 4 + 31) / 32, nslabs), block(32, 8);
+        ce_bwd_colsum_kernel<<<grid, block, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
+            mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, ag, partial, n_slices, per);
+        LAUNCHED(masked ? "ce_masked_bwd_kernel" : "ce_bwd_kernel");
+        k_colsum_finish(sums, partial, nslabs, map.C);
+        // rows of the root that the slices do not cover were zero-filled: they add nothing to the sums
+        colsum_cache_publish(ag, numel_of(root) / map.C, map.C);
+        return;
+    }
     ce_bwd_kernel<<<(unsigned)n_slices, 256, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
         mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, ag, acc ? 1 : 0);
     LAUNCHED(masked ? "ce_masked_bwd_kernel" : "ce_bwd_kernel");

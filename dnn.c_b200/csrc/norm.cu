@@ -181,9 +181,13 @@ norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w,
     if (lane == 0) { bar_init(&bars[0], 1); bar_init(&bars[1], 1); asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
     __syncwarp();
     const float inv_d = 1.0f / (float)d;
-    float4 aw[T], ab[LN ? T : 1];
+    float4 aw[T], ab[LN ? T : 1], wr[T];          // wr: this lane's weights, the same for every row
 #pragma unroll
-    for (int t = 0; t < T; t++) { aw[t] = make_float4(0.f, 0.f, 0.f, 0.f); if (LN) ab[t] = aw[t]; }
+    for (int t = 0; t < T; t++) {
+        aw[t] = make_float4(0.f, 0.f, 0.f, 0.f); if (LN) ab[t] = aw[t];
+        int j = (lane + 32 * t) * 4;
+        wr[t] = (w && j < d) ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+    }
     auto fetch = [&](int64_t r, int b) {
         if (lane == 0) {
             bar_expect(&bars[b], 2 * row_bytes);
@@ -197,8 +201,9 @@ norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w,
         const int b = it & 1;
         if (r + nwarps < rows) fetch(r + nwarps, b ^ 1);       // the other buffer was consumed in the previous trip
         const float rs = rstd[r], mu = LN ? mean[r] : 0.f;
-        bool ok = bar_wait(&bars[b], (uint32_t)(it >> 1) & 1u);
-        if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) atomicCAS(&g_norm_error, 0, 1); break; }
+        int ok = 1;
+        if (lane == 0) ok = bar_wait(&bars[b], (uint32_t)(it >> 1) & 1u);       // one poller per warp
+        if (!__shfl_sync(0xffffffffu, ok, 0)) { if (lane == 0) atomicCAS(&g_norm_error, 0, 1); break; }
         const float *xs = buf + (size_t)b * 2 * d, *gs = xs + d;
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -206,7 +211,7 @@ norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w,
             int j = (lane + 32 * t) * 4;
             if (j < d) {
                 float4 v = ld4(xs + j), gg = ld4(gs + j);
-                float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+                const float4 ww = wr[t];
                 v.x -= mu; v.y -= mu; v.z -= mu; v.w -= mu;
                 s1 += gg.x * ww.x * v.x + gg.y * ww.y * v.y + gg.z * ww.z * v.z + gg.w * ww.w * v.w;
                 if (LN) s2 += gg.x * ww.x + gg.y * ww.y + gg.z * ww.z + gg.w * ww.w;
@@ -227,7 +232,7 @@ norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w,
                 int j = (lane + 32 * t) * 4;
                 if (j < d) {
                     float4 v = ld4(xs + j), gg = ld4(gs + j);
-                    float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+                    const float4 ww = wr[t];
                     float4 o = acc_dx ? ld4(dxr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
                     v.x -= mu; v.y -= mu; v.z -= mu; v.w -= mu;
                     o.x += rs * (gg.x * ww.x - mdy) - rs * k1 * v.x; o.y += rs * (gg.y * ww.y - mdy) - rs * k1 * v.y;

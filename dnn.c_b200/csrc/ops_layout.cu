@@ -182,28 +182,28 @@ __global__ void emb_count_kernel(const int *__restrict__ ids, int n, int vocab, 
     int id = ids[i];
     if (id >= 0 && id < vocab) atomicAdd(&count[id], 1);
 }
-// start[v] = sum of count[0..v); one CTA walks the vocabulary in chunks of its size
+// start[v] = sum of count[0..v).  One CTA of 1024 threads: every thread owns a contiguous run of
+// the vocabulary, the 1024 run totals are scanned with warp shuffles, then each thread writes the
+// exclusive prefix of its run.
 __global__ void emb_scan_kernel(const int *__restrict__ count, int vocab, int *__restrict__ start) {
-    __shared__ int sh[1024];
-    __shared__ int carry;
-    if (threadIdx.x == 0) carry = 0;
+    __shared__ int warp_tot[32];
+    const int per = (vocab + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int lo = threadIdx.x * per, hi = min(lo + per, vocab);
+    int tot = 0;
+    for (int v = lo; v < hi; v++) tot += count[v];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int incl = tot;
+    for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+    if (lane == 31) warp_tot[wid] = incl;
     __syncthreads();
-    for (int v0 = 0; v0 < vocab; v0 += blockDim.x) {
-        int v = v0 + threadIdx.x;
-        int c = v < vocab ? count[v] : 0;
-        sh[threadIdx.x] = c;
-        __syncthreads();
-        for (int off = 1; off < (int)blockDim.x; off <<= 1) {
-            int t = threadIdx.x >= off ? sh[threadIdx.x - off] : 0;
-            __syncthreads();
-            sh[threadIdx.x] += t;
-            __syncthreads();
-        }
-        if (v < vocab) start[v] = carry + sh[threadIdx.x] - c;
-        __syncthreads();
-        if (threadIdx.x == blockDim.x - 1) carry += sh[threadIdx.x];
-        __syncthreads();
+    if (wid == 0) {
+        int w = lane < (int)(blockDim.x >> 5) ? warp_tot[lane] : 0, wi = w;
+        for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
+        warp_tot[lane] = wi - w;                      // exclusive prefix of the warp totals
     }
+    __syncthreads();
+    int run = warp_tot[wid] + incl - tot;             // exclusive prefix of this thread's run
+    for (int v = lo; v < hi; v++) { start[v] = run; run += count[v]; }
 }
 __global__ void emb_fill_kernel(const int *__restrict__ ids, int n, int vocab, const int *__restrict__ start,
                                 int *__restrict__ cursor, int *__restrict__ list) {
