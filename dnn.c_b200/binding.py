@@ -175,6 +175,7 @@ API = {
     "decoder_lm_forward": (TensorP, [PoolP, VP, TensorP]),
     "decoder_lm_shift_targets": (TensorP, [PoolP, TensorP]),
     "decoder_lm_generate": (C.POINTER(C.c_int), [PoolP, PoolP, VP, TensorP, I, F, I, C.POINTER(C.c_int)]),
+    "vision_lm_generate": (C.POINTER(C.c_int), [PoolP, PoolP, VP, TensorP, TensorP, I, F, I, C.POINTER(C.c_int)]),
     "decoder_lm_argmax_token": (I, [C.POINTER(C.c_float), I]),
     "decoder_lm_sample_with_temp": (I, [C.POINTER(C.c_float), I, F]),
     "kv_cache_create": (VP, [PoolP, I, I, I, I]),
@@ -213,6 +214,12 @@ CUDA_API = {
     "dnn_cuda_get_fused_attention": (I, []),
     "dnn_cuda_colsum_acc_static": (I, [VP, VP, C.c_longlong, I]),
     "dnn_cuda_colsum_acc_static_error": (C.c_char_p, []),
+    "dnn_cuda_vlm_stager_create": (VP, [I, I, I, I, I, I, I, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "dnn_cuda_vlm_stager_destroy": (None, [VP]),
+    "dnn_cuda_vlm_stager_put": (I, [VP, I, I, C.POINTER(C.c_int), I, VP, I, I]),
+    "dnn_cuda_vlm_stager_submit": (I, [VP, I, I]),
+    "dnn_cuda_vlm_stager_assemble": (I, [VP, I, TensorP, TensorP, TensorP, TensorP, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "dnn_cuda_vlm_stager_error": (C.c_char_p, []),
     "dnn_cuda_launch_count": (C.c_longlong, []),
     "dnn_cuda_timer_start": (I, []),
     "dnn_cuda_timer_stop_ms": (F, []),

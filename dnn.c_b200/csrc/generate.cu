@@ -1,6 +1,6 @@
-// Evaluation-only generation for the decoder LM: KV cache, cached transformer block, sampling
-// helpers and decoder_lm_generate.  replaces src/transformer.c:28-112,211-416 and
-// src/gpt.c:220-421 of the reference.
+// Evaluation-only generation for the decoder LM and the vision LM: KV cache, cached transformer
+// block, sampling helpers, decoder_lm_generate and vision_lm_generate.  replaces
+// src/transformer.c:28-112,211-416, src/gpt.c:220-421 and src/vlm.c:436-611 of the reference.
 //
 // No tape is built (generation runs with gradients off).  The cache lives in device memory as
 // [B,H,max_seq,d]; a step projects the new tokens, rotates Q and K at their absolute positions,
@@ -235,6 +235,90 @@ done_cached:
             DNN_CHECK(dnn_cuda_upload(ids, output, (size_t)cur * sizeof(int)) == 0, "generate: upload failed");
             tensor *logits = decoder_lm_forward(scratch_pool, lm, ids);
             int next = pick(logits, cur - 1);
+            mem_pool_reset(scratch_pool);
+            mem_pool_release(data_pool, mark);
+            output[cur++] = next;
+            if (next == kEosId) break;
+        }
+    }
+    dnn_no_grad_exit(ng);
+    *n_out = cur;
+    return output;
+}
+
+// vision_lm_generate (src/vlm.c:436-611 of the reference): batch 1, image [1,C,H,W] or pre-patched
+// [1,I,C*P*P].  With a cache the image tokens and the prompt are pre-filled together under the
+// prefix-LM mask and the image embeddings go in WITHOUT the learned image positions (the reference's
+// cached path calls vision_lm_image_embeds directly, src/vlm.c:505); without a cache every token
+// reruns vision_lm_forward, which adds them.  Both behaviours are kept.
+int *vision_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_pool, vision_lm *vlm, const tensor *image,
+                        const tensor *prompt_ids, int max_new_tokens, float temperature, int use_cache, int *n_out) {
+    DNN_CHECK(vlm && image && prompt_ids && n_out, "vision_lm_generate: NULL argument");
+    DNN_CHECK((image->ndim == 4 || image->ndim == 3) && image->shape[0] == 1 && image->contiguous,
+              "vision_lm_generate: image must be contiguous [1,C,H,W] or [1,patches,patch_dim]");
+    DNN_CHECK(prompt_ids->ndim == 2 && prompt_ids->shape[0] == 1 && prompt_ids->contiguous, "vision_lm_generate: prompt_ids must be contiguous [1, T]");
+    DNN_CHECK(max_new_tokens > 0 && temperature >= 0.0f, "vision_lm_generate: bad max_new_tokens / temperature");
+    decoder_lm *lm = vlm->lm;
+    const int prompt_len = prompt_ids->shape[1], max_len = prompt_len + max_new_tokens;
+    const int V = vlm->vocab_size, D = vlm->d_model, I = vlm->n_img_tokens;
+    // the image moves to the data pool so that it survives the scratch resets between tokens
+    tensor *img_keep = tensor_zeros_data(data_pool, image->ndim, image->shape);
+    CUDA_OK(cudaMemcpyAsync(img_keep->data, (const float *)image->data + image->offset, (size_t)numel_of(image) * sizeof(float),
+                            cudaMemcpyDeviceToDevice, stream()));
+    int *output = host_alloc_t<int>(data_pool, (size_t)max_len);
+    DNN_CHECK(dnn_cuda_download(prompt_ids, output, (size_t)prompt_len * sizeof(int)) == 0, "vision_lm_generate: cannot read the prompt");
+    int cur = prompt_len;
+    std::vector<float> logits_host((size_t)V);
+    dnn_grad_ctx ng = dnn_no_grad_enter();
+
+    auto pick = [&](const tensor *logits, int row) {
+        const float *src = (const float *)logits->data + logits->offset + (size_t)row * V;
+        DNN_CHECK(dnn_cuda_memcpy_d2h(logits_host.data(), src, (size_t)V * sizeof(float)) == 0, "vision_lm_generate: cannot read logits");
+        return temperature == 0.0f ? decoder_lm_argmax_token(logits_host.data(), V)
+                                   : decoder_lm_sample_with_temp(logits_host.data(), V, temperature);
+    };
+
+    if (use_cache && lm->n_layers > 0) {
+        const int d_k = lm->blocks[0]->d_k, H = lm->blocks[0]->n_heads;
+        size_t mark = mem_pool_mark(data_pool);
+        std::vector<kv_cache *> caches((size_t)lm->n_layers);
+        for (int i = 0; i < lm->n_layers; i++) caches[(size_t)i] = kv_cache_create(data_pool, 1, H, I + max_len, d_k);
+        int one_shape[1] = {1};
+        tensor *single = tensor_zeros_data(data_pool, 1, one_shape);
+        int next;
+        {   // prefill: image tokens and prompt in one prefix-LM pass
+            tensor *img = vision_lm_image_embeds(scratch_pool, vlm, img_keep);
+            tensor *txt = decoder_lm_token_embeds(scratch_pool, lm, prompt_ids);
+            tensor *h = tensor_cat(scratch_pool, img, txt, 1);
+            for (int i = 0; i < lm->n_layers; i++)
+                h = transformer_block_forward_cached_ex(scratch_pool, lm->blocks[i], h, caches[(size_t)i], ATTENTION_PREFIX_LM, I);
+            tensor *lastc = tensor_contiguous(scratch_pool, tensor_slice(scratch_pool, h, 1, I + prompt_len - 1, 1));
+            tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, lastc));
+            next = pick(logits, 0);
+            mem_pool_reset(scratch_pool);
+            output[cur++] = next;
+        }
+        while (next != kEosId && cur < max_len) {
+            DNN_CHECK(dnn_cuda_upload(single, &output[cur - 1], sizeof(int)) == 0, "vision_lm_generate: upload failed");
+            tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, single);
+            int hs[3] = {1, 1, D};
+            tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
+            for (int i = 0; i < lm->n_layers; i++) h = transformer_block_forward_cached(scratch_pool, lm->blocks[i], h, caches[(size_t)i]);
+            tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, h));
+            next = pick(logits, 0);
+            mem_pool_reset(scratch_pool);
+            output[cur++] = next;
+        }
+        dnn_cuda_sync();
+        mem_pool_release(data_pool, mark);
+    } else {
+        while (cur < max_len) {
+            size_t mark = mem_pool_mark(data_pool);
+            int ishape[2] = {1, cur};
+            tensor *ids = tensor_zeros_data(data_pool, 2, ishape);
+            DNN_CHECK(dnn_cuda_upload(ids, output, (size_t)cur * sizeof(int)) == 0, "vision_lm_generate: upload failed");
+            tensor *logits = vision_lm_forward(scratch_pool, vlm, img_keep, ids);
+            int next = pick(logits, I + cur - 1);
             mem_pool_reset(scratch_pool);
             mem_pool_release(data_pool, mark);
             output[cur++] = next;

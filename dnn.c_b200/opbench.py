@@ -18,6 +18,7 @@ import importlib.util
 import json
 import os
 import sys
+import time
 
 import numpy as np
 
@@ -185,7 +186,6 @@ def main():
         # BASELINE config 1 (V 256, d 128, 4 blocks, 4 heads, FFN 512, batch 16 x 128): kernels of a
         # few microseconds, so the step is bound by launch overhead; eager steps against replays of
         # the recorded step, wall time per step including the loss read-back
-        import time
         V, D, L, H, F, Bsz, N = 256, 128, 4, 4, 512, 16, 128
         if args.shapes == "gpt124m":                      # BASELINE config 5 instead: GPU-bound, shows what launch gaps cost
             V, D, L, H, F, Bsz, N = 32000, 768, 12, 12, 2048, 16, 1024
@@ -224,6 +224,72 @@ def main():
                           "kernels_per_step": int(per_step), "eager_ms_per_step": round(ms_eager, 3), "graph_ms_per_step": round(ms_graph, 3),
                           "eager_tokens_per_s": round(Bsz * N / ms_eager * 1e3), "graph_tokens_per_s": round(Bsz * N / ms_graph * 1e3),
                           "speedup": round(ms_eager / ms_graph, 2)}), flush=True)
+    if "vlm_batch" in ops:
+        # Padded vision-LM batch of BASELINE config 4 (64 images 3x224x224, texts up to 32): device assembly alone
+        # (uint8 HWC -> normalised NCHW floats, ids / targets / mask rows) and the whole put + upload + assemble
+        # pipeline over two slots, beside the upload of the same batch as ready-made floats.
+        Bsz, Hh, Ww, Cc, Tm = (8 if args.small else 64), 224, 224, 3, 32
+        mean, std = (C.c_float * 3)(0.485, 0.456, 0.406), (C.c_float * 3)(0.229, 0.224, 0.225)
+        st = lib.dnn_cuda_vlm_stager_create(2, Bsz, Tm, Hh, Ww, Cc, 0, mean, std)
+        px = rng.integers(0, 256, size=(Bsz, Hh, Ww, Cc)).astype(np.uint8)
+        texts = [rng.integers(0, 257, size=int(rng.integers(7, Tm))).astype(np.int32) for _ in range(Bsz)]
+
+        def stage(slot):
+            for i in range(Bsz):
+                lib.dnn_cuda_vlm_stager_put(st, slot, i, texts[i].ctypes.data_as(C.POINTER(C.c_int)), len(texts[i]),
+                                            px[i].ctypes.data_as(C.c_void_p), i & 1, i)
+            lib.dnn_cuda_vlm_stager_submit(st, slot, Bsz)
+
+        def tensors():
+            return (lib.tensor_scratch(d.scratch, 4, B.ints([Bsz, Cc, Hh, Ww]), 0), lib.tensor_zeros_data(d.data, 2, B.ints([Bsz, Tm])),
+                    lib.tensor_zeros_data(d.data, 2, B.ints([Bsz, Tm])), lib.tensor_scratch(d.scratch, 2, B.ints([Bsz, Tm]), 0))
+
+        ts = []
+        for it in range(3 + args.iters):
+            d.reset_step()
+            stage(0)
+            img, ids, tgt, mask = tensors()
+            lib.dnn_cuda_sync()                    # the copy stream is not the compute stream: wait for the upload on the host
+            time.sleep(0.01)
+            b.flush_l2()
+            ms = b.time(lambda: lib.dnn_cuda_vlm_stager_assemble(st, 0, img, ids, tgt, mask, None, None))
+            if it >= 3:
+                ts.append(ms)
+        ms_dev = float(np.median(ts))
+        dev_bytes = Bsz * Hh * Ww * Cc * 5 + Bsz * Tm * 16
+        reps = 20
+        d.reset_step()
+        stage(0)
+        lib.dnn_cuda_sync()
+        t0 = time.perf_counter()
+        for r in range(reps):
+            stage((r + 1) & 1)                     # fill and upload the next slot while this one is assembled
+            img, ids, tgt, mask = tensors()
+            lib.dnn_cuda_vlm_stager_assemble(st, r & 1, img, ids, tgt, mask, None, None)
+            lib.dnn_cuda_sync()
+            d.reset_step()
+        ms_e2e = (time.perf_counter() - t0) * 1e3 / reps
+        # the reference's hand-over: a finished float batch in host memory, uploaded as it is
+        fl = lib.dnn_cuda_host_alloc(Bsz * Cc * Hh * Ww * 4)
+        C.memset(fl, 0, Bsz * Cc * Hh * Ww * 4)
+        img = lib.tensor_zeros_data(d.data, 4, B.ints([Bsz, Cc, Hh, Ww]))
+        for _ in range(3):
+            lib.dnn_cuda_upload(img, fl, Bsz * Cc * Hh * Ww * 4)
+        lib.dnn_cuda_sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            lib.dnn_cuda_upload(img, fl, Bsz * Cc * Hh * Ww * 4)
+            lib.dnn_cuda_sync()
+        ms_float = (time.perf_counter() - t0) * 1e3 / reps
+        lib.dnn_cuda_host_free(fl)
+        lib.dnn_cuda_vlm_stager_destroy(st)
+        a = dev_bytes / (ms_dev * 1e-3) / 1e9
+        print(json.dumps({"op": "vlm_batch", "workload": "%d images %dx%dx%d uint8, texts <= %d" % (Bsz, Cc, Hh, Ww, Tm), "bound": "hbm",
+                          "assemble_ms": round(ms_dev, 4), "assemble_bytes": dev_bytes, "achieved": round(a, 1), "unit": "GB/s",
+                          "peak": b.hbm, "frac": round(a / b.hbm, 3), "peak_source": b.src,
+                          "pipeline_ms_per_batch": round(ms_e2e, 3), "pipeline_images_per_s": round(Bsz / ms_e2e * 1e3),
+                          "h2d_bytes_per_batch": Bsz * Hh * Ww * Cc + Bsz * (2 + Tm) * 4,
+                          "float_upload_ms_per_batch": round(ms_float, 3), "float_h2d_bytes_per_batch": Bsz * Cc * Hh * Ww * 4}), flush=True)
     if want("adamw"):
         P = (16 if args.small else 124) * 1000 * 1000
         t = lib.tensor_zeros(d.params, 1, B.ints([P]), 1)

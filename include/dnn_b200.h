@@ -421,6 +421,13 @@ tensor *vision_lm_train_step_masked(struct mem_pool *scratch_pool, vision_lm *vl
                                     const tensor *loss_mask, adamw_opt *opt,
                                     float grad_clip, float *grad_norm_out);
 
+/* Generation with the vision LM, batch 1 (replaces src/vlm.c:436-611).  Returns host token ids
+ * (prompt + new) allocated from data_pool; *n_out = their count.  As in the reference, the cached
+ * path feeds the image embeddings without the learned image positions, the uncached path with them. */
+int *vision_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_pool, vision_lm *vlm,
+                        const tensor *image, const tensor *prompt_ids, int max_new_tokens,
+                        float temperature, int use_cache, int *n_out);
+
 #ifdef __cplusplus
 }
 #endif

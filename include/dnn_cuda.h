@@ -132,6 +132,37 @@ long long dnn_cuda_launch_count(void);
 size_t dnn_cuda_pool_device_used(const mem_pool *pool);
 size_t dnn_cuda_pool_device_peak(const mem_pool *pool);
 
+/* Padded vision-LM batches assembled on the device, with upload prefetch.  Replaces the per-sample
+ * host loops at the end of imagenet_vlm_dl_next_batch (src/imagenet_vlm.c:598-647) and convert_pixels
+ * (src/imagenet_vlm.c:31-46): a loader hands over RAW samples -- the stored token ids (no BOS) and the
+ * uint8 HWC pixels, or the ready float patches of a version-3 shard -- and the device writes
+ * input_ids (BOS + text + PAD), target_ids (text + PAD), loss_mask (1 on the first stored_len slots)
+ * and the normalised NCHW image (val = px/255; (val - mean[c]) / std[c], optional horizontal flip),
+ * bit-identical to the reference.
+ *   create   : `slots` staging buffers (pinned host + device) for up to max_bs samples of H x W x C
+ *              and texts of at most t_max - 1 stored ids; float_patches = 1 for version-3 payloads
+ *              (H*W*C floats per sample, copied as they are).  mean/std: C floats (NULL = 0 / 1).
+ *   put      : copies sample `index` of the batch being built in `slot` into pinned memory.  Returns
+ *              -1 when stored_len + 1 > t_max, like the reference.  Waits only if the previous upload
+ *              of this slot is still reading the memory.
+ *   submit   : queues ONE host-to-device copy of the slot's first `bs` samples on a copy stream.
+ *   assemble : on the compute stream, after the upload: writes the batch tensors (device tensors
+ *              from dnn.c pools; img [>=bs,C,H,W] or [>=bs,patches,patch_dim], the others [>=bs,T])
+ *              and fills the host arrays text_lens (stored_len + 1) and label_ids (may be NULL).
+ *              Returns the number of samples, -1 for a geometry mismatch or a text longer than T.
+ * Per slot the order is put..., submit, assemble; different slots overlap freely, so slot k+1 can be
+ * filled and uploaded while the step that consumes slot k runs.  Errors: dnn_cuda_vlm_stager_error(). */
+typedef struct dnn_cuda_vlm_stager dnn_cuda_vlm_stager;
+dnn_cuda_vlm_stager *dnn_cuda_vlm_stager_create(int slots, int max_bs, int t_max, int H, int W, int C,
+                                                int float_patches, const float *mean, const float *std);
+void dnn_cuda_vlm_stager_destroy(dnn_cuda_vlm_stager *s);
+int  dnn_cuda_vlm_stager_put(dnn_cuda_vlm_stager *s, int slot, int index, const int *text, int stored_len,
+                             const void *image, int flip, int label);
+int  dnn_cuda_vlm_stager_submit(dnn_cuda_vlm_stager *s, int slot, int bs);
+int  dnn_cuda_vlm_stager_assemble(dnn_cuda_vlm_stager *s, int slot, tensor *img, tensor *input_ids,
+                                  tensor *target_ids, tensor *loss_mask, int *text_lens, int *label_ids);
+const char *dnn_cuda_vlm_stager_error(void);
+
 /* Data-parallel gradient exchange (one process per GPU).  The reference has
  * no multi-process path; these follow the place where a DDP hook would sit in
  * src/gpt.c:201-206, between dnn_backward() and clip_grad_norm().

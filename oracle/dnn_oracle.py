@@ -570,3 +570,42 @@ def lm_loss_and_grads(P, ids, targets, n_layers, n_heads, rope_base=10000.0, eps
     np.add.at(dE, ids.reshape(-1), dx.reshape(-1, D))
     G["embed.weight"] = G["embed.weight"] + dE
     return np.float32(loss), {k: _f32(v) for k, v in G.items()}
+
+
+# ── padded vision-LM batch assembly (src/imagenet_vlm.c:31-46, 598-647) ───
+BOS_ID, EOS_ID, PAD_ID = 257, 258, 259          # include/tokenizer.h:23-25
+
+
+def vlm_batch_text(texts, t_max):
+    """Rows of a padded batch from stored token lists (no BOS; src/imagenet_vlm.c:612-629):
+    input = BOS + text + PAD..., target = text + PAD..., mask = 1 on the first len(text) slots,
+    text_lens = len(text) + 1.  Integer work: bit-exact."""
+    n = len(texts)
+    inp = np.full((n, t_max), PAD_ID, np.int32)
+    tgt = np.full((n, t_max), PAD_ID, np.int32)
+    mask = np.zeros((n, t_max), np.float32)
+    lens = np.zeros(n, np.int32)
+    for b, t in enumerate(texts):
+        t = np.asarray(t, np.int32)
+        assert len(t) + 1 <= t_max
+        inp[b, 0] = BOS_ID
+        inp[b, 1:1 + len(t)] = t
+        tgt[b, :len(t)] = t
+        mask[b, :len(t)] = 1.0
+        lens[b] = len(t) + 1
+    return inp, tgt, mask, lens
+
+
+def vlm_batch_pixels(pixels_hwc, flips, mean, std):
+    """uint8 [B,H,W,C] -> normalised float32 [B,C,H,W], optional horizontal flip per sample
+    (convert_pixels, src/imagenet_vlm.c:31-46).  Each operation is rounded to fp32 on its own, as the
+    reference's scalar code does, so the result is bit-exact."""
+    px = np.asarray(pixels_hwc, np.uint8)
+    out = np.empty((px.shape[0], px.shape[3], px.shape[1], px.shape[2]), np.float32)
+    inv255 = np.float32(1.0) / np.float32(255.0)
+    mean, std = np.asarray(mean, np.float32), np.asarray(std, np.float32)
+    for b in range(px.shape[0]):
+        src = px[b, :, ::-1, :] if flips[b] else px[b]
+        val = src.astype(np.float32) * inv255
+        out[b] = np.transpose(((val - mean) / std).astype(np.float32), (2, 0, 1))
+    return out

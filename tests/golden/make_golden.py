@@ -1,6 +1,8 @@
 """Generates tests/golden/*.npz by running the UNMODIFIED reference library.
 
-    make -C oracle && OMP_NUM_THREADS=1 python tests/golden/make_golden.py
+    make -C oracle && OMP_NUM_THREADS=1 python tests/golden/make_golden.py [ops] [generate] [models] [batch]
+
+Without arguments all four files are written; with arguments only the named ones.
 
 Needs oracle/_ref/libdnn_ref.so (built from the reference's own sources by
 oracle/Makefile), so it runs only where the reference sources are mounted.
@@ -32,8 +34,7 @@ def store(dst, prefix, arr):
     dst[prefix + "#"] = stats
 
 
-def main():
-    B = load_binding()
+def write_ops(B):
     ops = {}
     ref = B.Dnn(REF_LIB, params_mb=256, scratch_mb=2048, data_mb=64)
     for case in CASES:
@@ -44,6 +45,8 @@ def main():
     ref.close()
     np.savez_compressed(os.path.join(HERE, "ops.npz"), **ops)
 
+
+def write_generate(B):
     gen = {}
     for name, over, prompt, max_new, temp, use_cache in models.GEN_CASES:
         d = B.Dnn(REF_LIB, params_mb=64, scratch_mb=512, data_mb=64)
@@ -51,8 +54,15 @@ def main():
         gen[name] = np.array(models.run_generate(d, cfg, prompt, max_new, temp, use_cache, seed=77), np.int32)
         d.close()
         print("generate", name, gen[name].tolist())
+    for name, prompt, max_new, temp, use_cache, patched in models.VLM_GEN_CASES:
+        d = B.Dnn(REF_LIB, params_mb=64, scratch_mb=512, data_mb=64)
+        gen[name] = np.array(models.run_vlm_generate(d, prompt, max_new, temp, use_cache, patched, seed=77), np.int32)
+        d.close()
+        print("generate", name, gen[name].tolist())
     np.savez_compressed(os.path.join(HERE, "generate.npz"), **gen)
 
+
+def write_models(B):
     mdl = {}
 
     def model(tag, fn, **kw):
@@ -77,9 +87,58 @@ def main():
     model("cnn", models.run_cnn, batch=8, steps=2)
     model("vlm", models.run_vlm, steps=2)
     np.savez_compressed(os.path.join(HERE, "models.npz"), **mdl)
-    for f in ("ops.npz", "models.npz"):
-        print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
     print("lm_c1 loss", mdl["lm_c1/loss"], "grad_norm", mdl["lm_c1/grad_norm"])
+
+
+def write_batch(B):
+    """Padded vision-LM batches built by the reference's own loader (imagenet_vlm_dl_next_batch) from a
+    synthetic dataset written in its on-disk format; shuffle off, so no flips."""
+    import ctypes as C
+    import tempfile
+    import vlm_batch_data as D
+    out = {}
+    ref = B.Dnn(REF_LIB, params_mb=16, scratch_mb=64, data_mb=16)
+    lib = ref.lib
+    lib.imagenet_vlm_dl_create.restype = C.c_void_p
+    lib.imagenet_vlm_dl_create.argtypes = [C.c_char_p, C.c_char_p, C.c_int, C.c_ulong]
+    lib.imagenet_vlm_dl_free.argtypes = [C.c_void_p]
+    lib.imagenet_vlm_dl_next_batch.restype = C.c_int
+    lib.imagenet_vlm_dl_next_batch.argtypes = [C.c_void_p] + [B.TensorP] * 4 + [C.POINTER(C.c_int)] * 2 + [C.c_int]
+    with tempfile.TemporaryDirectory() as root:
+        for version in (1, 2, 3):
+            split = "v%d" % version
+            D.write_dataset(root, split, D.make_samples(SEED + version, 5, version), version)
+            dl = lib.imagenet_vlm_dl_create(split.encode(), root.encode(), 0, 1)
+            assert dl, "the reference rejected the synthetic dataset"
+            for batch, bs in enumerate((3, 3)):        # 5 samples: a full batch, then a short one
+                ishape = (bs, 2, 768) if version == 3 else (bs, D.C, D.H, D.W)
+                img = ref.tensor(np.zeros(ishape, np.float32), ref.data)
+                ids = ref.tensor(np.zeros((bs, D.T_MAX), np.int32), ref.data)
+                tgt = ref.tensor(np.zeros((bs, D.T_MAX), np.int32), ref.data)
+                mask = ref.tensor(np.zeros((bs, D.T_MAX), np.float32), ref.data)
+                lens, labels = (C.c_int * bs)(), (C.c_int * bs)()
+                n = lib.imagenet_vlm_dl_next_batch(dl, img, ids, tgt, mask, lens, labels, bs)
+                assert n == (3, 2)[batch], n
+                tag = "%s/b%d/" % (split, batch)
+                out[tag + "img"] = ref.download(img)[:n]
+                out[tag + "input_ids"] = ref.download(ids, np.int32)[:n]
+                out[tag + "target_ids"] = ref.download(tgt, np.int32)[:n]
+                out[tag + "loss_mask"] = ref.download(mask)[:n]
+                out[tag + "text_lens"] = np.array(lens[:n], np.int32)
+                out[tag + "label_ids"] = np.array(labels[:n], np.int32)
+                ref.reset_step()
+            lib.imagenet_vlm_dl_free(dl)
+    ref.close()
+    np.savez_compressed(os.path.join(HERE, "batch.npz"), **out)
+
+
+def main():
+    B = load_binding()
+    which = sys.argv[1:] or ["ops", "generate", "models", "batch"]
+    for name, fn in (("ops", write_ops), ("generate", write_generate), ("models", write_models), ("batch", write_batch)):
+        if name in which:
+            fn(B)
+            print(name + ".npz", os.path.getsize(os.path.join(HERE, name + ".npz")) // 1024, "KiB")
 
 
 if __name__ == "__main__":

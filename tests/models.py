@@ -187,3 +187,32 @@ def run_vlm(dnn, steps=2, seed=3, Bsz=3, img=32, patch=16, V=40, D=32, L=2, H=2,
     out["params"] = {n: dnn.download(t) for n, t in zip(names, params)}
     out["_keep"] = (arr,)
     return out
+
+
+def run_vlm_generate(dnn, prompt, max_new, temperature, use_cache, patched=False, seed=0,
+                     img=32, patch=16, V=300, D=32, L=2, H=2, F=48):
+    """vision_lm_generate on a seeded model; returns the token list (prompt + new).  V > 258 so that the
+    end-of-sequence id can be drawn; `patched` feeds the image as [1, patches, patch_dim]."""
+    lib = dnn.lib
+    vlm = lib.vision_lm_create(dnn.params, V, D, L, H, D // H, F, 3, img, img, patch, 1)
+    lib.vision_lm_enable_rope(dnn.params, vlm, len(prompt) + max_new, 10000.0)
+    seeded_weights(dnn, vlm, vlm_param_names(L), seed + 100, std=0.3)
+    rng = np.random.default_rng(seed + 5)
+    n_patch = (img // patch) ** 2
+    image = rng.standard_normal((1, n_patch, 3 * patch * patch) if patched else (1, 3, img, img)).astype(np.float32)
+    lib.dnn_seed(seed)
+    ids = dnn.tensor(np.asarray(prompt, np.int32).reshape(1, -1), dnn.data)
+    n = C.c_int(0)
+    out = lib.vision_lm_generate(dnn.scratch, dnn.data, vlm, dnn.tensor(image, dnn.data), ids, max_new, temperature,
+                                 use_cache, C.byref(n))
+    toks = [int(out[i]) for i in range(n.value)]
+    dnn.reset_step()
+    return toks
+
+
+VLM_GEN_CASES = [   # name, prompt, max_new, temperature, use_cache, patched
+    ("vlm-greedy-cache", [3, 17, 42, 5], 10, 0.0, 1, False),
+    ("vlm-greedy-nocache", [3, 17, 42, 5], 10, 0.0, 0, False),
+    ("vlm-sampled-cache", [1, 2, 3], 8, 0.7, 1, False),
+    ("vlm-greedy-cache-patched", [9, 8, 7, 6, 5], 6, 0.0, 1, True),
+]

@@ -1,4 +1,4 @@
-"""GPU: KV-cache generation of the decoder LM against the token sequences the unmodified
+"""GPU: KV-cache generation of the decoder LM and the vision LM against the token sequences the unmodified
 reference produced for the same seeded weights, prompt and random stream (tests/golden/generate.npz)."""
 import os
 
@@ -45,3 +45,25 @@ def test_cache_and_full_forward_agree(binding):
         d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
         d.close()
     assert out[0] == out[1]
+
+
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
+@pytest.mark.parametrize("case", models.VLM_GEN_CASES, ids=[c[0] for c in models.VLM_GEN_CASES])
+def test_vision_lm_generated_tokens_equal_the_reference(binding, case, mode):
+    """vision_lm_generate: prefix-LM prefill of image tokens + prompt, then cached decoding.  The cached and
+    uncached reference sequences differ (only the uncached path adds the image positions); both are held."""
+    name, prompt, max_new, temp, use_cache, patched = case
+    want = np.load(GOLDEN)[name].tolist()
+    d = binding.Dnn(binding.B200_LIB, params_mb=64, scratch_mb=512, data_mb=64)
+    d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32 if mode == "fp32" else binding.GEMM_TF32)
+    try:
+        got = models.run_vlm_generate(d, prompt, max_new, temp, use_cache, patched, seed=77)
+    finally:
+        d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        d.close()
+    if mode == "fp32":
+        assert got == want
+    else:
+        assert got[:len(prompt)] == want[:len(prompt)] and len(got) <= len(prompt) + max_new
+        if temp == 0.0 and name != "vlm-greedy-nocache":
+            assert got == want
