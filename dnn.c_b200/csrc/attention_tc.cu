@@ -62,6 +62,10 @@ __device__ __forceinline__ int vis_len(int i, int prefix, int nb) {
 // raises a per-CTA abort flag in shared memory; from then on all waits of the CTA return at
 // once, the loops run to their end without touching TMEM or the tensor core (so named
 // barriers still see every thread), and the CTA frees its TMEM and exits.
+// Bits of x rounded to TF32 (nearest, ties away) for a value the tensor core will read: adding half
+// of the dropped range is enough, the core ignores the low 13 mantissa bits itself.  One integer add
+// instead of a conversion instruction, which shares its unit with the exponentials.  Finite inputs only.
+__device__ __forceinline__ uint32_t tf32_bits(float x) { return __float_as_uint(x) + 0x1000u; }
 constexpr uint32_t kAttnSpins = 1u << 22;
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     uint32_t addr = smem_u32(bar);
@@ -247,6 +251,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int r = warp * 32 + lane, row = i0 + r;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         const int vis = row < nb ? vis_len(row, p.prefix, nb) : 0;
+        const int vis_min = __reduce_min_sync(0xffffffffu, vis);
         // the running maximum is kept in units of log2(e)*scale so that exp() is one ex2
         const float sl2 = p.scale * 1.4426950408889634f;
         float m = -INFINITY, l = 0.f, corr_prev = 1.f;
@@ -270,15 +275,25 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc_fence_after();
             // pass 1: row maximum over the 64 columns of this key tile (TMEM reads are cheap,
             // so the scores are read twice instead of being kept in 64 registers)
-            float mx = -INFINITY;
+            // A tile every row of the warp sees in full needs no mask tests: all but the one or two
+            // diagonal tiles of a causal CTA.  The maximum is taken over the raw scores on four
+            // independent chains and scaled once (the scale is positive).
+            const bool full = j0 + BN <= vis_min;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int half = 0; half < BN / 32; half++) {
                 uint32_t s[32];
                 tc_ld32(tmem_s + half * 32, s);
+                if (full) {
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    if (j0 + half * 32 + j < vis) mx = fmaxf(mx, __uint_as_float(s[j]) * sl2);
+                    for (int j = 0; j < 32; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(s[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (j0 + half * 32 + j < vis) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(s[j]));
+                }
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
             const float mnew = fmaxf(m, mx);
             const float corr = (mnew == -INFINITY) ? 1.f : fast_exp2(m - mnew);
             // fold the previous tile's PV (scaled by the previous correction)
@@ -289,21 +304,29 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 fold_pv(t - 1, corr_prev);
             }
             corr_prev = corr;
-            float rs = 0.f;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             // pass 2: probabilities, rounded to TF32, written over the scores
 #pragma unroll
             for (int half = 0; half < BN / 32; half++) {
                 uint32_t s[32];
                 tc_ld32(tmem_s + half * 32, s);
+                if (full) {
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    float e = (j0 + half * 32 + j < vis) ? fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -mnew)) : 0.f;
-                    rs += e; s[j] = __float_as_uint(to_tf32(e));
+                    for (int j = 0; j < 32; j++) {
+                        const float e = fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -mnew));
+                        rs4[j & 3] += e; s[j] = tf32_bits(e);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float e = (j0 + half * 32 + j < vis) ? fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -mnew)) : 0.f;
+                        rs4[j & 3] += e; s[j] = tf32_bits(e);
+                    }
                 }
                 tc_st32(tmem_s + half * 32, s);
             }
             tc_wait_st();
-            l = l * corr + rs;
+            l = l * corr + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
             m = mnew;
             tc_fence_before();
             __syncwarp();
@@ -341,7 +364,7 @@ struct DkvCfg {
     static constexpr int kKt = KB * BKEY * 128;            // K and V tiles, K-major A operands
     static constexpr int kQk = KB * BQ * 128;              // Q / dO of one query tile, K-major B (for S^T, dP^T)
     static constexpr int kQm = KB * BQ * 128;              // the same rows, MN-major B (for dK, dV)
-    static constexpr int kSmem = 2 * kKt + 4 * kQk + 4 * kQm + 6 * BQ * 4 + 1024 + 256;
+    static constexpr int kSmem = 2 * kKt + 4 * kQk + 4 * kQm + 3 * 8 * 64 * 4 + 1024 + 256;
     static constexpr int kTmemCols = 512;                  // S^T/P^T 0,64,128 ; dP^T/dS^T 192,256,320 ; dV 384.. ; dK 448..
     static constexpr int kThreads = 352;                   // 8 compute warps, ring-1 loader, MMA warp, ring-2 loader
 };
@@ -357,9 +380,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_co
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sK = smem, *sV = sK + Cfg::kKt, *sQk = sV + Cfg::kKt, *sGk = sQk + 2 * Cfg::kQk, *sQm = sGk + 2 * Cfg::kQk,
             *sGm = sQm + 2 * Cfg::kQm;
-    float *s_lse = (float *)(sGm + 2 * Cfg::kQm), *s_d = s_lse + 2 * BQ;       // [2][BQ] each
-    int *s_vis = (int *)(s_d + 2 * BQ);
-    uint64_t *bars = (uint64_t *)(((uintptr_t)(s_vis + 2 * BQ) + 15) & ~(uintptr_t)15);
+    float *s_lse = (float *)(sGm + 2 * Cfg::kQm), *s_d = s_lse + 8 * 64;       // [8 warps][2][32] each
+    int *s_vis = (int *)(s_d + 8 * 64);
+    uint64_t *bars = (uint64_t *)(((uintptr_t)(s_vis + 8 * 64) + 15) & ~(uintptr_t)15);
     uint64_t *bar_kv = bars, *in1_full = bars + 1 /*[2]*/, *in2_full = bars + 3 /*[2]*/, *bar_o = bars + 5 /*[2]*/,
              *bar_s = bars + 7 /*[3]*/, *bar_p = bars + 10 /*[3]*/;
     uint32_t *tmem_slot = (uint32_t *)(bars + 13);
@@ -472,23 +495,28 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_co
         const int r = q4 * 32 + lane, key = j0 + r;
         const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
         const float sl2 = p.scale * 1.4426950408889634f;
-        // per-query statistics of tile t are fetched one tile ahead by the first 64 threads
+        // Per-query statistics of tile t (log-sum-exp in log2 units, negated; D times the scale; visible
+        // length) are fetched one tile ahead, each lane for one of the warp's 32 queries, and handed
+        // round through a strip of shared memory that belongs to this warp alone: no CTA-wide barrier.
+        float *w_lse = s_lse + warp * 64, *w_d = s_d + warp * 64;                // [2][32] each
+        int *w_vis = s_vis + warp * 64;
         float pre_lse = 0.f, pre_d = 0.f; int pre_vis = 0;
         auto prefetch_stats = [&](int t) {
-            int row = i_begin + t * BQ + (int)threadIdx.x;
+            int row = i_begin + t * BQ + hq * 32 + lane;
             bool live = t < n_iter && row < nb;
-            pre_lse = live ? p.lse_in[slice + row] * 1.4426950408889634f : 0.f;      // log2 units
-            pre_d = live ? p.dvec[slice + row] : 0.f;
+            pre_lse = live ? -p.lse_in[slice + row] * 1.4426950408889634f : 0.f;
+            pre_d = live ? p.dvec[slice + row] * p.scale : 0.f;
             pre_vis = live ? vis_len(row, p.prefix, nb) : 0;
         };
-        if (threadIdx.x < BQ) prefetch_stats(0);
+        prefetch_stats(0);
+        const int key_last = j0 + q4 * 32 + 31;          // last key of this warp's lane quadrant
         for (int t = 0; t < n_iter; t++) {
-            const int sb = t & 1, buf = buf3(t);
-            if (threadIdx.x < BQ) {
-                s_lse[sb * BQ + threadIdx.x] = pre_lse; s_d[sb * BQ + threadIdx.x] = pre_d; s_vis[sb * BQ + threadIdx.x] = pre_vis;
-                prefetch_stats(t + 1);
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");        // every thread reaches this in every trip, also after an abort
+            const int sb = (t & 1) * 32, buf = buf3(t);
+            w_lse[sb + lane] = pre_lse; w_d[sb + lane] = pre_d; w_vis[sb + lane] = pre_vis;
+            // every key of the warp visible to every query of the tile: no mask tests (all but the diagonal tiles)
+            const bool full = key_last < __reduce_min_sync(0xffffffffu, pre_vis);
+            prefetch_stats(t + 1);
+            __syncwarp();
             WARP_WAIT(&bar_s[buf], use_parity3(t), 0x221);
             if (ok) {
                 tc_fence_after();
@@ -496,12 +524,29 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_co
                 const uint32_t a_s = tmem + (uint32_t)(buf * 64) + lane_base + hq * 32, a_dp = a_s + 192;
                 tc_ld32(a_s, s);
                 tc_ld32(a_dp, dp);
+                const float4 *l4 = reinterpret_cast<const float4 *>(w_lse + sb), *d4 = reinterpret_cast<const float4 *>(w_d + sb);
+                const int4 *v4 = reinterpret_cast<const int4 *>(w_vis + sb);
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    int q = sb * BQ + hq * 32 + j;
-                    float pe = (key < s_vis[q]) ? fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -s_lse[q])) : 0.f;
-                    s[j] = __float_as_uint(to_tf32(pe));
-                    dp[j] = __float_as_uint(to_tf32(pe * (__uint_as_float(dp[j]) - s_d[q]) * p.scale));
+                for (int j = 0; j < 32; j += 4) {
+                    const float4 L = l4[j >> 2], D = d4[j >> 2];
+                    const float ls[4] = {L.x, L.y, L.z, L.w}, ds[4] = {D.x, D.y, D.z, D.w};
+                    if (full) {
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float pe = fast_exp2(fmaf(__uint_as_float(s[j + e]), sl2, ls[e]));
+                            s[j + e] = tf32_bits(pe);
+                            dp[j + e] = tf32_bits(pe * fmaf(__uint_as_float(dp[j + e]), p.scale, -ds[e]));
+                        }
+                    } else {
+                        const int4 V = v4[j >> 2];
+                        const int vs[4] = {V.x, V.y, V.z, V.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float pe = (key < vs[e]) ? fast_exp2(fmaf(__uint_as_float(s[j + e]), sl2, ls[e])) : 0.f;
+                            s[j + e] = tf32_bits(pe);
+                            dp[j + e] = tf32_bits(pe * fmaf(__uint_as_float(dp[j + e]), p.scale, -ds[e]));
+                        }
+                    }
                 }
                 tc_st32(a_s, s);            // P^T over S^T
                 tc_st32(a_dp, dp);          // dS^T over dP^T
@@ -663,7 +708,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_con
         const int vis = live ? vis_len(row, p.prefix, nb) : 0;
         const float sl2 = p.scale * 1.4426950408889634f;
         const float lse2 = live ? p.lse_in[slice + row] * 1.4426950408889634f : 0.f;
-        const float dvec = live ? p.dvec[slice + row] : 0.f;
+        const float dvec_s = live ? p.dvec[slice + row] * p.scale : 0.f;
+        const int vis_min = __reduce_min_sync(0xffffffffu, vis);
         for (int t = 0; t < n_iter; t++) {
             const int buf = buf3(t);
             WARP_WAIT(&bar_s[buf], use_parity3(t), 0x321);
@@ -674,10 +720,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_con
                 tc_ld32(a_s, s);
                 tc_ld32(a_dp, dp);
                 const int jb = t * BN + hq * 32;
+                if (jb + 32 <= vis_min) {          // all 32 keys visible to every row of the warp: no mask tests
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    float pe = (jb + j < vis) ? fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -lse2)) : 0.f;
-                    dp[j] = __float_as_uint(to_tf32(pe * (__uint_as_float(dp[j]) - dvec) * p.scale));
+                    for (int j = 0; j < 32; j++) {
+                        const float pe = fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -lse2));
+                        dp[j] = tf32_bits(pe * fmaf(__uint_as_float(dp[j]), p.scale, -dvec_s));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float pe = (jb + j < vis) ? fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -lse2)) : 0.f;
+                        dp[j] = tf32_bits(pe * fmaf(__uint_as_float(dp[j]), p.scale, -dvec_s));
+                    }
                 }
                 tc_st32(a_dp, dp);          // dS over dP
                 tc_wait_st();
