@@ -16,6 +16,30 @@ using namespace dnnb;
 
 static thread_local int g_grad_enabled = 1;
 
+namespace dnnb {
+// Gradients whose first contribution is a plain copy that has not been carried out yet
+// (grad_defer_copy).  A handful at most: a residual stream defers one per add.
+struct DeferredCopy { tensor *base; const float *src; };
+static std::vector<DeferredCopy> g_deferred;
+
+static void settle_deferred(tensor *base) {
+    if (g_deferred.empty()) return;
+    for (size_t i = 0; i < g_deferred.size(); i++)
+        if (g_deferred[i].base == base) {
+            const float *src = g_deferred[i].src;
+            g_deferred.erase(g_deferred.begin() + (long)i);
+            k_copy(base->grad, src, numel_of(base));
+            return;
+        }
+}
+static void settle_all_deferred() {
+    while (!g_deferred.empty()) settle_deferred(g_deferred.back().base);
+}
+// Pools call this before they hand memory out again: a pending copy runs while its source still
+// exists (stream order keeps it ahead of whatever reuses the memory).
+void grad_settle_all_deferred() { settle_all_deferred(); }
+}  // namespace dnnb
+
 extern "C" {
 
 int dnn_grad_enabled(void) { return g_grad_enabled; }
@@ -37,6 +61,7 @@ grad_fn *_grad_fn_create(struct mem_pool *pool) {
 float *_grad_ensure(tensor *t) {
     tensor *base = t;
     while (base->parent) base = base->parent;
+    dnnb::settle_deferred(base);
     if (!base->pool) {
         fprintf(stderr, "_grad_ensure: tensor %p has NULL pool (ndim=%d)\n", (void *)base, base->ndim);
         abort();
@@ -59,6 +84,7 @@ namespace dnnb {
 float *grad_full(tensor *t, bool *accumulate) {
     tensor *base = t;
     while (base->parent) base = base->parent;
+    settle_deferred(base);
     // the caller writes every element of t; that is every element of the root's buffer only
     // if t spans it (the root itself, or a contiguous reshape of all of it)
     bool spans = t->contiguous && t->offset == 0 && numel_of(t) == numel_of(base);
@@ -91,6 +117,7 @@ __global__ void zero_outside_kernel(float *__restrict__ p, int64_t pitch, int64_
 float *grad_rows(tensor *t, bool *accumulate) {
     tensor *base = t;
     while (base->parent) base = base->parent;
+    settle_deferred(base);
     bool fresh = !base->grad || base->grad_fresh;
     int nd = t->ndim;
     if (!fresh || nd < 1 || t == base) return grad_full(t, accumulate);
@@ -117,7 +144,40 @@ float *grad_rows(tensor *t, bool *accumulate) {
     return base->grad;
 }
 
+bool grad_defer_copy(tensor *t, const float *src) {
+    tensor *base = t;
+    while (base->parent) base = base->parent;
+    const bool spans = t->contiguous && t->offset == 0 && numel_of(t) == numel_of(base);
+    if (!spans || !base->pool || (base->grad && !base->grad_fresh)) return false;
+    if (!base->grad) base->grad = (float *)dev_alloc(base->pool, (size_t)numel_of(base) * sizeof(float), false);
+    base->grad_fresh = 0;                      // it has content now, even if the content is still a promise
+    colsum_cache_forget(base->grad);
+    g_deferred.push_back(DeferredCopy{base, src});
+    return true;
+}
+
+float *grad_full_based(tensor *t, bool *accumulate, const float **basep) {
+    *basep = nullptr;
+    if (!g_deferred.empty()) {
+        tensor *base = t;
+        while (base->parent) base = base->parent;
+        const bool spans = t->contiguous && t->offset == 0 && numel_of(t) == numel_of(base);
+        for (size_t i = 0; spans && i < g_deferred.size(); i++)
+            if (g_deferred[i].base == base) {
+                *basep = g_deferred[i].src;
+                g_deferred.erase(g_deferred.begin() + (long)i);
+                *accumulate = false;
+                colsum_cache_forget(base->grad);
+                return base->grad;
+            }
+    }
+    return grad_full(t, accumulate);
+}
+
 void grad_settle(tensor *t) {
+    tensor *base = t;
+    while (base->parent) base = base->parent;
+    settle_deferred(base);
     if (t->grad && t->grad_fresh) { k_fill(t->grad, numel_of(t), 0.0f); t->grad_fresh = 0; }
 }
 
@@ -183,6 +243,7 @@ extern "C" void dnn_backward(struct mem_pool *scratch, tensor *loss) {
         tensor *t = topo.order[i];
         grad_fn *fn = t->grad_fn;
         if (!fn) continue;
+        settle_deferred(root_of(t));         // a copy nobody folded into a later write happens now
         if (t->grad) {                       // a node whose output never received a gradient is skipped
             tensor gv;
             memset(&gv, 0, sizeof gv);
@@ -200,5 +261,6 @@ extern "C" void dnn_backward(struct mem_pool *scratch, tensor *loss) {
                 if (it != owed.end() && --it->second == 0) g_leaf_ready(r);
             }
     }
+    settle_all_deferred();
     colsum_cache_forget(nullptr);
 }

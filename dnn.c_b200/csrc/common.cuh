@@ -114,9 +114,20 @@ void opt_graph_destroy(OptGraph *og);
 //                      fresh buffer outside the slabs is zeroed, the slabs are stored to.
 //   _grad_ensure(t)    for everything else: the buffer is zero-filled if it was fresh.
 //   grad_settle(t)     before a gradient is READ (norm, clip, AdamW, all-reduce, download).
+//   grad_defer_copy(t, src)   "t's gradient := src" without doing the copy yet (t fresh and spanning
+//                      its root; returns false otherwise).  The next op that writes t's gradient
+//                      through grad_full_based() adds src while it writes and the copy never runs;
+//                      every other access (any helper above, dnn_backward reaching t's node, the
+//                      end of dnn_backward) performs the copy first.  src must stay valid and
+//                      unchanged until the end of the backward pass.
+//   grad_full_based(t, acc, base)  grad_full that accepts such a pending source: *base != nullptr
+//                      means "store base + contribution".
 float *grad_full(tensor *t, bool *accumulate);
 float *grad_rows(tensor *t, bool *accumulate);
 void   grad_settle(tensor *t);
+bool   grad_defer_copy(tensor *t, const float *src);
+float *grad_full_based(tensor *t, bool *accumulate, const float **base);
+void   grad_settle_all_deferred();
 
 // Attaches a tape node to `out` (src/autograd.c:29-33 + the per-op boilerplate).
 grad_fn *attach(struct mem_pool *scratch, tensor *out, void (*bw)(grad_fn *, tensor *),

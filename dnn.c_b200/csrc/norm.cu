@@ -73,8 +73,8 @@ __global__ void norm_fwd_kernel(const float *__restrict__ x, const float *__rest
 template <bool LN, int T>
 __global__ void norm_bwd_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
                                 const float *__restrict__ mean, const float *__restrict__ rstd,
-                                float *__restrict__ dx, float *__restrict__ dw_part, float *__restrict__ db_part,
-                                int64_t rows, int d, int acc_dx) {
+                                float *dx, float *__restrict__ dw_part, float *__restrict__ db_part,
+                                int64_t rows, int d, const float *addend) {
     int lane = threadIdx.x & 31;
     int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
@@ -116,7 +116,7 @@ __global__ void norm_bwd_kernel(const float *__restrict__ x, const float *__rest
             for (int t = 0; t < T; t++) {
                 int j = (lane + 32 * t) * 4;
                 if (j < d) {
-                    float4 o = acc_dx ? ld4(dxr + j) : make_float4(0.f, 0.f, 0.f, 0.f), v = xv[t], dy = dyv[t];
+                    float4 o = addend ? ld4(addend + r * d + j) : make_float4(0.f, 0.f, 0.f, 0.f), v = xv[t], dy = dyv[t];
                     o.x += rs * (dy.x - mdy) - rs * k1 * v.x; o.y += rs * (dy.y - mdy) - rs * k1 * v.y;
                     o.z += rs * (dy.z - mdy) - rs * k1 * v.z; o.w += rs * (dy.w - mdy) - rs * k1 * v.w;
                     st4(dxr + j, o);
@@ -168,8 +168,8 @@ template <bool LN, int T>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
 norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
                        const float *__restrict__ mean, const float *__restrict__ rstd,
-                       float *__restrict__ dx, float *__restrict__ dw_part, float *__restrict__ db_part,
-                       int64_t rows, int d, int acc_dx) {
+                       float *dx, float *__restrict__ dw_part, float *__restrict__ db_part,
+                       int64_t rows, int d, const float *addend) {
     extern __shared__ __align__(128) uint8_t norm_smem[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + wid;
@@ -233,7 +233,7 @@ norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w,
                 if (j < d) {
                     float4 v = ld4(xs + j), gg = ld4(gs + j);
                     const float4 ww = wr[t];
-                    float4 o = acc_dx ? ld4(dxr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    float4 o = addend ? ld4(addend + r * d + j) : make_float4(0.f, 0.f, 0.f, 0.f);
                     v.x -= mu; v.y -= mu; v.z -= mu; v.w -= mu;
                     o.x += rs * (gg.x * ww.x - mdy) - rs * k1 * v.x; o.y += rs * (gg.y * ww.y - mdy) - rs * k1 * v.y;
                     o.z += rs * (gg.z * ww.z - mdy) - rs * k1 * v.z; o.w += rs * (gg.w * ww.w - mdy) - rs * k1 * v.w;
@@ -258,7 +258,7 @@ norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w,
 template <bool LN>
 __global__ void norm_bwd_dx_scalar_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ g,
                                           const float *__restrict__ mean, const float *__restrict__ rstd,
-                                          float *__restrict__ dx, int d, int acc_dx) {
+                                          float *dx, int d, const float *addend) {
     __shared__ float sh[32];
     int64_t r = blockIdx.x;
     const float *xr = x + r * d, *gr = g + r * d;
@@ -274,7 +274,7 @@ __global__ void norm_bwd_dx_scalar_kernel(const float *__restrict__ x, const flo
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
         float dy = gr[j] * (w ? w[j] : 1.f), v = xr[j] - mu;
         float val = rs * (dy - mdy) - rs * k1 * v;
-        dx[r * d + j] = acc_dx ? dx[r * d + j] + val : val;
+        dx[r * d + j] = addend ? addend[r * d + j] + val : val;
     }
 }
 // t[r,j] = g*(x-mu)*rs, to be column-summed
@@ -327,26 +327,26 @@ static void norm_forward(const float *x, const float *w, const float *b, float *
 
 template <bool LN, int T>
 static void launch_bwd(const float *x, const float *w, const float *g, const float *mean, const float *rstd,
-                       float *dx, float *dwp, float *dbp, int64_t rows, int d, int grid, int acc_dx) {
+                       float *dx, float *dwp, float *dbp, int64_t rows, int d, int grid, const float *addend) {
     // rows staged through shared memory when two CTAs of 8 warps with two row pairs each fit on an SM
     const size_t smem = (size_t)kWarpsPerCta * 4 * d * sizeof(float) + kWarpsPerCta * 2 * sizeof(uint64_t);
     if (smem <= 100 * 1024 && d % 4 == 0 && T <= 6) {
         static bool once = false;
         if (!once) { CUDA_OK(cudaFuncSetAttribute(norm_bwd_staged_kernel<LN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)); once = true; }
-        norm_bwd_staged_kernel<LN, T><<<grid, kWarpsPerCta * 32, smem, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, acc_dx);
+        norm_bwd_staged_kernel<LN, T><<<grid, kWarpsPerCta * 32, smem, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, addend);
         LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
         return;
     }
-    norm_bwd_kernel<LN, T><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, acc_dx);
+    norm_bwd_kernel<LN, T><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, addend);
     LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
 }
 
 template <bool LN>
 static void norm_backward(struct mem_pool *pool, const float *x, const float *w, const float *g, const float *mean,
                           const float *rstd, float *dx, float *dw, float *db, int64_t rows, int d,
-                          bool acc_dx, bool acc_dw, bool acc_db) {
+                          const float *addend, bool acc_dw, bool acc_db) {
     if (rows <= 0) return;
-    bool vec = d % 4 == 0 && d <= 2048 && aligned16(x) && aligned16(g) && (!w || aligned16(w)) && (!dx || aligned16(dx));
+    bool vec = d % 4 == 0 && d <= 2048 && aligned16(x) && aligned16(g) && (!w || aligned16(w)) && (!dx || aligned16(dx)) && (!addend || aligned16(addend));
     if (vec) {
         int grid = (int)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
         int cap = kNumSMs * 2;
@@ -355,18 +355,18 @@ static void norm_backward(struct mem_pool *pool, const float *x, const float *w,
         float *dwp = dw ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
         float *dbp = (LN && db) ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
         int T = (d + 127) / 128;
-        if (T <= 1)      launch_bwd<LN, 1>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
-        else if (T <= 2) launch_bwd<LN, 2>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
-        else if (T <= 4) launch_bwd<LN, 4>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
-        else if (T <= 6) launch_bwd<LN, 6>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
-        else if (T <= 8) launch_bwd<LN, 8>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
-        else             launch_bwd<LN, 16>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, acc_dx);
+        if (T <= 1)      launch_bwd<LN, 1>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, addend);
+        else if (T <= 2) launch_bwd<LN, 2>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, addend);
+        else if (T <= 4) launch_bwd<LN, 4>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, addend);
+        else if (T <= 6) launch_bwd<LN, 6>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, addend);
+        else if (T <= 8) launch_bwd<LN, 8>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, addend);
+        else             launch_bwd<LN, 16>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, grid, addend);
         if (dwp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(dw, dwp, nparts, d, acc_dw); LAUNCHED("norm_part_reduce_kernel"); }
         if (dbp) { norm_part_reduce_kernel<<<(d + 31) / 32, dim3(32, 32), 0, stream()>>>(db, dbp, nparts, d, acc_db); LAUNCHED("norm_part_reduce_kernel"); }
         return;
     }
     if (dx) {
-        norm_bwd_dx_scalar_kernel<LN><<<(unsigned)rows, 256, 0, stream()>>>(x, w, g, mean, rstd, dx, d, acc_dx);
+        norm_bwd_dx_scalar_kernel<LN><<<(unsigned)rows, 256, 0, stream()>>>(x, w, g, mean, rstd, dx, d, addend);
         LAUNCHED("norm_bwd_dx_scalar_kernel");
     }
     if (dw) {
@@ -388,9 +388,10 @@ static void rms_backward(grad_fn *fn, tensor *go) {
     const float *gd = (const float *)go->data;
     const float *wd = weight ? (const float *)weight->data + weight->offset : nullptr;
     bool acc_w = true, acc_x = true;
+    const float *base = nullptr;          // a residual gradient still waiting to be copied into dx: added here instead
     float *dw = (weight && weight->requires_grad) ? grad_full(weight, &acc_w) : nullptr;
-    float *dx = x->requires_grad ? grad_full(x, &acc_x) : nullptr;   // the reference indexes dx from 0 (src/norm.c:339)
-    norm_backward<false>(fn->pool, xd, wd, gd, nullptr, rstd, dx, dw, nullptr, rows, d, acc_x, acc_w, true);
+    float *dx = x->requires_grad ? grad_full_based(x, &acc_x, &base) : nullptr;   // the reference indexes dx from 0 (src/norm.c:339)
+    norm_backward<false>(fn->pool, xd, wd, gd, nullptr, rstd, dx, dw, nullptr, rows, d, base ? base : (acc_x ? dx : nullptr), acc_w, true);
 }
 
 static void ln_backward(grad_fn *fn, tensor *go) {
@@ -405,8 +406,9 @@ static void ln_backward(grad_fn *fn, tensor *go) {
     bool acc_w = true, acc_b = true, acc_x = true;
     float *dw = (weight && weight->requires_grad) ? grad_full(weight, &acc_w) : nullptr;
     float *db = (bias && bias->requires_grad) ? grad_full(bias, &acc_b) : nullptr;
-    float *dx = x->requires_grad ? grad_full(x, &acc_x) : nullptr;
-    norm_backward<true>(fn->pool, xd, wd, gd, mean, rstd, dx, dw, db, rows, d, acc_x, acc_w, acc_b);
+    const float *base = nullptr;
+    float *dx = x->requires_grad ? grad_full_based(x, &acc_x, &base) : nullptr;
+    norm_backward<true>(fn->pool, xd, wd, gd, mean, rstd, dx, dw, db, rows, d, base ? base : (acc_x ? dx : nullptr), acc_w, acc_b);
 }
 
 }  // namespace dnnb

@@ -184,7 +184,7 @@ static void matmul_add_backward(grad_fn *fn, tensor *go) {
 // inputs: a, b, bias, x (the residual).  d(out)/dx = identity; the rest is matmul_add's backward.
 static void matmul_add_residual_backward(grad_fn *fn, tensor *go) {
     tensor *x = fn->inputs[3];
-    if (wants_grad(x)) {
+    if (wants_grad(x) && !grad_defer_copy(x, (const float *)go->data)) {     // usually deferred: the norm backward that writes dx next adds go
         bool acc = true;
         float *xg = grad_full(x, &acc);
         int64_t n = numel_of(go);

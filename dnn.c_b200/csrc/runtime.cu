@@ -175,6 +175,7 @@ mem_pool mem_pool_create(size_t capacity) {
 
 void mem_pool_destroy(mem_pool *pool) {
     if (!pool || !pool->buffer) return;
+    grad_settle_all_deferred();
     auto it = g_rt.arenas.find(pool->buffer);
     if (it != g_rt.arenas.end()) {
         cudaStreamSynchronize(g_rt.compute);
@@ -188,6 +189,7 @@ void mem_pool_destroy(mem_pool *pool) {
 }
 
 void mem_pool_reset(mem_pool *pool) {
+    grad_settle_all_deferred();
     pool->offset = 0;
     Arena *a = arena_of(pool, false);
     if (a) { a->off = 0; a->marks.clear(); }
@@ -200,6 +202,7 @@ size_t mem_pool_mark(mem_pool *pool) {
 }
 
 void mem_pool_release(mem_pool *pool, size_t mark) {
+    grad_settle_all_deferred();
     pool->offset = mark;
     Arena *a = arena_of(pool, false);
     if (!a) return;
