@@ -189,20 +189,36 @@ __global__ void colsum_final_kernel(float *__restrict__ out, const float *__rest
 // here.  k_colsum_acc uses them when it is asked for the same buffer, rows and width, which saves
 // a pass over the buffer.  The entry dies with any later write to the buffer (the gradient
 // helpers call colsum_cache_forget) and at both ends of dnn_backward.
-struct ColsumCache { const float *src = nullptr; int64_t rows = 0; int C = 0; float *sums = nullptr; size_t cap = 0; bool valid = false; };
-static ColsumCache g_cc;
+// A few entries, used round-robin: one backward kernel may leave sums for two buffers (SwiGLU
+// backward writes d(gate) and d(up), each consumed by its own linear layer).
+struct ColsumEntry { const float *src = nullptr; int64_t rows = 0; int C = 0; float *sums = nullptr; size_t cap = 0; bool valid = false; };
+constexpr int kColsumEntries = 4;
+static ColsumEntry g_cc[kColsumEntries];
+static int g_cc_last = 0;
 float *colsum_cache_reserve(int C) {
-    if ((size_t)C > g_cc.cap) {
+    g_cc_last = (g_cc_last + 1) % kColsumEntries;
+    ColsumEntry &e = g_cc[g_cc_last];
+    if ((size_t)C > e.cap) {
         CUDA_OK(cudaStreamSynchronize(stream()));
-        if (g_cc.sums) CUDA_OK(cudaFree(g_cc.sums));
-        g_cc.cap = (size_t)C * 2;
-        CUDA_OK(cudaMalloc((void **)&g_cc.sums, g_cc.cap * sizeof(float)));
+        if (e.sums) CUDA_OK(cudaFree(e.sums));
+        e.cap = (size_t)C * 2;
+        CUDA_OK(cudaMalloc((void **)&e.sums, e.cap * sizeof(float)));
     }
-    g_cc.valid = false;
-    return g_cc.sums;
+    e.valid = false;
+    return e.sums;
 }
-void colsum_cache_publish(const float *src, int64_t rows, int C) { g_cc.src = src; g_cc.rows = rows; g_cc.C = C; g_cc.valid = true; }
-void colsum_cache_forget(const void *buffer) { if (buffer == nullptr || buffer == (const void *)g_cc.src) g_cc.valid = false; }
+// Describes what the sums handed out by the latest colsum_cache_reserve() belong to.
+void colsum_cache_publish(const float *src, int64_t rows, int C) {
+    ColsumEntry &e = g_cc[g_cc_last];
+    e.src = src; e.rows = rows; e.C = C; e.valid = true;
+}
+void colsum_cache_forget(const void *buffer) {
+    for (auto &e : g_cc) if (buffer == nullptr || buffer == (const void *)e.src) e.valid = false;
+}
+static const ColsumEntry *colsum_cache_find(const float *g, int64_t rows, int C) {
+    for (auto &e : g_cc) if (e.valid && e.src == g && e.rows == rows && e.C == C) return &e;
+    return nullptr;
+}
 
 __global__ void colsum_apply_kernel(float *__restrict__ out, const float *__restrict__ sums, int C, int acc) {
     int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -222,8 +238,8 @@ static size_t g_colsum_cap = 0;
 
 void k_colsum_acc(float *out, const float *g, int64_t rows, int C, bool accumulate) {
     if (rows <= 0 || C <= 0) return;
-    if (g_cc.valid && g_cc.src == g && g_cc.rows == rows && g_cc.C == C) {          // the producer of g left its column sums
-        colsum_apply_kernel<<<(C + 255) / 256, 256, 0, stream()>>>(out, g_cc.sums, C, accumulate ? 1 : 0);
+    if (const ColsumEntry *e = colsum_cache_find(g, rows, C)) {                      // the producer of g left its column sums
+        colsum_apply_kernel<<<(C + 255) / 256, 256, 0, stream()>>>(out, e->sums, C, accumulate ? 1 : 0);
         LAUNCHED("colsum_apply_kernel");
         return;
     }

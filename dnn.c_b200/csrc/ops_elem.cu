@@ -200,6 +200,45 @@ struct SwigluB4 { float4 *dg, *du; const float4 *g, *u, *go; int acc_g, acc_u; _
 struct SwigluBcast { float *o; const float *g, *u; View vg, vu;
     __device__ void operator()(int64_t i) const { o[i] = swiglu1(g[voff(vg, i)], u[voff(vu, i)]); } };
 
+// SwiGLU backward for packed [rows, C] operands with fresh gradient buffers: a CTA owns 128 columns
+// and a slab of rows, stores d(gate) and d(up) and keeps their running column sums, which end up
+// in part_g / part_u [slab][C].  The consumers of the two gradients are linear layers whose bias
+// gradients are exactly these sums, so the separate pass over each buffer disappears.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_colsum_kernel(const float *__restrict__ gate, const float *__restrict__ up, const float *__restrict__ go,
+                         float *__restrict__ dgate, float *__restrict__ dup, float *__restrict__ part_g, float *__restrict__ part_u,
+                         int64_t rows, int C, int rows_per) {
+    __shared__ float4 tile[2][8][33];
+    const int c = (blockIdx.x * 32 + threadIdx.x) * 4;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per;
+    int64_t r1 = r0 + rows_per; if (r1 > rows) r1 = rows;
+    float4 sg = make_float4(0.f, 0.f, 0.f, 0.f), su = sg;
+    if (c < C) {
+#pragma unroll 2
+        for (int64_t r = r0 + threadIdx.y; r < r1; r += 8) {
+            const int64_t i = r * C + c;
+            const float4 a = *reinterpret_cast<const float4 *>(gate + i), b = *reinterpret_cast<const float4 *>(up + i),
+                         o = *reinterpret_cast<const float4 *>(go + i);
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+            swiglu_b1(a.x, b.x, o.x, x.x, y.x); swiglu_b1(a.y, b.y, o.y, x.y, y.y);
+            swiglu_b1(a.z, b.z, o.z, x.z, y.z); swiglu_b1(a.w, b.w, o.w, x.w, y.w);
+            *reinterpret_cast<float4 *>(dgate + i) = x;
+            *reinterpret_cast<float4 *>(dup + i) = y;
+            sg.x += x.x; sg.y += x.y; sg.z += x.z; sg.w += x.w;
+            su.x += y.x; su.y += y.y; su.z += y.z; su.w += y.w;
+        }
+    }
+    tile[0][threadIdx.y][threadIdx.x] = sg;
+    tile[1][threadIdx.y][threadIdx.x] = su;
+    __syncthreads();
+    if (threadIdx.y < 2 && c < C) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; j++) { float4 v = tile[threadIdx.y][j][threadIdx.x]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+        *reinterpret_cast<float4 *>((threadIdx.y ? part_u : part_g) + (int64_t)blockIdx.y * C + c) = t;
+    }
+}
+
 static bool v4ok(int64_t n, std::initializer_list<const void *> ps) {
     if (n % 4) return false;
     for (auto p : ps) if (p && !aligned16(p)) return false;
@@ -253,6 +292,30 @@ static void swiglu_backward(grad_fn *fn, tensor *go) {
     if (grad_contig(gate, go) && grad_contig(up, go)) {
         float *dg = ag ? ag + gate->offset : nullptr, *du = bg ? bg + up->offset : nullptr;
         const float *g = (const float *)gate->data + gate->offset, *u = (const float *)up->data + up->offset;
+        const int C = go->shape[go->ndim - 1];
+        const int64_t rows = C > 0 ? n / C : 0;
+        // both buffers fresh and whole: the tiled kernel that also leaves the column sums of d(gate) and d(up)
+        if (dg && du && dg != du && !acc_g && !acc_u && gate->offset == 0 && up->offset == 0 && C % 4 == 0 && C >= 128 && rows >= 256 &&
+            v4ok(n, {dg, du, g, u, god})) {
+            // one wave: 8 CTAs of 256 threads per SM, column groups x row slabs
+            const int col_groups = (C / 4 + 31) / 32;
+            int nslabs = kNumSMs * 8 / col_groups;
+            if (nslabs < 1) nslabs = 1;
+            if ((int64_t)nslabs * 32 > rows) nslabs = (int)(rows / 32);
+            int per = (int)((rows + nslabs - 1) / nslabs);
+            nslabs = (int)((rows + per - 1) / per);
+            float *pg = dev_alloc_t<float>(fn->pool, (size_t)nslabs * C), *pu = dev_alloc_t<float>(fn->pool, (size_t)nslabs * C);
+            dim3 grid((C / 4 + 31) / 32, nslabs), block(32, 8);
+            swiglu_bwd_colsum_kernel<<<grid, block, 0, stream()>>>(g, u, god, dg, du, pg, pu, rows, C, per);
+            LAUNCHED("swiglu_bwd_kernel");
+            float *sums = colsum_cache_reserve(C);
+            k_colsum_finish(sums, pg, nslabs, C);
+            colsum_cache_publish(dg, rows, C);
+            sums = colsum_cache_reserve(C);
+            k_colsum_finish(sums, pu, nslabs, C);
+            colsum_cache_publish(du, rows, C);
+            return;
+        }
         if (dg && du && dg != du && v4ok(n, {dg, du, g, u, god}))
             ew_launch("swiglu_bwd_kernel", n / 4, SwigluB4{(float4 *)dg, (float4 *)du, (const float4 *)g, (const float4 *)u, (const float4 *)god, acc_g, acc_u});
         else
