@@ -305,6 +305,24 @@ __global__ void splitk_reduce_kernel(float *__restrict__ C, int64_t ldc, const f
     }
 }
 
+// The same with four columns per thread (N, ldc multiples of 4; all pointers 16-byte aligned).
+__global__ void splitk_reduce_v4_kernel(float *__restrict__ C, int64_t ldc, const float4 *__restrict__ part, int splits,
+                                        int M, int N4, const float4 *__restrict__ bias, int accumulate) {
+    const int64_t total = (int64_t)M * N4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / N4), n = (int)(i - (int64_t)m * N4);
+        float4 s = part[i];
+        for (int k = 1; k < splits; k++) {
+            const float4 v = part[(int64_t)k * total + i];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        if (bias) { const float4 b = bias[n]; s.x += b.x; s.y += b.y; s.z += b.z; s.w += b.w; }
+        float4 *c = reinterpret_cast<float4 *>(C + (int64_t)m * ldc) + n;
+        if (accumulate) { const float4 o = *c; s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w; }
+        *c = s;
+    }
+}
+
 // big = x with the 13 low mantissa bits cleared (exactly a TF32 value), small = x - big
 __global__ void tf32_split_kernel(const float *__restrict__ x, float *__restrict__ big, float *__restrict__ small,
                                   int64_t rows, int64_t cols, int64_t pitch) {
@@ -532,8 +550,14 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     LAUNCHED("gemm_tf32_kernel");
     prof_end(0, 2.0 * g.M * g.N * g.K);
     if (splits > 1) {
-        splitk_reduce_kernel<<<grid_for((int64_t)g.M * g.N, 256), 256, 0, stream()>>>(g.C, g.c_rs, t.C, splits, g.M, g.N, g.bias,
-                                                                                     g.accumulate ? 1 : 0);
+        const bool v4 = g.N % 4 == 0 && g.c_rs % 4 == 0 && ((uintptr_t)g.C & 15) == 0 && ((uintptr_t)t.C & 15) == 0 &&
+                        (!g.bias || ((uintptr_t)g.bias & 15) == 0);
+        if (v4)
+            splitk_reduce_v4_kernel<<<grid_for((int64_t)g.M * (g.N / 4), 256), 256, 0, stream()>>>(
+                g.C, g.c_rs, (const float4 *)t.C, splits, g.M, g.N / 4, (const float4 *)g.bias, g.accumulate ? 1 : 0);
+        else
+            splitk_reduce_kernel<<<grid_for((int64_t)g.M * g.N, 256), 256, 0, stream()>>>(g.C, g.c_rs, t.C, splits, g.M, g.N, g.bias,
+                                                                                         g.accumulate ? 1 : 0);
         LAUNCHED("splitk_reduce_kernel");
     }
 }

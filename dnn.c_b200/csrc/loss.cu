@@ -29,6 +29,14 @@ __device__ __forceinline__ void slice_offsets(const SliceMap &m, int64_t s, int6
     }
 }
 
+// e^x through the special-function unit: x * log2(e) rounded once, then ex2.approx (about 2 ulp).
+// Used where x <= 0 and the result is scaled into a gradient; the loss itself keeps expf / logf.
+__device__ __forceinline__ float fast_expf(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+    return y;
+}
+
 __device__ __forceinline__ void online_add(float &mx, float &se, float v) {
     if (v > mx) { se *= expf(mx - v); mx = v; }
     se += expf(v - mx);
@@ -158,35 +166,51 @@ __global__ void ce_bwd_kernel(const float *__restrict__ logits, const int *__res
 // end up in partial[slab][C].  The consumer of d(logits) is normally a linear layer whose bias
 // gradient is exactly these sums.  Only for stores into a fresh buffer (acc = 0) with packed
 // classes; one CTA per slice (above) serves everything else.
+// Per-slice constants of the tiled kernel, computed once instead of by every thread of every CTA
+// that touches the slice: where the slice starts, -max, scale / sum-of-exponentials, the scale itself
+// (0 for a masked-out slice, which then writes zeros) and the target class.
+struct __align__(16) CeRow { long long lo; float neg_max, k_exp, k_hot; int tgt; int pad[2]; };
+__global__ void ce_rows_kernel(const int *__restrict__ target, const float *__restrict__ mask, SliceMap map,
+                               const float *__restrict__ max_in, const float *__restrict__ se_in, const float *__restrict__ gout,
+                               const float *__restrict__ inv, CeRow *__restrict__ rows, int64_t n_slices) {
+    int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n_slices) return;
+    int64_t lo, mo;
+    slice_offsets(map, s, lo, mo);
+    const float m = mask ? mask[mo] : 1.0f;
+    const bool skip = mask && m == 0.0f;
+    const float scale = skip ? 0.f : (mask ? gout[0] * inv[0] * m : gout[0] * inv[0]);
+    CeRow r;
+    r.lo = lo; r.neg_max = skip ? 0.f : -max_in[s]; r.k_exp = skip ? 0.f : scale / se_in[s]; r.k_hot = scale;
+    r.tgt = skip ? -1 : target[s]; r.pad[0] = skip ? 1 : 0; r.pad[1] = 0;
+    rows[s] = r;
+}
+
 __global__ void __launch_bounds__(256)
-ce_bwd_colsum_kernel(const float *__restrict__ logits, const int *__restrict__ target, const float *__restrict__ mask, SliceMap map,
-                     const float *__restrict__ max_in, const float *__restrict__ se_in, const float *__restrict__ gout,
-                     const float *__restrict__ inv, float *__restrict__ dlogits, float *__restrict__ partial,
-                     int64_t n_slices, int slices_per) {
+ce_bwd_colsum_kernel(const float *__restrict__ logits, const CeRow *__restrict__ rows, float *__restrict__ dlogits,
+                     float *__restrict__ partial, int C, int64_t n_slices, int slices_per) {
     __shared__ float4 tile[8][33];
-    const int C = map.C, c = (blockIdx.x * 32 + threadIdx.x) * 4;
+    const int c = (blockIdx.x * 32 + threadIdx.x) * 4;
     const int64_t s0 = (int64_t)blockIdx.y * slices_per;
     int64_t s1 = s0 + slices_per; if (s1 > n_slices) s1 = n_slices;
-    const float base_scale = gout[0] * inv[0];
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c < C)
+    if (c < C) {
+#pragma unroll 2
         for (int64_t s = s0 + threadIdx.y; s < s1; s += 8) {
-            int64_t lo, mo;
-            slice_offsets(map, s, lo, mo);
-            const float m = mask ? mask[mo] : 1.0f;
+            const CeRow r = rows[s];
             float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (!(mask && m == 0.0f)) {
-                const float4 v = *reinterpret_cast<const float4 *>(logits + lo + c);
-                const float mx = max_in[s], se = se_in[s], scale = mask ? base_scale * m : base_scale;
-                const int tgt = target[s];
-                d.x = (expf(v.x - mx) / se - (c == tgt ? 1.f : 0.f)) * scale;
-                d.y = (expf(v.y - mx) / se - (c + 1 == tgt ? 1.f : 0.f)) * scale;
-                d.z = (expf(v.z - mx) / se - (c + 2 == tgt ? 1.f : 0.f)) * scale;
-                d.w = (expf(v.w - mx) / se - (c + 3 == tgt ? 1.f : 0.f)) * scale;
+            if (!r.pad[0]) {                                    // warp-uniform: a warp works on one slice
+                const float4 v = *reinterpret_cast<const float4 *>(logits + r.lo + c);
+                const int hot = r.tgt - c;                       // 0..3 when the target class is one of these four
+                d.x = fmaf(fast_expf(v.x + r.neg_max), r.k_exp, hot == 0 ? -r.k_hot : 0.f);
+                d.y = fmaf(fast_expf(v.y + r.neg_max), r.k_exp, hot == 1 ? -r.k_hot : 0.f);
+                d.z = fmaf(fast_expf(v.z + r.neg_max), r.k_exp, hot == 2 ? -r.k_hot : 0.f);
+                d.w = fmaf(fast_expf(v.w + r.neg_max), r.k_exp, hot == 3 ? -r.k_hot : 0.f);
             }
-            *reinterpret_cast<float4 *>(dlogits + lo + c) = d;
+            *reinterpret_cast<float4 *>(dlogits + r.lo + c) = d;
             sum.x += d.x; sum.y += d.y; sum.z += d.z; sum.w += d.w;
         }
+    }
     tile[threadIdx.y][threadIdx.x] = sum;
     __syncthreads();
     if (threadIdx.y == 0 && c < C) {
@@ -245,8 +269,11 @@ static void ce_backward_common(grad_fn *fn, tensor *go, bool masked) {
         float *partial = dev_alloc_t<float>(fn->pool, (size_t)nslabs * map.C);
         float *sums = colsum_cache_reserve(map.C);
         dim3 grid((map.C / 4 + 31) / 32, nslabs), block(32, 8);
-        ce_bwd_colsum_kernel<<<grid, block, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
-            mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, ag, partial, n_slices, per);
+        CeRow *rows = dev_alloc_t<CeRow>(fn->pool, (size_t)n_slices);
+        ce_rows_kernel<<<(unsigned)((n_slices + 255) / 256), 256, 0, stream()>>>((const int *)target->data,
+            mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, rows, n_slices);
+        LAUNCHED("ce_rows_kernel");
+        ce_bwd_colsum_kernel<<<grid, block, 0, stream()>>>((const float *)logits->data, rows, ag, partial, map.C, n_slices, per);
         LAUNCHED(masked ? "ce_masked_bwd_kernel" : "ce_bwd_kernel");
         k_colsum_finish(sums, partial, nslabs, map.C);
         // rows of the root that the slices do not cover were zero-filled: they add nothing to the sums
