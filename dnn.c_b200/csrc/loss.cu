@@ -30,10 +30,16 @@ __device__ __forceinline__ void slice_offsets(const SliceMap &m, int64_t s, int6
 }
 
 // e^x through the special-function unit: x * log2(e) rounded once, then ex2.approx (about 2 ulp).
-// Used where x <= 0 and the result is scaled into a gradient; the loss itself keeps expf / logf.
+// Used where x <= 0: softmax terms of the loss statistics and of the gradient; the logarithm stays logf.
 __device__ __forceinline__ float fast_expf(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+    return y;
+}
+
+__device__ __forceinline__ float fast_exp2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
@@ -66,12 +72,28 @@ __global__ void ce_fwd_kernel(const float *__restrict__ logits, const int *__res
     int C = map.C;
     float mx = -INFINITY, se = 0.f;
     if (map.cstride == 1 && (C & 3) == 0 && (((uintptr_t)row) & 15) == 0) {
+        // Four float4 per trip, loaded before any of them is used, so that a thread keeps 64 bytes in
+        // flight; one rescale per trip; exponentials through ex2 on the scores times log2(e).
         const float4 *r4 = reinterpret_cast<const float4 *>(row);
-        for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
-            float4 v = r4[j];
-            float cm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-            if (cm > mx) { se *= expf(mx - cm); mx = cm; }
-            se += expf(v.x - mx) + expf(v.y - mx) + expf(v.z - mx) + expf(v.w - mx);
+        const int n4 = C / 4, bd = blockDim.x;
+        constexpr float kL2e = 1.4426950408889634f;
+        float mx2 = -INFINITY;                           // running maximum times log2(e)
+        for (int j = threadIdx.x; j < n4; j += 4 * bd) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                v[u] = (j + u * bd < n4) ? r4[j + u * bd] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            float cm = mx;
+#pragma unroll
+            for (int u = 0; u < 4; u++) cm = fmaxf(cm, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+            if (cm > mx) { const float c2 = cm * kL2e; se *= fast_exp2f(mx2 - c2); mx = cm; mx2 = c2; }
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                a0 += fast_exp2f(fmaf(v[u].x, kL2e, -mx2)); a1 += fast_exp2f(fmaf(v[u].y, kL2e, -mx2));
+                a2 += fast_exp2f(fmaf(v[u].z, kL2e, -mx2)); a3 += fast_exp2f(fmaf(v[u].w, kL2e, -mx2));
+            }
+            se += (a0 + a1) + (a2 + a3);
         }
     } else {
         for (int j = threadIdx.x; j < C; j += blockDim.x) online_add(mx, se, row[(int64_t)j * map.cstride]);

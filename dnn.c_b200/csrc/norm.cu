@@ -243,12 +243,31 @@ norm_bwd_staged_kernel(const float *__restrict__ x, const float *__restrict__ w,
         }
         __syncwarp();          // every lane is done with this buffer before lane 0 refills it two trips on
     }
+    // The CTA's eight partial sums are added in shared memory (the row buffers are free now; every copy
+    // a warp asked for has been waited for), so one row of partials per CTA leaves the kernel.
+    __syncthreads();
+    float *red = reinterpret_cast<float *>(norm_smem);             // [8 warps][2][d]
 #pragma unroll
     for (int t = 0; t < T; t++) {
         int j = (lane + 32 * t) * 4;
         if (j < d) {
-            if (dw_part) st4(dw_part + warp * d + j, aw[t]);
-            if (LN && db_part) st4(db_part + warp * d + j, ab[t]);
+            if (dw_part) st4(red + (size_t)(wid * 2) * d + j, aw[t]);
+            if (LN && db_part) st4(red + (size_t)(wid * 2 + 1) * d + j, ab[t]);
+        }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        if (dw_part) {
+            float s = 0.f;
+#pragma unroll
+            for (int w8 = 0; w8 < kWarpsPerCta; w8++) s += red[(size_t)(w8 * 2) * d + j];
+            dw_part[(int64_t)blockIdx.x * d + j] = s;
+        }
+        if (LN && db_part) {
+            float s = 0.f;
+#pragma unroll
+            for (int w8 = 0; w8 < kWarpsPerCta; w8++) s += red[(size_t)(w8 * 2 + 1) * d + j];
+            db_part[(int64_t)blockIdx.x * d + j] = s;
         }
     }
 }
@@ -325,12 +344,15 @@ static void norm_forward(const float *x, const float *w, const float *b, float *
     LAUNCHED(LN ? "layernorm_fwd_kernel" : "rmsnorm_fwd_kernel");
 }
 
+// rows staged through shared memory when two CTAs of 8 warps with two row pairs each fit on an SM
+static size_t staged_smem(int d) { return (size_t)kWarpsPerCta * 4 * d * sizeof(float) + kWarpsPerCta * 2 * sizeof(uint64_t); }
+static bool staged_ok(int d) { return d % 4 == 0 && (d + 127) / 128 <= 6 && staged_smem(d) <= 100 * 1024; }
+
 template <bool LN, int T>
 static void launch_bwd(const float *x, const float *w, const float *g, const float *mean, const float *rstd,
                        float *dx, float *dwp, float *dbp, int64_t rows, int d, int grid, const float *addend) {
-    // rows staged through shared memory when two CTAs of 8 warps with two row pairs each fit on an SM
-    const size_t smem = (size_t)kWarpsPerCta * 4 * d * sizeof(float) + kWarpsPerCta * 2 * sizeof(uint64_t);
-    if (smem <= 100 * 1024 && d % 4 == 0 && T <= 6) {
+    const size_t smem = staged_smem(d);
+    if (staged_ok(d)) {
         static bool once = false;
         if (!once) { CUDA_OK(cudaFuncSetAttribute(norm_bwd_staged_kernel<LN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)); once = true; }
         norm_bwd_staged_kernel<LN, T><<<grid, kWarpsPerCta * 32, smem, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, addend);
@@ -351,7 +373,7 @@ static void norm_backward(struct mem_pool *pool, const float *x, const float *w,
         int grid = (int)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
         int cap = kNumSMs * 2;
         if (grid > cap) grid = cap;
-        int nparts = grid * kWarpsPerCta;
+        int nparts = staged_ok(d) ? grid : grid * kWarpsPerCta;      // the staged kernel adds its warps' partials itself
         float *dwp = dw ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
         float *dbp = (LN && db) ? dev_alloc_t<float>(pool, (size_t)nparts * d) : nullptr;
         int T = (d + 127) / 128;
