@@ -88,5 +88,9 @@ def test_two_ranks_match_one_rank_with_the_whole_batch(tmp_path, overlap):
     for k in one.files:
         if k.startswith(("g/", "p/")):
             a, b = r0[k].astype(np.float64), one[k].astype(np.float64)
-            assert np.linalg.norm(a - b) <= 2e-5 * np.linalg.norm(b) + 1e-9, k
+            # Gradients agree to fp32 rounding (half and whole batches take different kernels and summation
+            # orders).  AdamW divides by sqrt(v): where a gradient is mathematically zero (the key part of a
+            # QKV bias) the update is normalised rounding noise, so parameters get a wider bound.
+            tol = 2e-5 if k.startswith("g/") else 1e-4
+            assert np.linalg.norm(a - b) <= tol * np.linalg.norm(b) + 1e-9, k
             assert np.array_equal(r0[k], r1[k]), "ranks diverged on " + k
