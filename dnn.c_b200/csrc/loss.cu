@@ -1,11 +1,13 @@
 // Cross-entropy and masked cross-entropy, forward and backward.
 // replaces src/ops_activation.c:852-1145 (plain) and :1154-1410 (masked).
 //
-// A "slice" is one vector along the class dimension.  One CTA owns one slice:
-// forward makes a single pass (online max / sum-of-exponentials per thread,
-// merged across the CTA), backward makes one read pass over the logits and one
-// read-modify-write pass over their gradient.  Rows whose last stride is 1 and
-// whose start is 16-byte aligned move as float4.  The scalar loss is produced
+// A "slice" is one vector along the class dimension.  Forward: one CTA owns one slice and makes a
+// single pass (online max / sum-of-exponentials per thread, four float4 loads in flight, merged
+// across the CTA).  Backward into a fresh, packed gradient buffer is tiled the other way round
+// (128 classes x a slab of slices per CTA) so that the column sums of d(logits) -- the bias
+// gradient of the layer that produced the logits -- fall out of the same pass; accumulating or
+// strided cases keep one CTA per slice (read logits, read-modify-write the gradient).  Rows whose
+// last stride is 1 and whose start is 16-byte aligned move as float4.  The scalar loss is produced
 // by a single-CTA tree sum over the per-slice terms (fixed order).
 #include "common.cuh"
 #include "device_utils.cuh"
