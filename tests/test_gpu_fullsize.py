@@ -1,0 +1,134 @@
+"""GPU: the headline configuration at its FULL size (124M-shaped decoder LM, 16 x 1024 tokens), where
+neither the reference nor the numpy oracle finishes in useful time.  The checks are properties that
+do not depend on the size: agreement of the fast arithmetic mode with the exact one, run-to-run
+determinism, softmax rows that sum to one, causality, gradient rows of the cross entropy that sum
+to zero, conservation in the embedding scatter."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import models
+
+pytestmark = pytest.mark.gpu
+
+C5 = dict(V=32000, D=768, L=12, H=12, F=2048, B=16, N=1024, lr=6e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, seed=5)
+PICK = ("embed.weight", "blocks.0.qkv_proj.weight", "blocks.0.qkv_proj.bias", "blocks.5.out_proj.bias", "blocks.5.ffn_norm.weight",
+        "blocks.11.ffn.gate_proj.bias", "blocks.11.ffn.down_proj.weight", "norm.weight", "lm_head.bias")
+
+
+def big(binding, mode):
+    d = binding.Dnn(binding.B200_LIB, params_mb=4096, scratch_mb=40 * 1024, data_mb=256)
+    d.lib.dnn_cuda_set_gemm_mode(mode)
+    return d
+
+
+def step(binding, mode):
+    d = big(binding, mode)
+    try:
+        out = models.run_lm(d, C5, steps=1)
+        return dict(loss=out["loss"][0], grad_norm=out["grad_norm"][0], grads={n: out["grads"][n] for n in PICK})
+    finally:
+        d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        d.close()
+
+
+@pytest.fixture(scope="module")
+def tf32_step(binding):
+    return step(binding, binding.GEMM_TF32)
+
+
+def test_config5_tf32_step_agrees_with_the_exact_mode(binding, tf32_step):
+    """One full-size training step in TF32 mode (tensor-core GEMM and attention) against the same step in
+    3xTF32 mode (split GEMM, fp32 attention kernels), which holds 3e-5 against the reference at small sizes.
+    Bars: the TF32 bars of the small-size parity tests."""
+    exact = step(binding, binding.GEMM_3XTF32)
+    assert abs(tf32_step["loss"] - exact["loss"]) <= 5e-4 * abs(exact["loss"])
+    assert abs(tf32_step["grad_norm"] - exact["grad_norm"]) <= 2e-3 * exact["grad_norm"]
+    for n in PICK:
+        a, b = tf32_step["grads"][n].astype(np.float64), exact["grads"][n].astype(np.float64)
+        assert np.linalg.norm(a - b) <= 3e-3 * np.linalg.norm(b), n
+
+
+def test_config5_step_is_deterministic(binding, tf32_step):
+    """No atomics on floating-point data anywhere in the step: a second run gives the same bits."""
+    again = step(binding, binding.GEMM_TF32)
+    assert again["loss"] == tf32_step["loss"] and again["grad_norm"] == tf32_step["grad_norm"]
+    for n in PICK:
+        assert np.array_equal(again["grads"][n], tf32_step["grads"][n]), n
+
+
+def test_full_size_attention_rows_sum_to_one_and_are_causal(binding):
+    """[16,12,1024,64] causal attention on the tensor-core path.  V = 1 makes every output element the sum
+    of a softmax row; changing K and V at positions >= 512 must leave the first 512 output rows of every
+    head bit-identical."""
+    d = big(binding, binding.GEMM_TF32)
+    try:
+        rng = np.random.default_rng(3)
+        shape = (16, 12, 1024, 64)
+        q = rng.standard_normal(shape, dtype=np.float32)
+        k = rng.standard_normal(shape, dtype=np.float32)
+        v = rng.standard_normal(shape, dtype=np.float32)
+
+        def run(kk, vv):
+            out = d.lib.tensor_attention_ex(d.scratch, d.tensor(q, d.scratch), d.tensor(kk, d.scratch), d.tensor(vv, d.scratch), None, 0, 0, None)
+            res = d.download(out)
+            d.reset_step()
+            return res
+
+        ones = run(k, np.ones(shape, np.float32))
+        assert np.abs(ones - 1.0).max() <= 1e-3
+        base = run(k, v)
+        k2, v2 = k.copy(), v.copy()
+        k2[:, :, 512:] = rng.standard_normal((16, 12, 512, 64), dtype=np.float32)
+        v2[:, :, 512:] = -v[:, :, 512:]
+        moved = run(k2, v2)
+        assert np.array_equal(base[:, :, :512], moved[:, :, :512])
+        assert not np.array_equal(base[:, :, 512:], moved[:, :, 512:])
+    finally:
+        d.close()
+
+
+def test_full_size_cross_entropy_gradient_rows_sum_to_zero(binding):
+    """[16368, 32000] logits: every row of d(logits) = (softmax - onehot) / rows sums to zero, the bias
+    gradient left in passing equals the column sums of what was written, and constant logits give log(V)."""
+    d = big(binding, binding.GEMM_TF32)
+    try:
+        rng = np.random.default_rng(4)
+        R, V = 16368, 32000
+        logits = d.tensor((rng.standard_normal((R, V), dtype=np.float32) * 3.0), d.scratch, requires_grad=True)
+        tgt = d.tensor(rng.integers(0, V, size=R).astype(np.int32), d.data)
+        loss = d.lib.tensor_cross_entropy(d.scratch, logits, tgt, 1)
+        d.lib.dnn_backward(d.scratch, loss)
+        g = d.download_grad(logits).astype(np.float64)
+        assert np.abs(g.sum(axis=1)).max() <= 2e-9            # terms are about 1/(R*V): 2e-9 is rounding of 32000 of them
+        assert abs(g.sum()) <= 1e-7
+        assert (g.max(axis=1) > 0).all() and (g.min(axis=1) < 0).all()    # one negative entry per row: the target
+        d.reset_step()
+        flat = d.tensor(np.full((R, V), 0.25, np.float32), d.scratch, requires_grad=True)
+        loss = d.lib.tensor_cross_entropy(d.scratch, flat, tgt, 1)
+        assert abs(d.scalar(loss) - np.log(V)) <= 2e-6 * np.log(V)
+    finally:
+        d.close()
+
+
+def test_full_size_embedding_backward_conserves_the_gradient(binding):
+    """16384 ids into a [32000, 768] table with many duplicates: the column sums of the table gradient
+    equal the column sums of the upstream gradient, and rows no id points at stay zero."""
+    d = big(binding, binding.GEMM_TF32)
+    try:
+        rng = np.random.default_rng(6)
+        table = d.param(np.zeros((32000, 768), np.float32))
+        ids_np = rng.integers(0, 2000, size=16384).astype(np.int32)          # about 8 hits per used row
+        ids_np[:64] = 31999
+        ids = d.tensor(ids_np, d.data)
+        out = d.lib.tensor_embedding(d.scratch, table, ids)
+        gout = rng.standard_normal((16384, 768), dtype=np.float32)
+        d.backward_from(out, gout)
+        g = d.download_grad(table).astype(np.float64)
+        want = gout.astype(np.float64).sum(axis=0)
+        assert np.abs(g.sum(axis=0) - want).max() <= 1e-4 * np.abs(want).max()
+        assert not g[2000:31999].any() and g[31999].any()
+        np.testing.assert_allclose(g[31999], gout[:64].astype(np.float64).sum(axis=0), rtol=1e-5, atol=1e-5)
+    finally:
+        d.close()
