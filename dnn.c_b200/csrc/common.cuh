@@ -139,6 +139,7 @@ float *colsum_cache_reserve(int C);
 void colsum_cache_publish(const float *src, int64_t rows, int C);
 void colsum_cache_forget(const void *buffer);          // nullptr: forget whatever is cached
 void k_colsum_finish(float *sums, const float *partial, int nparts, int C);
+void k_colsum_finish2(float *sums0, const float *part0, float *sums1, const float *part1, int nparts, int C);
 void k_fill(float *p, int64_t n, float v);
 void k_axpy_acc(float *dst, const float *src, int64_t n);                 // dst += src
 void k_copy(float *dst, const float *src, int64_t n);

@@ -225,11 +225,34 @@ __global__ void colsum_apply_kernel(float *__restrict__ out, const float *__rest
     if (c < C) out[c] = acc ? out[c] + sums[c] : sums[c];
 }
 
-// Partials [nparts, C] -> sums[C] in slab order (deterministic); used by producers that leave sums in the cache.
-void k_colsum_finish(float *sums, const float *partial, int nparts, int C) {
-    colsum_final_kernel<<<(C + 127) / 128, 128, 0, stream()>>>(sums, partial, nparts, C, 0);
-    LAUNCHED("colsum_final_kernel");
+// Partials [nparts, C] -> sums[C] for one or two producers' outputs in one launch (blockIdx.y picks
+// the job).  CTA = 32 columns x 32 slab lanes: lane y adds slabs y, y+32, ... and the 32 lane sums
+// are added in lane order, so the result does not depend on scheduling.
+struct FinishJobs { float *sums[2]; const float *part[2]; };
+__global__ void colsum_finish_kernel(FinishJobs jobs, int nparts, int C) {
+    __shared__ float tile[32][33];
+    float *__restrict__ sums = jobs.sums[blockIdx.y];
+    const float *__restrict__ part = jobs.part[blockIdx.y];
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    float s = 0.f;
+    if (c < C)
+        for (int p = threadIdx.y; p < nparts; p += 32) s += part[(int64_t)p * C + c];
+    tile[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float t = 0.f;
+#pragma unroll
+        for (int y = 0; y < 32; y++) t += tile[y][threadIdx.x];
+        sums[c] = t;
+    }
 }
+void k_colsum_finish2(float *sums0, const float *part0, float *sums1, const float *part1, int nparts, int C) {
+    FinishJobs jobs;
+    jobs.sums[0] = sums0; jobs.part[0] = part0; jobs.sums[1] = sums1; jobs.part[1] = part1;
+    colsum_finish_kernel<<<dim3((C + 31) / 32, sums1 ? 2 : 1), dim3(32, 32), 0, stream()>>>(jobs, nparts, C);
+    LAUNCHED("colsum_finish_kernel");
+}
+void k_colsum_finish(float *sums, const float *partial, int nparts, int C) { k_colsum_finish2(sums, partial, nullptr, nullptr, nparts, C); }
 
 // Scratch for the partials lives in a small cache owned by this file, grown
 // on demand (never shrinks; one per process).

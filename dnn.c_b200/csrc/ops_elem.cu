@@ -308,12 +308,11 @@ static void swiglu_backward(grad_fn *fn, tensor *go) {
             dim3 grid((C / 4 + 31) / 32, nslabs), block(32, 8);
             swiglu_bwd_colsum_kernel<<<grid, block, 0, stream()>>>(g, u, god, dg, du, pg, pu, rows, C, per);
             LAUNCHED("swiglu_bwd_kernel");
-            float *sums = colsum_cache_reserve(C);
-            k_colsum_finish(sums, pg, nslabs, C);
+            float *sums_g = colsum_cache_reserve(C);
             colsum_cache_publish(dg, rows, C);
-            sums = colsum_cache_reserve(C);
-            k_colsum_finish(sums, pu, nslabs, C);
+            float *sums_u = colsum_cache_reserve(C);
             colsum_cache_publish(du, rows, C);
+            k_colsum_finish2(sums_g, pg, sums_u, pu, nslabs, C);
             return;
         }
         if (dg && du && dg != du && v4ok(n, {dg, du, g, u, god}))
