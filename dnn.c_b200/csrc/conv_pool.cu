@@ -74,18 +74,46 @@ __global__ void conv_permute_kernel(float *__restrict__ dst, const float *__rest
     }
 }
 
-// dbias[oc] += sum_{n,hw} g[(n*OC + oc)*HW + hw]; one CTA per channel, fixed order.
-__global__ void conv_dbias_kernel(float *__restrict__ db, const float *__restrict__ g, int N, int OC, int HW) {
+// dbias[oc] += sum_{n,hw} g[(n*OC + oc)*HW + hw].  CTA (oc, s) sums the images n = s, s + S, ... of its
+// channel into part[oc*S + s]; conv_dbias_final_kernel adds the S partials in order (fixed order).
+__global__ void conv_dbias_kernel(float *__restrict__ part, const float *__restrict__ g, int N, int OC, int HW) {
     __shared__ float sh[32];
-    int oc = blockIdx.x;
+    const int oc = blockIdx.x, S = gridDim.y;
     float s = 0.f;
-    int64_t per = (int64_t)N * HW;
-    for (int64_t i = threadIdx.x; i < per; i += blockDim.x) {
-        int n = (int)(i / HW), hw = (int)(i % HW);
-        s += g[((int64_t)n * OC + oc) * HW + hw];
+    for (int n = blockIdx.y; n < N; n += S) {
+        const float *row = g + ((int64_t)n * OC + oc) * HW;
+        for (int hw = threadIdx.x; hw < HW; hw += blockDim.x) s += row[hw];
     }
     s = block_sum(s, sh);
-    if (threadIdx.x == 0) db[oc] += s;
+    if (threadIdx.x == 0) part[oc * S + blockIdx.y] = s;
+}
+__global__ void conv_dbias_final_kernel(float *__restrict__ db, const float *__restrict__ part, int OC, int S) {
+    int oc = blockIdx.x * blockDim.x + threadIdx.x;
+    if (oc >= OC) return;
+    float s = 0.f;
+    for (int i = 0; i < S; i++) s += part[oc * S + i];
+    db[oc] += s;
+}
+// Filters whose row length K = C*kH*kW is not a multiple of 4 floats (the first layer of an image model:
+// 1 x 3 x 3 = 9) cannot be described to the copy engine.  They are copied into rows padded to Kp floats
+// (zeros behind K), the GEMMs run on the padded rows, and the filter gradient is added back without the pad.
+__global__ void conv_pad_rows_kernel(float *__restrict__ dst, const float *__restrict__ src, int rows, int K, int Kp) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * Kp) return;
+    int r = i / Kp, k = i - r * Kp;
+    dst[i] = k < K ? src[r * K + k] : 0.f;
+}
+__global__ void conv_unpad_add_kernel(float *__restrict__ dst, const float *__restrict__ src, int rows, int K, int Kp) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * K) return;
+    int r = i / K, k = i - r * K;
+    dst[i] += src[r * Kp + k];
+}
+static const float *padded_filters(struct mem_pool *pool, const float *w, int out_C, int K, int Kp) {
+    float *wp = dev_alloc_t<float>(pool, (size_t)out_C * Kp);
+    conv_pad_rows_kernel<<<(out_C * Kp + 255) / 256, 256, 0, stream()>>>(wp, w, out_C, K, Kp);
+    LAUNCHED("conv_pad_rows_kernel");
+    return wp;
 }
 
 struct ConvSaved { ConvGeom g; float *col; tensor *bias; int nchw; };
@@ -105,10 +133,18 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
     float *xg = input->requires_grad ? _grad_ensure(input) : nullptr;
     if (bias && bias->requires_grad) {
         float *bg = _grad_ensure(bias);
-        conv_dbias_kernel<<<g.out_C, 256, 0, stream()>>>(bg, gd, g.N, g.out_C, HW);
+        int S = g.N < 32 ? g.N : 32;
+        float *part = dev_alloc_t<float>(fn->pool, (size_t)g.out_C * S);
+        conv_dbias_kernel<<<dim3(g.out_C, S), 256, 0, stream()>>>(part, gd, g.N, g.out_C, HW);
         LAUNCHED("conv_dbias_kernel");
+        conv_dbias_final_kernel<<<(g.out_C + 127) / 128, 128, 0, stream()>>>(bg, part, g.out_C, S);
+        LAUNCHED("conv_dbias_final_kernel");
     }
     size_t mark = mem_pool_mark(fn->pool);
+    const int Kp = (g.K + 3) & ~3;
+    const bool padded = Kp != g.K && gemm_mode() != DNN_CUDA_GEMM_FP32;
+    const float *wk = padded ? padded_filters(fn->pool, wd, g.out_C, g.K, Kp) : wd;
+    const int wpitch = padded ? Kp : g.K;
     const float *g_mc = gd;                 // upstream gradient read as (M, out_C)
     if (sv->nchw) {
         float *tmp = dev_alloc_t<float>(fn->pool, (size_t)g.M * g.out_C);
@@ -120,14 +156,19 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
         GemmArgs a;     // dW[oc,k] += sum_m g_mc[m,oc] * col[k,m]
         a.A = g_mc; a.a_rs = 1; a.a_cs = g.out_C; a.a_bs = 0;
         a.B = sv->col; a.b_rs = 1; a.b_cs = g.M; a.b_bs = 0;
-        a.C = wg + weight->offset; a.c_rs = g.K; a.c_cs = 1; a.c_bs = 0;
-        a.bias = nullptr; a.M = g.out_C; a.N = g.K; a.K = g.M; a.batch = 1; a.accumulate = true;
+        float *dwp = padded ? dev_alloc_t<float>(fn->pool, (size_t)g.out_C * Kp) : nullptr;
+        a.C = padded ? dwp : wg + weight->offset; a.c_rs = wpitch; a.c_cs = 1; a.c_bs = 0;
+        a.bias = nullptr; a.M = g.out_C; a.N = g.K; a.K = g.M; a.batch = 1; a.accumulate = !padded;
         gemm(a);
+        if (padded) {
+            conv_unpad_add_kernel<<<(g.out_C * g.K + 255) / 256, 256, 0, stream()>>>(wg + weight->offset, dwp, g.out_C, g.K, Kp);
+            LAUNCHED("conv_unpad_add_kernel");
+        }
     }
     if (xg) {
         float *dcol = dev_alloc_t<float>(fn->pool, (size_t)g.K * g.M);
         GemmArgs a;     // dcol[k,m] = sum_oc W[oc,k] * g_mc[m,oc]
-        a.A = wd; a.a_rs = 1; a.a_cs = g.K; a.a_bs = 0;
+        a.A = wk; a.a_rs = 1; a.a_cs = wpitch; a.a_bs = 0;
         a.B = g_mc; a.b_rs = 1; a.b_cs = g.out_C; a.b_bs = 0;
         a.C = dcol; a.c_rs = g.M; a.c_cs = 1; a.c_bs = 0;
         a.bias = nullptr; a.M = g.K; a.N = g.M; a.K = g.out_C; a.batch = 1; a.accumulate = false;
@@ -215,7 +256,10 @@ tensor *tensor_conv2d(struct mem_pool *scratch, tensor *input, tensor *weight, t
     float *mc = nchw ? dev_alloc_t<float>(scratch, (size_t)g.M * g.out_C) : (float *)out->data;
     GemmArgs a;         // mc[m,oc] = sum_k col[k,m] * W[oc,k] + bias[oc]
     a.A = col; a.a_rs = 1; a.a_cs = g.M; a.a_bs = 0;
-    a.B = (const float *)weight->data + weight->offset; a.b_rs = 1; a.b_cs = g.K; a.b_bs = 0;
+    const int Kp = (g.K + 3) & ~3;
+    const bool padded = Kp != g.K && gemm_mode() != DNN_CUDA_GEMM_FP32;
+    const float *wsrc = (const float *)weight->data + weight->offset;
+    a.B = padded ? padded_filters(scratch, wsrc, g.out_C, g.K, Kp) : wsrc; a.b_rs = 1; a.b_cs = padded ? Kp : g.K; a.b_bs = 0;
     a.C = mc; a.c_rs = g.out_C; a.c_cs = 1; a.c_bs = 0;
     a.bias = bias ? (const float *)bias->data + bias->offset : nullptr;
     a.M = g.M; a.N = g.out_C; a.K = g.K; a.batch = 1; a.accumulate = false;

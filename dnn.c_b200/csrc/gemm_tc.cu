@@ -292,13 +292,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // C (=|+=) sum_s part[s] (+ bias), fixed order
-__global__ void splitk_reduce_kernel(float *__restrict__ C, int64_t ldc, const float *__restrict__ part, int splits,
+__global__ void splitk_reduce_kernel(float *__restrict__ C, int64_t ldc, const float *__restrict__ part, int64_t part_ld, int splits,
                                      int M, int N, const float *__restrict__ bias, int accumulate) {
     int64_t total = (int64_t)M * N;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int m = (int)(i / N), n = (int)(i - (int64_t)m * N);
         float s = 0.f;
-        for (int k = 0; k < splits; k++) s += part[(int64_t)k * total + i];
+        for (int k = 0; k < splits; k++) s += part[((int64_t)k * M + m) * part_ld + n];
         if (bias) s += bias[n];
         float *c = C + (int64_t)m * ldc + n;
         *c = accumulate ? *c + s : s;
@@ -531,7 +531,8 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
         g_rope.pending = false; g_rope.honoured = true;
     }
     if (splits == 1) { t.C = g.C; t.ldc = g.c_rs; t.bias = g.bias; t.accumulate = g.accumulate ? 1 : 0; }
-    else { t.C = scratch((size_t)splits * g.M * g.N * 4); t.ldc = g.N; t.bias = nullptr; t.accumulate = 0; }
+    else { t.ldc = (g.N + 3) & ~(int64_t)3;      // rows of the partials padded to 16 bytes: the copy engine's stride rule
+           t.C = scratch((size_t)splits * g.M * t.ldc * 4); t.bias = nullptr; t.accumulate = 0; }
     int units = tiles * splits;
     int walkers = units < slots ? units : slots;
     CUtensorMap tmC = make_out_map(t.C, g.N, g.M, t.ldc, splits);
@@ -556,7 +557,7 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
             splitk_reduce_v4_kernel<<<grid_for((int64_t)g.M * (g.N / 4), 256), 256, 0, stream()>>>(
                 g.C, g.c_rs, (const float4 *)t.C, splits, g.M, g.N / 4, (const float4 *)g.bias, g.accumulate ? 1 : 0);
         else
-            splitk_reduce_kernel<<<grid_for((int64_t)g.M * g.N, 256), 256, 0, stream()>>>(g.C, g.c_rs, t.C, splits, g.M, g.N, g.bias,
+            splitk_reduce_kernel<<<grid_for((int64_t)g.M * g.N, 256), 256, 0, stream()>>>(g.C, g.c_rs, t.C, t.ldc, splits, g.M, g.N, g.bias,
                                                                                          g.accumulate ? 1 : 0);
         LAUNCHED("splitk_reduce_kernel");
     }

@@ -224,6 +224,81 @@ def main():
                           "kernels_per_step": int(per_step), "eager_ms_per_step": round(ms_eager, 3), "graph_ms_per_step": round(ms_graph, 3),
                           "eager_tokens_per_s": round(Bsz * N / ms_eager * 1e3), "graph_tokens_per_s": round(Bsz * N / ms_graph * 1e3),
                           "speedup": round(ms_eager / ms_graph, 2)}), flush=True)
+    if "cnn_step" in ops:
+        # BASELINE config 3: 512 images 1x28x28, conv 3x3 (1->32) + pool, conv 3x3 (32->64) + pool, 3136->128->10,
+        # cross entropy, backward, AdamW; wall time per step with the loss read back
+        Bsz = 64 if args.small else 512
+        lib.dnn_seed(2)
+        c1, c2 = lib.conv2d_create(d.params, 1, 32, 3, 1, 1), lib.conv2d_create(d.params, 32, 64, 3, 1, 1)
+        f1, f2 = lib.linear_create(d.params, 3136, 128), lib.linear_create(d.params, 128, 10)
+        params = []
+        for m in (c1, c2, f1, f2):
+            params += d.parameters(m)
+        arr = (B.TensorP * len(params))(*params)
+        opt = lib.adamw_create(d.params, arr, len(params), 1e-3, 0.9, 0.999, 1e-8, 0.01)
+        x = d.tensor(rng.random((Bsz, 1, 28, 28), dtype=np.float32), d.params)
+        y = d.tensor(rng.integers(0, 10, size=Bsz).astype(np.int32), d.params)
+
+        def cnn_step():
+            lib.adamw_zero_grad(opt)
+            h = lib.tensor_avg_pool2d(d.scratch, lib.tensor_relu(d.scratch, lib.conv2d_forward(d.scratch, c1, x)), 2, 2)
+            h = lib.tensor_avg_pool2d(d.scratch, lib.tensor_relu(d.scratch, lib.conv2d_forward(d.scratch, c2, h)), 2, 2)
+            h = lib.tensor_reshape(d.scratch, h, 2, B.ints([Bsz, 3136]))
+            h = lib.tensor_relu(d.scratch, lib.linear_forward(d.scratch, f1, h))
+            loss = lib.tensor_cross_entropy(d.scratch, lib.linear_forward(d.scratch, f2, h), y, 1)
+            lib.dnn_backward(d.scratch, loss)
+            lib.adamw_step(opt)
+            v = d.scalar(loss)
+            d.reset_step()
+            return v
+
+        for _ in range(5):
+            cnn_step()
+        before = lib.dnn_cuda_launch_count()
+        t0 = time.perf_counter()
+        reps = 50
+        for _ in range(reps):
+            last = cnn_step()
+        ms = (time.perf_counter() - t0) * 1e3 / reps
+        print(json.dumps({"op": "cnn_step", "workload": "BASELINE config 3: %d images 1x28x28, 2 conv + 2 linear" % Bsz, "ms_per_step": round(ms, 3),
+                          "images_per_s": round(Bsz / ms * 1e3), "kernels_per_step": int((lib.dnn_cuda_launch_count() - before) // reps),
+                          "loss": round(last, 4)}), flush=True)
+    if "vlm_step" in ops:
+        # BASELINE config 4: 64 images 3x224x224 (196 image tokens) + up to 32 text tokens, d 512, 8 blocks, 8 heads,
+        # FFN 1376, vocabulary 1024; vision_lm_train_step_padded with per-sample text lengths and loss mask
+        Bsz, Tm = (8 if args.small else 64), 32
+        vlm = lib.vision_lm_create(d.params, 1024, 512, 8, 8, 64, 1376, 3, 224, 224, 16, 1)
+        lib.vision_lm_enable_rope(d.params, vlm, Tm, 10000.0)
+        lib.dnn_seed(3); lib.vision_lm_init_weights(vlm)
+        params = d.parameters(vlm)
+        arr = (B.TensorP * len(params))(*params)
+        opt = lib.adamw_create(d.params, arr, len(params), 6e-4, 0.9, 0.95, 1e-8, 0.1)
+        lens = rng.integers(8, Tm + 1, size=Bsz).astype(np.int32)
+        img = d.tensor(rng.standard_normal((Bsz, 3, 224, 224), dtype=np.float32), d.params)
+        ids = d.tensor(rng.integers(0, 1024, size=(Bsz, Tm)).astype(np.int32), d.params)
+        tgt = d.tensor(rng.integers(0, 1024, size=(Bsz, Tm)).astype(np.int32), d.params)
+        mask = d.tensor((np.arange(Tm)[None, :] < (lens[:, None] - 1)).astype(np.float32), d.params)
+        lp = lens.ctypes.data_as(C.POINTER(C.c_int))
+        gn = C.c_float(0)
+
+        def vlm_step():
+            loss = lib.vision_lm_train_step_padded(d.scratch, vlm, img, ids, tgt, mask, lp, opt, 1.0, C.byref(gn))
+            v = d.scalar(loss)
+            d.reset_step()
+            return v
+
+        for _ in range(3):
+            vlm_step()
+        before = lib.dnn_cuda_launch_count()
+        t0 = time.perf_counter()
+        reps = 20
+        for _ in range(reps):
+            last = vlm_step()
+        ms = (time.perf_counter() - t0) * 1e3 / reps
+        print(json.dumps({"op": "vlm_step", "workload": "BASELINE config 4: %d images 3x224x224 + texts <= %d, d 512, 8 blocks" % (Bsz, Tm),
+                          "ms_per_step": round(ms, 3), "images_per_s": round(Bsz / ms * 1e3),
+                          "tokens_per_s": round(Bsz * (196 + Tm) / ms * 1e3),
+                          "kernels_per_step": int((lib.dnn_cuda_launch_count() - before) // reps), "loss": round(last, 4)}), flush=True)
     if "vlm_batch" in ops:
         # Padded vision-LM batch of BASELINE config 4 (64 images 3x224x224, texts up to 32): device assembly alone
         # (uint8 HWC -> normalised NCHW floats, ids / targets / mask rows) and the whole put + upload + assemble
