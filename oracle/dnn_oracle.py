@@ -387,7 +387,7 @@ def adamw_update(p, g, m, v, t, lr, b1, b2, eps, wd):
 def lr_schedule(schedule, base, min_lr, warmup, total, step_size, gamma, t):
     f = np.float32
     if min_lr < 0:
-        min_lr = base / 10.0
+        min_lr = f(base) / f(10.0)                       # src/optim.c:165, float division
     if warmup > 0 and t < warmup:
         return f(f(base) * f(t + 1) / f(warmup))
     post = max(t - warmup, 0)

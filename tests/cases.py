@@ -635,6 +635,157 @@ for shape, k, s in (((2, 3, 28, 28), 2, 2), ((2, 2, 9, 9), 2, 1), ((1, 2, 11, 10
             return dict(y=y, dx=dx)
 
 
+# ── optimiser: AdamW, gradient norm / clipping, LR schedules (src/optim.c:104-316) ─────────
+def _give_grads(dnn, params, grads):
+    """p.grad += g through the public API only: the backward of p * g started from a non-scalar root,
+    whose gradient dnn_backward sets to ones (src/autograd.c:106-110).  None leaves grad == NULL."""
+    for p, g in zip(params, grads):
+        if g is None:
+            continue
+        y = dnn.lib.tensor_mul(dnn.scratch, p, dnn.tensor(g, dnn.scratch))
+        dnn.lib.dnn_backward(dnn.scratch, y)
+    dnn.sync()
+
+
+ADAM_SHAPES = [(33, 17), (1025,), (8,), (5, 7)]          # the last one never receives a gradient
+ADAM_HYPER = dict(lr=1e-3, b1=0.9, b2=0.95, eps=1e-8, wd=0.1)
+
+for mults, lrs in ((None, (1e-3, 1e-3, 1e-3)), ((1.0, 0.5, 2.0, 1.0), (1e-3, 7e-4, 2e-4))):
+    @case("adamw[3 steps, lr_mults=%s]" % (mults is not None), tol=1e-6, exact=("t",))
+    class _:
+        @staticmethod
+        def make(rng, mults=mults, lrs=lrs):
+            i = dict(mults=None if mults is None else np.array(mults, np.float32), lrs=lrs)
+            for k, shape in enumerate(ADAM_SHAPES):
+                i["p%d" % k] = _r(rng, *shape, scale=0.05)
+                i["m%d" % k] = _r(rng, *shape, scale=0.01)
+                i["v%d" % k] = (_r(rng, *shape, scale=0.01) ** 2).astype(np.float32)
+                for s in range(3):
+                    i["g%d_%d" % (k, s)] = None if k == 3 else _r(rng, *shape, scale=0.02 * (s + 1))
+            return i
+
+        @staticmethod
+        def run(dnn, i):
+            B = load_binding()
+            n = len(ADAM_SHAPES)
+            params = [dnn.param(i["p%d" % k]) for k in range(n)]
+            arr = (B.TensorP * n)(*params)
+            h = ADAM_HYPER
+            opt = dnn.lib.adamw_create(dnn.params, arr, n, h["lr"], h["b1"], h["b2"], h["eps"], h["wd"])
+            for k in range(n):
+                dnn.upload(opt.contents.m[k], i["m%d" % k])
+                dnn.upload(opt.contents.v[k], i["v%d" % k])
+            out = {}
+            for s in range(3):
+                dnn.lib.adamw_zero_grad(opt)
+                _give_grads(dnn, params, [i["g%d_%d" % (k, s)] for k in range(n)])
+                opt.contents.lr = i["lrs"][s]                       # what lr_scheduler_step does between steps
+                if i["mults"] is None:
+                    dnn.lib.adamw_step(opt)
+                else:
+                    dnn.lib.adamw_step_with_lr_multipliers(opt, i["mults"].ctypes.data_as(C.POINTER(C.c_float)))
+                dnn.sync()
+                if s == 0:
+                    out.update({"p%d_step1" % k: dnn.download(params[k]) for k in range(n)})
+                dnn.lib.mem_pool_reset(dnn.scratch)
+            for k in range(n):
+                out["p%d" % k], out["m%d" % k], out["v%d" % k] = dnn.download(params[k]), dnn.download(opt.contents.m[k]), dnn.download(opt.contents.v[k])
+            out["t"] = np.array([opt.contents.t], np.int32)
+            return out
+
+        @staticmethod
+        def oracle(i):
+            h = ADAM_HYPER
+            out = {}
+            for k in range(len(ADAM_SHAPES)):
+                p, m, v = i["p%d" % k], i["m%d" % k], i["v%d" % k]
+                for s in range(3):
+                    g = i["g%d_%d" % (k, s)]
+                    if g is not None:
+                        lr = np.float32(i["lrs"][s]) * (np.float32(1.0) if i["mults"] is None else i["mults"][k])
+                        p, m, v = O.adamw_update(p, g, m, v, s + 1, lr, h["b1"], h["b2"], h["eps"], h["wd"])
+                    if s == 0:
+                        out["p%d_step1" % k] = p
+                out["p%d" % k], out["m%d" % k], out["v%d" % k] = p, m, v
+            out["t"] = np.array([3], np.int32)
+            return out
+
+
+for max_norm in (0.5, 1e6, 0.0, -1.0):
+    @case("clip_grad_norm[max %g]" % max_norm, tol=1e-6)
+    class _:
+        @staticmethod
+        def make(rng, max_norm=max_norm):
+            return dict(max_norm=max_norm, g0=_r(rng, 40, 9), g1=_r(rng, 1030), g2=_r(rng, 3, 3, 3, scale=4.0))
+
+        @staticmethod
+        def run(dnn, i):
+            B = load_binding()
+            params = [dnn.param(np.ones_like(i[k])) for k in ("g0", "g1", "g2")] + [dnn.param(np.ones((4, 4), np.float32))]
+            arr = (B.TensorP * 4)(*params)
+            _give_grads(dnn, params, [i["g0"], i["g1"], i["g2"], None])
+            before = dnn.lib.grad_norm(arr, 4)
+            ret = dnn.lib.clip_grad_norm(arr, 4, i["max_norm"])
+            after = dnn.lib.grad_norm(arr, 4)
+            dnn.sync()
+            out = {"g%d" % k: dnn.download_grad(params[k]) for k in range(3)}
+            out["norms"] = np.array([before, ret, after], np.float32)
+            assert not params[3].contents.grad, "a parameter outside the graph must keep grad == NULL"
+            return out
+
+        @staticmethod
+        def oracle(i):
+            gs = [i["g0"], i["g1"], i["g2"]]
+            total = O.grad_norm(gs)
+            if i["max_norm"] <= 0:                                   # src/optim.c:207: no-op that returns 0
+                return dict(g0=gs[0], g1=gs[1], g2=gs[2], norms=np.array([total, 0.0, total], np.float32))
+            scale = O.clip_scale(total, i["max_norm"])
+            gs = [(g * scale).astype(np.float32) for g in gs]
+            return dict(g0=gs[0], g1=gs[1], g2=gs[2], norms=np.array([total, total, O.grad_norm(gs)], np.float32))
+
+
+LR_SCHEDULES = [  # schedule id (include/optim.h:113-118), warmup, total, step_size, gamma, min_lr
+    (0, 0, 100, 0, 0.0, -1.0), (1, 10, 100, 0, 0.0, -1.0), (2, 5, 50, 0, 0.0, -1.0), (3, 0, 40, 0, 0.0, 1e-5),
+    (4, 3, 100, 7, 0.5, -1.0), (5, 0, 30, 0, 0.9, -1.0), (1, 100, 10000, 0, 0.0, -1.0), (1, 8, 8, 0, 0.0, -1.0),
+]
+
+
+@case("lr_schedules", tol=1e-6, golden_exact=tuple("lr%d" % k for k in range(len(LR_SCHEDULES))) + ("get_lr", "after_reset"))
+class _:
+    @staticmethod
+    def make(rng):
+        return dict(base=6e-4, steps=130)
+
+    @staticmethod
+    def run(dnn, i):
+        B = load_binding()
+        out, get, reset = {}, [], []
+        for k, (sched, warmup, total, step, gamma, min_lr) in enumerate(LR_SCHEDULES):
+            opt = B.AdamW()
+            s = dnn.lib.lr_scheduler_create(dnn.params, C.byref(opt), sched, i["base"], warmup, total, min_lr, step, gamma)
+            lrs = []
+            for t in range(i["steps"]):
+                lrs.append(opt.lr)
+                dnn.lib.lr_scheduler_step(s)
+            out["lr%d" % k] = np.array(lrs, np.float32)
+            get.append(dnn.lib.lr_scheduler_get_lr(s))
+            dnn.lib.lr_scheduler_reset(s)
+            reset.append(opt.lr)
+        out["get_lr"], out["after_reset"] = np.array(get, np.float32), np.array(reset, np.float32)
+        return out
+
+    @staticmethod
+    def oracle(i):
+        out, get, reset = {}, [], []
+        for k, (sched, warmup, total, step, gamma, min_lr) in enumerate(LR_SCHEDULES):
+            f = lambda t: O.lr_schedule(sched, i["base"], min_lr, warmup, total, step, gamma, t)
+            out["lr%d" % k] = np.array([f(t) for t in range(i["steps"])], np.float32)
+            get.append(f(i["steps"]))
+            reset.append(f(0))
+        out["get_lr"], out["after_reset"] = np.array(get, np.float32), np.array(reset, np.float32)
+        return out
+
+
 # ── views ─────────────────────────────────────────────────────────────────
 @case("transpose+contiguous+reshape (VLM image-embed path)", exact=("y", "dx"))
 class _:

@@ -71,7 +71,7 @@ def test_host_rng_matches_oracle(lib):
 
 def _ctx(lib):
     for n in ("dnn_ctx_init", "dnn_ctx_destroy", "_mem_pool_alloc", "mem_pool_mark", "mem_pool_release", "mem_pool_reset",
-              "lr_scheduler_create", "lr_scheduler_step", "lr_scheduler_get_lr"):
+              "lr_scheduler_create", "lr_scheduler_step", "lr_scheduler_get_lr", "lr_scheduler_reset"):
         getattr(lib, n).restype, getattr(lib, n).argtypes = B.API[n]
     ctx = B.DnnCtx()
     assert lib.dnn_ctx_init(C.byref(ctx), 1 << 20, 1 << 20, 1 << 20) == 0
@@ -106,6 +106,27 @@ def test_lr_schedules_match_oracle(lib, schedule, warmup, total, step, gamma):
         want = O.lr_schedule(schedule, 6e-4, -1.0, warmup, total, step, gamma, t)
         assert abs(opt.lr - want) <= 2e-7 * abs(want) + 1e-12, (t, opt.lr, want)
         lib.lr_scheduler_step(s)
+    lib.dnn_ctx_destroy(C.byref(ctx))
+
+
+def test_lr_schedules_equal_the_reference_bit_for_bit(lib):
+    """The schedules are host arithmetic (src/optim.c:104-189): the library's learning rates over 130 steps
+    of eight scheduler set-ups, lr_scheduler_get_lr and lr_scheduler_reset must equal the vectors the
+    unmodified reference produced (tests/golden/ops.npz) exactly.  Needs no device."""
+    from cases import CASES
+    from golden_util import check
+    case = [c for c in CASES if c.name == "lr_schedules"][0]
+    ctx = _ctx(lib)
+
+    class Host:
+        pass
+    h = Host()
+    h.lib, h.params = lib, ctx.params
+    got = case.run(h, case.make(None))
+    golden = np.load(os.path.join(ROOT, "tests", "golden", "ops.npz"))
+    for k, v in got.items():
+        key = "lr_schedules/" + k
+        check(key, v, golden[key], golden[key + "#"], 0, exact=True)
     lib.dnn_ctx_destroy(C.byref(ctx))
 
 

@@ -95,7 +95,7 @@ class _TwiceBackward:
 OVERWRITING = ("merge_heads", "split_heads")     # their backward stores (src/multihead.c:92,177)
 
 
-@pytest.mark.parametrize("case", [c for c in CASES if not c.name.startswith(("rope_freqs_init", "transpose+", "mean"))],
+@pytest.mark.parametrize("case", [c for c in CASES if not c.name.startswith(("rope_freqs_init", "transpose+", "mean", "adamw", "clip_grad_norm", "lr_schedules"))],
                          ids=lambda c: c.name)
 def test_second_backward_accumulates(gpu, binding, case):
     """The first gradient written to a buffer may be a plain store; every later one must add.
