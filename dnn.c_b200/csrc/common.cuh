@@ -99,7 +99,10 @@ int  dp_overlap_finish();
 struct OptGraph;
 OptGraph *opt_graph_prepare(adamw_opt *opt, float grad_clip);
 void opt_graph_launch(OptGraph *og, adamw_opt *opt);
-void opt_graph_advance(OptGraph *og, adamw_opt *opt);
+const void *opt_graph_advance(OptGraph *og, adamw_opt *opt);
+void opt_graph_launched(OptGraph *og);
+const void *opt_graph_state_dev(const OptGraph *og);
+size_t opt_graph_state_bytes();
 const float *opt_graph_norm(const OptGraph *og);
 void opt_graph_destroy(OptGraph *og);
 

@@ -247,6 +247,7 @@ tensor *dnn_cuda_dp_decoder_lm_train_step(struct mem_pool *scratch, decoder_lm *
 struct dnn_cuda_step_graph {
     cudaGraph_t graph; cudaGraphExec_t exec;
     OptGraph *og; adamw_opt *opt; tensor *loss;
+    cudaGraphNode_t state_copy; // the node that brings learning rate and bias corrections in
     long long kernels;          // kernel launches recorded in the graph
 };
 
@@ -281,6 +282,21 @@ dnn_cuda_step_graph *dnn_cuda_graph_capture_decoder_lm_step(struct mem_pool *scr
         delete sg;
         return nullptr;
     }
+    // find the copy node of the optimiser state: every replay redirects it to its own pinned slot
+    size_t n_nodes = 0;
+    CUDA_OK(cudaGraphGetNodes(sg->graph, nullptr, &n_nodes));
+    std::vector<cudaGraphNode_t> nodes(n_nodes);
+    CUDA_OK(cudaGraphGetNodes(sg->graph, nodes.data(), &n_nodes));
+    sg->state_copy = nullptr;
+    for (cudaGraphNode_t nd : nodes) {
+        cudaGraphNodeType ty;
+        CUDA_OK(cudaGraphNodeGetType(nd, &ty));
+        if (ty != cudaGraphNodeTypeMemcpy) continue;
+        cudaMemcpy3DParms mp;
+        CUDA_OK(cudaGraphMemcpyNodeGetParams(nd, &mp));
+        if (mp.dstPtr.ptr == opt_graph_state_dev(sg->og)) { sg->state_copy = nd; break; }
+    }
+    DNN_CHECK(sg->state_copy, "graph capture: the optimiser-state copy node was not recorded");
     e = cudaGraphInstantiate(&sg->exec, sg->graph, 0);
     DNN_CHECK(e == cudaSuccess, "graph capture: cudaGraphInstantiate failed");
     return sg;
@@ -288,8 +304,11 @@ dnn_cuda_step_graph *dnn_cuda_graph_capture_decoder_lm_step(struct mem_pool *scr
 
 int dnn_cuda_graph_replay(dnn_cuda_step_graph *sg, float *loss_out, float *grad_norm_out) {
     if (!sg) return -1;
-    opt_graph_advance(sg->og, sg->opt);
+    const void *state = opt_graph_advance(sg->og, sg->opt);
+    if (cudaGraphExecMemcpyNodeSetParams1D(sg->exec, sg->state_copy, const_cast<void *>(opt_graph_state_dev(sg->og)), state,
+                                           opt_graph_state_bytes(), cudaMemcpyHostToDevice) != cudaSuccess) return -3;
     if (cudaGraphLaunch(sg->exec, stream()) != cudaSuccess) return -2;
+    opt_graph_launched(sg->og);
     add_launches(sg->kernels);
     int rc = 0;
     if (loss_out) rc |= dnn_cuda_memcpy_d2h(loss_out, (const float *)sg->loss->data + sg->loss->offset, sizeof(float));

@@ -345,10 +345,20 @@ namespace dnnb {
 // Optimiser tail of a captured step: its own tables and reduction buffers (the eager path's are
 // re-uploaded on every call, which a graph cannot replay), a device StepState and its pinned
 // host copy.
+// The graph's copy node reads pinned host memory when the graph EXECUTES, not when it is
+// launched, so replays queued back to back without a readback must not share one host struct:
+// the state lives in a ring of kStateSlots pinned structs, each replay points the copy node at
+// the next slot (cudaGraphExecMemcpyNodeSetParams1D) and a slot is rewritten only after the
+// replay that last read it has finished (one event per slot).
+constexpr int kStateSlots = 8;
 struct OptGraph {
     TensorRef *tab = nullptr; int nt = 0, chunks = 0;
     double *partial = nullptr, *sq = nullptr; float *norm = nullptr;
-    StepState *state_dev = nullptr, *state_host = nullptr;
+    StepState *state_dev = nullptr, *state_host = nullptr;       // state_host: kStateSlots structs
+    cudaEvent_t slot_done[kStateSlots] = {};
+    bool slot_used[kStateSlots] = {};
+    int next_slot = 0;
+    float max_norm = 0.0f;
     AdamHyper h;
 };
 
@@ -375,9 +385,11 @@ OptGraph *opt_graph_prepare(adamw_opt *opt, float grad_clip) {
     CUDA_OK(cudaMalloc((void **)&og->sq, sizeof(double)));
     CUDA_OK(cudaMalloc((void **)&og->norm, sizeof(float)));
     CUDA_OK(cudaMalloc((void **)&og->state_dev, sizeof(StepState)));
-    CUDA_OK(cudaMallocHost((void **)&og->state_host, sizeof(StepState)));
+    CUDA_OK(cudaMallocHost((void **)&og->state_host, kStateSlots * sizeof(StepState)));
+    memset(og->state_host, 0, kStateSlots * sizeof(StepState));
+    for (int i = 0; i < kStateSlots; i++) CUDA_OK(cudaEventCreateWithFlags(&og->slot_done[i], cudaEventDisableTiming));
     og->h.b1 = opt->beta1; og->h.b2 = opt->beta2; og->h.eps = opt->eps; og->h.wd = opt->weight_decay; og->h.bc1 = og->h.bc2_sqrt = 1.0f;
-    og->state_host->max_norm = grad_clip;
+    og->max_norm = grad_clip;
     return og;
 }
 // Inside capture, after backward: norm, clip, AdamW.
@@ -394,16 +406,32 @@ void opt_graph_launch(OptGraph *og, adamw_opt *opt) {
     LAUNCHED("adamw_kernel");
 }
 // Before every replay: the step counter moves on the host, the graph reads the derived numbers.
-void opt_graph_advance(OptGraph *og, adamw_opt *opt) {
+// Returns the pinned struct this replay's copy node must read (see kStateSlots).
+const void *opt_graph_advance(OptGraph *og, adamw_opt *opt) {
     opt->t++;
-    og->state_host->lr = opt->lr;
-    og->state_host->bc1 = 1.0f - powf(opt->beta1, (float)opt->t);
-    og->state_host->bc2_sqrt = sqrtf(1.0f - powf(opt->beta2, (float)opt->t));
+    const int slot = og->next_slot;
+    og->next_slot = (slot + 1) % kStateSlots;
+    if (og->slot_used[slot]) CUDA_OK(cudaEventSynchronize(og->slot_done[slot]));   // the replay kStateSlots ago
+    StepState *st = og->state_host + slot;
+    st->lr = opt->lr;
+    st->bc1 = 1.0f - powf(opt->beta1, (float)opt->t);
+    st->bc2_sqrt = sqrtf(1.0f - powf(opt->beta2, (float)opt->t));
+    st->max_norm = og->max_norm;
+    return st;
 }
+// After the replay has been launched: marks when the slot handed out by the last advance is free again.
+void opt_graph_launched(OptGraph *og) {
+    const int slot = (og->next_slot + kStateSlots - 1) % kStateSlots;
+    CUDA_OK(cudaEventRecord(og->slot_done[slot], stream()));
+    og->slot_used[slot] = true;
+}
+const void *opt_graph_state_dev(const OptGraph *og) { return og->state_dev; }
+size_t opt_graph_state_bytes() { return sizeof(StepState); }
 const float *opt_graph_norm(const OptGraph *og) { return og->norm; }
 void opt_graph_destroy(OptGraph *og) {
     if (!og) return;
     cudaFree(og->tab); cudaFree(og->partial); cudaFree(og->sq); cudaFree(og->norm); cudaFree(og->state_dev); cudaFreeHost(og->state_host);
+    for (int i = 0; i < kStateSlots; i++) if (og->slot_done[i]) cudaEventDestroy(og->slot_done[i]);
     delete og;
 }
 

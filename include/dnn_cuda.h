@@ -86,8 +86,11 @@ int  dnn_cuda_optimizer_load(adamw_opt *opt, const char *path);
  * on demand must have their final size, parameters must own gradient buffers); new batches are
  * written into the SAME input_ids / target tensors with dnn_cuda_upload; the scratch pool may be
  * reset and used between replays, but not while a replay is in flight; data-parallel runs are not
- * captured.  capture returns NULL with a message when recording fails.  Results equal the eager
- * step bit for bit.  No counterpart in the reference (whose ops run synchronously on the host). */
+ * captured.  Replays may be queued back to back without reading anything back: each one carries its
+ * own copy of the learning rate and bias corrections (a ring of eight pinned slots; the ninth queued
+ * replay waits on the host for the first to finish).  capture returns NULL with a message when
+ * recording fails.  Results equal the eager step bit for bit.  No counterpart in the reference
+ * (whose ops run synchronously on the host). */
 typedef struct dnn_cuda_step_graph dnn_cuda_step_graph;
 dnn_cuda_step_graph *dnn_cuda_graph_capture_decoder_lm_step(struct mem_pool *scratch_pool, decoder_lm *lm,
                                                             const tensor *input_ids, const tensor *target,

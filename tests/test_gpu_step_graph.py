@@ -84,3 +84,34 @@ def test_new_batches_go_through_the_same_tensors(binding):
     assert l0 == l1
     for n in p0:
         assert np.array_equal(p0[n], p1[n]), n
+
+
+def test_replays_queued_without_readback_equal_eager_steps(binding):
+    """Twenty replays launched back to back with NULL outputs (nothing makes the host wait), each with its
+    own learning rate.  The graph reads learning rate and bias corrections from pinned host memory when
+    it EXECUTES, so every replay needs its own copy of them: the parameters must equal twenty eager steps
+    bit for bit."""
+    cfg = dict(models.lm_config("c1")); cfg.update(L=2, B=4, N=64)
+    ids_np, _ = models.lm_inputs(cfg)
+    lrs = [cfg["lr"] * (1.0 + 0.37 * (s % 5)) for s in range(21)]
+
+    d, lm, opt, params, names, keep = _build(binding, cfg)
+    ids = d.tensor(ids_np, d.data); tgt = d.lib.decoder_lm_shift_targets(d.data, ids)
+    _eager(d, lm, opt, cfg, ids, tgt, lrs)
+    want = {n: d.download(t) for n, t in zip(names, params)}
+    d.close()
+
+    d, lm, opt, params, names, keep = _build(binding, cfg)
+    ids = d.tensor(ids_np, d.data); tgt = d.lib.decoder_lm_shift_targets(d.data, ids)
+    _eager(d, lm, opt, cfg, ids, tgt, lrs[:1])
+    g = d.lib.dnn_cuda_graph_capture_decoder_lm_step(d.scratch, lm, ids, tgt, opt, cfg["clip"])
+    assert g, "capture failed"
+    for lr in lrs[1:]:
+        opt.contents.lr = lr
+        assert d.lib.dnn_cuda_graph_replay(g, None, None) == 0
+    d.sync()
+    assert opt.contents.t == len(lrs)
+    for n, t in zip(names, params):
+        assert np.array_equal(d.download(t), want[n]), n
+    d.lib.dnn_cuda_graph_destroy(g)
+    d.close()
