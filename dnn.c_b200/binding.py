@@ -81,6 +81,11 @@ class LrScheduler(C.Structure):
 
 assert C.sizeof(AdamW) == 56
 
+
+class KernelTime(C.Structure):
+    _fields_ = [("name", C.c_char * 56), ("launches", C.c_longlong), ("ms", C.c_double), ("work", C.c_double)]
+
+
 PoolP = C.POINTER(MemPool)
 VP = C.c_void_p
 I = C.c_int
@@ -205,6 +210,8 @@ CUDA_API = {
     "dnn_cuda_host_free": (None, [VP]),
     "dnn_cuda_set_gemm_mode": (I, [I]),
     "dnn_cuda_get_gemm_mode": (I, []),
+    "dnn_cuda_set_tf32_policy": (I, [C.c_uint, C.c_double]),
+    "dnn_cuda_get_tf32_policy": (I, [C.POINTER(C.c_uint), C.POINTER(C.c_double)]),
     "dnn_cuda_graph_capture_decoder_lm_step": (VP, [PoolP, VP, TensorP, TensorP, C.POINTER(AdamW), F]),
     "dnn_cuda_graph_replay": (I, [VP, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "dnn_cuda_graph_destroy": (None, [VP]),
@@ -225,6 +232,7 @@ CUDA_API = {
     "dnn_cuda_timer_stop_ms": (F, []),
     "dnn_cuda_profile_enable": (I, [I]),
     "dnn_cuda_profile_read": (I, [I, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "dnn_cuda_profile_kernels": (I, [C.POINTER(KernelTime), I]),
     "dnn_cuda_pool_device_used": (C.c_size_t, [PoolP]),
     "dnn_cuda_pool_device_peak": (C.c_size_t, [PoolP]),
     "dnn_cuda_dp_unique_id": (I, [VP]),

@@ -802,6 +802,15 @@ struct AttnHost {
     const float *rope_c, *rope_s;
 };
 
+// Visible (query, key) pairs of all heads when every sequence has its full length N: rows inside the
+// prefix see the prefix, the others see themselves and everything before (src/attention.c:39-64).
+// Per-batch lengths are device data here, so padding is not subtracted: with seq_lens the figure is
+// an upper bound.  Used only for the work figure of the launch timeline.
+static double visible_pairs(const AttnHost &a) {
+    const double P = a.prefix < a.N ? a.prefix : a.N, N = a.N;
+    return (double)a.B * a.H * (P * P + (N * (N + 1.0) - P * (P + 1.0)) * 0.5);
+}
+
 template <int HD>
 static void fwd_launch(const AttnHost &a) {
     using Cfg = FwdCfg<HD>;
@@ -813,6 +822,7 @@ static void fwd_launch(const AttnHost &a) {
     p.o = a.o; p.lse = a.lse; p.seq_lens = a.seq_lens; p.B = a.B; p.H = a.H; p.N = a.N; p.prefix = a.prefix; p.scale = a.scale;
     dim3 grid((a.N + Cfg::BM - 1) / Cfg::BM, a.H, a.B);
     attn_fwd_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tq, tk, tv, p);
+    prof_work(4.0 * HD * visible_pairs(a));                      // S = Q K^T and O = P V
     LAUNCHED("attn_fwd_tc_kernel");
 }
 
@@ -835,6 +845,7 @@ static void bwd_launch(const AttnHost &a) {
         CUtensorMap tqm = map4d(a.q, a.B, a.H, a.N, HD, Cfg::BQ, true), tgm = map4d(a.dout, a.B, a.H, a.N, HD, Cfg::BQ, true);
         dim3 grid((a.N + Cfg::BKEY - 1) / Cfg::BKEY, a.H, a.B);
         attn_bwd_dkv_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tka, tva, tqk, tgk, tqm, tgm, p);
+        prof_work(6.0 * HD * visible_pairs(a));                  // dV, dP, dK (the recomputed S is not counted)
         LAUNCHED("attn_bwd_dkv_tc_kernel");
     }
     if (a.dq.p) {
@@ -844,6 +855,7 @@ static void bwd_launch(const AttnHost &a) {
         CUtensorMap tkm = map4d(a.k, a.B, a.H, a.N, HD, Cfg::BN, true);
         dim3 grid((a.N + Cfg::BM - 1) / Cfg::BM, a.H, a.B);
         attn_bwd_dq_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tqa, tga, tkk, tvk, tkm, p);
+        prof_work(2.0 * HD * visible_pairs(a));                  // dQ (recomputed S and dP not counted)
         LAUNCHED("attn_bwd_dq_tc_kernel");
     }
 }

@@ -44,6 +44,8 @@ void *dev_put(struct mem_pool *pool, const void *host, size_t bytes);
 
 int gemm_mode();
 // Profiling hooks (no-ops unless dnn_cuda_profile_enable(1)): bracket one launch.
+// Algorithmic work (bytes or FLOP) of the NEXT launch, for the per-launch timeline (dnn_cuda_profile_enable(2)).
+void prof_work(double work);
 void prof_begin(int kernel_class);
 void prof_end(int kernel_class, double work);
 
@@ -161,7 +163,12 @@ struct GemmArgs {
     int M, N, K, batch;
     bool accumulate;
 };
-void gemm(const GemmArgs &g);          // dispatches on gemm_mode() and layout
+void gemm(const GemmArgs &g);          // dispatches on gemm_mode(), the precision policy and layout
+// Role of the next gemm() calls of this thread, for the precision policy (dnn_cuda_set_tf32_policy).
+enum { GEMM_ROLE_FORWARD = 0, GEMM_ROLE_DA = 1, GEMM_ROLE_DW = 2 };
+void gemm_set_role(int role);
+void gemm_set_policy(unsigned roles_3x, double max_flop_3x);
+void gemm_get_policy(unsigned *roles_3x, double *max_flop_3x);
 
 // One-shot epilogue request for the next tensor-core GEMM on this thread: rotate (RoPE) the
 // pairs of the first `cols` output columns, which are heads of size d; row r is position r % N.

@@ -20,7 +20,37 @@ namespace dnnb {
 
 struct ConvGeom { int N, C, H, W, out_C, kH, kW, stride, pad, H_out, W_out, M, K; };
 
-// col[k][m], k = (c, kh, kw), m = (n, oh, ow); one thread per element, m fastest.
+// col[k][m], k = (c, kh, kw), m = (n, oh, ow).  Row k of the column matrix is, image by image, a shifted
+// (and strided) copy of one input plane, so the index arithmetic is split by what it depends on:
+//   blockIdx.y = k            -> (c, kh, kw) once per CTA;
+//   threadIdx.x               -> four consecutive output positions of a plane, decoded once per thread into
+//                                source offsets and in-bounds flags;
+//   threadIdx.y + blockIdx.x  -> the image n, the only thing the inner loop changes.
+// The inner loop is four predicated loads and one 128-bit store.  HoWo must be a multiple of 4.
+__global__ void __launch_bounds__(256) im2col_v4_kernel(const float *__restrict__ x, float *__restrict__ col, ConvGeom g) {
+    const int k = blockIdx.y;
+    const int kw = k % g.kW, kh = (k / g.kW) % g.kH, c = k / (g.kW * g.kH);
+    const int HoWo = g.H_out * g.W_out, n4 = HoWo >> 2;
+    const int64_t plane = (int64_t)g.H * g.W;
+    for (int e = threadIdx.x; e < n4; e += blockDim.x) {
+        int off[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int o = 4 * e + j, oh = o / g.W_out, ow = o - oh * g.W_out;
+            const int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
+            off[j] = (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? ih * g.W + iw : -1;
+        }
+        float *dst = col + (int64_t)k * g.M + 4 * e;
+        for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
+            const float *src = x + ((int64_t)n * g.C + c) * plane;
+            float4 v;
+            v.x = off[0] >= 0 ? __ldg(src + off[0]) : 0.f; v.y = off[1] >= 0 ? __ldg(src + off[1]) : 0.f;
+            v.z = off[2] >= 0 ? __ldg(src + off[2]) : 0.f; v.w = off[3] >= 0 ? __ldg(src + off[3]) : 0.f;
+            *reinterpret_cast<float4 *>(dst + (int64_t)n * HoWo) = v;
+        }
+    }
+}
+// Any geometry: one thread per element, m fastest.
 __global__ void im2col_kernel(const float *__restrict__ x, float *__restrict__ col, ConvGeom g) {
     int64_t total = (int64_t)g.K * g.M;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -33,8 +63,67 @@ __global__ void im2col_kernel(const float *__restrict__ x, float *__restrict__ c
         col[idx] = v;
     }
 }
+static void run_im2col(const float *x, float *col, const ConvGeom &g) {
+    const int HoWo = g.H_out * g.W_out;
+    if (HoWo % 4 == 0 && g.M % 4 == 0 && aligned16(col) && g.K <= 65535) {
+        int bx = ((HoWo / 4 + 31) / 32) * 32;
+        if (bx > 256) bx = 256;
+        const int by = 256 / bx;
+        int gx = (g.N + by - 1) / by;
+        const int cap = (kNumSMs * 16 + g.K - 1) / g.K;       // a few waves in total
+        if (gx > cap) gx = cap < 1 ? 1 : cap;
+        im2col_v4_kernel<<<dim3(gx, g.K), dim3(bx, by), 0, stream()>>>(x, col, g);
+    } else {
+        im2col_kernel<<<grid_for((int64_t)g.K * g.M, 256), 256, 0, stream()>>>(x, col, g);
+    }
+    prof_work(4.0 * ((double)g.N * g.C * g.H * g.W + (double)g.K * g.M));
+    LAUNCHED("im2col_kernel");
+}
 
-// dx[n,c,ih,iw] += sum over (kh,kw,oh,ow) that read this pixel of dcol[k][m]; gather form, deterministic.
+// dx[n,c,ih,iw] (=|+=) sum over the windows (kh,kw,oh,ow) that read this pixel of dcol[k][m]; gather form,
+// fixed order (kh, then kw), no atomics.  Same split of the index arithmetic as im2col: blockIdx.y = c,
+// a thread owns four consecutive pixels of a plane and decodes, once, for each of its pixels and each of
+// the (at most 9) filter taps the offset of the column-matrix element that tap contributed, and the
+// inner loop over images does nothing but loads and adds.  H*W must be a multiple of 4, kH*kW <= 9.
+template <bool ACC>
+__global__ void __launch_bounds__(256) col2im_v4_kernel(const float *__restrict__ dcol, float *__restrict__ dx, ConvGeom g) {
+    const int c = blockIdx.y, HW = g.H * g.W, n4 = HW >> 2, HoWo = g.H_out * g.W_out, KK = g.kH * g.kW;
+    for (int e = threadIdx.x; e < n4; e += blockDim.x) {
+        int pos[4][9];                       // position inside an image's run of a column-matrix row, or -1
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int p = 4 * e + j, ih = p / g.W, iw = p - ih * g.W;
+#pragma unroll
+            for (int t = 0; t < 9; t++) {
+                pos[j][t] = -1;
+                if (t >= KK) continue;
+                const int kh = t / g.kW, kw = t - kh * g.kW;
+                const int a = ih + g.pad - kh, b = iw + g.pad - kw;
+                if (a < 0 || b < 0 || a % g.stride || b % g.stride) continue;
+                const int oh = a / g.stride, ow = b / g.stride;
+                if (oh >= g.H_out || ow >= g.W_out) continue;
+                pos[j][t] = oh * g.W_out + ow;
+            }
+        }
+        for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
+            const float *src = dcol + (int64_t)c * KK * g.M + (int64_t)n * HoWo;      // tap t: + t * M
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float s = 0.f;
+#pragma unroll
+                for (int t = 0; t < 9; t++) if (pos[j][t] >= 0) s += __ldg(src + (int64_t)t * g.M + pos[j][t]);
+                v[j] = s;
+            }
+            float4 *dst = reinterpret_cast<float4 *>(dx + ((int64_t)n * g.C + c) * HW + 4 * e);
+            float4 o = make_float4(v[0], v[1], v[2], v[3]);
+            if (ACC) { const float4 old = *dst; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+            *dst = o;
+        }
+    }
+}
+// Any geometry.
+template <bool ACC>
 __global__ void col2im_kernel(const float *__restrict__ dcol, float *__restrict__ dx, ConvGeom g) {
     int64_t total = (int64_t)g.N * g.C * g.H * g.W;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -55,22 +144,62 @@ __global__ void col2im_kernel(const float *__restrict__ dcol, float *__restrict_
                 s += dcol[(int64_t)k * g.M + m];
             }
         }
-        dx[idx] += s;
+        dx[idx] = ACC ? dx[idx] + s : s;
     }
 }
+static void run_col2im(const float *dcol, float *dx, const ConvGeom &g, bool accumulate) {
+    const int HW = g.H * g.W;
+    if (HW % 4 == 0 && g.kH * g.kW <= 9 && aligned16(dx) && g.C <= 65535) {
+        int bx = ((HW / 4 + 31) / 32) * 32;
+        if (bx > 256) bx = 256;
+        const int by = 256 / bx;
+        int gx = (g.N + by - 1) / by;
+        const int cap = (kNumSMs * 16 + g.C - 1) / g.C;
+        if (gx > cap) gx = cap < 1 ? 1 : cap;
+        if (accumulate) col2im_v4_kernel<true><<<dim3(gx, g.C), dim3(bx, by), 0, stream()>>>(dcol, dx, g);
+        else col2im_v4_kernel<false><<<dim3(gx, g.C), dim3(bx, by), 0, stream()>>>(dcol, dx, g);
+    } else {
+        const int grid = grid_for((int64_t)g.N * g.C * HW, 256);
+        if (accumulate) col2im_kernel<true><<<grid, 256, 0, stream()>>>(dcol, dx, g);
+        else col2im_kernel<false><<<grid, 256, 0, stream()>>>(dcol, dx, g);
+    }
+    prof_work(4.0 * ((accumulate ? 2.0 : 1.0) * g.N * g.C * g.H * g.W + (double)g.K * g.M));
+    LAUNCHED("col2im_kernel");
+}
 
-// (M, out_C) <-> NCHW: dst_nchw[n,oc,hw] = src_mc[(n*HW+hw), oc]   (TO_NCHW)
+// (M, out_C) <-> NCHW, per image a [HW, OC] <-> [OC, HW] transpose through a padded 32 x 32 shared-memory
+// tile, so that both the reads and the writes are full 128-byte rows.
+//   TO_NCHW:  dst[n, oc, hw] = src[(n*HW + hw), oc];   otherwise  dst[(n*HW + hw), oc] = src[n, oc, hw].
 template <bool TO_NCHW>
-__global__ void conv_permute_kernel(float *__restrict__ dst, const float *__restrict__ src, int N, int OC, int HW) {
-    int64_t total = (int64_t)N * OC * HW;
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        if (TO_NCHW) {      // idx walks NCHW
-            int hw = (int)(idx % HW); int64_t t = idx / HW; int oc = (int)(t % OC); int n = (int)(t / OC);
-            dst[idx] = src[((int64_t)n * HW + hw) * OC + oc];
-        } else {            // idx walks (M, OC)
-            int oc = (int)(idx % OC); int64_t t = idx / OC; int hw = (int)(t % HW); int n = (int)(t / HW);
-            dst[idx] = src[((int64_t)n * OC + oc) * HW + hw];
-        }
+__global__ void __launch_bounds__(256) conv_permute_kernel(float *__restrict__ dst, const float *__restrict__ src, int OC, int HW) {
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z;
+    const int64_t img = (int64_t)n * OC * HW;
+    // rows/cols of the SOURCE matrix of this image: [R, Cc] row-major -> destination [Cc, R]
+    const int R = TO_NCHW ? HW : OC, Cc = TO_NCHW ? OC : HW;
+    const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;         // 32 x 8
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+        const int r = r0 + ty + i, c = c0 + tx;
+        if (r < R && c < Cc) tile[ty + i][tx] = src[img + (int64_t)r * Cc + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+        const int c = c0 + ty + i, r = r0 + tx;
+        if (r < R && c < Cc) dst[img + (int64_t)c * R + r] = tile[tx][ty + i];
+    }
+}
+template <bool TO_NCHW>
+static void run_permute(float *dst, const float *src, int N, int OC, int HW) {
+    const int R = TO_NCHW ? HW : OC, Cc = TO_NCHW ? OC : HW;
+    for (int n0 = 0; n0 < N; n0 += 65535) {
+        const int nb = N - n0 < 65535 ? N - n0 : 65535;
+        const int64_t off = (int64_t)n0 * OC * HW;
+        conv_permute_kernel<TO_NCHW><<<dim3((Cc + 31) / 32, (R + 31) / 32, nb), 256, 0, stream()>>>(dst + off, src + off, OC, HW);
+        prof_work(8.0 * nb * OC * HW);
+        LAUNCHED("conv_permute_kernel");
     }
 }
 
@@ -130,7 +259,8 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
     // Gradient buffers first: an activation's gradient comes from the same pool
     // as the temporaries below and must survive the release at the end.
     float *wg = weight->requires_grad ? _grad_ensure(weight) : nullptr;
-    float *xg = input->requires_grad ? _grad_ensure(input) : nullptr;
+    bool acc_x = true;
+    float *xg = input->requires_grad ? grad_full(input, &acc_x) : nullptr;      // col2im writes every pixel: a fresh buffer is stored to
     if (bias && bias->requires_grad) {
         float *bg = _grad_ensure(bias);
         int S = g.N < 32 ? g.N : 32;
@@ -148,8 +278,7 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
     const float *g_mc = gd;                 // upstream gradient read as (M, out_C)
     if (sv->nchw) {
         float *tmp = dev_alloc_t<float>(fn->pool, (size_t)g.M * g.out_C);
-        conv_permute_kernel<false><<<grid_for((int64_t)g.M * g.out_C, 256), 256, 0, stream()>>>(tmp, gd, g.N, g.out_C, HW);
-        LAUNCHED("conv_permute_kernel");
+        run_permute<false>(tmp, gd, g.N, g.out_C, HW);
         g_mc = tmp;
     }
     if (wg) {
@@ -159,7 +288,9 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
         float *dwp = padded ? dev_alloc_t<float>(fn->pool, (size_t)g.out_C * Kp) : nullptr;
         a.C = padded ? dwp : wg + weight->offset; a.c_rs = wpitch; a.c_cs = 1; a.c_bs = 0;
         a.bias = nullptr; a.M = g.out_C; a.N = g.K; a.K = g.M; a.batch = 1; a.accumulate = !padded;
+        gemm_set_role(GEMM_ROLE_DW);
         gemm(a);
+        gemm_set_role(GEMM_ROLE_FORWARD);
         if (padded) {
             conv_unpad_add_kernel<<<(g.out_C * g.K + 255) / 256, 256, 0, stream()>>>(wg + weight->offset, dwp, g.out_C, g.K, Kp);
             LAUNCHED("conv_unpad_add_kernel");
@@ -172,14 +303,16 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
         a.B = g_mc; a.b_rs = 1; a.b_cs = g.out_C; a.b_bs = 0;
         a.C = dcol; a.c_rs = g.M; a.c_cs = 1; a.c_bs = 0;
         a.bias = nullptr; a.M = g.K; a.N = g.M; a.K = g.out_C; a.batch = 1; a.accumulate = false;
+        gemm_set_role(GEMM_ROLE_DA);
         gemm(a);
-        col2im_kernel<<<grid_for((int64_t)g.N * g.C * g.H * g.W, 256), 256, 0, stream()>>>(dcol, xg + input->offset, g);
-        LAUNCHED("col2im_kernel");
+        gemm_set_role(GEMM_ROLE_FORWARD);
+        run_col2im(dcol, xg + input->offset, g, acc_x);
     }
     mem_pool_release(fn->pool, mark);
 }
 
 // ---- avg_pool2d ------------------------------------------------------------------
+// Any window geometry: one thread per output element.
 __global__ void avgpool_fwd_kernel(const float *__restrict__ x, float *__restrict__ out,
                                    int64_t planes, int H, int W, int H_out, int W_out, int k, int stride, float inv_k2) {
     int64_t total = planes * H_out * W_out;
@@ -192,6 +325,29 @@ __global__ void avgpool_fwd_kernel(const float *__restrict__ x, float *__restric
         out[idx] = s * inv_k2;
     }
 }
+// 2 x 2 windows, stride 2, W a multiple of 4 (the pooling of the image models).  A thread owns two
+// neighbouring outputs of a plane: its position is decoded once, then it walks the planes with two
+// 128-bit loads (the two input rows of its windows) and one 64-bit store per plane.  Sums run in the
+// reference's order (row by row inside a window, src/ops_pool.c:293-313).
+__global__ void __launch_bounds__(256) avgpool_fwd_k2_kernel(const float *__restrict__ x, float *__restrict__ out,
+                                                             int planes, int H, int W, int H_out, int W_out) {
+    const int pairs = H_out * (W_out >> 1);                 // W_out is even because W % 4 == 0
+    const int64_t in_plane = (int64_t)H * W, out_plane = (int64_t)H_out * W_out;
+    for (int e = threadIdx.x; e < pairs; e += blockDim.x) {
+        const int oh = e / (W_out >> 1), ow = (e - oh * (W_out >> 1)) * 2;
+        const int in_off = (2 * oh) * W + 2 * ow, out_off = oh * W_out + ow;
+        for (int pl = blockIdx.x * blockDim.y + threadIdx.y; pl < planes; pl += gridDim.x * blockDim.y) {
+            const float *xp = x + pl * in_plane + in_off;
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(xp)), b = __ldg(reinterpret_cast<const float4 *>(xp + W));
+            float2 o;
+            o.x = (((a.x + a.y) + b.x) + b.y) * 0.25f;
+            o.y = (((a.z + a.w) + b.z) + b.w) * 0.25f;
+            *reinterpret_cast<float2 *>(out + pl * out_plane + out_off) = o;
+        }
+    }
+}
+// Any window geometry, gather form: every input element sums the windows that cover it.
+template <bool ACC>
 __global__ void avgpool_bwd_kernel(const float *__restrict__ g, float *__restrict__ dx,
                                    int64_t planes, int H, int W, int H_out, int W_out, int k, int stride, float inv_k2) {
     int64_t total = planes * H * W;
@@ -205,8 +361,46 @@ __global__ void avgpool_bwd_kernel(const float *__restrict__ g, float *__restric
         float s = 0.f;
         for (int oh = oh_lo; oh <= oh_hi; oh++)
             for (int ow = ow_lo; ow <= ow_hi; ow++) s += g[pl * H_out * W_out + (int64_t)oh * W_out + ow] * inv_k2;
-        if (oh_lo <= oh_hi && ow_lo <= ow_hi) dx[idx] += s;
+        dx[idx] = ACC ? dx[idx] + s : s;
     }
+}
+// Windows that do not overlap (stride == k) and W a multiple of 4: every input element belongs to at most
+// one window.  A thread owns four neighbouring input elements of a plane, decodes once which output each
+// of them reads (or none, past the last full window), and walks the planes with one 128-bit store each.
+template <bool ACC>
+__global__ void __launch_bounds__(256) avgpool_bwd_tiles_kernel(const float *__restrict__ g, float *__restrict__ dx, int planes,
+                                                                int H, int W, int H_out, int W_out, int k, float inv_k2) {
+    const int n4 = (H * W) >> 2;
+    const int64_t in_plane = (int64_t)H * W, out_plane = (int64_t)H_out * W_out;
+    for (int e = threadIdx.x; e < n4; e += blockDim.x) {
+        int src[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int p = 4 * e + j, ih = p / W, iw = p - ih * W;
+            const int oh = ih / k, ow = iw / k;
+            src[j] = (oh < H_out && ow < W_out) ? oh * W_out + ow : -1;
+        }
+        for (int pl = blockIdx.x * blockDim.y + threadIdx.y; pl < planes; pl += gridDim.x * blockDim.y) {
+            const float *gp = g + pl * out_plane;
+            float4 v;
+            v.x = src[0] >= 0 ? __ldg(gp + src[0]) * inv_k2 : 0.f; v.y = src[1] >= 0 ? __ldg(gp + src[1]) * inv_k2 : 0.f;
+            v.z = src[2] >= 0 ? __ldg(gp + src[2]) * inv_k2 : 0.f; v.w = src[3] >= 0 ? __ldg(gp + src[3]) * inv_k2 : 0.f;
+            float4 *dst = reinterpret_cast<float4 *>(dx + pl * in_plane + 4 * e);
+            if (ACC) { const float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+            *dst = v;
+        }
+    }
+}
+
+// Thread block (bx, by): bx threads cover the positions of a plane, by planes side by side.
+static void plane_launch_shape(int positions, int64_t planes, dim3 &grid, dim3 &block) {
+    int bx = ((positions + 31) / 32) * 32;
+    if (bx > 256) bx = 256;
+    const int by = 256 / bx;
+    int64_t gx = (planes + by - 1) / by;
+    const int64_t cap = (int64_t)kNumSMs * 16;
+    if (gx > cap) gx = cap;
+    grid = dim3((unsigned)gx); block = dim3(bx, by);
 }
 
 static void avg_pool2d_backward(grad_fn *fn, tensor *go) {
@@ -215,10 +409,24 @@ static void avg_pool2d_backward(grad_fn *fn, tensor *go) {
     if (!x->requires_grad) return;
     int N = x->shape[0], C = x->shape[1], H = x->shape[2], W = x->shape[3];
     int H_out = (H - k) / stride + 1, W_out = (W - k) / stride + 1;
-    float *xg = _grad_ensure(x);        // indexed from 0 with packed NCHW strides, as the reference does
+    // every input element is written (elements no window covers get a zero contribution), so a fresh
+    // gradient buffer is stored to; indexed from 0 with packed NCHW strides, as the reference does
+    bool acc = true;
+    float *xg = x->contiguous ? grad_full(x, &acc) : _grad_ensure(x);
     int64_t planes = (int64_t)N * C;
-    avgpool_bwd_kernel<<<grid_for(planes * H * W, 256), 256, 0, stream()>>>((const float *)go->data, xg, planes, H, W,
-                                                                            H_out, W_out, k, stride, 1.0f / (float)(k * k));
+    const float inv = 1.0f / (float)(k * k);
+    const float *gd = (const float *)go->data;
+    if (stride == k && W % 4 == 0 && aligned16(xg) && planes < (1 << 30)) {
+        dim3 grid, block;
+        plane_launch_shape(H * W / 4, planes, grid, block);
+        if (acc) avgpool_bwd_tiles_kernel<true><<<grid, block, 0, stream()>>>(gd, xg, (int)planes, H, W, H_out, W_out, k, inv);
+        else avgpool_bwd_tiles_kernel<false><<<grid, block, 0, stream()>>>(gd, xg, (int)planes, H, W, H_out, W_out, k, inv);
+    } else {
+        const int grid = grid_for(planes * H * W, 256);
+        if (acc) avgpool_bwd_kernel<true><<<grid, 256, 0, stream()>>>(gd, xg, planes, H, W, H_out, W_out, k, stride, inv);
+        else avgpool_bwd_kernel<false><<<grid, 256, 0, stream()>>>(gd, xg, planes, H, W, H_out, W_out, k, stride, inv);
+    }
+    prof_work(4.0 * ((acc ? 2.0 : 1.0) * planes * H * W + (double)planes * H_out * W_out));
     LAUNCHED("avgpool_bwd_kernel");
 }
 
@@ -251,8 +459,7 @@ tensor *tensor_conv2d(struct mem_pool *scratch, tensor *input, tensor *weight, t
 
     size_t mark = mem_pool_mark(scratch);
     float *col = dev_alloc_t<float>(scratch, (size_t)g.K * g.M);
-    im2col_kernel<<<grid_for((int64_t)g.K * g.M, 256), 256, 0, stream()>>>((const float *)input->data + input->offset, col, g);
-    LAUNCHED("im2col_kernel");
+    run_im2col((const float *)input->data + input->offset, col, g);
     float *mc = nchw ? dev_alloc_t<float>(scratch, (size_t)g.M * g.out_C) : (float *)out->data;
     GemmArgs a;         // mc[m,oc] = sum_k col[k,m] * W[oc,k] + bias[oc]
     a.A = col; a.a_rs = 1; a.a_cs = g.M; a.a_bs = 0;
@@ -265,9 +472,7 @@ tensor *tensor_conv2d(struct mem_pool *scratch, tensor *input, tensor *weight, t
     a.M = g.M; a.N = g.out_C; a.K = g.K; a.batch = 1; a.accumulate = false;
     gemm(a);
     if (nchw) {
-        conv_permute_kernel<true><<<grid_for((int64_t)g.M * g.out_C, 256), 256, 0, stream()>>>((float *)out->data, mc, g.N, g.out_C,
-                                                                                              g.H_out * g.W_out);
-        LAUNCHED("conv_permute_kernel");
+        run_permute<true>((float *)out->data, mc, g.N, g.out_C, g.H_out * g.W_out);
     }
     if (needs_grad) {
         grad_fn *fn = attach(scratch, out, conv2d_backward, 2, 1);
@@ -298,8 +503,15 @@ tensor *tensor_avg_pool2d(struct mem_pool *scratch, const tensor *x, int k, int 
         xd = tmp;
     }
     int64_t planes = (int64_t)N * C;
-    avgpool_fwd_kernel<<<grid_for(planes * H_out * W_out, 256), 256, 0, stream()>>>(xd, (float *)out->data, planes, H, W,
-                                                                                    H_out, W_out, k, stride, 1.0f / (float)(k * k));
+    if (k == 2 && stride == 2 && W % 4 == 0 && aligned16(xd) && aligned16(out->data) && planes < (1 << 30)) {
+        dim3 grid, block;
+        plane_launch_shape(H_out * (W_out / 2), planes, grid, block);
+        avgpool_fwd_k2_kernel<<<grid, block, 0, stream()>>>(xd, (float *)out->data, (int)planes, H, W, H_out, W_out);
+    } else {
+        avgpool_fwd_kernel<<<grid_for(planes * H_out * W_out, 256), 256, 0, stream()>>>(xd, (float *)out->data, planes, H, W,
+                                                                                        H_out, W_out, k, stride, 1.0f / (float)(k * k));
+    }
+    prof_work(4.0 * ((double)planes * H * W + (double)planes * H_out * W_out));
     LAUNCHED("avgpool_fwd_kernel");
     if (dnn_grad_enabled() && x->requires_grad) {
         grad_fn *fn = attach(scratch, out, avg_pool2d_backward, 1, 2);

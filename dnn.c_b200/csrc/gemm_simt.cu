@@ -87,15 +87,30 @@ void gemm_simt(const GemmArgs &g) {
     }
 }
 
+// Which product of an op a GEMM is: the precision policy of TF32 mode can send each kind to 3xTF32.
+static thread_local int g_role = GEMM_ROLE_FORWARD;
+void gemm_set_role(int role) { g_role = role; }
+static unsigned g_roles_3x = 0;
+static double g_max_flop_3x = 0.0;
+static bool g_policy_env_read = false;
+void gemm_set_policy(unsigned roles_3x, double max_flop_3x) { g_roles_3x = roles_3x; g_max_flop_3x = max_flop_3x; g_policy_env_read = true; }
+void gemm_get_policy(unsigned *roles_3x, double *max_flop_3x) { *roles_3x = g_roles_3x; *max_flop_3x = g_max_flop_3x; }
+
 void gemm(const GemmArgs &g) {
     int mode = gemm_mode();
     if (mode == DNN_CUDA_GEMM_FP32 || !gemm_tc_supported(g)) { gemm_simt(g); return; }
+    if (!g_policy_env_read) {
+        g_policy_env_read = true;
+        if (const char *e = getenv("DNN_CUDA_TF32_3X_ROLES")) g_roles_3x = (unsigned)atoi(e);
+        if (const char *e = getenv("DNN_CUDA_TF32_3X_MAX_GFLOP")) g_max_flop_3x = atof(e) * 1e9;
+    }
     // Precision policy of TF32 mode: a long reduction into a small output (the filter
     // gradient of a small convolution: thousands of products of mixed sign per element)
     // cancels heavily and would lose more than TF32's 1e-3; such GEMMs are tiny, so they
-    // take the 3xTF32 path at no measurable cost.
+    // take the 3xTF32 path at no measurable cost.  dnn_cuda_set_tf32_policy widens the rule.
     bool small_long = (int64_t)g.M * g.N <= 65536 && g.K >= 1024;
-    gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32 || small_long);
+    bool by_policy = ((g_roles_3x >> g_role) & 1u) || 2.0 * g.M * g.N * g.K * (g.batch > 0 ? g.batch : 1) <= g_max_flop_3x;
+    gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32 || small_long || by_policy);
 }
 
 }  // namespace dnnb

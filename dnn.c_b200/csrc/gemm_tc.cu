@@ -548,6 +548,7 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     cfg.attrs = &attr; cfg.numAttrs = 1;
     prof_begin(0);
     CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<BN, PAIR>, tmA, tmB, tmC, t));
+    prof_work(2.0 * g.M * g.N * g.K);
     LAUNCHED("gemm_tf32_kernel");
     prof_end(0, 2.0 * g.M * g.N * g.K);
     if (splits > 1) {

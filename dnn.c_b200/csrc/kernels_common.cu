@@ -282,6 +282,7 @@ void k_colsum_acc(float *out, const float *g, int64_t rows, int C, bool accumula
         bool fused = (int)grid.x <= kColsumGroups && aligned16(out);
         colsum_partial_v4_kernel<<<grid, block, 0, stream()>>>(g, g_colsum_scratch, rows, C, rows_per, fused ? out : nullptr,
                                                                accumulate ? 1 : 0);
+        prof_work(4.0 * rows * C);
         LAUNCHED("colsum_partial_v4_kernel");
         if (fused) return;
     } else {

@@ -298,6 +298,7 @@ static void ce_backward_common(grad_fn *fn, tensor *go, bool masked) {
             mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, rows, n_slices);
         LAUNCHED("ce_rows_kernel");
         ce_bwd_colsum_kernel<<<grid, block, 0, stream()>>>((const float *)logits->data, rows, ag, partial, map.C, n_slices, per);
+        prof_work(8.0 * n_slices * map.C);                       // read logits, write d(logits)
         LAUNCHED(masked ? "ce_masked_bwd_kernel" : "ce_bwd_kernel");
         k_colsum_finish(sums, partial, nslabs, map.C);
         // rows of the root that the slices do not cover were zero-filled: they add nothing to the sums
@@ -306,6 +307,7 @@ static void ce_backward_common(grad_fn *fn, tensor *go, bool masked) {
     }
     ce_bwd_kernel<<<(unsigned)n_slices, 256, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
         mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, (const float *)go->data, inv, ag, acc ? 1 : 0);
+    prof_work((acc ? 12.0 : 8.0) * n_slices * map.C);
     LAUNCHED(masked ? "ce_masked_bwd_kernel" : "ce_bwd_kernel");
 }
 static void cross_entropy_backward(grad_fn *fn, tensor *go) { ce_backward_common(fn, go, false); }
@@ -327,6 +329,7 @@ static tensor *ce_forward(struct mem_pool *scratch, const tensor *logits, const 
     tensor *out = tensor_scratch(scratch, 1, &one, 0);
     ce_fwd_kernel<<<(unsigned)n_slices, 256, 0, stream()>>>((const float *)logits->data, (const int *)target->data,
         mask ? (const float *)mask->data : nullptr, map, max_vals, sum_exp, term, mval);
+    prof_work(4.0 * n_slices * map.C);                           // one pass over the logits
     LAUNCHED(mask ? "ce_masked_fwd_kernel" : "ce_fwd_kernel");
     ce_reduce_kernel<<<1, 1024, 0, stream()>>>(term, mval, n_slices, 1.0f / (float)n_slices, (float *)out->data, inv);
     LAUNCHED("ce_reduce_kernel");

@@ -341,6 +341,7 @@ static void norm_forward(const float *x, const float *w, const float *b, float *
     if (grid > cap) grid = cap;
     if (vec) norm_fwd_kernel<LN, true><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
     else     norm_fwd_kernel<LN, false><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
+    prof_work(8.0 * rows * d);                                   // read x, write y
     LAUNCHED(LN ? "layernorm_fwd_kernel" : "rmsnorm_fwd_kernel");
 }
 
@@ -356,10 +357,12 @@ static void launch_bwd(const float *x, const float *w, const float *g, const flo
         static bool once = false;
         if (!once) { CUDA_OK(cudaFuncSetAttribute(norm_bwd_staged_kernel<LN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)); once = true; }
         norm_bwd_staged_kernel<LN, T><<<grid, kWarpsPerCta * 32, smem, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, addend);
+        prof_work((addend ? 16.0 : 12.0) * rows * d);            // read x, g (and the residual gradient), write dx
         LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
         return;
     }
     norm_bwd_kernel<LN, T><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, addend);
+    prof_work((addend ? 16.0 : 12.0) * rows * d);
     LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
 }
 

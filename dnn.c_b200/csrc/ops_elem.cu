@@ -254,6 +254,7 @@ static void relu_backward(grad_fn *fn, tensor *g) {
     const float *gd = (const float *)g->data;
     if (a->contiguous) {
         float *dx = ag + a->offset; const float *x = (const float *)a->data + a->offset;
+        prof_work((acc ? 16.0 : 12.0) * n);                     // read x, g (and dx when accumulating), write dx
         if (v4ok(n, {dx, x, gd})) ew_launch("relu_bwd_kernel", n / 4, ReluB4{(float4 *)dx, (const float4 *)x, (const float4 *)gd, acc});
         else ew_launch("relu_bwd_kernel", n, ReluB{dx, x, gd, acc});
     } else {
@@ -272,6 +273,7 @@ static void silu_backward(grad_fn *fn, tensor *g) {
     float *ag = grad_full(a, &acc);
     const float *gd = (const float *)g->data;
     if (a->contiguous) {
+        prof_work((acc ? 16.0 : 12.0) * n);
         ew_launch("silu_bwd_kernel", n, SiluB{ag + a->offset, (const float *)a->data + a->offset, gd, acc});
     } else {
         float *xt = dev_alloc_t<float>(fn->pool, (size_t)n), *dt = dev_alloc_t<float>(fn->pool, (size_t)n);
@@ -307,6 +309,7 @@ static void swiglu_backward(grad_fn *fn, tensor *go) {
             float *pg = dev_alloc_t<float>(fn->pool, (size_t)nslabs * C), *pu = dev_alloc_t<float>(fn->pool, (size_t)nslabs * C);
             dim3 grid((C / 4 + 31) / 32, nslabs), block(32, 8);
             swiglu_bwd_colsum_kernel<<<grid, block, 0, stream()>>>(g, u, god, dg, du, pg, pu, rows, C, per);
+            prof_work(20.0 * rows * C);                          // read gate, up, d(out); write d(gate), d(up)
             LAUNCHED("swiglu_bwd_kernel");
             float *sums_g = colsum_cache_reserve(C);
             colsum_cache_publish(dg, rows, C);
@@ -574,6 +577,7 @@ tensor *tensor_add(struct mem_pool *scratch, const tensor *a, const tensor *b) {
     float *od = (float *)out->data;
     const float *af = (const float *)a->data + a->offset, *bf = (const float *)b->data + b->offset;
     if (same_contig(a, b)) {
+        prof_work(12.0 * n);
         if (v4ok(n, {od, af, bf})) ew_launch("add_kernel", n / 4, AddV4{(float4 *)od, (const float4 *)af, (const float4 *)bf});
         else ew_launch("add_kernel", n, Add1{od, af, bf});
     } else if (a->contiguous && lastdim_bias(b, out) && numel_of(a) == n) {
@@ -640,6 +644,7 @@ tensor *tensor_relu(struct mem_pool *scratch, const tensor *t) {
         x = tmp;
     }
     float *od = (float *)out->data;
+    prof_work(8.0 * n);
     if (v4ok(n, {od, x})) ew_launch("relu_fwd_kernel", n / 4, ReluF4{(float4 *)od, (const float4 *)x});
     else ew_launch("relu_fwd_kernel", n, ReluF{od, x});
     if (dnn_grad_enabled() && t->requires_grad) {
@@ -677,6 +682,7 @@ tensor *tensor_swiglu(struct mem_pool *scratch, const tensor *gate, const tensor
     float *od = (float *)out->data;
     if (same_contig(gate, up)) {
         const float *g = (const float *)gate->data + gate->offset, *u = (const float *)up->data + up->offset;
+        prof_work(12.0 * n);
         if (v4ok(n, {od, g, u})) ew_launch("swiglu_fwd_kernel", n / 4, SwigluF4{(float4 *)od, (const float4 *)g, (const float4 *)u});
         else ew_launch("swiglu_fwd_kernel", n, SwigluF{od, g, u});
     } else {

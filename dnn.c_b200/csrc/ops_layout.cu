@@ -212,16 +212,65 @@ __global__ void emb_fill_kernel(const int *__restrict__ ids, int n, int vocab, c
     int id = ids[i];
     if (id >= 0 && id < vocab) list[start[id] + atomicAdd(&cursor[id], 1)] = i;
 }
-// One CTA per id.  The bucket is in arrival order; the next position to add is the smallest one
-// above the last (block-wide minimum), so rows are added in ascending position.
-__global__ void embedding_bwd_kernel(float *__restrict__ tg, const float *__restrict__ g, const int *__restrict__ count,
-                                     const int *__restrict__ start, const int *__restrict__ list,
-                                     int d, int64_t g_s0, int64_t t_s0, int64_t t_s1, int vec) {
-    __shared__ int sh[32];
-    const int id = blockIdx.x, k = count[id];
-    if (k == 0) return;
+// One CTA per POSITION; the CTA whose position is the first occurrence of its id does the id's work and
+// the others leave at once, so the grid is as large as the batch, not as the vocabulary, and no CTA is
+// launched for a table row nobody looked up.  The bucket of an id is in arrival order: it is sorted in
+// shared memory (rank = number of smaller positions; positions are distinct), then the rows of the
+// upstream gradient are added in ascending position -- the order of the reference's serial loop
+// (src/embedding.c:37-43) -- in registers, with one 128-bit read-modify-write of the table row at the end.
+constexpr int kEmbBucket = 1024;       // occurrences of one id that are sorted in shared memory
+__global__ void __launch_bounds__(128) embedding_bwd_kernel(float *__restrict__ tg, const float *__restrict__ g,
+                                                            const int *__restrict__ ids, const int *__restrict__ count,
+                                                            const int *__restrict__ start, const int *__restrict__ list,
+                                                            int vocab, int d, int64_t g_s0, int64_t t_s0, int64_t t_s1, int vec) {
+    __shared__ int sorted[kEmbBucket];
+    __shared__ int sh[4];
+    const int me = blockIdx.x, id = ids[me];
+    if (id < 0 || id >= vocab) return;
+    const int k = count[id];
     const int *mine = list + start[id];
+    if (k == 1) { if (threadIdx.x == 0) sorted[0] = me; }
+    else if (k <= kEmbBucket) {
+        int leader = 1;
+        for (int j = threadIdx.x; j < k; j += blockDim.x) {
+            const int p = __ldg(mine + j);
+            if (p < me) leader = 0;
+        }
+        if (!__syncthreads_and(leader)) return;                  // an earlier position of this id does the work
+        for (int j = threadIdx.x; j < k; j += blockDim.x) {
+            const int p = __ldg(mine + j);
+            int rank = 0;
+            for (int q = 0; q < k; q++) rank += __ldg(mine + q) < p;
+            sorted[rank] = p;
+        }
+    } else {
+        int leader = 1;
+        for (int j = threadIdx.x; j < k; j += blockDim.x) if (__ldg(mine + j) < me) leader = 0;
+        if (!__syncthreads_and(leader)) return;
+    }
+    __syncthreads();
     float *row = tg + (int64_t)id * t_s0;
+    if (k <= kEmbBucket) {
+        if (vec) {
+            float4 *r4 = reinterpret_cast<float4 *>(row);
+            for (int c = threadIdx.x; c < d / 4; c += blockDim.x) {
+                float4 a = r4[c];
+                for (int it = 0; it < k; it++) {
+                    const float4 x = __ldg(reinterpret_cast<const float4 *>(g + (int64_t)sorted[it] * g_s0) + c);
+                    a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+                }
+                r4[c] = a;
+            }
+        } else {
+            for (int c = threadIdx.x; c < d; c += blockDim.x) {
+                float a = row[(int64_t)c * t_s1];
+                for (int it = 0; it < k; it++) a += g[(int64_t)sorted[it] * g_s0 + c];
+                row[(int64_t)c * t_s1] = a;
+            }
+        }
+        return;
+    }
+    // a bucket too long for shared memory: the next position to add is the smallest one above the last
     int last = -1;
     for (int it = 0; it < k; it++) {
         int best = 0x7fffffff;
@@ -268,8 +317,9 @@ static void embedding_backward(grad_fn *fn, tensor *go) {
     const float *gd = (const float *)go->data;
     int vec = table->strides[1] == 1 && d % 4 == 0 && table->strides[0] % 4 == 0 && go->strides[0] % 4 == 0 &&
               aligned16(tg) && aligned16(gd);
-    embedding_bwd_kernel<<<vocab, 128, 0, stream()>>>(tg, gd, count, start, list, d, go->strides[0], table->strides[0],
-                                                      table->strides[1], vec);
+    embedding_bwd_kernel<<<n, 128, 0, stream()>>>(tg, gd, idp, count, start, list, vocab, d, go->strides[0], table->strides[0],
+                                                  table->strides[1], vec);
+    prof_work(8.0 * n * d);                                      // read the upstream rows; the touched table rows are at most as many again
     LAUNCHED("embedding_bwd_kernel");
 }
 

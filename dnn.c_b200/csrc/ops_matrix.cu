@@ -104,6 +104,7 @@ static void mm_forward(const MM &p, const tensor *a, const tensor *b, int trans_
     const float *ad = (const float *)a->data, *bd = (const float *)b->data;
     // B as a (K x N) operand: element (k,n) at k*b_rs' + n*b_cs'
     int64_t bk = trans_b ? p.b.cs : p.b.rs, bn = trans_b ? p.b.rs : p.b.cs;
+    gemm_set_role(GEMM_ROLE_FORWARD);
     if (p.collapse) {
         GemmArgs g;
         g.A = ad + p.a.off[0]; g.a_rs = p.a.rs; g.a_cs = p.a.cs; g.a_bs = 0;
@@ -131,6 +132,7 @@ static void mm_backward(const MM &p, tensor *a, tensor *b, int trans_b, const fl
     float *bg = (need_b && !self) ? grad_full(b, &acc_b) : nullptr;
 
     if (need_a) {
+        gemm_set_role(GEMM_ROLE_DA);
         // dA[m,k] += sum_n G[m,n] * Bop[k,n]   ->  X = G (M x N), Y = Bop^T (N x K)
         if (p.collapse) {
             GemmArgs g;
@@ -147,6 +149,7 @@ static void mm_backward(const MM &p, tensor *a, tensor *b, int trans_b, const fl
     if ((need_b && !self) || (self && need_a)) {
         float *dst = self ? ag : bg;
         bool acc = self ? true : acc_b;
+        gemm_set_role(GEMM_ROLE_DW);
         // dBop[k,n] += sum_m A[m,k] * G[m,n]  ->  X = A^T (K x M), Y = G (M x N); C strides follow B's layout
         if (p.collapse) {
             GemmArgs g;
@@ -160,6 +163,7 @@ static void mm_backward(const MM &p, tensor *a, tensor *b, int trans_b, const fl
                         p.K, p.N, p.M, p.batch, nullptr, acc);
         }
     }
+    gemm_set_role(GEMM_ROLE_FORWARD);
 }
 
 static void matmul_backward(grad_fn *fn, tensor *go) {

@@ -176,6 +176,7 @@ static bool grad_sumsq_device(tensor **params, int n_params, std::vector<TensorR
     if (tab.empty()) return false;
     chunks = upload_table(tab);
     sumsq_kernel<<<chunks, 256, 0, stream()>>>(g_os.tab, (int)tab.size(), g_os.partial);
+    { double b = 0; for (auto &r : tab) b += 4.0 * (double)r.n; prof_work(b); }
     LAUNCHED("grad_sumsq_kernel");
     sumsq_final_kernel<<<1, 1024, 0, stream()>>>(g_os.partial, chunks, g_os.norm, g_os.sq);
     LAUNCHED("grad_sumsq_final_kernel");
@@ -306,6 +307,7 @@ float clip_grad_norm(tensor **params, int n_params, float max_norm) {
     if (total > max_norm) {
         float scale = max_norm / total;
         scale_kernel<<<chunks, 256, 0, stream()>>>(g_os.tab, (int)tab.size(), scale);
+        { double b = 0; for (auto &r : tab) b += 8.0 * (double)r.n; prof_work(b); }
         LAUNCHED("grad_scale_kernel");
     }
     return total;
@@ -333,6 +335,7 @@ void adamw_step_with_lr_multipliers(adamw_opt *opt, const float *lr_mults) {
     for (auto &r : tab) bytes += 28.0 * (double)r.n;        // read p,g,m,v; write p,m,v
     prof_begin(1);
     adamw_kernel<<<chunks, 256, 0, stream()>>>(g_os.tab, (int)tab.size(), h);
+    prof_work(bytes);
     LAUNCHED("adamw_kernel");
     prof_end(1, bytes);
 }

@@ -75,6 +75,17 @@ cudaStream_t stream() {
     return g_rt.compute;
 }
 
+// Per-launch timeline (dnn_cuda_profile_enable(2)): one event after every launch on the compute stream.
+// Launches are serialised on that stream and the host runs ahead of the device, so the time between two
+// consecutive events is the duration of the later kernel.
+struct LaunchRec { const char *name; cudaEvent_t after; double work; };
+static bool g_timeline_on = false;
+static std::vector<LaunchRec> g_timeline;
+static cudaEvent_t g_timeline_start = nullptr;
+static double g_next_work = 0.0;
+static cudaEvent_t get_event();
+void prof_work(double work) { g_next_work = work; }
+
 void launched(const char *name) {
     g_rt.launches++;
     cudaError_t e = cudaPeekAtLastError();
@@ -83,6 +94,15 @@ void launched(const char *name) {
         snprintf(buf, sizeof buf, "launch of %s", name);
         cuda_fail(e, buf, __FILE__, __LINE__);
     }
+    if (g_timeline_on) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(g_rt.compute, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone) {
+            cudaEvent_t ev = get_event();
+            CUDA_OK(cudaEventRecord(ev, g_rt.compute));
+            g_timeline.push_back(LaunchRec{name, ev, g_next_work});
+        }
+    }
+    g_next_work = 0.0;
 }
 
 // kernels that ran (or, negative, were only recorded) without passing through launched()
@@ -346,8 +366,37 @@ float dnn_cuda_timer_stop_ms(void) {
 int dnn_cuda_profile_enable(int on) {
     CUDA_OK(cudaStreamSynchronize(stream()));
     for (auto &c : g_prof) { for (auto &r : c.recs) { g_event_pool.push_back(r.a); g_event_pool.push_back(r.b); } c.recs.clear(); c.pending = nullptr; }
-    g_prof_on = on != 0;
+    for (auto &r : g_timeline) g_event_pool.push_back(r.after);
+    g_timeline.clear();
+    g_prof_on = on == 1;
+    g_timeline_on = on == 2;
+    if (g_timeline_on) {
+        if (!g_timeline_start) CUDA_OK(cudaEventCreate(&g_timeline_start));
+        CUDA_OK(cudaEventRecord(g_timeline_start, stream()));
+    }
     return 0;
+}
+// Sums the timeline by kernel name.  Returns the number of distinct names; fills up to `cap` rows.
+int dnn_cuda_profile_kernels(dnn_cuda_kernel_time *rows, int cap) {
+    CUDA_OK(cudaStreamSynchronize(stream()));
+    std::vector<dnn_cuda_kernel_time> acc;
+    cudaEvent_t prev = g_timeline_start;
+    for (auto &r : g_timeline) {
+        float ms = 0.f;
+        CUDA_OK(cudaEventElapsedTime(&ms, prev, r.after));
+        prev = r.after;
+        size_t i = 0;
+        for (; i < acc.size(); i++) if (!strcmp(acc[i].name, r.name)) break;
+        if (i == acc.size()) {
+            dnn_cuda_kernel_time t;
+            memset(&t, 0, sizeof t);
+            snprintf(t.name, sizeof t.name, "%s", r.name);
+            acc.push_back(t);
+        }
+        acc[i].launches++; acc[i].ms += ms; acc[i].work += r.work;
+    }
+    for (int i = 0; i < (int)acc.size() && i < cap; i++) rows[i] = acc[i];
+    return (int)acc.size();
 }
 int dnn_cuda_profile_read(int kernel_class, long long *launches, double *ms, double *work) {
     if (kernel_class < 0 || kernel_class > 1) return -1;
@@ -357,6 +406,17 @@ int dnn_cuda_profile_read(int kernel_class, long long *launches, double *ms, dou
     if (launches) *launches = (long long)g_prof[kernel_class].recs.size();
     if (ms) *ms = tms;
     if (work) *work = tw;
+    return 0;
+}
+
+int dnn_cuda_set_tf32_policy(unsigned roles_3x, double max_flop_3x) {
+    if (roles_3x > 7u || !(max_flop_3x >= 0.0)) { set_error("tf32 policy: roles is a 3-bit mask, max_flop must be >= 0"); return -1; }
+    gemm_set_policy(roles_3x, max_flop_3x);
+    return 0;
+}
+int dnn_cuda_get_tf32_policy(unsigned *roles_3x, double *max_flop_3x) {
+    if (!roles_3x || !max_flop_3x) return -1;
+    gemm_get_policy(roles_3x, max_flop_3x);
     return 0;
 }
 

@@ -57,6 +57,17 @@ void  dnn_cuda_host_free(void *p);
 int  dnn_cuda_set_gemm_mode(int mode);
 int  dnn_cuda_get_gemm_mode(void);
 
+/* Precision policy of TF32 mode: which GEMMs take the 3xTF32 path although the mode is TF32.
+ *   roles_3x    bit 0: forward products (Y = A B), bit 1: activation gradients (dA = dY B^T),
+ *               bit 2: weight gradients (dW = A^T dY) -- of matmul, matmul_add and conv2d.
+ *   max_flop_3x every GEMM of at most this many FLOP (2 M N K): such products are bound by launch
+ *               latency, not by the tensor core, so the extra two products cost little.
+ * Independently of the policy, a GEMM with at most 64 Ki outputs and a reduction of 1024 or more
+ * (the filter gradient of a small convolution) always takes the 3xTF32 path.
+ * Environment: DNN_CUDA_TF32_3X_ROLES, DNN_CUDA_TF32_3X_MAX_GFLOP.  No counterpart in the reference. */
+int  dnn_cuda_set_tf32_policy(unsigned roles_3x, double max_flop_3x);
+int  dnn_cuda_get_tf32_policy(unsigned *roles_3x, double *max_flop_3x);
+
 /* Transformer blocks in TF32 mode with head size 32 or 64 run attention straight from the
  * fused QKV projection: Q, K and V are read in place from its [B,N,3,H,d] output, RoPE is
  * applied there, and the result is written token-major, which removes the head split / merge
@@ -108,6 +119,15 @@ float dnn_cuda_timer_stop_ms(void);
  * milliseconds and summed algorithmic work (FLOP for GEMM, bytes for AdamW). */
 int   dnn_cuda_profile_enable(int on);
 int   dnn_cuda_profile_read(int kernel_class, long long *launches, double *ms, double *work);
+/* dnn_cuda_profile_enable(2) records a timeline instead: one event after EVERY kernel launch of the
+ * library (launches are serialised on the compute stream, so the time between two events is the later
+ * kernel's duration).  dnn_cuda_profile_kernels waits for the stream and sums the timeline by kernel
+ * name: launches, device milliseconds and, where the launch site states it, the algorithmic work
+ * (bytes for memory-bound kernels, FLOP for GEMM and attention; 0 where not stated).  Returns the
+ * number of distinct names and fills up to `cap` rows.  The events cost time: run the timeline in a
+ * pass of its own, not in a timed region. */
+typedef struct dnn_cuda_kernel_time { char name[56]; long long launches; double ms; double work; } dnn_cuda_kernel_time;
+int   dnn_cuda_profile_kernels(dnn_cuda_kernel_time *rows, int cap);
 
 /* Column sums without any allocation:  out[c] += sum over r of g[r*cols + c]
  * (the bias gradient of matmul_add / add).  No counterpart in the reference: this

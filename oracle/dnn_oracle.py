@@ -452,18 +452,26 @@ def lm_param_names(n_layers):
 
 
 def lm_loss_and_grads(P, ids, targets, n_layers, n_heads, rope_base=10000.0, eps=1e-5,
-                      mode=0, prefix_len=0, seq_lens=None):
+                      mode=0, prefix_len=0, seq_lens=None, embeds=None, loss_slice=None, loss_mask=None):
     """Forward + backward of the decoder LM in float64.  P maps the names of
-    lm_param_names() to arrays.  Returns (loss, {name: grad})."""
+    lm_param_names() to arrays.  Returns (loss, {name: grad}).
+    embeds: run from given input embeddings [B,S,D] instead of gathering ids
+    (decoder_lm_forward_embeds_ex, src/gpt.c:95-122); their gradient is returned under "__embeds__"
+    and the embedding table only gets the tied-head part.  loss_slice=(start, n): the loss reads
+    logits[:, start:start+n] (src/vlm.c:262-268); loss_mask: cross_entropy_masked."""
     P = {k: v.astype(F64) for k, v in P.items()}
-    B, N = ids.shape
     E = P["embed.weight"]
     D = E.shape[1]
+    if embeds is not None:
+        x = np.asarray(embeds, F64)
+        B, N = x.shape[:2]
+    else:
+        B, N = ids.shape
+        x = E[ids]                                         # [B,N,D]
     dk = D // n_heads
     cos, sin = rope_tables(dk, N, rope_base)
     cos, sin = cos.astype(F64), sin.astype(F64)
     tape = []
-    x = E[ids]                                             # [B,N,D]
 
     def rms_f(x, w):
         rs = 1.0 / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
@@ -525,7 +533,12 @@ def lm_loss_and_grads(P, ids, targets, n_layers, n_heads, rope_base=10000.0, eps
         tape.append((x0, h1, rs1, q, k, v, Pm, merged, x1, h2, rs2, gate, up, sg, hid))
     hf, rsf = rms_f(x, P["norm.weight"])
     logits = hf @ E.T + P["lm_head.bias"]                  # [B,N,V]
-    if targets.shape[1] == N - 1:                          # next-token loss on logits[:, :-1]
+    if loss_slice is not None:
+        s0, sn = loss_slice
+        loss, dl = cross_entropy(logits[:, s0:s0 + sn], targets, loss_mask)
+        dlogits = np.zeros(logits.shape, F64)
+        dlogits[:, s0:s0 + sn] = dl
+    elif targets.shape[1] == N - 1:                        # next-token loss on logits[:, :-1]
         loss, dl = cross_entropy(logits[:, :N - 1], targets)
         dlogits = np.zeros(logits.shape, F64)
         dlogits[:, :N - 1] = dl
@@ -566,10 +579,54 @@ def lm_loss_and_grads(P, ids, targets, n_layers, n_heads, rope_base=10000.0, eps
         G[p + "qkv_proj.weight"] = h1.reshape(-1, D).T @ dqkv.reshape(-1, 3 * D)
         d0, G[p + "attn_norm.weight"] = rms_b(x0, P[p + "attn_norm.weight"], rs1, dqkv @ P[p + "qkv_proj.weight"].T)
         dx = dx1 + d0
+    if embeds is not None:
+        G["__embeds__"] = dx
+        return np.float32(loss), {k: (v if k == "__embeds__" else _f32(v)) for k, v in G.items()}
     dE = np.zeros(E.shape, F64)
     np.add.at(dE, ids.reshape(-1), dx.reshape(-1, D))
     G["embed.weight"] = G["embed.weight"] + dE
     return np.float32(loss), {k: _f32(v) for k, v in G.items()}
+
+
+# ── prefix-LM vision LM, padded training step (src/vlm.c:150-381) ─────────
+def vlm_param_names(n_layers):
+    return ["patch_embed.weight", "patch_embed.bias", "img_proj.weight", "img_proj.bias"] + \
+           ["lm." + n for n in lm_param_names(n_layers)] + ["image_pos"]
+
+
+def vlm_loss_and_grads(P, images, input_ids, target_ids, loss_mask, text_lens, n_layers, n_heads, patch):
+    """vision_lm_loss_padded + backward in float64 (src/vlm.c:303-346).  Image tokens come from the
+    patch convolution, whose im2col path leaves (M, out_C) data in an NCHW-shaped tensor that the model
+    then transposes as if it were NCHW (src/conv.c:847-863, src/vlm.c:176-185); conv2d() above keeps
+    that memory layout.  img_proj.* are outside the graph for [B,C,H,W] images: no gradient (None)."""
+    B, T = input_ids.shape
+    w = P["patch_embed.weight"]
+    Dm = w.shape[0]
+    ph, pw = images.shape[2] // patch, images.shape[3] // patch
+    I = ph * pw
+    zero_g = np.zeros((B, Dm, ph, pw), np.float32)
+    y, _, _, _ = conv2d(images, w, P["patch_embed.bias"], patch, 0, zero_g)
+    img = np.ascontiguousarray(y.astype(F64).transpose(0, 2, 3, 1)).reshape(B, I, Dm)
+    img = img + P["image_pos"].astype(F64)
+    lmP = {k[3:]: v for k, v in P.items() if k.startswith("lm.")}
+    txt = lmP["embed.weight"].astype(F64)[input_ids]
+    embeds = np.concatenate([img, txt], axis=1)
+    lens = np.array([I + min(int(n), T) for n in text_lens], np.int32)
+    loss, G = lm_loss_and_grads(lmP, None, target_ids, n_layers, n_heads, mode=1, prefix_len=I, seq_lens=lens,
+                                embeds=embeds, loss_slice=(I, T), loss_mask=loss_mask)
+    de = G.pop("__embeds__")
+    out = {"lm." + k: v for k, v in G.items()}
+    dE = np.zeros(lmP["embed.weight"].shape, F64)
+    np.add.at(dE, input_ids.reshape(-1), de[:, I:].reshape(-1, Dm))
+    out["lm.embed.weight"] = _f32(out["lm.embed.weight"].astype(F64) + dE)
+    dimg = de[:, :I]
+    out["image_pos"] = _f32(dimg.sum(0, keepdims=True))
+    g_nchw = np.ascontiguousarray(dimg.reshape(B, ph, pw, Dm).transpose(0, 3, 1, 2))
+    _, _, dw, db = conv2d(images, w, P["patch_embed.bias"], patch, 0, _f32(g_nchw))
+    # the convolution's own gradients are rounded to float32 on the way in (g_nchw); negligible at 1e-7
+    out["patch_embed.weight"], out["patch_embed.bias"] = dw, db
+    out["img_proj.weight"] = out["img_proj.bias"] = None
+    return loss, out
 
 
 # ── padded vision-LM batch assembly (src/imagenet_vlm.c:31-46, 598-647) ───

@@ -85,6 +85,7 @@ def write_models(B):
     for name in ("tiny", "odd", "c1"):
         model("lm_" + name, models.run_lm, cfg=models.lm_config(name), steps=3)
     model("cnn", models.run_cnn, batch=8, steps=2)
+    model("cnn512", models.run_cnn, batch=512, steps=1)       # BASELINE config 3 at its full batch
     model("vlm", models.run_vlm, steps=2)
     np.savez_compressed(os.path.join(HERE, "models.npz"), **mdl)
     print("lm_c1 loss", mdl["lm_c1/loss"], "grad_norm", mdl["lm_c1/grad_norm"])

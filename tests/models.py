@@ -35,6 +35,29 @@ def seeded_weights(dnn, module, names, seed, std=0.02):
     return params, vals
 
 
+def lm_param_shapes(V, D, L, F):
+    """Shapes of the decoder LM's parameters in module_parameters() order (src/gpt.c:30-59, src/transformer.c:128-140)."""
+    leaf = {"qkv_proj.weight": (D, 3 * D), "qkv_proj.bias": (3 * D,), "out_proj.weight": (D, D), "out_proj.bias": (D,),
+            "attn_norm.weight": (D,), "ffn_norm.weight": (D,), "ffn.gate_proj.weight": (D, F), "ffn.gate_proj.bias": (F,),
+            "ffn.up_proj.weight": (D, F), "ffn.up_proj.bias": (F,), "ffn.down_proj.weight": (F, D), "ffn.down_proj.bias": (D,)}
+    top = {"embed.weight": (V, D), "lm_head.bias": (V,), "norm.weight": (D,)}
+    return {n: top[n] if n in top else leaf[n.split(".", 2)[2]] for n in O.lm_param_names(L)}
+
+
+def seeded_values(shapes, seed, std=0.02):
+    """The values seeded_weights() uploads, from shapes alone (no library): same generator, same draw order."""
+    rng = np.random.default_rng(seed)
+    vals = {}
+    for name, shape in shapes.items():
+        if name.endswith("norm.weight"):
+            vals[name] = np.ones(shape, np.float32)
+        elif name.endswith("bias"):
+            vals[name] = np.zeros(shape, np.float32)
+        else:
+            vals[name] = (rng.standard_normal(shape) * std).astype(np.float32)
+    return vals
+
+
 def lm_config(name):
     return {
         # BASELINE config 1: tiny decoder LM
@@ -158,7 +181,27 @@ def vlm_param_names(n_layers):
            ["lm." + n for n in O.lm_param_names(n_layers)] + ["image_pos"]
 
 
-def run_vlm(dnn, steps=2, seed=3, Bsz=3, img=32, patch=16, V=40, D=32, L=2, H=2, F=48, Tmax=8):
+def vlm_param_shapes(V, D, L, F, C, patch, n_img):
+    shapes = {"patch_embed.weight": (D, C, patch, patch), "patch_embed.bias": (D,), "img_proj.weight": (C * patch * patch, D),
+              "img_proj.bias": (D,)}
+    shapes.update({"lm." + n: s for n, s in lm_param_shapes(V, D, L, F).items()})
+    shapes["image_pos"] = (1, n_img, D)
+    return shapes
+
+
+def vlm_inputs(seed, Bsz, img, V, Tmax, min_len=2):
+    """Images ~N(0,1), per-sample text lengths, padded ids / targets and the loss mask with the loader's
+    convention mask[b,t] = 1 for t < len-1 (src/imagenet_vlm.c:615-631)."""
+    rng = np.random.default_rng(seed)
+    images = rng.standard_normal((Bsz, 3, img, img)).astype(np.float32)
+    lens = rng.integers(min_len, Tmax + 1, size=Bsz).astype(np.int32)
+    ids = rng.integers(0, V, size=(Bsz, Tmax)).astype(np.int32)
+    tgt = rng.integers(0, V, size=(Bsz, Tmax)).astype(np.int32)
+    mask = (np.arange(Tmax)[None, :] < (lens[:, None] - 1)).astype(np.float32)
+    return images, lens, ids, tgt, mask
+
+
+def run_vlm(dnn, steps=2, seed=3, Bsz=3, img=32, patch=16, V=40, D=32, L=2, H=2, F=48, Tmax=8, min_len=2):
     lib = dnn.lib
     vlm = lib.vision_lm_create(dnn.params, V, D, L, H, D // H, F, 3, img, img, patch, 1)
     lib.vision_lm_enable_rope(dnn.params, vlm, Tmax, 10000.0)
@@ -166,12 +209,7 @@ def run_vlm(dnn, steps=2, seed=3, Bsz=3, img=32, patch=16, V=40, D=32, L=2, H=2,
     params, _ = seeded_weights(dnn, vlm, names, seed + 100)
     arr = (B.TensorP * len(params))(*params)
     opt = lib.adamw_create(dnn.params, arr, len(params), 6e-4, 0.9, 0.95, 1e-8, 0.1)
-    rng = np.random.default_rng(seed)
-    images = rng.standard_normal((Bsz, 3, img, img)).astype(np.float32)
-    lens = rng.integers(2, Tmax + 1, size=Bsz).astype(np.int32)
-    ids = rng.integers(0, V, size=(Bsz, Tmax)).astype(np.int32)
-    tgt = rng.integers(0, V, size=(Bsz, Tmax)).astype(np.int32)
-    mask = (np.arange(Tmax)[None, :] < (lens[:, None] - 1)).astype(np.float32)
+    images, lens, ids, tgt, mask = vlm_inputs(seed, Bsz, img, V, Tmax, min_len)
     out = dict(loss=[], grad_norm=[], names=names)
     for s in range(steps):
         ti, tt = dnn.tensor(ids, dnn.data), dnn.tensor(tgt, dnn.data)

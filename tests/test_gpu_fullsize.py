@@ -1,27 +1,356 @@
-"""GPU: the BASELINE configurations at their FULL sizes (the 124M-shaped decoder LM with 16 x 1024 tokens,
-the config-2 operator shapes, the 512-image CNN, the 64-image vision LM), where neither the reference nor
-the numpy oracle finishes in useful time.  The checks are properties that
-do not depend on the size: agreement of the fast arithmetic mode with the exact one, run-to-run
-determinism, softmax rows that sum to one, causality, gradient rows of the cross entropy that sum
-to zero, conservation in the embedding scatter."""
+"""GPU: the BASELINE configurations at their FULL sizes against an independent checker.
+
+  * config 2: every operator at its stated shape against the float64 numpy oracle (the oracle is pinned
+    to the reference by tests/test_oracle_golden.py; big inputs go through it in slices);
+  * config 3: the 512-image CNN step against the unmodified reference (vectors in
+    tests/golden/models.npz, and the reference library itself where a build of it is present);
+  * config 4: the 64-image vision-LM step against the float64 oracle;
+  * config 5's width (vocab 32000, d_model 768, 12 heads, FFN 2048, 1024 tokens per sequence, 2 and 12
+    blocks) on two sequences against the float64 oracle: 2048-row GEMMs on the CTA-pair path, the
+    vocabulary projection, 1024-token tensor-core attention and the 32000-wide cross entropy.
+
+Every comparison prints the measured error next to its bar.  Bars are the ones the hot path is specified
+with: relative L2 error of the loss and of every gradient at most 1e-3 with TF32 products, 1e-5 with
+3xTF32 products and for everything that does not go through the tensor core; index work is bit-exact.
+A bar that is wider than that says so where it is set.  The size-independent properties further down
+(determinism, causality, rows that sum to one or to zero) stay as cheap smoke checks at 16 x 1024 tokens."""
 import ctypes as C
+import json
+import os
 
 import numpy as np
 import pytest
 
+from conftest import REF_LIB
+from golden_util import check
 import models
+from oracle import dnn_oracle as O
 
 pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
+BAR = {"tf32": 1e-3, "3xtf32": 1e-5, "fp32": 1e-5}
+MODES = [("tf32", 1), ("3xtf32", 2)]
+REPORT = []
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64).reshape(-1), np.asarray(b, np.float64).reshape(-1)
+    den = np.linalg.norm(b)
+    return float(np.linalg.norm(a - b) / den) if den > 0 else float(np.linalg.norm(a - b))
+
+
+def report(what, err, bar):
+    """One line per comparison: `-s` shows them, and DNN_PARITY_REPORT=<file> collects them as JSON."""
+    print("PARITY %-72s err %.3g  bar %.1g  %s" % (what, err, bar, "ok" if err <= bar else "MISS"))
+    REPORT.append({"what": what, "err": err, "bar": bar})
+    path = os.environ.get("DNN_PARITY_REPORT")
+    if path:
+        with open(path, "w") as f:
+            json.dump(REPORT, f, indent=0)
+    return err <= bar
+
+
+def expect(what, got, want, bar):
+    assert got is not None, what + ": never written"
+    assert report(what, rel(got, want), bar), "%s: relative L2 error above %.1g" % (what, bar)
+
+
+def big(binding, mode, scratch_gb=40):
+    d = binding.Dnn(binding.B200_LIB, params_mb=4096, scratch_mb=scratch_gb * 1024, data_mb=512)
+    d.lib.dnn_cuda_set_gemm_mode(mode)
+    return d
+
+
+# ── config 2: operators at their stated shapes ───────────────────────────────────────────────────────
+def test_config2_rms_and_layer_norm_8192x768(binding):
+    d = big(binding, binding.GEMM_TF32, 4)
+    try:
+        rng = np.random.default_rng(1)
+        x = rng.standard_normal((8192, 768), dtype=np.float32)
+        w = (1.0 + 0.1 * rng.standard_normal(768)).astype(np.float32)
+        b = (0.1 * rng.standard_normal(768)).astype(np.float32)
+        g = rng.standard_normal((8192, 768), dtype=np.float32)
+        tx, tw = d.tensor(x, d.scratch, True), d.param(w)
+        y = d.lib.tensor_rms_norm(d.scratch, tx, tw, 1e-5)
+        d.backward_from(y, g)
+        wy, wdx, wdw = O.rms_norm(x, w, 1e-5, g)
+        for name, got, want in (("y", d.download(y), wy), ("dx", d.download_grad(tx), wdx), ("dw", d.download_grad(tw), wdw)):
+            expect("config2 rms_norm[8192,768] " + name, got, want, 1e-5)
+        d.reset_step()
+        tx, tw, tb = d.tensor(x, d.scratch, True), d.param(w), d.param(b)
+        y = d.lib.tensor_layer_norm(d.scratch, tx, tw, tb, 1e-5)
+        d.backward_from(y, g)
+        wy, wdx, wdw, wdb = O.layer_norm(x, w, b, 1e-5, g)
+        for name, got, want in (("y", d.download(y), wy), ("dx", d.download_grad(tx), wdx), ("dw", d.download_grad(tw), wdw),
+                                ("db", d.download_grad(tb), wdb)):
+            expect("config2 layer_norm[8192,768] " + name, got, want, 1e-5)
+    finally:
+        d.close()
+
+
+def test_config2_swiglu_8192x2048_and_rope_8x12x1024x64(binding):
+    d = big(binding, binding.GEMM_TF32, 4)
+    try:
+        rng = np.random.default_rng(1)
+        a, b, g = (rng.standard_normal((8192, 2048), dtype=np.float32) for _ in range(3))
+        ta, tb = d.tensor(a, d.scratch, True), d.tensor(b, d.scratch, True)
+        y = d.lib.tensor_swiglu(d.scratch, ta, tb)
+        d.backward_from(y, g)
+        wy, wda, wdb = O.swiglu(a, b, g)
+        for name, got, want in (("y", d.download(y), wy), ("dgate", d.download_grad(ta), wda), ("dup", d.download_grad(tb), wdb)):
+            expect("config2 swiglu[8192,2048] " + name, got, want, 1e-5)
+        d.reset_step()
+        shape = (8, 12, 1024, 64)
+        x, g = rng.standard_normal(shape, dtype=np.float32), rng.standard_normal(shape, dtype=np.float32)
+        cos, sin = O.rope_tables(64, 1024)
+        tx = d.tensor(x, d.scratch, True)
+        y = d.lib.tensor_rope(d.scratch, tx, d.tensor(cos, d.params), d.tensor(sin, d.params))
+        d.backward_from(y, g)
+        wy, wdx = O.rope(x, cos, sin, g)
+        expect("config2 rope[8,12,1024,64] y", d.download(y), wy, 1e-5)
+        expect("config2 rope[8,12,1024,64] dx", d.download_grad(tx), wdx, 1e-5)
+    finally:
+        d.close()
+
+
+def test_config2_masked_cross_entropy_8x1024x32000(binding):
+    """[8,1024,32000] logits ~ N(0,2), 10 % of the positions masked, through the 3-D path.  The oracle takes
+    the rows 512 at a time; its per-slice normalisation (by the slice's own mask sum) is undone."""
+    d = big(binding, binding.GEMM_TF32, 8)
+    try:
+        rng = np.random.default_rng(1)
+        Bn, T, V = 8, 1024, 32000
+        logits = rng.standard_normal((Bn, T, V), dtype=np.float32) * np.float32(2.0)
+        target = rng.integers(0, V, size=(Bn, T)).astype(np.int32)
+        mask = (rng.random((Bn, T)) >= 0.1).astype(np.float32)
+        tl = d.tensor(logits, d.scratch, True)
+        loss = d.lib.tensor_cross_entropy_masked(d.scratch, tl, d.tensor(target, d.data), d.tensor(mask, d.data), 2)
+        d.lib.dnn_backward(d.scratch, loss)
+        got_loss, got = d.scalar(loss), d.download_grad(tl).reshape(Bn * T, V)
+        total = max(float(mask.sum()), 1.0)
+        lf, tf, mf = logits.reshape(-1, V), target.reshape(-1), mask.reshape(-1)
+        want_loss, num, den = 0.0, 0.0, 0.0
+        for r0 in range(0, Bn * T, 512):
+            sl = slice(r0, r0 + 512)
+            cnt = max(float(mf[sl].sum()), 1.0)
+            l, dl = O.cross_entropy(lf[sl], tf[sl], mf[sl])
+            want_loss += float(l) * cnt / total
+            dl = dl.astype(np.float64) * (cnt / total)
+            num += float(((got[sl].astype(np.float64) - dl) ** 2).sum()); den += float((dl ** 2).sum())
+            assert not got[sl][mf[sl] == 0].any(), "a masked position received a gradient"
+        assert report("config2 cross_entropy_masked[8,1024,32000] loss", abs(got_loss - want_loss) / abs(want_loss), 1e-5)
+        assert report("config2 cross_entropy_masked[8,1024,32000] dlogits", float(np.sqrt(num / den)), 1e-5)
+    finally:
+        d.close()
+
+
+@pytest.mark.parametrize("mode,code", MODES, ids=[m[0] for m in MODES])
+def test_config2_matmul_add_8192x768x3072(binding, mode, code):
+    d = big(binding, code, 4)
+    try:
+        rng = np.random.default_rng(1)
+        a = rng.standard_normal((8192, 768), dtype=np.float32)
+        w = rng.standard_normal((768, 3072), dtype=np.float32) * np.float32(0.05)
+        bias = rng.standard_normal(3072, dtype=np.float32)
+        g = rng.standard_normal((8192, 3072), dtype=np.float32)
+        ta, tw, tb = d.tensor(a, d.scratch, True), d.param(w), d.param(bias)
+        y = d.lib.tensor_matmul_add(d.scratch, ta, tw, 0, tb)
+        d.backward_from(y, g)
+        wy, wda, wdw, wdb = O.matmul_add(a, w, 0, bias, g)
+        for name, got, want, bar in (("y", d.download(y), wy, BAR[mode]), ("dA", d.download_grad(ta), wda, BAR[mode]),
+                                     ("dW", d.download_grad(tw), wdw, BAR[mode]), ("dbias", d.download_grad(tb), wdb, 1e-5)):
+            expect("config2 matmul_add[8192x768 @ 768x3072] %s %s" % (mode, name), got, want, bar)
+    finally:
+        d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        d.close()
+
+
+@pytest.mark.parametrize("mode,code", MODES, ids=[m[0] for m in MODES])
+@pytest.mark.parametrize("kind", ["causal", "prefix196"])
+def test_config2_attention_8x12x1024x64(binding, kind, mode, code):
+    """Causal, and prefix-LM with prefix 196 and per-batch lengths in [200, 1024]; the oracle runs one
+    batch element at a time (96 heads of 1024 x 1024 scores in float64)."""
+    d = big(binding, code, 4)
+    try:
+        rng = np.random.default_rng(1)
+        shape = (8, 12, 1024, 64)
+        q, k, v, g = (rng.standard_normal(shape, dtype=np.float32) for _ in range(4))
+        amode, prefix, lens = (0, 0, None) if kind == "causal" else (1, 196, rng.integers(200, 1025, size=8).astype(np.int32))
+        if lens is not None:
+            lens[0] = 1024
+            for b in range(8):
+                g[b, :, lens[b]:] = 0                      # rows beyond a batch's length carry no gradient
+        tq, tk, tv = (d.tensor(t, d.scratch, True) for t in (q, k, v))
+        lp = None if lens is None else lens.ctypes.data_as(C.POINTER(C.c_int))
+        o = d.lib.tensor_attention_ex(d.scratch, tq, tk, tv, None, amode, prefix, lp)
+        d.backward_from(o, g)
+        got = dict(o=d.download(o), dq=d.download_grad(tq), dk=d.download_grad(tk), dv=d.download_grad(tv))
+        want = {n: np.empty(shape, np.float32) for n in got}
+        for b in range(8):
+            s = slice(b, b + 1)
+            res = O.attention(q[s], k[s], v[s], amode, prefix, None if lens is None else lens[s], g[s])
+            for n, r in zip(("o", "dq", "dk", "dv"), res):
+                want[n][s] = r
+        for n in ("o", "dq", "dk", "dv"):
+            expect("config2 attention[8,12,1024,64] %s %s %s" % (kind, mode, n), got[n], want[n], BAR[mode])
+    finally:
+        d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        d.close()
+
+
+def test_config2_adamw_124m_parameters(binding):
+    """One flat tensor of 124 M parameters, two AdamW steps with seeded p, g, m, v against the fp32
+    restatement of src/optim.c:270-310 (bar 1e-6: same operations, same order)."""
+    d = big(binding, binding.GEMM_TF32, 4)
+    try:
+        n = 124_000_000
+        rng = np.random.default_rng(1)
+        p = rng.standard_normal(n, dtype=np.float32) * np.float32(0.02)
+        m = rng.standard_normal(n, dtype=np.float32) * np.float32(0.01)
+        v = (rng.standard_normal(n, dtype=np.float32) * np.float32(0.01)) ** 2
+        tp = d.param(p)
+        arr = (binding.TensorP * 1)(tp)
+        opt = d.lib.adamw_create(d.params, arr, 1, 6e-4, 0.9, 0.95, 1e-8, 0.1)
+        d.upload(opt.contents.m[0], m); d.upload(opt.contents.v[0], v)
+        for step in (1, 2):
+            g = rng.standard_normal(n, dtype=np.float32) * np.float32(0.02 * step)
+            d.lib.adamw_zero_grad(opt)
+            y = d.lib.tensor_mul(d.scratch, tp, d.tensor(g, d.scratch))
+            d.lib.dnn_backward(d.scratch, y)               # p.grad = g (non-scalar root: upstream gradient of ones)
+            d.lib.adamw_step(opt)
+            d.reset_step()
+            p, m, v = O.adamw_update(p, g, m, v, step, 6e-4, 0.9, 0.95, 1e-8, 0.1)
+        expect("config2 adamw[124M] p after 2 steps", d.download(tp), p, 1e-6)
+        expect("config2 adamw[124M] m after 2 steps", d.download(opt.contents.m[0]), m, 1e-6)
+        expect("config2 adamw[124M] v after 2 steps", d.download(opt.contents.v[0]), v, 1e-6)
+    finally:
+        d.close()
+
+
+# ── config 3: 512-image CNN step against the unmodified reference ───────────────────────────────────
+# TF32 bars of the CNN.  With random labels and freshly initialised weights the batch gradient is what is
+# left after 512 per-sample gradients cancel, so the relative effect of rounding the operands to TF32 is
+# several times larger than on a transformer; the bars below are the measured errors + 20 %.
+CNN_TF32_BAR = {"conv1.weight": 1.3e-2, "conv1.bias": 1.3e-2, "conv2.weight": 1.3e-2, "conv2.bias": 1.3e-2,
+                "fc1.weight": 1.3e-2, "fc1.bias": 1.3e-2, "fc2.weight": 1e-3, "fc2.bias": 1e-3}
+
+
+@pytest.mark.parametrize("mode,code", MODES, ids=[m[0] for m in MODES])
+def test_config3_cnn_batch512_against_the_reference(binding, mode, code):
+    golden = np.load(os.path.join(GOLDEN, "models.npz"))
+    d = big(binding, code, 8)
+    try:
+        out = models.run_cnn(d, batch=512, steps=1)
+    finally:
+        d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        d.close()
+    want_loss = float(golden["cnn512/loss"][0])
+    assert report("config3 cnn[512] %s loss" % mode, abs(out["loss"][0] - want_loss) / abs(want_loss), BAR[mode])
+    live = None
+    if os.path.exists(REF_LIB):                            # the reference itself, one thread (about ten seconds)
+        r = binding.Dnn(REF_LIB, params_mb=256, scratch_mb=8192, data_mb=64)
+        live = models.run_cnn(r, batch=512, steps=1)
+        r.close()
+    for n in models.CNN_NAMES:
+        bar = BAR[mode] if mode != "tf32" else CNN_TF32_BAR[n]
+        key = "cnn512/grad/" + n
+        stride = int(golden[key + "#"][3])
+        assert report("config3 cnn[512] %s grad %s (reference vectors)" % (mode, n),
+                      rel(out["grads"][n].reshape(-1)[::stride], golden[key]), bar), n
+        if live is not None:
+            assert report("config3 cnn[512] %s grad %s (reference, live)" % (mode, n), rel(out["grads"][n], live["grads"][n]), bar), n
+
+
+# ── config 4: 64-image vision-LM step against the float64 oracle ────────────────────────────────────
+C4 = dict(V=1024, D=512, L=8, H=8, F=1376, img=224, patch=16, Tmax=32, Bsz=64, seed=3)
+
+
+@pytest.fixture(scope="module")
+def c4_oracle():
+    c = C4
+    P = models.seeded_values(models.vlm_param_shapes(c["V"], c["D"], c["L"], c["F"], 3, c["patch"], (c["img"] // c["patch"]) ** 2), c["seed"] + 100)
+    images, lens, ids, tgt, mask = models.vlm_inputs(c["seed"], c["Bsz"], c["img"], c["V"], c["Tmax"], min_len=8)
+    loss, G = O.vlm_loss_and_grads(P, images, ids, tgt, mask, lens, c["L"], c["H"], c["patch"])
+    return float(loss), G
+
+
+@pytest.mark.parametrize("mode,code", MODES, ids=[m[0] for m in MODES])
+def test_config4_vision_lm_step_against_the_oracle(binding, c4_oracle, mode, code):
+    """64 images 3x224x224 (196 image tokens through the patch convolution) + up to 32 text tokens, d 512,
+    8 blocks, prefix-LM attention with per-sample lengths, masked cross entropy, clip 1.0."""
+    c = C4
+    want_loss, G = c4_oracle
+    d = big(binding, code)
+    try:
+        out = models.run_vlm(d, steps=1, seed=c["seed"], Bsz=c["Bsz"], img=c["img"], patch=c["patch"], V=c["V"], D=c["D"], L=c["L"],
+                             H=c["H"], F=c["F"], Tmax=c["Tmax"], min_len=8)
+    finally:
+        d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        d.close()
+    check_step("config4 vlm[64 x (196+32)] " + mode, out, want_loss, G, 1.0, BAR[mode])
+
+
+def check_step(tag, out, want_loss, G, clip, bar, wide=None):
+    """Loss, gradient norm and every parameter gradient (after clipping, as the library leaves them)."""
+    ok = report(tag + " loss", abs(out["loss"][0] - want_loss) / abs(want_loss), bar)
+    gn = float(O.grad_norm([g for g in G.values() if g is not None]))
+    ok &= report(tag + " grad_norm", abs(out["grad_norm"][0] - gn) / gn, bar)
+    scale = float(O.clip_scale(gn, clip))
+    worst = ("", 0.0)
+    for n, g in G.items():
+        got = out["grads"][n]
+        if g is None:
+            assert got is None, "%s: %s has a gradient here but not in the reference" % (tag, n)
+            continue
+        e = rel(got, g.astype(np.float64) * scale)
+        b = bar if wide is None or n not in wide else wide[n]
+        if e > worst[1]:
+            worst = (n, e)
+        if e > b:
+            ok = False
+            report("%s grad %s" % (tag, n), e, b)
+    ok &= report("%s worst parameter gradient (%s)" % (tag, worst[0]), worst[1], bar if wide is None else max([bar] + list(wide.values())))
+    assert ok, tag + ": a bar was missed (lines marked MISS above)"
+
+
+# ── config 5's width on two sequences against the float64 oracle ────────────────────────────────────
+def c5_cfg(L):
+    return dict(V=32000, D=768, L=L, H=12, F=2048, B=2, N=1024, lr=6e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, seed=5)
+
+
+_c5_cache = {}
+
+
+def c5_oracle(L):
+    if L not in _c5_cache:
+        cfg = c5_cfg(L)
+        ids, tgt = models.lm_inputs(cfg)
+        P = models.seeded_values(models.lm_param_shapes(cfg["V"], cfg["D"], cfg["L"], cfg["F"]), cfg["seed"] + 100)
+        loss, G = O.lm_loss_and_grads(P, ids, tgt, cfg["L"], cfg["H"])
+        _c5_cache.clear()                                  # one at a time: the 12-block gradients are 0.4 GB
+        _c5_cache[L] = (float(loss), G)
+    return _c5_cache[L]
+
+
+@pytest.mark.parametrize("mode,code", MODES, ids=[m[0] for m in MODES])
+@pytest.mark.parametrize("L", [2, 12])
+def test_config5_width_step_against_the_oracle(binding, L, mode, code):
+    cfg = c5_cfg(L)
+    want_loss, G = c5_oracle(L)
+    d = big(binding, code)
+    try:
+        out = models.run_lm(d, cfg, steps=1)
+    finally:
+        d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        d.close()
+    check_step("config5-width lm[2 x 1024, %d blocks] %s" % (L, mode), out, want_loss, G, cfg["clip"], BAR[mode])
+
+
+# ── size-independent properties at 16 x 1024 tokens ─────────────────────────────────────────────────
 C5 = dict(V=32000, D=768, L=12, H=12, F=2048, B=16, N=1024, lr=6e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, seed=5)
 PICK = ("embed.weight", "blocks.0.qkv_proj.weight", "blocks.0.qkv_proj.bias", "blocks.5.out_proj.bias", "blocks.5.ffn_norm.weight",
         "blocks.11.ffn.gate_proj.bias", "blocks.11.ffn.down_proj.weight", "norm.weight", "lm_head.bias")
-
-
-def big(binding, mode):
-    d = binding.Dnn(binding.B200_LIB, params_mb=4096, scratch_mb=40 * 1024, data_mb=256)
-    d.lib.dnn_cuda_set_gemm_mode(mode)
-    return d
 
 
 def step(binding, mode):
@@ -34,29 +363,20 @@ def step(binding, mode):
         d.close()
 
 
-@pytest.fixture(scope="module")
-def tf32_step(binding):
-    return step(binding, binding.GEMM_TF32)
-
-
-def test_config5_tf32_step_agrees_with_the_exact_mode(binding, tf32_step):
-    """One full-size training step in TF32 mode (tensor-core GEMM and attention) against the same step in
-    3xTF32 mode (split GEMM, fp32 attention kernels), which holds 3e-5 against the reference at small sizes.
-    Bars: the TF32 bars of the small-size parity tests."""
+def test_config5_step_is_deterministic_and_close_to_the_exact_mode(binding):
+    """The full 16 x 1024-token step twice in TF32 mode: no atomics on floating-point data anywhere, so the
+    second run gives the same bits.  Then once in 3xTF32 mode: the two arithmetic modes of the library agree
+    to TF32 rounding (a consistency check of the mode switch at the benchmarked size; parity with the
+    reference at this width is test_config5_width_step_against_the_oracle's job)."""
+    a, b = step(binding, binding.GEMM_TF32), step(binding, binding.GEMM_TF32)
+    assert a["loss"] == b["loss"] and a["grad_norm"] == b["grad_norm"]
+    for n in PICK:
+        assert np.array_equal(a["grads"][n], b["grads"][n]), n
     exact = step(binding, binding.GEMM_3XTF32)
-    assert abs(tf32_step["loss"] - exact["loss"]) <= 5e-4 * abs(exact["loss"])
-    assert abs(tf32_step["grad_norm"] - exact["grad_norm"]) <= 2e-3 * exact["grad_norm"]
+    report("config5 lm[16 x 1024] tf32 vs 3xtf32 loss", abs(a["loss"] - exact["loss"]) / abs(exact["loss"]), 1e-3)
+    assert abs(a["loss"] - exact["loss"]) <= 1e-3 * abs(exact["loss"])
     for n in PICK:
-        a, b = tf32_step["grads"][n].astype(np.float64), exact["grads"][n].astype(np.float64)
-        assert np.linalg.norm(a - b) <= 3e-3 * np.linalg.norm(b), n
-
-
-def test_config5_step_is_deterministic(binding, tf32_step):
-    """No atomics on floating-point data anywhere in the step: a second run gives the same bits."""
-    again = step(binding, binding.GEMM_TF32)
-    assert again["loss"] == tf32_step["loss"] and again["grad_norm"] == tf32_step["grad_norm"]
-    for n in PICK:
-        assert np.array_equal(again["grads"][n], tf32_step["grads"][n]), n
+        assert report("config5 lm[16 x 1024] tf32 vs 3xtf32 grad " + n, rel(a["grads"][n], exact["grads"][n]), 3e-3), n
 
 
 def test_full_size_attention_rows_sum_to_one_and_are_causal(binding):
@@ -91,8 +411,8 @@ def test_full_size_attention_rows_sum_to_one_and_are_causal(binding):
 
 
 def test_full_size_cross_entropy_gradient_rows_sum_to_zero(binding):
-    """[16368, 32000] logits: every row of d(logits) = (softmax - onehot) / rows sums to zero, the bias
-    gradient left in passing equals the column sums of what was written, and constant logits give log(V)."""
+    """[16368, 32000] logits: every row of d(logits) = (softmax - onehot) / rows sums to zero and constant
+    logits give log(V)."""
     d = big(binding, binding.GEMM_TF32)
     try:
         rng = np.random.default_rng(4)
@@ -113,9 +433,9 @@ def test_full_size_cross_entropy_gradient_rows_sum_to_zero(binding):
         d.close()
 
 
-def test_full_size_embedding_backward_conserves_the_gradient(binding):
-    """16384 ids into a [32000, 768] table with many duplicates: the column sums of the table gradient
-    equal the column sums of the upstream gradient, and rows no id points at stay zero."""
+def test_full_size_embedding_backward_against_numpy(binding):
+    """16384 ids into a [32000, 768] table with many duplicates: the table gradient equals numpy's
+    scatter-add of the upstream gradient (float64), rows no id points at stay exactly zero."""
     d = big(binding, binding.GEMM_TF32)
     try:
         rng = np.random.default_rng(6)
@@ -126,65 +446,18 @@ def test_full_size_embedding_backward_conserves_the_gradient(binding):
         out = d.lib.tensor_embedding(d.scratch, table, ids)
         gout = rng.standard_normal((16384, 768), dtype=np.float32)
         d.backward_from(out, gout)
-        g = d.download_grad(table).astype(np.float64)
-        want = gout.astype(np.float64).sum(axis=0)
-        assert np.abs(g.sum(axis=0) - want).max() <= 1e-4 * np.abs(want).max()
+        g = d.download_grad(table)
+        want = np.zeros((32000, 768), np.float64)
+        np.add.at(want, ids_np, gout.astype(np.float64))
+        expect("embedding backward [16384 ids -> 32000 x 768]", g, want, 1e-5)
         assert not g[2000:31999].any() and g[31999].any()
-        np.testing.assert_allclose(g[31999], gout[:64].astype(np.float64).sum(axis=0), rtol=1e-5, atol=1e-5)
     finally:
         d.close()
 
 
-def _close(a, b, tol):
-    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
-    return np.linalg.norm(a - b) <= tol * np.linalg.norm(b) + 1e-12
-
-
-def test_config4_vision_lm_step_tf32_agrees_with_the_exact_mode(binding):
-    """BASELINE config 4 at full size: 64 images 3x224x224 (196 image tokens) + up to 32 text tokens,
-    d 512, 8 blocks, prefix-LM attention with per-sample lengths, masked cross entropy."""
-    outs = []
-    for mode in (binding.GEMM_TF32, binding.GEMM_3XTF32):
-        d = big(binding, mode)
-        try:
-            outs.append(models.run_vlm(d, steps=1, Bsz=64, img=224, patch=16, V=1024, D=512, L=8, H=8, F=1376, Tmax=32))
-        finally:
-            d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
-            d.close()
-    fast, exact = outs
-    assert abs(fast["loss"][0] - exact["loss"][0]) <= 5e-4 * abs(exact["loss"][0])
-    assert abs(fast["grad_norm"][0] - exact["grad_norm"][0]) <= 3e-3 * exact["grad_norm"][0]
-    for n in exact["names"]:
-        if exact["grads"][n] is None:
-            assert fast["grads"][n] is None, n
-            continue
-        assert _close(fast["grads"][n], exact["grads"][n], 6e-3), n       # the patch convolution stacks a TF32 GEMM on the LM's
-
-
-def test_config3_cnn_step_tf32_agrees_with_the_exact_mode(binding):
-    """BASELINE config 3 at full size: 512 images 1x28x28 through two 3x3 convolutions, pooling and two
-    linear layers.  With random labels and fresh weights the batch gradient is what is left after 512
-    per-sample gradients cancel, so the relative effect of TF32 operand rounding grows with the batch
-    (measured 0.9-1.0e-2 on the convolutions and fc1, 3e-4 on fc2; 4e-3 at batch 8); 3xTF32 is the mode that
-    holds 3e-5.  The bar keeps a factor of two over the measurement."""
-    outs = []
-    for mode in (binding.GEMM_TF32, binding.GEMM_3XTF32):
-        d = big(binding, mode)
-        try:
-            outs.append(models.run_cnn(d, batch=512, steps=1))
-        finally:
-            d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
-            d.close()
-    fast, exact = outs
-    assert abs(fast["loss"][0] - exact["loss"][0]) <= 5e-4 * abs(exact["loss"][0])
-    for n in models.CNN_NAMES:
-        assert _close(fast["grads"][n], exact["grads"][n], 1e-3 if n.startswith("fc2") else 2e-2), n
-
-
-def test_config2_prefix_attention_and_masked_cross_entropy_at_full_size(binding):
-    """BASELINE config 2 shapes: prefix-LM attention [8,12,1024,64] with prefix 196 and per-batch lengths
-    (rows beyond a batch's length are zero and keys beyond it are never read), and the 3-D masked cross
-    entropy [8,1024,32000] (masked positions take no gradient, the others sum to zero per row)."""
+def test_config2_prefix_attention_padding_is_invisible(binding):
+    """Prefix-LM attention [8,12,1024,64], prefix 196, per-batch lengths: rows beyond a batch's length are
+    zero, keys beyond it are never read, and a change inside the prefix reaches every live row."""
     d = big(binding, binding.GEMM_TF32)
     try:
         rng = np.random.default_rng(1)
@@ -211,17 +484,5 @@ def test_config2_prefix_attention_and_masked_cross_entropy_at_full_size(binding)
         k3[:, :, 190:196] += 1.0                                           # inside the prefix: every live row changes
         moved = run(k3, v)
         assert all((moved[b, :, :lens[b]] != base[b, :, :lens[b]]).any(axis=-1).all() for b in range(8))
-
-        R, T, V = 8, 1024, 32000
-        logits = d.tensor(rng.standard_normal((R, T, V), dtype=np.float32) * 2.0, d.scratch, requires_grad=True)
-        tgt = d.tensor(rng.integers(0, V, size=(R, T)).astype(np.int32), d.data)
-        mask_np = (rng.random((R, T)) >= 0.1).astype(np.float32)
-        mask = d.tensor(mask_np, d.data)
-        loss = d.lib.tensor_cross_entropy_masked(d.scratch, logits, tgt, mask, 2)
-        d.lib.dnn_backward(d.scratch, loss)
-        g = d.download_grad(logits).astype(np.float64)
-        assert not g[mask_np == 0].any()
-        assert np.abs(g.sum(axis=2)).max() <= 5e-9
-        assert abs(d.scalar(loss) - 12.4) < 0.3                            # log(32000) + sigma^2/2 = 10.37 + 2.0 for N(0,2) logits
     finally:
         d.close()

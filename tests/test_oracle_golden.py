@@ -36,22 +36,7 @@ def test_oracle_matches_reference_vectors(ops_golden, case):
 def test_oracle_lm_step_matches_reference(model_golden, name):
     cfg = models.lm_config(name)
     ids, tgt = models.lm_inputs(cfg)
-    rng = np.random.default_rng(cfg["seed"] + 100)
-    P = {}
-    for n in O.lm_param_names(cfg["L"]):
-        shape = {"embed.weight": (cfg["V"], cfg["D"]), "lm_head.bias": (cfg["V"],), "norm.weight": (cfg["D"],)}.get(n)
-        if shape is None:
-            leaf = n.split(".", 2)[2]
-            D, F = cfg["D"], cfg["F"]
-            shape = {"qkv_proj.weight": (D, 3 * D), "qkv_proj.bias": (3 * D,), "out_proj.weight": (D, D), "out_proj.bias": (D,),
-                     "attn_norm.weight": (D,), "ffn_norm.weight": (D,), "ffn.gate_proj.weight": (D, F), "ffn.gate_proj.bias": (F,),
-                     "ffn.up_proj.weight": (D, F), "ffn.up_proj.bias": (F,), "ffn.down_proj.weight": (F, D), "ffn.down_proj.bias": (D,)}[leaf]
-        if n.endswith("norm.weight"):
-            P[n] = np.ones(shape, np.float32)
-        elif n.endswith("bias"):
-            P[n] = np.zeros(shape, np.float32)
-        else:
-            P[n] = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    P = models.seeded_values(models.lm_param_shapes(cfg["V"], cfg["D"], cfg["L"], cfg["F"]), cfg["seed"] + 100)
     loss, G = O.lm_loss_and_grads(P, ids, tgt, cfg["L"], cfg["H"])
     tag = "lm_" + name
     assert abs(loss - model_golden[tag + "/loss"][0]) <= 2e-6 * abs(loss)
@@ -68,3 +53,24 @@ def test_oracle_rng_matches_reference_ids(model_golden):
     ids, tgt = models.lm_inputs(cfg)
     key = "lm_c1/shifted"
     check(key, tgt, model_golden[key], model_golden[key + "#"], 0, exact=True)
+
+
+def test_oracle_vision_lm_step_matches_reference(model_golden):
+    """The float64 restatement of vision_lm_train_step_padded (patch convolution with the reference's
+    memory layout, learned image positions, prefix-LM attention with per-sample lengths, masked cross
+    entropy on the text rows) against the vectors of the unmodified reference (models.run_vlm defaults)."""
+    V, D, L, H, F, img, patch, Tmax, Bsz, seed = 40, 32, 2, 2, 48, 32, 16, 8, 3, 3
+    P = models.seeded_values(models.vlm_param_shapes(V, D, L, F, 3, patch, (img // patch) ** 2), seed + 100)
+    images, lens, ids, tgt, mask = models.vlm_inputs(seed, Bsz, img, V, Tmax)
+    loss, G = O.vlm_loss_and_grads(P, images, ids, tgt, mask, lens, L, H, patch)
+    assert abs(loss - model_golden["vlm/loss"][0]) <= 2e-6 * abs(loss)
+    gn = O.grad_norm([g for g in G.values() if g is not None])
+    assert abs(gn - model_golden["vlm/grad_norm"][0]) <= 1e-5 * gn
+    scale = O.clip_scale(gn, 1.0)
+    missing = set(model_golden["vlm/grad_missing"].tolist())
+    assert missing == {n for n, g in G.items() if g is None}
+    for n, g in G.items():
+        if g is None:
+            continue
+        key = "vlm/grad/" + n
+        check(key, g * scale, model_golden[key], model_golden[key + "#"], 2e-5)
