@@ -240,6 +240,9 @@ CUDA_API = {
     "dnn_cuda_dp_allreduce_grads": (I, [C.POINTER(TensorP), I]),
     "dnn_cuda_dp_world_size": (I, []),
     "dnn_cuda_dp_finalize": (I, []),
+    "dnn_cuda_dp_last_error": (C.c_char_p, []),
+    "dnn_cuda_dp_backward": (I, [PoolP, TensorP, C.POINTER(TensorP), I]),
+    "dnn_cuda_dp_vision_lm_train_step_padded": (TensorP, [PoolP, VP, TensorP, TensorP, TensorP, TensorP, IP, C.POINTER(AdamW), F, C.POINTER(C.c_float)]),
     "dnn_cuda_dp_decoder_lm_train_step": (TensorP, [PoolP, VP, TensorP, TensorP, C.POINTER(AdamW), F, C.POINTER(C.c_float)]),
 }
 

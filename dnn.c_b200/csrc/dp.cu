@@ -76,6 +76,40 @@ std::vector<Span> plan_buckets(std::vector<Span> grads, size_t bucket_bytes) {
     return out;
 }
 
+// Every rank must issue the same collectives: same number of buckets, same sizes, same order.  A rank
+// whose model differs (a parameter without a gradient, another allocation order) would leave the others
+// waiting inside NCCL with no diagnosis.  So whenever a rank's bucket plan changes (first step, and the
+// step after the gradient buffers were allocated) the ranks compare a fingerprint of the plan -- bucket
+// count and a hash of the sizes -- with one tiny all-reduce (max of h and of ~h: both equal the local
+// values on every rank only if all ranks hold the same h) and return an error instead of entering the
+// exchange when they differ.
+static uint64_t g_plan_seen = 0;
+static unsigned long long *g_plan_dev = nullptr;
+static uint64_t plan_fingerprint(const std::vector<Span> &buckets) {
+    uint64_t h = 0xcbf29ce484222325ull ^ (uint64_t)buckets.size();
+    for (const Span &b : buckets) { h ^= (uint64_t)b.bytes; h *= 0x100000001b3ull; }
+    return h ? h : 1;
+}
+static int plan_agree(const std::vector<Span> &buckets, cudaStream_t s) {
+    const uint64_t h = plan_fingerprint(buckets);
+    if (h == g_plan_seen) return 0;
+    if (!g_plan_dev) CUDA_OK(cudaMalloc((void **)&g_plan_dev, 2 * sizeof(unsigned long long)));
+    unsigned long long host[2] = {h, ~h}, got[2] = {0, 0};
+    CUDA_OK(cudaMemcpyAsync(g_plan_dev, host, sizeof host, cudaMemcpyHostToDevice, s));
+    ncclResult_t r = g_nccl.AllReduce(g_plan_dev, g_plan_dev, 2, ncclUint64, ncclMax, g_comm, s);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce (plan fingerprint)");
+    CUDA_OK(cudaMemcpyAsync(got, g_plan_dev, sizeof got, cudaMemcpyDeviceToHost, s));
+    CUDA_OK(cudaStreamSynchronize(s));
+    if (got[0] != host[0] || got[1] != host[1]) {
+        g_dp_error = "data-parallel ranks disagree on the gradient buckets (a different set of parameters has gradients, or they "
+                     "were allocated in another order); no gradient was exchanged";
+        fprintf(stderr, "dnn_b200: %s\n", g_dp_error.c_str());
+        return -5;
+    }
+    g_plan_seen = h;
+    return 0;
+}
+
 // ── exchange overlapped with backward ────────────────────────────────────
 // Gradient buffers keep their addresses from the second step on, so the buckets are planned up
 // front.  dnn_backward reports every parameter whose gradient is final; when all parameters
@@ -142,6 +176,7 @@ bool dp_overlap_begin(tensor **params, int n_params) {
         CUDA_OK(cudaEventCreateWithFlags(&g_ov.done, cudaEventDisableTiming));
     }
     g_ov.buckets = plan_buckets(grads, bucket_bytes());
+    if (plan_agree(g_ov.buckets, stream()) != 0) return false;       // the serial path reports the disagreement
     const int nb = (int)g_ov.buckets.size();
     g_ov.remaining.assign(nb, 0);
     g_ov.launched.assign(nb, 0);
@@ -197,12 +232,13 @@ int dnn_cuda_dp_init(int rank, int world_size, const void *id_128_bytes) {
     if (g_comm) { g_dp_error = "dp_init: already initialised"; return -3; }
     g_world = world_size;
     if (world_size == 1) return 0;
-    if (!load_nccl()) return -1;
+    if (!load_nccl()) { g_world = 1; return -1; }
     stream();       // binds the device chosen by dnn_cuda_init()
     ncclUniqueId id;
     memcpy(&id, id_128_bytes, 128);
     ncclResult_t r = g_nccl.CommInitRank(&g_comm, world_size, id, rank);
-    if (r != ncclSuccess) { g_comm = nullptr; return nccl_fail(r, "ncclCommInitRank"); }
+    if (r != ncclSuccess) { g_comm = nullptr; g_world = 1; return nccl_fail(r, "ncclCommInitRank"); }
+    g_plan_seen = 0;
     return 0;
 }
 
@@ -230,6 +266,7 @@ int dnn_cuda_dp_allreduce_grads(tensor **params, int n_params) {
         if (params[i]->grad) grads.push_back(Span{(char *)params[i]->grad, (size_t)numel_of(params[i]) * 4});
     if (grads.empty()) return 0;
     std::vector<Span> buckets = plan_buckets(grads, bucket_bytes());
+    if (int rc = plan_agree(buckets, stream())) return rc;
     ncclResult_t r = g_nccl.GroupStart();
     if (r != ncclSuccess) return nccl_fail(r, "ncclGroupStart");
     for (const Span &b : buckets) {
@@ -245,12 +282,26 @@ int dnn_cuda_dp_allreduce_grads(tensor **params, int n_params) {
     return 0;
 }
 
+const char *dnn_cuda_dp_last_error(void) { return g_dp_error.c_str(); }
+
+// dnn_backward followed by the exchange; from the second step on (gradient buffers allocated) and with the
+// overlap on, buckets are sent while backward still runs.
+int dnn_cuda_dp_backward(struct mem_pool *scratch, tensor *loss, tensor **params, int n_params) {
+    const bool dp = g_world > 1;
+    const bool overlapped = dp && dp_overlap_begin(params, n_params);
+    dnn_backward(scratch, loss);
+    if (!dp) return 0;
+    return overlapped ? dp_overlap_finish() : dnn_cuda_dp_allreduce_grads(params, n_params);
+}
+
 int dnn_cuda_dp_finalize(void) {
     if (g_comm) {
         cudaStreamSynchronize(stream());
         g_nccl.CommDestroy(g_comm);
         g_comm = nullptr;
     }
+    if (g_plan_dev) { cudaFree(g_plan_dev); g_plan_dev = nullptr; }
+    g_plan_seen = 0;
     g_world = 1;
     return 0;
 }

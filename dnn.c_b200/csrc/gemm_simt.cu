@@ -8,6 +8,7 @@
 // operand is the one adjacent threads walk.
 #include "common.cuh"
 #include "device_utils.cuh"
+#include <vector>
 
 namespace dnnb {
 
@@ -96,6 +97,26 @@ static bool g_policy_env_read = false;
 void gemm_set_policy(unsigned roles_3x, double max_flop_3x) { g_roles_3x = roles_3x; g_max_flop_3x = max_flop_3x; g_policy_env_read = true; }
 void gemm_get_policy(unsigned *roles_3x, double *max_flop_3x) { *roles_3x = g_roles_3x; *max_flop_3x = g_max_flop_3x; }
 
+// DNN_CUDA_TF32_3X_SHAPES="role:N:K,role:N:K,...": single GEMM shapes (role 0/1/2, output columns N, reduction K of
+// the product as the op states it) that take the 3xTF32 path; a measurement aid for choosing the policy.
+struct ShapeRule { int role, N, K; };
+static std::vector<ShapeRule> g_shape_rules;
+static bool g_shapes_read = false;
+static void read_shape_rules() {
+    g_shapes_read = true;
+    g_shape_rules.clear();
+    const char *e = getenv("DNN_CUDA_TF32_3X_SHAPES");
+    while (e && *e) {
+        ShapeRule r;
+        int used = 0;
+        if (sscanf(e, "%d:%d:%d%n", &r.role, &r.N, &r.K, &used) == 3) g_shape_rules.push_back(r);
+        e += used;
+        while (*e && *e != ',') e++;
+        if (*e == ',') e++;
+    }
+}
+void gemm_reread_env() { g_shapes_read = false; }
+
 void gemm(const GemmArgs &g) {
     int mode = gemm_mode();
     if (mode == DNN_CUDA_GEMM_FP32 || !gemm_tc_supported(g)) { gemm_simt(g); return; }
@@ -104,13 +125,16 @@ void gemm(const GemmArgs &g) {
         if (const char *e = getenv("DNN_CUDA_TF32_3X_ROLES")) g_roles_3x = (unsigned)atoi(e);
         if (const char *e = getenv("DNN_CUDA_TF32_3X_MAX_GFLOP")) g_max_flop_3x = atof(e) * 1e9;
     }
+    if (!g_shapes_read) read_shape_rules();
+    bool by_shape = false;
+    for (const ShapeRule &r : g_shape_rules) if (r.role == g_role && r.N == g.N && r.K == g.K) by_shape = true;
     // Precision policy of TF32 mode: a long reduction into a small output (the filter
     // gradient of a small convolution: thousands of products of mixed sign per element)
     // cancels heavily and would lose more than TF32's 1e-3; such GEMMs are tiny, so they
     // take the 3xTF32 path at no measurable cost.  dnn_cuda_set_tf32_policy widens the rule.
     bool small_long = (int64_t)g.M * g.N <= 65536 && g.K >= 1024;
     bool by_policy = ((g_roles_3x >> g_role) & 1u) || 2.0 * g.M * g.N * g.K * (g.batch > 0 ? g.batch : 1) <= g_max_flop_3x;
-    gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32 || small_long || by_policy);
+    gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32 || small_long || by_policy || by_shape);
 }
 
 }  // namespace dnnb

@@ -487,6 +487,13 @@ static int choose_splits(int tiles, int slots, int num_kb, int64_t M, int64_t N)
     return best;
 }
 
+// Longest accumulation chain, in k-blocks of 32, that one work unit may run inside the tensor core (0: no limit).
+// The tensor core adds into its fp32 accumulator with truncation, so a chain of K products is biased low by about
+// 2.4e-9 x K relative (measured: 1.6e-6 at K = 768, 7.3e-6 at K = 3072).  That is invisible next to TF32 rounding,
+// but it is the error floor of the 3xTF32 mode, whose main product therefore runs as split-K pieces of bounded
+// length that splitk_reduce adds in fp32 with round-to-nearest, in fixed order.
+static thread_local int g_chain_kb = 0;
+
 template <int BN, bool PAIR>
 static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     using Cfg = TcCfg<BN, PAIR>;
@@ -516,6 +523,7 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     const int slots = PAIR ? kNumSMs / 2 : kNumSMs;      // work units in flight: one per CTA, or per CTA pair
     // split-K when the output has too few tiles to fill the SMs and K is long
     int splits = choose_splits(tiles, slots, num_kb, g.M, g.N);
+    if (g_chain_kb > 0 && (num_kb + splits - 1) / splits > g_chain_kb) splits = (num_kb + g_chain_kb - 1) / g_chain_kb;
     t.kb_per_split = (num_kb + splits - 1) / splits;
     splits = (num_kb + t.kb_per_split - 1) / t.kb_per_split;
     t.splits = splits;
@@ -615,7 +623,11 @@ void gemm_tc(const GemmArgs &in, bool split3) {
     t.A = As; t.B = Bb; t.bias = nullptr; run_tc(t);
     t.accumulate = true;
     t.A = Ab; t.B = Bs; run_tc(t);
+    static int chain = -1;
+    if (chain < 0) { const char *e = getenv("DNN_CUDA_3X_CHAIN_KB"); chain = e ? atoi(e) : 16; }
+    g_chain_kb = chain;
     t.A = Ab; t.B = Bb; t.bias = g.bias; run_tc(t);
+    g_chain_kb = 0;
 }
 
 int gemm_tc_error() {

@@ -42,11 +42,11 @@ struct StepTail { float gn; };
 float finish_step(struct mem_pool *scratch, tensor *loss, adamw_opt *opt, float grad_clip, bool dp) {
     // data parallel: from the second step on the buckets of the gradient exchange are sent while
     // backward still runs; the first step (gradient buffers not allocated yet) exchanges afterwards
-    bool overlapped = dp && dp_overlap_begin(opt->params, opt->n_params);
-    dnn_backward(scratch, loss);
     if (dp) {
-        int rc = overlapped ? dp_overlap_finish() : dnn_cuda_dp_allreduce_grads(opt->params, opt->n_params);
+        int rc = dnn_cuda_dp_backward(scratch, loss, opt->params, opt->n_params);
         DNN_CHECK(rc == 0, "data-parallel gradient all-reduce failed");
+    } else {
+        dnn_backward(scratch, loss);
     }
     float gn = grad_clip > 0.0f ? clip_grad_norm(opt->params, opt->n_params, grad_clip)
                                 : grad_norm(opt->params, opt->n_params);
@@ -453,6 +453,18 @@ tensor *vision_lm_train_step_padded(struct mem_pool *scratch, vision_lm *v, cons
     adamw_zero_grad(opt);
     tensor *loss = vision_lm_loss_padded(scratch, v, images, input_ids, target_ids, loss_mask, text_lens);
     float gn = finish_step(scratch, loss, opt, grad_clip, false);
+    if (grad_norm_out) *grad_norm_out = gn;
+    return loss;
+}
+// The same step with the gradient exchange between backward and clipping (the place of a DDP hook in
+// src/vlm.c:348-381).  Every rank normalises its loss by its own mask sum; the gradients are averaged.
+tensor *dnn_cuda_dp_vision_lm_train_step_padded(struct mem_pool *scratch, vision_lm *v, const tensor *images, const tensor *input_ids,
+                                                const tensor *target_ids, const tensor *loss_mask, const int *text_lens,
+                                                adamw_opt *opt, float grad_clip, float *grad_norm_out) {
+    DNN_CHECK(opt, "dnn_cuda_dp_vision_lm_train_step_padded: opt is NULL");
+    adamw_zero_grad(opt);
+    tensor *loss = vision_lm_loss_padded(scratch, v, images, input_ids, target_ids, loss_mask, text_lens);
+    float gn = finish_step(scratch, loss, opt, grad_clip, dnn_cuda_dp_world_size() > 1);
     if (grad_norm_out) *grad_norm_out = gn;
     return loss;
 }

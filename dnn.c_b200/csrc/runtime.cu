@@ -410,6 +410,7 @@ int dnn_cuda_profile_read(int kernel_class, long long *launches, double *ms, dou
 }
 
 int dnn_cuda_set_tf32_policy(unsigned roles_3x, double max_flop_3x) {
+    gemm_reread_env();
     if (roles_3x > 7u || !(max_flop_3x >= 0.0)) { set_error("tf32 policy: roles is a 3-bit mask, max_flop must be >= 0"); return -1; }
     gemm_set_policy(roles_3x, max_flop_3x);
     return 0;

@@ -46,14 +46,16 @@ def peaks():
 
 
 class Bench:
-    def __init__(self, B, iters, small, params_mb=8192, scratch_mb=24 * 1024):
-        self.B, self.iters, self.small = B, iters, small
-        self.d = B.Dnn(B.B200_LIB, params_mb=params_mb, scratch_mb=scratch_mb, data_mb=256)
+    def __init__(self, B, iters, small, params_mb=8192, scratch_mb=24 * 1024, echo=True, device=0, tf32_peak=None):
+        self.B, self.iters, self.small, self.echo, self.rows = B, iters, small, echo, []
+        self.d = B.Dnn(B.B200_LIB, params_mb=params_mb, scratch_mb=scratch_mb, data_mb=256, device=device)
         self.lib = self.d.lib
         self.rng = np.random.default_rng(1)
         # 256 MiB rewritten between iterations: twice the 126 MB L2
         self.flush = self.lib.tensor_zeros(self.d.params, 1, B.ints([64 << 20]), 0)
         self.hbm, self.tf32, self.src = peaks()
+        if tf32_peak:                                        # a TF32 figure measured in this run replaces the bf16-derived one
+            self.tf32, self.src = tf32_peak, "TF32 matmul measured in this run"
 
     def dev(self, arr, grad=False):
         return self.d.tensor(arr, self.d.params, grad)         # params pool: survives reset_step
@@ -97,10 +99,24 @@ class Bench:
         ms_f, ms_b = float(np.median(tf)), float(np.median(tb))
         peak, unit, scale = (self.hbm, "GB/s", 1e9) if bound == "hbm" else (self.tf32, "TFLOP/s", 1e12)
         af, ab = work_fwd / (ms_f * 1e-3) / scale, work_bwd / (ms_b * 1e-3) / scale
-        print(json.dumps({"op": name, "bound": bound, "fwd_ms": round(ms_f, 4), "bwd_ms": round(ms_b, 4),
-                          "fwd_achieved": round(af, 1), "bwd_achieved": round(ab, 1), "unit": unit, "peak": round(peak, 1),
-                          "fwd_frac": round(af / peak, 3), "bwd_frac": round(ab / peak, 3), "peak_source": self.src,
-                          "work_fwd": work_fwd, "work_bwd": work_bwd}), flush=True)
+        row = {"op": name, "bound": bound, "fwd_ms": round(ms_f, 4), "bwd_ms": round(ms_b, 4),
+               "fwd_achieved": round(af, 1), "bwd_achieved": round(ab, 1), "unit": unit, "peak": round(peak, 1),
+               "fwd_frac": round(af / peak, 3), "bwd_frac": round(ab / peak, 3), "peak_source": self.src,
+               "work_fwd": work_fwd, "work_bwd": work_bwd}
+        self.emit(row)
+        return row
+
+    def emit(self, row):
+        self.rows.append(row)
+        if self.echo:
+            print(json.dumps(row), flush=True)
+
+
+class Args:
+    """What run_ops needs from the command line: small (reduced batch), shapes (matmul_shapes / step_graph variant), iters."""
+
+    def __init__(self, small=False, shapes="", iters=10):
+        self.small, self.shapes, self.iters = small, shapes, iters
 
 
 def main():
@@ -115,12 +131,17 @@ def main():
     B = load_binding()
     pm, sm = (int(x) for x in args.pools_mb.split(","))
     b = Bench(B, args.iters, args.small, pm, sm)
+    b.lib.dnn_cuda_set_gemm_mode({"fp32": 0, "tf32": 1, "3xtf32": 2}[args.gemm])
+    run_ops(b, args.op.split(","), args)
+    b.d.close()
+
+
+def run_ops(b, ops, args):
+    """Runs the named workloads on the Bench `b`; every result is appended to b.rows (and printed when b.echo)."""
+    B = b.B
     lib, d, rng = b.lib, b.d, b.rng
-    lib.dnn_cuda_set_gemm_mode({"fp32": 0, "tf32": 1, "3xtf32": 2}[args.gemm])
     R = 1024 if args.small else 8192
     Bt = 2 if args.small else 8
-
-    ops = args.op.split(",")
 
     def want(n):
         return "all" in ops or n in ops
@@ -220,10 +241,10 @@ def main():
             lib.dnn_cuda_graph_replay(g, C.byref(loss), None)
         ms_graph = (time.perf_counter() - t0) * 1e3 / reps
         lib.dnn_cuda_graph_destroy(g)
-        print(json.dumps({"op": "step_graph", "workload": "decoder LM V%d d%d L%d H%d F%d, %dx%d tokens" % (V, D, L, H, F, Bsz, N),
+        b.emit(({"op": "step_graph", "workload": "decoder LM V%d d%d L%d H%d F%d, %dx%d tokens" % (V, D, L, H, F, Bsz, N),
                           "kernels_per_step": int(per_step), "eager_ms_per_step": round(ms_eager, 3), "graph_ms_per_step": round(ms_graph, 3),
                           "eager_tokens_per_s": round(Bsz * N / ms_eager * 1e3), "graph_tokens_per_s": round(Bsz * N / ms_graph * 1e3),
-                          "speedup": round(ms_eager / ms_graph, 2)}), flush=True)
+                          "speedup": round(ms_eager / ms_graph, 2)}))
     if "cnn_step" in ops:
         # BASELINE config 3: 512 images 1x28x28, conv 3x3 (1->32) + pool, conv 3x3 (32->64) + pool, 3136->128->10,
         # cross entropy, backward, AdamW; wall time per step with the loss read back
@@ -260,9 +281,9 @@ def main():
         for _ in range(reps):
             last = cnn_step()
         ms = (time.perf_counter() - t0) * 1e3 / reps
-        print(json.dumps({"op": "cnn_step", "workload": "BASELINE config 3: %d images 1x28x28, 2 conv + 2 linear" % Bsz, "ms_per_step": round(ms, 3),
+        b.emit(({"op": "cnn_step", "workload": "BASELINE config 3: %d images 1x28x28, 2 conv + 2 linear" % Bsz, "ms_per_step": round(ms, 3),
                           "images_per_s": round(Bsz / ms * 1e3), "kernels_per_step": int((lib.dnn_cuda_launch_count() - before) // reps),
-                          "loss": round(last, 4)}), flush=True)
+                          "loss": round(last, 4)}))
     if "vlm_step" in ops:
         # BASELINE config 4: 64 images 3x224x224 (196 image tokens) + up to 32 text tokens, d 512, 8 blocks, 8 heads,
         # FFN 1376, vocabulary 1024; vision_lm_train_step_padded with per-sample text lengths and loss mask
@@ -295,10 +316,10 @@ def main():
         for _ in range(reps):
             last = vlm_step()
         ms = (time.perf_counter() - t0) * 1e3 / reps
-        print(json.dumps({"op": "vlm_step", "workload": "BASELINE config 4: %d images 3x224x224 + texts <= %d, d 512, 8 blocks" % (Bsz, Tm),
+        b.emit(({"op": "vlm_step", "workload": "BASELINE config 4: %d images 3x224x224 + texts <= %d, d 512, 8 blocks" % (Bsz, Tm),
                           "ms_per_step": round(ms, 3), "images_per_s": round(Bsz / ms * 1e3),
                           "tokens_per_s": round(Bsz * (196 + Tm) / ms * 1e3),
-                          "kernels_per_step": int((lib.dnn_cuda_launch_count() - before) // reps), "loss": round(last, 4)}), flush=True)
+                          "kernels_per_step": int((lib.dnn_cuda_launch_count() - before) // reps), "loss": round(last, 4)}))
     if "vlm_batch" in ops:
         # Padded vision-LM batch of BASELINE config 4 (64 images 3x224x224, texts up to 32): device assembly alone
         # (uint8 HWC -> normalised NCHW floats, ids / targets / mask rows) and the whole put + upload + assemble
@@ -359,12 +380,12 @@ def main():
         lib.dnn_cuda_host_free(fl)
         lib.dnn_cuda_vlm_stager_destroy(st)
         a = dev_bytes / (ms_dev * 1e-3) / 1e9
-        print(json.dumps({"op": "vlm_batch", "workload": "%d images %dx%dx%d uint8, texts <= %d" % (Bsz, Cc, Hh, Ww, Tm), "bound": "hbm",
+        b.emit(({"op": "vlm_batch", "workload": "%d images %dx%dx%d uint8, texts <= %d" % (Bsz, Cc, Hh, Ww, Tm), "bound": "hbm",
                           "assemble_ms": round(ms_dev, 4), "assemble_bytes": dev_bytes, "achieved": round(a, 1), "unit": "GB/s",
                           "peak": b.hbm, "frac": round(a / b.hbm, 3), "peak_source": b.src,
                           "pipeline_ms_per_batch": round(ms_e2e, 3), "pipeline_images_per_s": round(Bsz / ms_e2e * 1e3),
                           "h2d_bytes_per_batch": Bsz * Hh * Ww * Cc + Bsz * (2 + Tm) * 4,
-                          "float_upload_ms_per_batch": round(ms_float, 3), "float_h2d_bytes_per_batch": Bsz * Cc * Hh * Ww * 4}), flush=True)
+                          "float_upload_ms_per_batch": round(ms_float, 3), "float_h2d_bytes_per_batch": Bsz * Cc * Hh * Ww * 4}))
     if want("adamw"):
         P = (16 if args.small else 124) * 1000 * 1000
         t = lib.tensor_zeros(d.params, 1, B.ints([P]), 1)
@@ -379,9 +400,9 @@ def main():
                 ts.append(ms)
         ms = float(np.median(ts))
         a = 28.0 * P / (ms * 1e-3) / 1e9
-        print(json.dumps({"op": "adamw", "bound": "hbm", "ms": round(ms, 4), "achieved": round(a, 1), "unit": "GB/s", "peak": b.hbm,
-                          "frac": round(a / b.hbm, 3), "params": P, "peak_source": b.src}), flush=True)
-    d.close()
+        b.emit(({"op": "adamw", "bound": "hbm", "ms": round(ms, 4), "achieved": round(a, 1), "unit": "GB/s", "peak": b.hbm,
+                          "frac": round(a / b.hbm, 3), "params": P, "peak_source": b.src}))
+    return b.rows
 
 
 if __name__ == "__main__":

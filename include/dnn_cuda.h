@@ -203,10 +203,25 @@ int  dnn_cuda_dp_world_size(void);
 int  dnn_cuda_dp_plan_buckets(const size_t *addrs, const size_t *bytes, int n, size_t bucket_bytes,
                               size_t *out_addrs, size_t *out_bytes, int cap);
 int  dnn_cuda_dp_finalize(void);
+const char *dnn_cuda_dp_last_error(void);
+/* dnn_backward(scratch, loss) followed by the exchange of the gradients of `params`: what a loop that
+ * calls the ops itself puts between its forward pass and adamw_step (the MNIST loop of the reference,
+ * examples/mnist/mnist_train.c:99-114, has dnn_backward at that place).  With the overlap enabled and the
+ * gradient buffers already allocated (from the second step on) buckets are exchanged while backward
+ * still runs.  Before the first exchange, and whenever a rank's bucket plan changes, the ranks compare a
+ * fingerprint of their plans; -5 means they differ (nothing was exchanged, dnn_cuda_dp_last_error() says
+ * why).  With one rank this is dnn_backward. */
+int  dnn_cuda_dp_backward(struct mem_pool *scratch_pool, tensor *loss, tensor **params, int n_params);
 /* decoder_lm_train_step with the all-reduce between backward and clipping. */
 tensor *dnn_cuda_dp_decoder_lm_train_step(struct mem_pool *scratch_pool, decoder_lm *lm,
                                           const tensor *input_ids, const tensor *target,
                                           adamw_opt *opt, float grad_clip, float *grad_norm_out);
+/* vision_lm_train_step_padded (src/vlm.c:348-381) with the all-reduce between backward and clipping;
+ * parameters outside the graph (img_proj.* for [B,C,H,W] images) have no gradient on any rank and are
+ * skipped by the exchange and by AdamW alike. */
+tensor *dnn_cuda_dp_vision_lm_train_step_padded(struct mem_pool *scratch_pool, vision_lm *v, const tensor *images,
+                                                const tensor *input_ids, const tensor *target_ids, const tensor *loss_mask,
+                                                const int *text_lens, adamw_opt *opt, float grad_clip, float *grad_norm_out);
 
 #ifdef __cplusplus
 }

@@ -629,6 +629,45 @@ def vlm_loss_and_grads(P, images, input_ids, target_ids, loss_mask, text_lens, n
     return loss, out
 
 
+# ── MNIST-shaped CNN step (examples/mnist/mnist_cnn_pool_model.c, mnist_train.c:99-114) ──
+CNN_PARAM_NAMES = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
+
+
+def cnn_loss_and_grads(P, x, labels):
+    """conv3x3(1->32) relu avgpool2 conv3x3(32->64) relu avgpool2 linear(3136->128) relu linear(128->10),
+    cross entropy; composed from the operator restatements above (float64 inside every operator, float32
+    between operators, as the library stores its activations).  x: [B, 784] or [B,1,28,28]."""
+    n = x.shape[0]
+    x = x.reshape(n, 1, 28, 28).astype(np.float32)
+    z = lambda a: np.zeros(a.shape, np.float32)
+
+    def fwd_conv(inp, w, b):
+        oc = w.shape[0]
+        return conv2d(inp, w, b, 1, 1, np.zeros((inp.shape[0], oc, inp.shape[2], inp.shape[3]), np.float32))[0]
+    c1 = fwd_conv(x, P["conv1.weight"], P["conv1.bias"])
+    r1 = relu(c1, z(c1))[0]
+    p1 = avg_pool2d(r1, 2, 2, np.zeros((n, 32, 14, 14), np.float32))[0]
+    c2 = fwd_conv(p1, P["conv2.weight"], P["conv2.bias"])
+    r2 = relu(c2, z(c2))[0]
+    p2 = avg_pool2d(r2, 2, 2, np.zeros((n, 64, 7, 7), np.float32))[0]
+    flat = p2.reshape(n, 3136)
+    h1 = matmul_add(flat, P["fc1.weight"], 0, P["fc1.bias"], np.zeros((n, 128), np.float32))[0]
+    a1 = relu(h1, z(h1))[0]
+    logits = matmul_add(a1, P["fc2.weight"], 0, P["fc2.bias"], np.zeros((n, 10), np.float32))[0]
+    loss, dlogits = cross_entropy(logits, labels)
+    G = {}
+    _, da1, G["fc2.weight"], G["fc2.bias"] = matmul_add(a1, P["fc2.weight"], 0, P["fc2.bias"], dlogits)
+    dh1 = relu(h1, da1)[1]
+    _, dflat, G["fc1.weight"], G["fc1.bias"] = matmul_add(flat, P["fc1.weight"], 0, P["fc1.bias"], dh1)
+    dr2 = avg_pool2d(r2, 2, 2, dflat.reshape(n, 64, 7, 7))[1]
+    dc2 = relu(c2, dr2)[1]
+    _, dp1, G["conv2.weight"], G["conv2.bias"] = conv2d(p1, P["conv2.weight"], P["conv2.bias"], 1, 1, dc2)
+    dr1 = avg_pool2d(r1, 2, 2, dp1)[1]
+    dc1 = relu(c1, dr1)[1]
+    _, _, G["conv1.weight"], G["conv1.bias"] = conv2d(x, P["conv1.weight"], P["conv1.bias"], 1, 1, dc1)
+    return np.float32(loss), G, logits
+
+
 # ── padded vision-LM batch assembly (src/imagenet_vlm.c:31-46, 598-647) ───
 BOS_ID, EOS_ID, PAD_ID = 257, 258, 259          # include/tokenizer.h:23-25
 

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the UNMODIFIED reference library.
 
-    make -C oracle && OMP_NUM_THREADS=1 python tests/golden/make_golden.py [ops] [generate] [models] [batch]
+    make -C oracle REF=<reference checkout> && OMP_NUM_THREADS=1 python tests/golden/make_golden.py [ops] [generate] [models] [batch]
 
 Without arguments all four files are written; with arguments only the named ones.
 

@@ -130,6 +130,26 @@ GEN_CASES = [   # name, config overrides, prompt, max_new, temperature, use_cach
 CNN_NAMES = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
 
 
+CNN_SHAPES = {"conv1.weight": (32, 1, 3, 3), "conv1.bias": (32,), "conv2.weight": (64, 32, 3, 3), "conv2.bias": (64,),
+              "fc1.weight": (3136, 128), "fc1.bias": (128,), "fc2.weight": (128, 10), "fc2.bias": (10,)}
+
+
+def cnn_values(batch, seed=2):
+    """Seeded weights (Kaiming-uniform filters, uniform +-1/sqrt(in) linear layers, zero conv biases) and the batch:
+    images uniform in [0,1), labels uniform in [0,10).  One generator, fixed draw order."""
+    rng = np.random.default_rng(seed)
+    P = {}
+    for n in CNN_NAMES:
+        shape = CNN_SHAPES[n]
+        fan_in = int(np.prod(shape[1:])) if len(shape) == 4 else shape[0]
+        bound = np.sqrt(6.0 / fan_in) if len(shape) == 4 else 1.0 / np.sqrt(3136 if n.startswith("fc1") else 128)
+        P[n] = np.zeros(shape, np.float32) if n.startswith("conv") and n.endswith("bias") else \
+            ((rng.random(shape) * 2 - 1) * bound).astype(np.float32)
+    x_np = rng.random((batch, 784)).astype(np.float32)
+    y_np = rng.integers(0, 10, size=batch).astype(np.int32)
+    return P, x_np, y_np
+
+
 def run_cnn(dnn, batch=8, steps=2, seed=2):
     lib = dnn.lib
     c1 = lib.conv2d_create(dnn.params, 1, 32, 3, 1, 1)
@@ -139,18 +159,12 @@ def run_cnn(dnn, batch=8, steps=2, seed=2):
     params = []
     for m in (c1, c2, f1, f2):
         params += dnn.parameters(m)
-    rng = np.random.default_rng(seed)
+    P, x_np, y_np = cnn_values(batch, seed)
     for t, n in zip(params, CNN_NAMES):
-        shape = dnn.shape_of(t)
-        fan_in = int(np.prod(shape[1:])) if len(shape) == 4 else shape[0]
-        bound = np.sqrt(6.0 / fan_in) if len(shape) == 4 else 1.0 / np.sqrt(3136 if n.startswith("fc1") else 128)
-        v = np.zeros(shape, np.float32) if n.startswith("conv") and n.endswith("bias") else \
-            ((rng.random(shape) * 2 - 1) * bound).astype(np.float32)
-        dnn.upload(t, v)
+        assert dnn.shape_of(t) == CNN_SHAPES[n], (n, dnn.shape_of(t))
+        dnn.upload(t, P[n])
     arr = (B.TensorP * len(params))(*params)
     opt = lib.adamw_create(dnn.params, arr, len(params), 1e-3, 0.9, 0.999, 1e-8, 0.01)
-    x_np = rng.random((batch, 784)).astype(np.float32)
-    y_np = rng.integers(0, 10, size=batch).astype(np.int32)
     out = dict(loss=[], names=CNN_NAMES)
     for s in range(steps):
         x = dnn.tensor(x_np, dnn.data)

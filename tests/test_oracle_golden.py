@@ -74,3 +74,20 @@ def test_oracle_vision_lm_step_matches_reference(model_golden):
             continue
         key = "vlm/grad/" + n
         check(key, g * scale, model_golden[key], model_golden[key + "#"], 2e-5)
+
+
+@pytest.mark.parametrize("tag,batch", [("cnn", 8), ("cnn512", 512)])
+def test_oracle_cnn_step_matches_reference(model_golden, tag, batch):
+    """The float64 restatement of the MNIST-shaped CNN step against the vectors of the unmodified reference, at
+    batch 8 and at BASELINE config 3's batch of 512.  The distance at batch 512 (3e-6 .. 5e-6 on the filter
+    gradients, which are serial fp32 sums of up to 401 408 cancelling products in the reference) is the
+    reference's own rounding noise: the floor below which a comparison with its vectors says nothing."""
+    P, x, y = models.cnn_values(batch)
+    loss, G, logits = O.cnn_loss_and_grads(P, x, y)
+    assert abs(loss - model_golden[tag + "/loss"][0]) <= 2e-6 * abs(loss)
+    if tag == "cnn":
+        check("cnn/logits", logits, model_golden["cnn/logits"], model_golden["cnn/logits#"], 2e-5)
+    for n, g in G.items():
+        key = tag + "/grad/" + n
+        err = check(key, g, model_golden[key], model_golden[key + "#"], 1e-5)
+        print("reference vs float64 oracle, %s %s: %.2e" % (tag, n, err))
