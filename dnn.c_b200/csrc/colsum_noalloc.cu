@@ -12,7 +12,6 @@
 // loading the library holds until the process exits.
 #include "common.cuh"
 #include "device_utils.cuh"
-#include <string>
 
 namespace dnnb {
 
@@ -55,7 +54,12 @@ __global__ void colsum_static_final_kernel(float *__restrict__ out, const float 
 constexpr int kMaxDevices = 64;
 static float *g_static_ptr[kMaxDevices] = {nullptr};
 
-static std::string g_static_error;
+// Last failure of the calling thread (the entry point may be called from several host threads).
+static thread_local char g_static_error[256] = "";
+static int static_fail(int code, const char *fmt, const char *detail = "") {
+    snprintf(g_static_error, sizeof g_static_error, fmt, detail);
+    return code;
+}
 
 }  // namespace dnnb
 
@@ -63,31 +67,28 @@ using namespace dnnb;
 
 extern "C" {
 
-const char *dnn_cuda_colsum_acc_static_error(void) { return g_static_error.c_str(); }
+const char *dnn_cuda_colsum_acc_static_error(void) { return g_static_error; }
 
 int dnn_cuda_colsum_acc_static(float *out, const float *g, long long rows, int cols) {
-    if (!out || !g) { g_static_error = "colsum_acc_static: NULL pointer"; return -1; }
-    if (rows < 0 || cols <= 0) { g_static_error = "colsum_acc_static: rows must be >= 0 and cols > 0"; return -1; }
+    if (!out || !g) return static_fail(-1, "colsum_acc_static: NULL pointer");
+    if (rows < 0 || cols <= 0) return static_fail(-1, "colsum_acc_static: rows must be >= 0 and cols > 0");
     if (cols > kStaticMaxCols) {
-        char buf[160];
-        snprintf(buf, sizeof buf, "colsum_acc_static: %d columns exceed the static scratch limit of %d; use the pooled path",
-                 cols, kStaticMaxCols);
-        g_static_error = buf;
+        snprintf(g_static_error, sizeof g_static_error,
+                 "colsum_acc_static: %d columns exceed the static scratch limit of %d; use the pooled path", cols, kStaticMaxCols);
         return -2;
     }
     if (rows == 0) return 0;
+    // stream() aborts the process when no device can be used; this entry point reports instead
+    if (!dnn_cuda_available()) return static_fail(-3, "colsum_acc_static: no usable CUDA device");
     cudaStream_t st = stream();
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) { g_static_error = "colsum_acc_static: cannot identify the current device"; return -3; }
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return static_fail(-3, "colsum_acc_static: cannot identify the current device");
     if (!g_static_ptr[dev]) {
         // one-time set-up for this device (the device is current here)
         float *p = nullptr;
         e = cudaGetSymbolAddress((void **)&p, g_static_partials);
-        if (e != cudaSuccess || !p) {
-            g_static_error = std::string("colsum_acc_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e);
-            return -4;
-        }
+        if (e != cudaSuccess || !p) return static_fail(-4, "colsum_acc_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
         g_static_ptr[dev] = p;
     }
     float *partial = g_static_ptr[dev];
@@ -99,9 +100,10 @@ int dnn_cuda_colsum_acc_static(float *out, const float *g, long long rows, int c
     // call, so nothing left over from an earlier call has to be cleared.
     dim3 grid((cols + 31) / 32, nparts), block(32, 32);
     colsum_static_partial_kernel<<<grid, block, 0, st>>>(g, partial, rows, cols, rows_per);
-    LAUNCHED("colsum_static_partial_kernel");
+    if ((e = cudaGetLastError()) != cudaSuccess) return static_fail(-5, "colsum_acc_static: launch failed: %s", cudaGetErrorString(e));
     colsum_static_final_kernel<<<(cols + 127) / 128, 128, 0, st>>>(out, partial, nparts, cols);
-    LAUNCHED("colsum_static_final_kernel");
+    if ((e = cudaGetLastError()) != cudaSuccess) return static_fail(-5, "colsum_acc_static: launch failed: %s", cudaGetErrorString(e));
+    add_launches(2);
     return 0;
 }
 

@@ -145,7 +145,8 @@ int   dnn_cuda_profile_kernels(dnn_cuda_kernel_time *rows, int cap);
  *   - All calls share the one array.  Each call rewrites the part it reads, so no
  *     clearing is needed between calls, but two calls that overlap on the GPU (for
  *     example from different streams or processes' threads) race on it.
- * Returns 0 on success, negative on failure. */
+ * Returns 0 on success, negative on failure (-1 bad argument, -2 too wide, -3 no usable device, -4 the array's
+ * address could not be resolved, -5 a launch failed); the message is kept per calling thread.  Never aborts. */
 int   dnn_cuda_colsum_acc_static(float *out, const float *g, long long rows, int cols);
 const char *dnn_cuda_colsum_acc_static_error(void);
 

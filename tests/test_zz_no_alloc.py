@@ -27,12 +27,15 @@ def reference_colsum(gpu, g_np):
     return gpu.download_grad(bias)
 
 
-@pytest.mark.parametrize("shapes", [[(1000, 768), (37, 130)], [(16384, 2304), (5, 8192)]])
+# the last pair has more than 128 x 256 rows, so the number of row blocks is clamped to the 128 the array holds
+@pytest.mark.parametrize("shapes", [[(1000, 768), (37, 130)], [(16384, 2304), (5, 8192)], [(40000, 96), (70001, 33)]])
 def test_static_colsum_matches_pooled_path_twice_in_a_row(gpu, shapes):
     rng = np.random.default_rng(5)
     for rows, cols in shapes:                       # two calls back to back on the shared array
         g_np = rng.standard_normal((rows, cols)).astype(np.float32)
         want = reference_colsum(gpu, g_np)
+        exact = g_np.astype(np.float64).sum(axis=0)            # and against plain numpy, independent of the library
+        assert np.linalg.norm(want - exact) <= 2e-5 * np.linalg.norm(exact)
         g = gpu.tensor(g_np, gpu.scratch)
         out = gpu.tensor(np.zeros(cols, np.float32), gpu.scratch)
         rc = gpu.lib.dnn_cuda_colsum_acc_static(out.contents.data, g.contents.data, rows, cols)
@@ -41,6 +44,7 @@ def test_static_colsum_matches_pooled_path_twice_in_a_row(gpu, shapes):
         gpu.reset_step()
         err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want.astype(np.float64))
         assert err <= 2e-5, (rows, cols, err)
+        assert np.linalg.norm(got - exact) <= 2e-5 * np.linalg.norm(exact), (rows, cols)
 
 
 def test_static_colsum_accumulates_and_rejects_oversize(gpu):
