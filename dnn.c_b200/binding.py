@@ -217,6 +217,8 @@ CUDA_API = {
     "dnn_cuda_graph_destroy": (None, [VP]),
     "dnn_cuda_optimizer_save": (I, [C.POINTER(AdamW), C.c_char_p]),
     "dnn_cuda_optimizer_load": (I, [C.POINTER(AdamW), C.c_char_p]),
+    "dnn_cuda_train_state_save": (I, [C.POINTER(AdamW), C.POINTER(LrScheduler), C.c_char_p]),
+    "dnn_cuda_train_state_load": (I, [C.POINTER(AdamW), C.POINTER(LrScheduler), C.c_char_p]),
     "dnn_cuda_set_fused_attention": (None, [I]),
     "dnn_cuda_get_fused_attention": (I, []),
     "dnn_cuda_colsum_acc_static": (I, [VP, VP, C.c_longlong, I]),

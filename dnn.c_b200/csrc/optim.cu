@@ -281,6 +281,42 @@ int dnn_cuda_optimizer_load(adamw_opt *opt, const char *path) {
     return 0;
 }
 
+// Whole resume state: the optimiser file above followed by a tail with what else a run carries between
+// steps -- the scheduler's step count (it keeps its own, src/optim.c:104-189) and the state of the calling
+// thread's default host generator (dropout masks and weight initialisation draw from it,
+// src/ops_activation.c:1460, src/rng.c:70).  Tail: magic "DNNT", u32 has_scheduler, i32 scheduler_t,
+// u64 rng_s0, u64 rng_s1.
+int dnn_cuda_train_state_save(const adamw_opt *opt, const lr_scheduler *sched, const char *path) {
+    int rc = dnn_cuda_optimizer_save(opt, path);
+    if (rc != 0) return rc;
+    FILE *f = fopen(path, "ab");
+    if (!f) return -2;
+    uint32_t has = sched ? 1u : 0u;
+    int32_t st = sched ? sched->t : 0;
+    const dnn_rng *r = dnn_get_rng();
+    uint64_t s[2] = {r->s[0], r->s[1]};
+    bool ok = fwrite("DNNT", 1, 4, f) == 4 && fwrite(&has, 4, 1, f) == 1 && fwrite(&st, 4, 1, f) == 1 && fwrite(s, 8, 2, f) == 2;
+    ok = (fclose(f) == 0) && ok;
+    return ok ? 0 : -3;
+}
+// Restores the optimiser, then the tail: sched->t and the learning rate that follows from it (when both the
+// file and the caller have a scheduler) and the default host generator.
+int dnn_cuda_train_state_load(adamw_opt *opt, lr_scheduler *sched, const char *path) {
+    int rc = dnn_cuda_optimizer_load(opt, path);
+    if (rc != 0) return rc;
+    FILE *f = fopen(path, "rb");
+    if (!f) return -2;
+    char magic[4]; uint32_t has = 0; int32_t st = 0; uint64_t s[2] = {0, 0};
+    bool ok = fseek(f, -28L, SEEK_END) == 0 && fread(magic, 1, 4, f) == 4 && memcmp(magic, "DNNT", 4) == 0 &&
+              fread(&has, 4, 1, f) == 1 && fread(&st, 4, 1, f) == 1 && fread(s, 8, 2, f) == 2;
+    fclose(f);
+    if (!ok) return -3;
+    if (sched && has) { sched->t = st; sched->opt->lr = lr_at(sched, st); }
+    dnn_rng *r = dnn_get_rng();
+    r->s[0] = s[0]; r->s[1] = s[1];
+    return 0;
+}
+
 // The reference memsets every parameter gradient here (src/optim.c:93-100).  The buffers are
 // only marked fresh: the first backward contribution of the step (a dW GEMM that covers the
 // whole tensor) stores instead of adding, and whatever is still fresh when gradients are

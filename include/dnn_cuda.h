@@ -87,6 +87,13 @@ int  dnn_cuda_get_fused_attention(void);
  * No counterpart in the reference. */
 int  dnn_cuda_optimizer_save(const adamw_opt *opt, const char *path);
 int  dnn_cuda_optimizer_load(adamw_opt *opt, const char *path);
+/* The whole resume state in one file: the optimiser state above plus the LR scheduler's own step count
+ * (`sched` may be NULL) and the state of the calling thread's default host random generator, from which
+ * dropout masks are drawn (src/ops_activation.c:1460).  load restores all three and sets opt->lr to the
+ * scheduler's value at the restored step, so a run that uses an LR schedule and dropout continues bit
+ * for bit.  Same return codes.  No counterpart in the reference. */
+int  dnn_cuda_train_state_save(const adamw_opt *opt, const lr_scheduler *sched, const char *path);
+int  dnn_cuda_train_state_load(adamw_opt *opt, lr_scheduler *sched, const char *path);
 
 /* Whole training step as one CUDA graph.  capture records zero_grad + forward + cross entropy +
  * backward + gradient clipping + AdamW of decoder_lm_train_step (src/gpt.c:178-216) on the

@@ -1,8 +1,8 @@
 """Generates tests/golden/*.npz by running the UNMODIFIED reference library.
 
-    make -C oracle REF=<reference checkout> && OMP_NUM_THREADS=1 python tests/golden/make_golden.py [ops] [generate] [models] [batch]
+    make -C oracle REF=<reference checkout> && OMP_NUM_THREADS=1 python tests/golden/make_golden.py [ops] [generate] [models] [batch] [module]
 
-Without arguments all four files are written; with arguments only the named ones.
+Without arguments all five files are written; with arguments only the named ones.
 
 Needs oracle/_ref/libdnn_ref.so (built from the reference's own sources by
 oracle/Makefile), so it runs only where the reference sources are mounted.
@@ -133,9 +133,25 @@ def write_batch(B):
     np.savez_compressed(os.path.join(HERE, "batch.npz"), **out)
 
 
+def write_module_file(B):
+    """A weight file written by the reference's own module_save (src/module.c:208-268) for the tiny decoder LM
+    with seeded weights: the bytes a drop-in library has to write, and has to be able to load."""
+    import ctypes as C
+    d = B.Dnn(REF_LIB, params_mb=64, scratch_mb=64, data_mb=16)
+    cfg = models.lm_config("tiny")
+    lm = d.lib.decoder_lm_create(d.params, cfg["V"], cfg["D"], cfg["L"], cfg["H"], cfg["D"] // cfg["H"], cfg["F"])
+    d.lib.decoder_lm_enable_rope(d.params, lm, cfg["N"], 10000.0)
+    models.seeded_weights(d, lm, models.O.lm_param_names(cfg["L"]), cfg["seed"] + 100)
+    d.lib.module_save(C.cast(lm, C.c_void_p), os.path.join(HERE, "lm_tiny.dnnm").encode())
+    d.close()
+
+
 def main():
     B = load_binding()
-    which = sys.argv[1:] or ["ops", "generate", "models", "batch"]
+    which = sys.argv[1:] or ["ops", "generate", "models", "batch", "module"]
+    if "module" in which:
+        write_module_file(B)
+        print("lm_tiny.dnnm", os.path.getsize(os.path.join(HERE, "lm_tiny.dnnm")) // 1024, "KiB")
     for name, fn in (("ops", write_ops), ("generate", write_generate), ("models", write_models), ("batch", write_batch)):
         if name in which:
             fn(B)
