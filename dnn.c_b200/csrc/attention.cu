@@ -614,6 +614,7 @@ extern "C" {
 
 tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tensor *v, tensor *mask,
                             attention_mode mode, int prefix_len, const int *seq_lens) {
+    require_device_payloads("tensor_attention_ex", {q, k, v, mask});
     DNN_CHECK(q && k && v, "tensor_attention: NULL operand");
     DNN_CHECK(q->ndim == 4 && k->ndim == 4 && v->ndim == 4, "tensor_attention: operands must be [B,H,N,d]");
     DNN_CHECK(q->contiguous && k->contiguous && v->contiguous, "tensor_attention: operands must be contiguous");
@@ -658,6 +659,7 @@ void dnn_cuda_set_fused_attention(int on) { g_fused_attention = on ? 1 : 0; }
 int dnn_cuda_get_fused_attention(void) { return fused_attention_enabled() ? 1 : 0; }
 
 tensor *tensor_attention(struct mem_pool *scratch, tensor *q, tensor *k, tensor *v, tensor *mask) {
+    require_device_payloads("tensor_attention", {q, k, v, mask});
     return tensor_attention_ex(scratch, q, k, v, mask, ATTENTION_CAUSAL, 0, nullptr);
 }
 

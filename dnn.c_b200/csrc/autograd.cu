@@ -22,7 +22,15 @@ namespace dnnb {
 struct DeferredCopy { tensor *base; const float *src; };
 static std::vector<DeferredCopy> g_deferred;
 
+// The fresh bit shares a 32-bit unit with the reference's two public flags, so a caller that fills a tensor
+// struct in by hand may leave it set by accident.  It only means something on a gradient buffer this
+// library allocated: anything else (no buffer, or a buffer outside the pool arenas) is not fresh.
+static inline void trust_fresh_bit(tensor *base) {
+    if (base->grad_fresh && !(base->grad && dev_ptr_in_arena(base->grad))) base->grad_fresh = 0;
+}
+
 static void settle_deferred(tensor *base) {
+    trust_fresh_bit(base);
     if (g_deferred.empty()) return;
     for (size_t i = 0; i < g_deferred.size(); i++)
         if (g_deferred[i].base == base) {
@@ -148,6 +156,7 @@ bool grad_defer_copy(tensor *t, const float *src) {
     tensor *base = t;
     while (base->parent) base = base->parent;
     const bool spans = t->contiguous && t->offset == 0 && numel_of(t) == numel_of(base);
+    trust_fresh_bit(base);
     if (!spans || !base->pool || (base->grad && !base->grad_fresh)) return false;
     if (!base->grad) base->grad = (float *)dev_alloc(base->pool, (size_t)numel_of(base) * sizeof(float), false);
     base->grad_fresh = 0;                      // it has content now, even if the content is still a promise
@@ -216,6 +225,7 @@ struct Topo {
 extern "C" void dnn_backward(struct mem_pool *scratch, tensor *loss) {
     (void)scratch;
     DNN_CHECK(loss, "dnn_backward: loss is NULL");
+    require_device_payloads("dnn_backward", {loss});
     Topo topo;
     topo.visit(loss);
     colsum_cache_forget(nullptr);                // cached column sums never outlive one backward pass

@@ -6,6 +6,7 @@
 #include <cstring>
 #include <cstdint>
 #include <cmath>
+#include <initializer_list>
 #include "dnn_b200.h"
 #include "dnn_cuda.h"
 
@@ -28,6 +29,13 @@ void launched(const char *name);
 void add_launches(long long n);
 #define LAUNCHED(name) ::dnnb::launched(name)
 
+// True when p points into the device arena of one of this process's pools.
+bool dev_ptr_in_arena(const void *p);
+// Every op reads its operands' payloads on the device.  A tensor whose `data` is host memory -- a struct the
+// caller filled in by hand around a malloc'd buffer, as CPU callers of dnn.c may -- would hand a host pointer to
+// a kernel; this check stops with a message instead (payloads inside a pool arena pass with a range compare,
+// other pointers are looked up once through cudaPointerGetAttributes).  NULL tensors are skipped.
+void require_device_payloads(const char *op, std::initializer_list<const tensor *> ts);
 // Device allocation from the arena attached to `pool` (256-byte aligned).
 void *dev_alloc(struct mem_pool *pool, size_t bytes, bool zero);
 // Device scratch valid until the pool is reset / released.

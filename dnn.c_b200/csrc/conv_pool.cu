@@ -437,6 +437,7 @@ using namespace dnnb;
 extern "C" {
 
 tensor *tensor_conv2d(struct mem_pool *scratch, tensor *input, tensor *weight, tensor *bias, int stride, int pad) {
+    require_device_payloads("tensor_conv2d", {input, weight, bias});
     DNN_CHECK(input && weight, "conv2d: NULL operand");
     DNN_CHECK(input->ndim == 4, "conv2d: input must be (N, C, H, W)");
     DNN_CHECK(weight->ndim == 4, "conv2d: weight must be (out_C, in_C, kH, kW)");
@@ -487,6 +488,7 @@ tensor *tensor_conv2d(struct mem_pool *scratch, tensor *input, tensor *weight, t
 }
 
 tensor *tensor_avg_pool2d(struct mem_pool *scratch, const tensor *x, int k, int stride) {
+    require_device_payloads("tensor_avg_pool2d", {x});
     DNN_CHECK(x, "avg_pool2d: NULL input");
     DNN_CHECK(x->ndim == 4, "avg_pool2d: input must be (N, C, H, W)");
     DNN_CHECK(k > 0, "avg_pool2d: kernel size must be positive");

@@ -355,12 +355,14 @@ using namespace dnnb;
 extern "C" {
 
 tensor *tensor_cross_entropy(struct mem_pool *scratch, const tensor *logits, const tensor *target, int dim) {
+    require_device_payloads("tensor_cross_entropy", {logits, target});
     DNN_CHECK(logits && target, "tensor_cross_entropy: NULL argument");
     return ce_forward(scratch, logits, target, nullptr, dim);
 }
 
 tensor *tensor_cross_entropy_masked(struct mem_pool *scratch, const tensor *logits, const tensor *target,
                                     const tensor *mask, int dim) {
+    require_device_payloads("tensor_cross_entropy_masked", {logits, target, mask});
     DNN_CHECK(logits && target && mask, "tensor_cross_entropy_masked: NULL argument");
     return ce_forward(scratch, logits, target, mask, dim);
 }

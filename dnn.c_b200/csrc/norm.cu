@@ -443,6 +443,7 @@ using namespace dnnb;
 extern "C" {
 
 tensor *tensor_rms_norm(struct mem_pool *scratch, const tensor *x, const tensor *weight, float eps) {
+    require_device_payloads("tensor_rms_norm", {x, weight});
     DNN_CHECK(x, "tensor_rms_norm: x is NULL");
     DNN_CHECK(x->contiguous, "tensor_rms_norm: x must be contiguous");
     int d = x->shape[x->ndim - 1];
@@ -461,6 +462,7 @@ tensor *tensor_rms_norm(struct mem_pool *scratch, const tensor *x, const tensor 
 }
 
 tensor *tensor_layer_norm(struct mem_pool *scratch, const tensor *x, const tensor *weight, const tensor *bias, float eps) {
+    require_device_payloads("tensor_layer_norm", {x, weight, bias});
     DNN_CHECK(x, "tensor_layer_norm: x is NULL");
     DNN_CHECK(x->contiguous, "tensor_layer_norm: x must be contiguous");
     int d = x->shape[x->ndim - 1];

@@ -391,6 +391,7 @@ static void binary_backward(grad_fn *fn, tensor *go) {
 
 template <int OP>
 static tensor *binary_forward(struct mem_pool *scratch, const tensor *a, const tensor *b, const char *name) {
+    require_device_payloads(name, {a, b});
     DNN_CHECK(a && b, "binary op: NULL operand");
     int shape[DNN_MAX_DIMS];
     int nd = bcast_shape(a->ndim, a->shape, b->ndim, b->shape, shape);
@@ -433,6 +434,7 @@ static void unary_backward(grad_fn *fn, tensor *go) {
                                                    (const float *)go->data + go->offset, view_of(a), sv->op, sv->e});
 }
 static tensor *unary_forward(struct mem_pool *scratch, const tensor *t, int op, float e) {
+    require_device_payloads("unary op", {t});
     DNN_CHECK(t, "unary op: NULL input");
     tensor *out = tensor_scratch(scratch, t->ndim, t->shape, 0);
     ew_launch("unary_fwd_kernel", numel_of(t), UnF{(float *)out->data, (const float *)t->data, view_of(t), op, e});
@@ -568,6 +570,7 @@ using namespace dnnb;
 extern "C" {
 
 tensor *tensor_add(struct mem_pool *scratch, const tensor *a, const tensor *b) {
+    require_device_payloads("tensor_add", {a, b});
     DNN_CHECK(a && b, "tensor_add: NULL operand");
     int shape[DNN_MAX_DIMS];
     int nd = bcast_shape(a->ndim, a->shape, b->ndim, b->shape, shape);
@@ -596,6 +599,7 @@ tensor *tensor_add(struct mem_pool *scratch, const tensor *a, const tensor *b) {
 }
 
 tensor *tensor_cat(struct mem_pool *scratch, const tensor *a, const tensor *b, int dim) {
+    require_device_payloads("tensor_cat", {a, b});
     DNN_CHECK(a && b && a->ndim == b->ndim, "tensor_cat: ndim must match");
     int nd = a->ndim;
     if (dim < 0) dim += nd;
@@ -634,6 +638,7 @@ tensor *tensor_cat(struct mem_pool *scratch, const tensor *a, const tensor *b, i
 }
 
 tensor *tensor_relu(struct mem_pool *scratch, const tensor *t) {
+    require_device_payloads("tensor_relu", {t});
     DNN_CHECK(t, "tensor_relu: NULL input");
     tensor *out = tensor_scratch(scratch, t->ndim, t->shape, 0);
     int64_t n = numel_of(t);
@@ -655,6 +660,7 @@ tensor *tensor_relu(struct mem_pool *scratch, const tensor *t) {
 }
 
 tensor *tensor_silu(struct mem_pool *scratch, const tensor *t) {
+    require_device_payloads("tensor_silu", {t});
     DNN_CHECK(t, "tensor_silu: NULL input");
     tensor *out = tensor_scratch(scratch, t->ndim, t->shape, 0);
     int64_t n = numel_of(t);
@@ -673,6 +679,7 @@ tensor *tensor_silu(struct mem_pool *scratch, const tensor *t) {
 }
 
 tensor *tensor_swiglu(struct mem_pool *scratch, const tensor *gate, const tensor *up) {
+    require_device_payloads("tensor_swiglu", {gate, up});
     DNN_CHECK(gate && up, "tensor_swiglu: NULL operand");
     int shape[DNN_MAX_DIMS];
     int nd = bcast_shape(gate->ndim, gate->shape, up->ndim, up->shape, shape);
@@ -704,6 +711,7 @@ tensor *tensor_pow(struct mem_pool *scratch, const tensor *t, float exp) { retur
 tensor *tensor_sigmoid(struct mem_pool *scratch, const tensor *t) { return unary_forward(scratch, t, UN_SIGMOID, 0.f); }
 
 tensor *tensor_sum(struct mem_pool *scratch, const tensor *t, int dim) {
+    require_device_payloads("tensor_sum", {t});
     DNN_CHECK(t, "tensor_sum: NULL input");
     int nd = t->ndim;
     if (dim < 0) dim += nd;
@@ -726,6 +734,7 @@ tensor *tensor_sum(struct mem_pool *scratch, const tensor *t, int dim) {
 
 // mean = sum * (1/n) through tensor_mul with a one-element tensor, like the reference (src/ops_reduce.c:138-153)
 tensor *tensor_mean(struct mem_pool *scratch, const tensor *t, int dim) {
+    require_device_payloads("tensor_mean", {t});
     DNN_CHECK(t, "tensor_mean: NULL input");
     int d = dim < 0 ? dim + t->ndim : dim;
     DNN_CHECK(d >= 0 && d < t->ndim, "tensor_mean: dim out of range");
@@ -737,6 +746,7 @@ tensor *tensor_mean(struct mem_pool *scratch, const tensor *t, int dim) {
 }
 
 tensor *tensor_softmax(struct mem_pool *scratch, const tensor *t, int dim) {
+    require_device_payloads("tensor_softmax", {t});
     DNN_CHECK(t, "tensor_softmax: NULL input");
     if (dim < 0) dim += t->ndim;
     DNN_CHECK(dim >= 0 && dim < t->ndim, "tensor_softmax: dim out of range");
@@ -744,12 +754,14 @@ tensor *tensor_softmax(struct mem_pool *scratch, const tensor *t, int dim) {
 }
 
 tensor *tensor_causal_softmax(struct mem_pool *scratch, const tensor *t) {
+    require_device_payloads("tensor_causal_softmax", {t});
     DNN_CHECK(t && t->ndim >= 2, "tensor_causal_softmax: need at least 2 dims");
     DNN_CHECK(t->shape[t->ndim - 2] == t->shape[t->ndim - 1], "tensor_causal_softmax: last two dims must be equal");
     return softmax_forward(scratch, t, t->ndim - 1, t->shape[t->ndim - 1]);
 }
 
 tensor *tensor_dropout(struct mem_pool *scratch, const tensor *t, float p) {
+    require_device_payloads("tensor_dropout", {t});
     DNN_CHECK(t, "tensor_dropout: NULL input");
     DNN_CHECK(p >= 0.0f && p < 1.0f, "tensor_dropout: p must be in [0, 1)");
     if (!dnn_grad_enabled()) return (tensor *)t;              // evaluation: identity (src/ops_activation.c:1449)

@@ -330,6 +330,7 @@ using namespace dnnb;
 extern "C" {
 
 tensor *tensor_rope(struct mem_pool *scratch, tensor *x, const tensor *freqs_cos, const tensor *freqs_sin) {
+    require_device_payloads("tensor_rope", {x, freqs_cos, freqs_sin});
     DNN_CHECK(x && freqs_cos && freqs_sin, "tensor_rope: NULL argument");
     DNN_CHECK(x->contiguous && freqs_cos->contiguous && freqs_sin->contiguous, "tensor_rope: operands must be contiguous");
     DNN_CHECK(x->ndim >= 2, "tensor_rope: x must have at least 2 dims");
@@ -376,6 +377,7 @@ void tensor_rope_freqs_init(struct mem_pool *params, tensor **freqs_cos, tensor 
 }
 
 tensor *tensor_split_heads(struct mem_pool *scratch, tensor *t, int H) {
+    require_device_payloads("tensor_split_heads", {t});
     DNN_CHECK(t->ndim == 3, "split_heads: input must be 3D [B, N, H*d_k]");
     DNN_CHECK(t->contiguous, "split_heads: input must be contiguous");
     int B = t->shape[0], N = t->shape[1], D = t->shape[2];
@@ -394,6 +396,7 @@ tensor *tensor_split_heads(struct mem_pool *scratch, tensor *t, int H) {
 }
 
 tensor *tensor_merge_heads(struct mem_pool *scratch, tensor *t) {
+    require_device_payloads("tensor_merge_heads", {t});
     DNN_CHECK(t->ndim == 4, "merge_heads: input must be 4D [B, H, N, d_k]");
     DNN_CHECK(t->contiguous, "merge_heads: input must be contiguous");
     int B = t->shape[0], H = t->shape[1], N = t->shape[2], dk = t->shape[3];
@@ -410,6 +413,7 @@ tensor *tensor_merge_heads(struct mem_pool *scratch, tensor *t) {
 
 void tensor_split_qkv_heads(struct mem_pool *scratch, tensor *qkv, int H,
                             tensor **Qh_out, tensor **Kh_out, tensor **Vh_out) {
+    require_device_payloads("tensor_split_qkv_heads", {qkv});
     DNN_CHECK(qkv->ndim == 3, "split_qkv_heads: qkv must be 3D [B,N,3*H*d_k]");
     DNN_CHECK(qkv->contiguous, "split_qkv_heads: qkv must be contiguous");
     int B = qkv->shape[0], N = qkv->shape[1], D = qkv->shape[2];
@@ -433,6 +437,7 @@ void tensor_split_qkv_heads(struct mem_pool *scratch, tensor *qkv, int H,
 }
 
 tensor *tensor_embedding(struct mem_pool *scratch, const tensor *table, const tensor *ids) {
+    require_device_payloads("tensor_embedding", {table, ids});
     DNN_CHECK(table && ids, "embedding: NULL argument");
     DNN_CHECK(table->ndim == 2, "embedding: table must be 2D");
     DNN_CHECK(ids->ndim == 1, "embedding: ids must be 1D");

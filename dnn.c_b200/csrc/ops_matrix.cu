@@ -238,6 +238,7 @@ using namespace dnnb;
 extern "C" {
 
 tensor *tensor_matmul(struct mem_pool *scratch, const tensor *a, const tensor *b) {
+    require_device_payloads("tensor_matmul", {a, b});
     DNN_CHECK(a && b, "tensor_matmul: NULL operand");
     DNN_CHECK(a->ndim >= 2 && b->ndim >= 2, "tensor_matmul: need at least 2D");
     DNN_CHECK(a->shape[a->ndim - 1] == b->shape[b->ndim - 2], "tensor_matmul: inner dim mismatch");
@@ -253,6 +254,7 @@ tensor *tensor_matmul(struct mem_pool *scratch, const tensor *a, const tensor *b
 }
 
 tensor *tensor_matmul_add(struct mem_pool *scratch, const tensor *a, const tensor *b, int trans_b, const tensor *bias) {
+    require_device_payloads("tensor_matmul_add", {a, b, bias});
     DNN_CHECK(a && b && bias, "tensor_matmul_add: NULL operand");
     DNN_CHECK(a->ndim >= 2 && b->ndim >= 2, "tensor_matmul_add: need at least 2D");
     DNN_CHECK(bias->ndim == 1, "tensor_matmul_add: bias must be 1-D");

@@ -151,6 +151,28 @@ static Arena *arena_of(const mem_pool *pool, bool create) {
     return &(g_rt.arenas[pool->buffer] = a);
 }
 
+bool dev_ptr_in_arena(const void *p) {
+    const char *c = (const char *)p;
+    for (auto &kv : g_rt.arenas)
+        if (c >= kv.second.base && c < kv.second.base + kv.second.cap) return true;
+    return false;
+}
+
+void require_device_payloads(const char *op, std::initializer_list<const tensor *> ts) {
+    for (const tensor *t : ts) {
+        if (!t || !t->data || dev_ptr_in_arena(t->data)) continue;
+        cudaPointerAttributes at;
+        cudaError_t e = cudaPointerGetAttributes(&at, t->data);
+        if (e == cudaSuccess && (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged)) continue;
+        cudaGetLastError();
+        fprintf(stderr, "dnn_b200: %s: a tensor's payload (data = %p, pool = %p) is host memory.  This library computes on the GPU: "
+                        "create tensors with tensor_scratch / tensor_zeros* in a dnn.c pool and fill them with dnn_cuda_upload "
+                        "(read results with dnn_cuda_download); hand-built tensor structs around malloc'd buffers are not accepted.\n",
+                op, t->data, (void *)t->pool);
+        abort();
+    }
+}
+
 void *dev_alloc(struct mem_pool *pool, size_t bytes, bool zero) {
     Arena *a = arena_of(pool, true);
     size_t need = (bytes + 255) & ~(size_t)255;

@@ -237,6 +237,7 @@ tensor *tensor_reshape(struct mem_pool *scratch, tensor *t, int ndim, const int 
 }
 
 tensor *tensor_contiguous(struct mem_pool *scratch, tensor *t) {
+    require_device_payloads("tensor_contiguous", {t});
     return t->contiguous ? t : copy_strided(scratch, t);
 }
 tensor *tensor_flatten(struct mem_pool *scratch, tensor *t) {
