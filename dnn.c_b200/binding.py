@@ -211,6 +211,8 @@ CUDA_API = {
     "dnn_cuda_set_gemm_mode": (I, [I]),
     "dnn_cuda_get_gemm_mode": (I, []),
     "dnn_cuda_set_tf32_policy": (I, [C.c_uint, C.c_double]),
+    "dnn_cuda_set_exact_policy": (I, [C.c_double]),
+    "dnn_cuda_get_exact_policy": (C.c_double, []),
     "dnn_cuda_get_tf32_policy": (I, [C.POINTER(C.c_uint), C.POINTER(C.c_double)]),
     "dnn_cuda_graph_capture_decoder_lm_step": (VP, [PoolP, VP, TensorP, TensorP, C.POINTER(AdamW), F]),
     "dnn_cuda_graph_replay": (I, [VP, C.POINTER(C.c_float), C.POINTER(C.c_float)]),

@@ -177,6 +177,8 @@ enum { GEMM_ROLE_FORWARD = 0, GEMM_ROLE_DA = 1, GEMM_ROLE_DW = 2 };
 void gemm_set_role(int role);
 void gemm_set_policy(unsigned roles_3x, double max_flop_3x);
 void gemm_get_policy(unsigned *roles_3x, double *max_flop_3x);
+void gemm_set_exact_policy(double simt_max_flop);
+double gemm_get_exact_policy();
 void gemm_reread_env();                // the next gemm() reads DNN_CUDA_TF32_3X_SHAPES again
 
 // One-shot epilogue request for the next tensor-core GEMM on this thread: rotate (RoPE) the

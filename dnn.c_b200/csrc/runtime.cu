@@ -437,6 +437,12 @@ int dnn_cuda_set_tf32_policy(unsigned roles_3x, double max_flop_3x) {
     gemm_set_policy(roles_3x, max_flop_3x);
     return 0;
 }
+int dnn_cuda_set_exact_policy(double simt_max_flop) {
+    if (!(simt_max_flop >= 0.0)) { set_error("exact policy: simt_max_flop must be >= 0"); return -1; }
+    gemm_set_exact_policy(simt_max_flop);
+    return 0;
+}
+double dnn_cuda_get_exact_policy(void) { return gemm_get_exact_policy(); }
 int dnn_cuda_get_tf32_policy(unsigned *roles_3x, double *max_flop_3x) {
     if (!roles_3x || !max_flop_3x) return -1;
     gemm_get_policy(roles_3x, max_flop_3x);

@@ -57,16 +57,26 @@ void  dnn_cuda_host_free(void *p);
 int  dnn_cuda_set_gemm_mode(int mode);
 int  dnn_cuda_get_gemm_mode(void);
 
-/* Precision policy of TF32 mode: which GEMMs take the 3xTF32 path although the mode is TF32.
- *   roles_3x    bit 0: forward products (Y = A B), bit 1: activation gradients (dA = dY B^T),
- *               bit 2: weight gradients (dW = A^T dY) -- of matmul, matmul_add and conv2d.
- *   max_flop_3x every GEMM of at most this many FLOP (2 M N K): such products are bound by launch
- *               latency, not by the tensor core, so the extra two products cost little.
- * Independently of the policy, a GEMM with at most 64 Ki outputs and a reduction of 1024 or more
- * (the filter gradient of a small convolution) always takes the 3xTF32 path.
- * Environment: DNN_CUDA_TF32_3X_ROLES, DNN_CUDA_TF32_3X_MAX_GFLOP.  No counterpart in the reference. */
+/* Precision policy: which GEMMs leave the arithmetic of the selected mode for a more exact one.
+ * TF32 mode (dnn_cuda_set_tf32_policy):
+ *   roles_3x    GEMM kinds that take the 3xTF32 path: bit 0 forward products (Y = A B), bit 1 activation
+ *               gradients (dA = dY B^T), bit 2 weight gradients (dW = A^T dY) -- of matmul, matmul_add and
+ *               conv2d.  Default 0.  roles_3x = 3 ("strict") is what brings every parameter gradient of a
+ *               12-block transformer within 1e-3 of the reference (plain TF32: up to 1.9e-3), at about twice
+ *               the GEMM time.
+ *   max_flop_3x every GEMM of at most this many FLOP (2 M N K) takes the 3xTF32 path.  Default 4e9: such
+ *               products are bound by launch latency and memory traffic, and the small models made of them
+ *               (the MNIST-shaped CNN) are the ones TF32 rounding hurts most.
+ *   Independently, a GEMM with at most 64 Ki outputs and a reduction of 1024 or more (the filter gradient of
+ *   a small convolution) always takes the 3xTF32 path.
+ * 3xTF32 mode (dnn_cuda_set_exact_policy):
+ *   simt_max_flop  every GEMM of at most this many FLOP takes the fp32 FMA kernel.  Default 8e9.
+ * Environment: DNN_CUDA_TF32_3X_ROLES, DNN_CUDA_TF32_3X_MAX_GFLOP, DNN_CUDA_3X_SIMT_MAX_GFLOP.
+ * No counterpart in the reference. */
 int  dnn_cuda_set_tf32_policy(unsigned roles_3x, double max_flop_3x);
 int  dnn_cuda_get_tf32_policy(unsigned *roles_3x, double *max_flop_3x);
+int  dnn_cuda_set_exact_policy(double simt_max_flop);
+double dnn_cuda_get_exact_policy(void);
 
 /* Transformer blocks in TF32 mode with head size 32 or 64 run attention straight from the
  * fused QKV projection: Q, K and V are read in place from its [B,N,3,H,d] output, RoPE is

@@ -25,7 +25,7 @@ def fresh(binding, mode):
     return d
 
 
-def check_model(golden, tag, out, tol_loss, tol_grad, tol_param, lr_steps, per_tensor_slack=False):
+def check_model(golden, tag, out, tol_loss, tol_grad, tol_param, lr_steps):
     want = golden[tag + "/loss"]
     for s, (a, b) in enumerate(zip(out["loss"], want)):
         assert abs(a - b) <= tol_loss * abs(b), "%s step %d loss %.8g vs reference %.8g" % (tag, s, a, b)
@@ -34,19 +34,18 @@ def check_model(golden, tag, out, tol_loss, tol_grad, tol_param, lr_steps, per_t
             assert abs(a - b) <= tol_grad * abs(b), "%s step %d grad norm %.8g vs reference %.8g" % (tag, s, a, b)
     missing = set(golden[tag + "/grad_missing"].tolist())
     num = den = 0.0
+    worst = (0.0, "")
     for n, g in out["grads"].items():
         if n in missing:
             assert g is None, "%s: %s has a gradient here but not in the reference" % (tag, n)
             continue
         key = tag + "/grad/" + n
-        # per tensor; a short, cancelling reduction (the 288-element conv1 filter gradient
-        # sums 6272 products of mixed sign) loses more than the bar in TF32, so in that
-        # mode single tensors get 25x the bar and the bar itself applies to all
-        # parameter gradients taken together (relative L2 over their concatenation)
-        check(key, g, golden[key], golden[key + "#"], tol_grad * (25 if per_tensor_slack else 1))
+        err = check(key, g, golden[key], golden[key + "#"], tol_grad)
+        worst = max(worst, (err, n))
         stride = int(golden[key + "#"][3])
         a, b = g.reshape(-1)[::stride].astype(np.float64), golden[key].astype(np.float64)
         num += float(((a - b) ** 2).sum()); den += float((b ** 2).sum())
+    print("PARITY %s: worst parameter gradient %s %.3g, all together %.3g, bar %.1g" % (tag, worst[1], worst[0], np.sqrt(num / den), tol_grad))
     assert np.sqrt(num / den) <= tol_grad, "%s: all gradients together: relative L2 %.3g > %.1g" % (tag, np.sqrt(num / den), tol_grad)
     rel, frac = tol_param
     for n, p in out["params"].items():
@@ -57,17 +56,19 @@ def check_model(golden, tag, out, tol_loss, tol_grad, tol_param, lr_steps, per_t
         assert np.linalg.norm(a - b) <= bound, "%s: |p - p_ref| = %.3g > %.3g" % (key, np.linalg.norm(a - b), bound)
 
 
-# fp32: exact-arithmetic kernels; 3xtf32: the north-star 1e-5 bar; tf32: the 1e-3 bar.
-# Parameters after three AdamW steps get a wider bar than gradients: biases start at zero,
-# so their value is a sum of normalised updates m/(sqrt(v)+eps) and inherits the
-# gradients' relative rounding error (<= 3e-5) several times over.
-# AdamW divides by sqrt(v): an element whose gradient is near zero still moves by about
-# +-lr per step, so its update is only as stable as the SIGN of a rounding-level number.
-# Parameters are therefore compared as ||p - p_ref|| <= rel*||p_ref|| + frac*lr*steps*sqrt(n),
-# i.e. a relative part plus a fraction of the largest distance AdamW can move n elements.
-# Gradients carry the parity claim; this check catches a broken optimiser, not rounding.
-PARAM_TOL = {"fp32": (5e-5, 0.01), "3xtf32": (5e-5, 0.01), "tf32": (2e-3, 0.2)}
-MODES = [("fp32", 0, 1e-5, 3e-5), ("3xtf32", 2, 1e-5, 3e-5), ("tf32", 1, 5e-4, 2e-3)]
+# Bars (relative L2 of the loss, the gradient norm and every parameter gradient): 1e-5 in fp32 and 3xtf32 mode, 1e-3
+# in tf32 mode.  These models are small, so in tf32 mode the default precision policy runs their products as 3xTF32
+# and in 3xtf32 mode as fp32 FMA (dnn_cuda_set_tf32_policy / dnn_cuda_set_exact_policy); the plain tensor-core
+# arithmetic of each mode is held to the same bars at full size (tests/test_gpu_fullsize.py) and op by op
+# (tests/test_gpu_ops.py).
+# Parameters after the AdamW steps get a wider bar than gradients: biases start at zero, so their value is a sum of
+# normalised updates m/(sqrt(v)+eps) and inherits the gradients' relative rounding error several times over, and an
+# element whose gradient is near zero still moves by about +-lr per step, so its update is only as stable as the SIGN
+# of a rounding-level number.  Parameters are therefore compared as ||p - p_ref|| <= rel*||p_ref|| + frac*lr*steps*sqrt(n),
+# a relative part plus a fraction of the largest distance AdamW can move n elements.  Gradients carry the parity
+# claim; AdamW itself is pinned directly by the adamw cases of tests/cases.py.
+PARAM_TOL = {"fp32": (5e-5, 0.01), "3xtf32": (5e-5, 0.01), "tf32": (1e-3, 0.1)}
+MODES = [("fp32", 0, 1e-5, 1e-5), ("3xtf32", 2, 1e-5, 1e-5), ("tf32", 1, 1e-3, 1e-3)]
 
 
 @pytest.mark.parametrize("mode,code,tol_loss,tol_grad", MODES, ids=[m[0] for m in MODES])
@@ -91,12 +92,7 @@ def test_cnn_train_steps(binding, golden, mode, code, tol_loss, tol_grad):
     finally:
         d.close()
     check("cnn/logits", out["logits"], golden["cnn/logits"], golden["cnn/logits#"], tol_grad)
-    if mode == "tf32":
-        # measured 4.4e-3 over all gradients: two stacked convolutions whose filter and input
-        # gradients are short sums of mixed sign amplify TF32 rounding beyond the 2e-3 that the
-        # transformer configs meet; 3xTF32 mode (above) holds 3e-5 on the same network
-        tol_grad = 6e-3
-    check_model(golden, "cnn", out, tol_loss, tol_grad, PARAM_TOL[mode], 2 * 1e-3, per_tensor_slack=(mode == "tf32"))
+    check_model(golden, "cnn", out, tol_loss, tol_grad, PARAM_TOL[mode], 2 * 1e-3)
 
 
 @pytest.mark.parametrize("mode,code,tol_loss,tol_grad", MODES, ids=[m[0] for m in MODES])
@@ -106,7 +102,7 @@ def test_vision_lm_padded_train_steps(binding, golden, mode, code, tol_loss, tol
         out = models.run_vlm(d, steps=2)
     finally:
         d.close()
-    check_model(golden, "vlm", out, tol_loss, tol_grad, PARAM_TOL[mode], 2 * 6e-4, per_tensor_slack=(mode == "tf32"))
+    check_model(golden, "vlm", out, tol_loss, tol_grad, PARAM_TOL[mode], 2 * 6e-4)
 
 
 def test_config1_against_live_reference(binding):
@@ -125,7 +121,7 @@ def test_config1_against_live_reference(binding):
     for n in want["names"]:
         a, b = got["grads"][n], want["grads"][n]
         err = np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b.astype(np.float64))
-        assert err <= 3e-5, (n, err)
+        assert err <= 1e-5, (n, err)
 
 
 @pytest.mark.parametrize("shape", [dict(D=128, H=4, N=128, B=4), dict(D=128, H=2, N=200, B=3), dict(D=192, H=3, N=77, B=2)],
