@@ -31,7 +31,14 @@ struct AttnParams {
     int prefix;                  // 0 for causal
     float scale;
     int store;                   // bit 0/1/2: dq/dk/dv are written, not added to
+    // additive mask broadcast to [B,H,N,N] (src/attention.c:314-325): element (b,h,i,j) at mask[b*m_sb + h*m_sh + i*m_si + j*m_sj],
+    // added to the scaled score of every visible column; null when there is none
+    const float *mask;
+    int64_t m_sb, m_sh, m_si, m_sj;
 };
+__device__ __forceinline__ float mask_at(const AttnParams &p, int b, int h, int i, int j) {
+    return p.mask ? p.mask[b * p.m_sb + h * p.m_sh + i * p.m_si + j * p.m_sj] : 0.f;
+}
 
 __device__ __forceinline__ int visible_len(int i, int prefix, int nb) {
     int v = (i < prefix) ? prefix : i + 1;       // prefix == 0 gives the causal rule
@@ -128,7 +135,7 @@ __global__ void __launch_bounds__(256) attn_fwd_kernel(AttnParams p) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 int col = j0 + tx + 16 * j;
-                s[i][j] = col < vis ? s[i][j] * p.scale : -INFINITY;
+                s[i][j] = col < vis ? s[i][j] * p.scale + mask_at(p, b, h, row, col) : -INFINITY;
                 mx = fmaxf(mx, s[i][j]);
             }
             mx = half_warp_max(mx);
@@ -192,7 +199,7 @@ __global__ void attn_bwd_prep_kernel(const float *__restrict__ dout, const float
 template <int HD>
 __device__ __forceinline__ void recompute_p_ds(const AttnParams &p, const float *Qs, const float *Ks, const float *Vs,
                                                const float *dOs, const float *lse_s, const float *d_s,
-                                               int i0, int j0, int nb, int ty, int tx, float *Ps, float *dSs) {
+                                               int i0, int j0, int nb, int ty, int tx, float *Ps, float *dSs, int b, int h) {
     float s[4][4], dp[4][4];
     tile_dot<HD>(Qs, Ks, ty, tx, s);
     tile_dot<HD>(dOs, Vs, ty, tx, dp);
@@ -204,7 +211,7 @@ __device__ __forceinline__ void recompute_p_ds(const AttnParams &p, const float 
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             int col = j0 + tx + 16 * j;
-            float pe = col < vis ? expf(s[i][j] * p.scale - lse) : 0.f;
+            float pe = col < vis ? expf(s[i][j] * p.scale + mask_at(p, b, h, row, col) - lse) : 0.f;
             Ps[r * PS + tx + 16 * j] = pe;
             dSs[r * PS + tx + 16 * j] = pe * (dp[i][j] - dd) * p.scale;
         }
@@ -245,7 +252,7 @@ __global__ void __launch_bounds__(256) attn_bwd_dkv_kernel(AttnParams p) {
             d_s[threadIdx.x] = row < nb ? p.dvec[slice + row] : 0.f;
         }
         __syncthreads();
-        recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs);
+        recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs, b, h);
         __syncthreads();
         // this thread owns key rows ty+16*jj and feature columns tx+16*c
 #pragma unroll 4
@@ -311,7 +318,7 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_kernel(AttnParams p) {
         load_tile<HD>(Ks, k, j0, nb, p.d);
         load_tile<HD>(Vs, v, j0, nb, p.d);
         __syncthreads();
-        recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs);
+        recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs, b, h);
         __syncthreads();
 #pragma unroll 4
         for (int j = 0; j < TB; j++) {
@@ -374,7 +381,7 @@ void attn_backward_tc(const HeadView &q, const HeadView &k, const HeadView &v, c
 // TF32 mode runs on the tensor core (head dims 32 and 64); the FP32 and 3xTF32 modes, and
 // other head dims, run the exact kernels of this file.
 static bool use_tc(const AttnParams &p) {
-    return gemm_mode() == DNN_CUDA_GEMM_TF32 &&
+    return gemm_mode() == DNN_CUDA_GEMM_TF32 && p.mask == nullptr &&
            attn_tc_supported(p.d, packed_heads(p.q, p.H, p.N, p.d), packed_heads(p.k, p.H, p.N, p.d), packed_heads(p.v, p.H, p.N, p.d));
 }
 
@@ -427,7 +434,26 @@ static void launch_prep_v4(const float *dout, const float *o, float *dvec, int B
     LAUNCHED("attn_bwd_prep_kernel");
 }
 
-struct AttnSaved { float *lse; const int *seq_lens_dev; int mode, prefix; float scale; tensor *out; };
+struct AttnSaved { float *lse; const int *seq_lens_dev; int mode, prefix; float scale; tensor *out; tensor *mask; };
+
+// Strides of an additive mask against the coordinates (b, h, i, j).  The reference looks the mask up with
+// _bcast_off(mask, mask->ndim, {b,h,i,j}) (src/attention.c:317-323, src/broadcast.h:26-44): dimension k of the
+// mask is indexed by the k-th coordinate, dimensions of size 1 repeat.  A 4-D mask therefore broadcasts as
+// documented, while a mask of fewer dimensions is read by the LEADING coordinates (an [N,N] mask at [b][h]).
+// That lookup is kept as it is; what is added is the bounds check the reference does not have.
+static void set_mask(AttnParams &p, const tensor *mask) {
+    p.mask = nullptr; p.m_sb = p.m_sh = p.m_si = p.m_sj = 0;
+    if (!mask) return;
+    DNN_CHECK(mask->ndim >= 1 && mask->ndim <= 4, "tensor_attention: mask must have 1 to 4 dims");
+    const int want[4] = {p.B, p.H, p.N, p.N};
+    int64_t st[4] = {0, 0, 0, 0};
+    for (int k = 0; k < mask->ndim; k++) {
+        DNN_CHECK(mask->shape[k] == 1 || mask->shape[k] >= want[k], "tensor_attention: mask dimension smaller than the coordinate that indexes it");
+        st[k] = mask->shape[k] == 1 ? 0 : mask->strides[k];
+    }
+    p.mask = (const float *)mask->data + mask->offset;
+    p.m_sb = st[0]; p.m_sh = st[1]; p.m_si = st[2]; p.m_sj = st[3];
+}
 
 static void attention_backward(grad_fn *fn, tensor *go) {
     tensor *q = fn->inputs[0], *k = fn->inputs[1], *v = fn->inputs[2];
@@ -439,6 +465,7 @@ static void attention_backward(grad_fn *fn, tensor *go) {
     p.o = (float *)sv->out->data; p.lse = sv->lse; p.seq_lens = sv->seq_lens_dev;
     p.prefix = sv->mode == ATTENTION_PREFIX_LM ? sv->prefix : 0; p.scale = sv->scale;
     p.dout = (const float *)go->data;
+    set_mask(p, sv->mask);
     // Without seq_lens the kernels write every row of dq, dk and dv, so a gradient buffer
     // that nothing has written yet is stored to instead of zero-filled and added to.
     // Operands that share a buffer, or padded batches, keep the add.
@@ -623,9 +650,8 @@ tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tens
         DNN_CHECK(k->shape[i] == q->shape[i] && v->shape[i] == q->shape[i], "tensor_attention: shape mismatch");
     if (mode == ATTENTION_PREFIX_LM) DNN_CHECK(prefix_len > 0 && prefix_len <= N, "tensor_attention: prefix_len out of range");
     if (mode == ATTENTION_CAUSAL) DNN_CHECK(prefix_len == 0, "tensor_attention: prefix_len must be 0 in causal mode");
-    // The additive mask of the reference is forward-only and never differentiated
-    // (src/attention.c:315-326); the training path always passes NULL.
-    DNN_CHECK(mask == nullptr, "tensor_attention: additive masks are not supported on this path");
+    // An additive mask (src/attention.c:314-325; no model of the reference passes one) is added to the scaled scores of
+    // the visible columns.  It gets no gradient itself; with a mask the exact fp32 kernels run in every mode.
     DNN_CHECK(d <= 128, "tensor_attention: head dim above 128 is not supported");
 
     int shape[4] = {B, H, N, d};
@@ -640,6 +666,7 @@ tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tens
     p.seq_lens = seq_lens ? (const int *)dev_put(scratch, seq_lens, (size_t)B * sizeof(int)) : nullptr;
     p.prefix = mode == ATTENTION_PREFIX_LM ? prefix_len : 0;
     p.scale = 1.0f / sqrtf((float)d);
+    set_mask(p, mask);
     if (use_tc(p)) attn_forward_tc(packed_heads(p.q, H, N, d), packed_heads(p.k, H, N, d), packed_heads(p.v, H, N, d),
                                    packed_heads(p.o, H, N, d), p.lse, p.seq_lens, B, H, N, d, p.prefix, p.scale);
     else attn_forward_fp32(p);
@@ -649,7 +676,7 @@ tensor *tensor_attention_ex(struct mem_pool *scratch, tensor *q, tensor *k, tens
         fn->inputs[0] = q; fn->inputs[1] = k; fn->inputs[2] = v;
         AttnSaved *sv = host_alloc_t<AttnSaved>(scratch);
         sv->lse = p.lse; sv->seq_lens_dev = p.seq_lens; sv->mode = (int)mode; sv->prefix = prefix_len;
-        sv->scale = p.scale; sv->out = out;
+        sv->scale = p.scale; sv->out = out; sv->mask = mask;
         fn->saved_tensors[0] = (tensor *)sv;
     }
     return out;

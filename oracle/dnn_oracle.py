@@ -195,8 +195,19 @@ def visible_len(mode, i, prefix_len, n_b):
     return min(v, n_b)
 
 
-def attention(q, k, v, mode, prefix_len, seq_lens, gout):
+def attention(q, k, v, mode, prefix_len, seq_lens, gout, mask=None):
+    """mask: additive, added to the scaled scores of the visible columns (src/attention.c:314-325); it gets no
+    gradient.  The reference looks it up with _bcast_off(mask, mask->ndim, {b,h,i,j}) (src/broadcast.h:26-44), i.e.
+    dimension k of the mask is indexed by the k-th of (b, h, i, j): a 4-D mask broadcasts as documented, a mask of
+    fewer dimensions is read by the LEADING coordinates ([N,N] is read at [b][h]).  Kept as it is."""
     B, H, N, d = q.shape
+    mfull = None
+    if mask is not None:
+        m = np.asarray(mask, F64)
+        ext = (B, H, N, N)
+        idx = np.ix_(*[np.zeros(ext[k], int) if m.shape[k] == 1 else np.arange(ext[k]) for k in range(m.ndim)])
+        sub = m[idx]                                          # shape ext[:ndim]
+        mfull = np.broadcast_to(sub.reshape(sub.shape + (1,) * (4 - m.ndim)), ext)
     scale = 1.0 / np.sqrt(np.float32(d)).astype(F64)
     o = np.zeros(q.shape, F64)
     dq, dk, dv = (np.zeros(q.shape, F64) for _ in range(3))
@@ -207,6 +218,8 @@ def attention(q, k, v, mode, prefix_len, seq_lens, gout):
         for h in range(H):
             Q, K, V = (t[b, h, :nb].astype(F64) for t in (q, k, v))
             S = scale * (Q @ K.T)
+            if mfull is not None:
+                S = S + mfull[b, h, :nb, :nb]
             S = np.where(allow, S, -np.inf)
             P = np.exp(S - S.max(-1, keepdims=True))
             P = np.where(allow, P, 0.0)

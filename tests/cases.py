@@ -410,6 +410,29 @@ for B, H, N, d, mode, prefix, lens in ATT:
             return dict(o=o, dq=dq, dk=dk, dv=dv)
 
 
+# 4-D masks broadcast over heads / batch; the [40,40] one is read at [b][h] by the reference (see O.attention)
+for B, H, N, d, mshape in ((2, 3, 40, 16, (40, 40)), (2, 2, 70, 32, (2, 1, 70, 70)), (1, 2, 33, 64, (1, 2, 33, 33)), (2, 2, 20, 8, (1, 1, 1, 20))):
+    @case("attention+mask[B%d H%d N%d d%d mask%s]" % (B, H, N, d, list(mshape)), tol=3e-5)
+    class _:
+        @staticmethod
+        def make(rng, B=B, H=H, N=N, d=d, mshape=mshape):
+            return dict(q=_r(rng, B, H, N, d), k=_r(rng, B, H, N, d), v=_r(rng, B, H, N, d), g=_r(rng, B, H, N, d),
+                        mask=_r(rng, *mshape, scale=1.5))
+
+        @staticmethod
+        def run(dnn, i):
+            q, k, v = (dnn.tensor(i[n], dnn.scratch, True) for n in "qkv")
+            o = dnn.lib.tensor_attention(dnn.scratch, q, k, v, dnn.tensor(i["mask"], dnn.scratch))
+            dnn.backward_from(o, i["g"])
+            dq, dk, dv = _grads(dnn, q, k, v)
+            return dict(o=dnn.download(o), dq=dq, dk=dk, dv=dv)
+
+        @staticmethod
+        def oracle(i):
+            o, dq, dk, dv = O.attention(i["q"], i["k"], i["v"], 0, 0, None, i["g"], mask=i["mask"])
+            return dict(o=o, dq=dq, dk=dk, dv=dv)
+
+
 # ── rope / head layout / embedding ────────────────────────────────────────
 for shape in ((2, 3, 17, 32), (1, 1, 5, 6), (2, 12, 64, 64)):
     @case("rope%s" % list(shape))
