@@ -173,7 +173,7 @@ struct GemmArgs {
 };
 void gemm(const GemmArgs &g);          // dispatches on gemm_mode(), the precision policy and layout
 // Role of the next gemm() calls of this thread, for the precision policy (dnn_cuda_set_tf32_policy).
-enum { GEMM_ROLE_FORWARD = 0, GEMM_ROLE_DA = 1, GEMM_ROLE_DW = 2 };
+enum { GEMM_ROLE_FORWARD = 0, GEMM_ROLE_DA = 1, GEMM_ROLE_DW = 2, GEMM_ROLE_CONV = 4 /* flag: the product of a convolution */ };
 void gemm_set_role(int role);
 void gemm_set_policy(unsigned roles_3x, double max_flop_3x);
 void gemm_get_policy(unsigned *roles_3x, double *max_flop_3x);

@@ -288,7 +288,7 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
         float *dwp = padded ? dev_alloc_t<float>(fn->pool, (size_t)g.out_C * Kp) : nullptr;
         a.C = padded ? dwp : wg + weight->offset; a.c_rs = wpitch; a.c_cs = 1; a.c_bs = 0;
         a.bias = nullptr; a.M = g.out_C; a.N = g.K; a.K = g.M; a.batch = 1; a.accumulate = !padded;
-        gemm_set_role(GEMM_ROLE_DW);
+        gemm_set_role(GEMM_ROLE_DW | GEMM_ROLE_CONV);
         gemm(a);
         gemm_set_role(GEMM_ROLE_FORWARD);
         if (padded) {
@@ -303,7 +303,7 @@ static void conv2d_backward(grad_fn *fn, tensor *go) {
         a.B = g_mc; a.b_rs = 1; a.b_cs = g.out_C; a.b_bs = 0;
         a.C = dcol; a.c_rs = g.M; a.c_cs = 1; a.c_bs = 0;
         a.bias = nullptr; a.M = g.K; a.N = g.M; a.K = g.out_C; a.batch = 1; a.accumulate = false;
-        gemm_set_role(GEMM_ROLE_DA);
+        gemm_set_role(GEMM_ROLE_DA | GEMM_ROLE_CONV);
         gemm(a);
         gemm_set_role(GEMM_ROLE_FORWARD);
         run_col2im(dcol, xg + input->offset, g, acc_x);
@@ -471,7 +471,9 @@ tensor *tensor_conv2d(struct mem_pool *scratch, tensor *input, tensor *weight, t
     a.C = mc; a.c_rs = g.out_C; a.c_cs = 1; a.c_bs = 0;
     a.bias = bias ? (const float *)bias->data + bias->offset : nullptr;
     a.M = g.M; a.N = g.out_C; a.K = g.K; a.batch = 1; a.accumulate = false;
+    gemm_set_role(GEMM_ROLE_FORWARD | GEMM_ROLE_CONV);
     gemm(a);
+    gemm_set_role(GEMM_ROLE_FORWARD);
     if (nchw) {
         run_permute<true>((float *)out->data, mc, g.N, g.out_C, g.H_out * g.W_out);
     }

@@ -92,7 +92,7 @@ void gemm_simt(const GemmArgs &g) {
 static thread_local int g_role = GEMM_ROLE_FORWARD;
 void gemm_set_role(int role) { g_role = role; }
 static unsigned g_roles_3x = 0;
-static double g_max_flop_3x = 4e9;          // TF32 mode: products of at most this many FLOP take the 3xTF32 path
+static double g_max_flop_3x = 4e9;          // TF32 mode: CONVOLUTION products of at most this many FLOP take the 3xTF32 path
 static double g_simt_max_flop = 8e9;        // 3xTF32 mode: products of at most this many FLOP take the fp32 FMA kernel
 static bool g_policy_env_read = false;
 void gemm_set_policy(unsigned roles_3x, double max_flop_3x) { g_roles_3x = roles_3x; g_max_flop_3x = max_flop_3x; g_policy_env_read = true; }
@@ -130,20 +130,25 @@ void gemm(const GemmArgs &g) {
         if (const char *e = getenv("DNN_CUDA_3X_SIMT_MAX_GFLOP")) g_simt_max_flop = atof(e) * 1e9;
     }
     if (!g_shapes_read) read_shape_rules();
-    bool by_shape = false;
-    for (const ShapeRule &r : g_shape_rules) if (r.role == g_role && r.N == g.N && r.K == g.K) by_shape = true;
-    // Precision policy.  Small products are bound by launch latency and memory, not by the tensor core, and the
-    // models made of them (the MNIST-shaped CNN: gradients that are what is left after 512 per-sample gradients
-    // cancel) are the ones that TF32 rounding hurts most: measured 1.7e-2 on the CNN's filter gradients in plain
-    // TF32, 2.9e-4 with 3xTF32 products.  So in TF32 mode products of at most 4 GFLOP take the 3xTF32 path, and in
-    // 3xTF32 mode products of at most 8 GFLOP take the fp32 FMA kernel: 3xTF32 leaves about 5e-7 per element
-    // (operand remainders rounded to TF32, the small x small term dropped), which that same cancellation amplifies
-    // past 1e-5.  A long reduction into a small output (a filter gradient) takes 3xTF32 whatever its size.
-    // dnn_cuda_set_tf32_policy / dnn_cuda_set_exact_policy change the thresholds.
+    // Precision policy.
+    // TF32 mode: a convolution lowered to a GEMM has a short reduction (C*k*k = 9 .. 288) or a narrow output (32 .. 64
+    // channels), so it uses a fraction of the tensor core and is bound by the traffic of its column matrix: two more
+    // products cost little.  And the gradients of a CNN are what TF32 rounding hurts most -- with random labels and
+    // fresh weights they are what is left after 512 per-sample gradients cancel (measured on the MNIST-shaped CNN:
+    // 1.7e-2 on the filter gradients in plain TF32, 2.9e-4 with 3xTF32 products).  So convolution GEMMs of at most
+    // 4 GFLOP take the 3xTF32 path; so does any GEMM with a long reduction into a small output (a filter gradient),
+    // and whatever dnn_cuda_set_tf32_policy names by role.
+    // 3xTF32 mode: products of at most 8 GFLOP take the fp32 FMA kernel -- 3xTF32 leaves about 5e-7 per element
+    // (operand remainders rounded to TF32, the small x small term dropped), which small models whose gradients cancel
+    // heavily amplify past 1e-5.
     const double flop = 2.0 * g.M * g.N * g.K * (g.batch > 0 ? g.batch : 1);
     if (mode == DNN_CUDA_GEMM_3XTF32 && flop <= g_simt_max_flop) { gemm_simt(g); return; }
+    const int role = g_role & 3;
+    const bool conv = (g_role & GEMM_ROLE_CONV) != 0;
     bool small_long = (int64_t)g.M * g.N <= 65536 && g.K >= 1024;
-    bool by_policy = ((g_roles_3x >> g_role) & 1u) || flop <= g_max_flop_3x;
+    bool by_policy = ((g_roles_3x >> role) & 1u) || (conv && flop <= g_max_flop_3x);
+    bool by_shape = false;
+    for (const ShapeRule &r : g_shape_rules) if (r.role == role && r.N == g.N && r.K == g.K) by_shape = true;
     gemm_tc(g, mode == DNN_CUDA_GEMM_3XTF32 || small_long || by_policy || by_shape);
 }
 

@@ -625,7 +625,7 @@ void gemm_tc(const GemmArgs &in, bool split3) {
     t.A = Ab; t.B = Bs; run_tc(t);
     static int chain = -1;
     if (chain < 0) { const char *e = getenv("DNN_CUDA_3X_CHAIN_KB"); chain = e ? atoi(e) : 16; }
-    g_chain_kb = chain;
+    g_chain_kb = gemm_mode() == DNN_CUDA_GEMM_3XTF32 ? chain : 0;      // only the exact mode is after the last 1e-5
     t.A = Ab; t.B = Bb; t.bias = g.bias; run_tc(t);
     g_chain_kb = 0;
 }

@@ -17,6 +17,7 @@ namespace dnnb {
 struct Arena {
     char  *base = nullptr;
     size_t cap = 0, off = 0, peak = 0;
+    size_t born_at = 0;                             // host offset of the pool when the arena was created (device offset 0)
     std::vector<std::pair<size_t, size_t>> marks;   // (host offset, device offset)
 };
 
@@ -143,6 +144,7 @@ static Arena *arena_of(const mem_pool *pool, bool create) {
     stream();   // make sure the device is initialised (aborts without one)
     Arena a;
     a.cap = pool->capacity;
+    a.born_at = pool->offset;
     cudaError_t e = cudaMalloc((void **)&a.base, a.cap ? a.cap : 256);
     if (e != cudaSuccess) {
         fprintf(stderr, "dnn_b200: cannot reserve %zu bytes of device memory for a pool\n", a.cap);
@@ -234,7 +236,7 @@ void mem_pool_reset(mem_pool *pool) {
     grad_settle_all_deferred();
     pool->offset = 0;
     Arena *a = arena_of(pool, false);
-    if (a) { a->off = 0; a->marks.clear(); }
+    if (a) { a->off = 0; a->born_at = 0; a->marks.clear(); }
 }
 
 size_t mem_pool_mark(mem_pool *pool) {
@@ -252,7 +254,8 @@ void mem_pool_release(mem_pool *pool, size_t mark) {
     if (!a->marks.empty() && a->marks.back().first == mark) {
         a->off = a->marks.back().second;
         a->marks.pop_back();
-    } else if (mark == 0) {
+    } else if (mark <= a->born_at) {
+        // a mark taken before the pool had a device arena (nothing was on the device yet): everything goes
         a->off = 0;
     }
 }

@@ -64,9 +64,10 @@ int  dnn_cuda_get_gemm_mode(void);
  *               conv2d.  Default 0.  roles_3x = 3 ("strict") is what brings every parameter gradient of a
  *               12-block transformer within 1e-3 of the reference (plain TF32: up to 1.9e-3), at about twice
  *               the GEMM time.
- *   max_flop_3x every GEMM of at most this many FLOP (2 M N K) takes the 3xTF32 path.  Default 4e9: such
- *               products are bound by launch latency and memory traffic, and the small models made of them
- *               (the MNIST-shaped CNN) are the ones TF32 rounding hurts most.
+ *   max_flop_3x every GEMM of a CONVOLUTION (forward, input gradient, filter gradient) of at most this many FLOP
+ *               (2 M N K) takes the 3xTF32 path.  Default 4e9: with reductions of 9 .. 288 and 32 .. 64 output
+ *               channels these products use a fraction of the tensor core and are bound by the traffic of the
+ *               column matrix, and a CNN's gradients are the ones TF32 rounding hurts most.
  *   Independently, a GEMM with at most 64 Ki outputs and a reduction of 1024 or more (the filter gradient of
  *   a small convolution) always takes the 3xTF32 path.
  * 3xTF32 mode (dnn_cuda_set_exact_policy):

@@ -67,3 +67,24 @@ def test_vision_lm_generated_tokens_equal_the_reference(binding, case, mode):
         assert got[:len(prompt)] == want[:len(prompt)] and len(got) <= len(prompt) + max_new
         if temp == 0.0 and name != "vlm-greedy-nocache":
             assert got == want
+
+
+def test_generate_gives_back_the_device_memory_of_its_caches(binding):
+    """decoder_lm_generate marks the data pool, builds its KV caches there and releases the mark
+    (src/gpt.c:220-421).  With a fresh data pool the mark is taken BEFORE the pool owns any device memory
+    (the output buffer is a host allocation); the release must still return the caches' device memory."""
+    import ctypes as C
+    cfg = dict(models.lm_config("tiny"))
+    d = binding.Dnn(binding.B200_LIB, params_mb=64, scratch_mb=256, data_mb=64)
+    lib = d.lib
+    lm = lib.decoder_lm_create(d.params, cfg["V"], cfg["D"], cfg["L"], cfg["H"], cfg["D"] // cfg["H"], cfg["F"])
+    lib.decoder_lm_enable_rope(d.params, lm, 32, 10000.0)
+    models.seeded_weights(d, lm, models.O.lm_param_names(cfg["L"]), 5, std=0.3)
+    ids = d.tensor(np.array([[3, 17, 42, 5]], np.int32), d.scratch)          # prompt NOT in the data pool
+    assert lib.dnn_cuda_pool_device_used(d.data) == 0
+    n = C.c_int(0)
+    out = lib.decoder_lm_generate(d.scratch, d.data, lm, ids, 6, 0.0, 1, C.byref(n))
+    assert n.value == 10 and out
+    d.sync()
+    assert lib.dnn_cuda_pool_device_used(d.data) == 0, "the KV caches stayed allocated on the device"
+    d.close()
