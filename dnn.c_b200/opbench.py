@@ -115,8 +115,8 @@ class Bench:
 class Args:
     """What run_ops needs from the command line: small (reduced batch), shapes (matmul_shapes / step_graph variant), iters."""
 
-    def __init__(self, small=False, shapes="", iters=10):
-        self.small, self.shapes, self.iters = small, shapes, iters
+    def __init__(self, small=False, shapes="", iters=10, rows=0, batch=0):
+        self.small, self.shapes, self.iters, self.rows, self.batch = small, shapes, iters, rows, batch
 
 
 def main():
@@ -127,6 +127,8 @@ def main():
     ap.add_argument("--gemm", default="tf32", choices=["tf32", "3xtf32", "fp32"])
     ap.add_argument("--pools-mb", default="8192,24576", help="params,scratch arena sizes (small arenas keep profiler captures fast)")
     ap.add_argument("--shapes", default="", help="matmul_shapes only: indices of the shapes to run, e.g. 0,1,2,3")
+    ap.add_argument("--rows", type=int, default=0, help="rows of the row-wise operators instead of 8192 (65536 makes every tensor larger than L2)")
+    ap.add_argument("--batch", type=int, default=0, help="cnn_step / cnn_ops: images per batch instead of 512")
     args = ap.parse_args()
     B = load_binding()
     pm, sm = (int(x) for x in args.pools_mb.split(","))
@@ -140,7 +142,7 @@ def run_ops(b, ops, args):
     """Runs the named workloads on the Bench `b`; every result is appended to b.rows (and printed when b.echo)."""
     B = b.B
     lib, d, rng = b.lib, b.d, b.rng
-    R = 1024 if args.small else 8192
+    R = args.rows if args.rows else (1024 if args.small else 8192)
     Bt = 2 if args.small else 8
 
     def want(n):
@@ -156,6 +158,32 @@ def run_ops(b, ops, args):
         b.run("layer_norm", lambda: dict(x=b.dev(randn(R, 768), True), w=b.dev(np.ones(768, np.float32), True),
                                          bb=b.dev(np.zeros(768, np.float32), True)),
               lambda i: lib.tensor_layer_norm(d.scratch, i["x"], i["w"], i["bb"], 1e-5), (R, 768), 8 * R * 768, 16 * R * 768, "hbm")
+    if "relu" in ops or "silu" in ops or "add" in ops:            # element-wise passes of the models, at [R, 2048]
+        n = R * 2048
+        if "relu" in ops:
+            b.run("relu", lambda: dict(x=b.dev(randn(R, 2048), True)), lambda i: lib.tensor_relu(d.scratch, i["x"]), (R, 2048), 8 * n, 12 * n, "hbm")
+        if "silu" in ops:
+            b.run("silu", lambda: dict(x=b.dev(randn(R, 2048), True)), lambda i: lib.tensor_silu(d.scratch, i["x"]), (R, 2048), 8 * n, 12 * n, "hbm")
+        if "add" in ops:
+            b.run("add", lambda: dict(x=b.dev(randn(R, 2048), True), y=b.dev(randn(R, 2048), True)),
+                  lambda i: lib.tensor_add(d.scratch, i["x"], i["y"]), (R, 2048), 12 * n, 12 * n, "hbm")
+    if "embedding" in ops:
+        V, D = 32000, 768
+        b.run("embedding", lambda: dict(t=b.dev(randn(V, D, scale=0.02), True), ids=b.dev(rng.integers(0, V, size=2 * R).astype(np.int32))),
+              lambda i: lib.tensor_embedding(d.scratch, i["t"], i["ids"]), (2 * R, D), 8 * 2 * R * D, 8 * 2 * R * D, "hbm")
+    if "cnn_ops" in ops:
+        # the convolution and pooling operators of BASELINE config 3 one by one: conv 3x3 (32 -> 64) on [N,32,14,14]
+        # (im2col, GEMM, permute forward; permute, two GEMMs, col2im backward) and avg_pool 2x2 on [N,32,28,28]
+        Nb = args.batch if args.batch else 512
+        w = b.dev((rng.random((64, 32, 3, 3), dtype=np.float32) - 0.5) * 0.1, True)
+        bias = b.dev(np.zeros(64, np.float32), True)
+        n_in, n_out, col = Nb * 32 * 14 * 14, Nb * 64 * 14 * 14, 288 * Nb * 196
+        b.run("conv2d_3x3_32to64", lambda: dict(x=b.dev(randn(Nb, 32, 14, 14), True), _zero=[w, bias]),
+              lambda i: lib.tensor_conv2d(d.scratch, i["x"], w, bias, 1, 1), (Nb, 64, 14, 14),
+              4.0 * (n_in + 2 * col + 2 * n_out), 4.0 * (2 * n_out + 3 * col + n_in), "hbm")
+        n_p = Nb * 32 * 28 * 28
+        b.run("avg_pool2d_2x2", lambda: dict(x=b.dev(randn(Nb, 32, 28, 28), True)),
+              lambda i: lib.tensor_avg_pool2d(d.scratch, i["x"], 2, 2), (Nb, 32, 14, 14), 5.0 * n_p, 5.0 * n_p, "hbm")
     if want("swiglu"):
         n = R * 2048
         b.run("swiglu", lambda: dict(g=b.dev(randn(R, 2048), True), u=b.dev(randn(R, 2048), True)),
@@ -248,7 +276,7 @@ def run_ops(b, ops, args):
     if "cnn_step" in ops:
         # BASELINE config 3: 512 images 1x28x28, conv 3x3 (1->32) + pool, conv 3x3 (32->64) + pool, 3136->128->10,
         # cross entropy, backward, AdamW; wall time per step with the loss read back
-        Bsz = 64 if args.small else 512
+        Bsz = args.batch if args.batch else (64 if args.small else 512)
         lib.dnn_seed(2)
         c1, c2 = lib.conv2d_create(d.params, 1, 32, 3, 1, 1), lib.conv2d_create(d.params, 32, 64, 3, 1, 1)
         f1, f2 = lib.linear_create(d.params, 3136, 128), lib.linear_create(d.params, 128, 10)

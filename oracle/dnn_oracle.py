@@ -646,39 +646,49 @@ def vlm_loss_and_grads(P, images, input_ids, target_ids, loss_mask, text_lens, n
 CNN_PARAM_NAMES = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
 
 
-def cnn_loss_and_grads(P, x, labels):
+def cnn_loss_and_grads(P, x, labels, relu_on=None):
     """conv3x3(1->32) relu avgpool2 conv3x3(32->64) relu avgpool2 linear(3136->128) relu linear(128->10),
     cross entropy; composed from the operator restatements above (float64 inside every operator, float32
-    between operators, as the library stores its activations).  x: [B, 784] or [B,1,28,28]."""
+    between operators, as the library stores its activations).  x: [B, 784] or [B,1,28,28].
+    relu_on: optional {"c1" | "c2" | "h1": bool array} -- which units of a ReLU are on, used in place of
+    (pre-activation > 0) in forward and backward.  A ReLU is discontinuous in its derivative at zero, so two
+    correct fp32 implementations may decide a unit whose pre-activation is zero to within rounding differently;
+    a checker passes the decisions of the implementation under test for exactly those units.
+    Returns (loss, grads, logits, pre) with pre = the three pre-activation arrays."""
     n = x.shape[0]
     x = x.reshape(n, 1, 28, 28).astype(np.float32)
-    z = lambda a: np.zeros(a.shape, np.float32)
+
+    def on(name, pre):
+        return (pre > 0) if relu_on is None or name not in relu_on else np.asarray(relu_on[name], bool).reshape(pre.shape)
 
     def fwd_conv(inp, w, b):
         oc = w.shape[0]
         return conv2d(inp, w, b, 1, 1, np.zeros((inp.shape[0], oc, inp.shape[2], inp.shape[3]), np.float32))[0]
     c1 = fwd_conv(x, P["conv1.weight"], P["conv1.bias"])
-    r1 = relu(c1, z(c1))[0]
+    m1 = on("c1", c1)
+    r1 = np.where(m1, c1, np.float32(0))
     p1 = avg_pool2d(r1, 2, 2, np.zeros((n, 32, 14, 14), np.float32))[0]
     c2 = fwd_conv(p1, P["conv2.weight"], P["conv2.bias"])
-    r2 = relu(c2, z(c2))[0]
+    m2 = on("c2", c2)
+    r2 = np.where(m2, c2, np.float32(0))
     p2 = avg_pool2d(r2, 2, 2, np.zeros((n, 64, 7, 7), np.float32))[0]
     flat = p2.reshape(n, 3136)
     h1 = matmul_add(flat, P["fc1.weight"], 0, P["fc1.bias"], np.zeros((n, 128), np.float32))[0]
-    a1 = relu(h1, z(h1))[0]
+    m3 = on("h1", h1)
+    a1 = np.where(m3, h1, np.float32(0))
     logits = matmul_add(a1, P["fc2.weight"], 0, P["fc2.bias"], np.zeros((n, 10), np.float32))[0]
     loss, dlogits = cross_entropy(logits, labels)
     G = {}
     _, da1, G["fc2.weight"], G["fc2.bias"] = matmul_add(a1, P["fc2.weight"], 0, P["fc2.bias"], dlogits)
-    dh1 = relu(h1, da1)[1]
+    dh1 = np.where(m3, da1, np.float32(0))
     _, dflat, G["fc1.weight"], G["fc1.bias"] = matmul_add(flat, P["fc1.weight"], 0, P["fc1.bias"], dh1)
     dr2 = avg_pool2d(r2, 2, 2, dflat.reshape(n, 64, 7, 7))[1]
-    dc2 = relu(c2, dr2)[1]
+    dc2 = np.where(m2, dr2, np.float32(0))
     _, dp1, G["conv2.weight"], G["conv2.bias"] = conv2d(p1, P["conv2.weight"], P["conv2.bias"], 1, 1, dc2)
     dr1 = avg_pool2d(r1, 2, 2, dp1)[1]
-    dc1 = relu(c1, dr1)[1]
+    dc1 = np.where(m1, dr1, np.float32(0))
     _, _, G["conv1.weight"], G["conv1.bias"] = conv2d(x, P["conv1.weight"], P["conv1.bias"], 1, 1, dc1)
-    return np.float32(loss), G, logits
+    return np.float32(loss), G, logits, {"c1": c1, "c2": c2, "h1": h1}
 
 
 # ── padded vision-LM batch assembly (src/imagenet_vlm.c:31-46, 598-647) ───

@@ -150,7 +150,7 @@ def cnn_values(batch, seed=2):
     return P, x_np, y_np
 
 
-def run_cnn(dnn, batch=8, steps=2, seed=2):
+def run_cnn(dnn, batch=8, steps=2, seed=2, want_relu=False):
     lib = dnn.lib
     c1 = lib.conv2d_create(dnn.params, 1, 32, 3, 1, 1)
     c2 = lib.conv2d_create(dnn.params, 32, 64, 3, 1, 1)
@@ -170,17 +170,19 @@ def run_cnn(dnn, batch=8, steps=2, seed=2):
         x = dnn.tensor(x_np, dnn.data)
         y = dnn.tensor(y_np, dnn.data)
         h = lib.tensor_reshape(dnn.scratch, x, 4, B.ints([batch, 1, 28, 28]))
-        h = lib.tensor_avg_pool2d(dnn.scratch, lib.tensor_relu(dnn.scratch, lib.conv2d_forward(dnn.scratch, c1, h)), 2, 2)
-        h = lib.tensor_avg_pool2d(dnn.scratch, lib.tensor_relu(dnn.scratch, lib.conv2d_forward(dnn.scratch, c2, h)), 2, 2)
-        h = lib.tensor_reshape(dnn.scratch, h, 2, B.ints([batch, 3136]))
-        h = lib.tensor_relu(dnn.scratch, lib.linear_forward(dnn.scratch, f1, h))
-        logits = lib.linear_forward(dnn.scratch, f2, h)
+        r1 = lib.tensor_relu(dnn.scratch, lib.conv2d_forward(dnn.scratch, c1, h))
+        r2 = lib.tensor_relu(dnn.scratch, lib.conv2d_forward(dnn.scratch, c2, lib.tensor_avg_pool2d(dnn.scratch, r1, 2, 2)))
+        h = lib.tensor_reshape(dnn.scratch, lib.tensor_avg_pool2d(dnn.scratch, r2, 2, 2), 2, B.ints([batch, 3136]))
+        r3 = lib.tensor_relu(dnn.scratch, lib.linear_forward(dnn.scratch, f1, h))
+        logits = lib.linear_forward(dnn.scratch, f2, r3)
         loss = lib.tensor_cross_entropy(dnn.scratch, logits, y, 1)
         lib.dnn_backward(dnn.scratch, loss)
         out["loss"].append(dnn.scalar(loss))
         if s == 0:
             out["logits"] = dnn.download(logits)
             out["grads"] = {n: dnn.download_grad(t) for n, t in zip(CNN_NAMES, params)}
+            if want_relu:                   # which units of the three ReLUs are on (their outputs are positive)
+                out["relu_on"] = {"c1": dnn.download(r1) > 0, "c2": dnn.download(r2) > 0, "h1": dnn.download(r3) > 0}
         lib.adamw_step(opt)
         lib.adamw_zero_grad(opt)
         dnn.reset_step()

@@ -83,7 +83,7 @@ def test_oracle_cnn_step_matches_reference(model_golden, tag, batch):
     gradients, which are serial fp32 sums of up to 401 408 cancelling products in the reference) is the
     reference's own rounding noise: the floor below which a comparison with its vectors says nothing."""
     P, x, y = models.cnn_values(batch)
-    loss, G, logits = O.cnn_loss_and_grads(P, x, y)
+    loss, G, logits, _ = O.cnn_loss_and_grads(P, x, y)
     assert abs(loss - model_golden[tag + "/loss"][0]) <= 2e-6 * abs(loss)
     if tag == "cnn":
         check("cnn/logits", logits, model_golden["cnn/logits"], model_golden["cnn/logits#"], 2e-5)
