@@ -126,6 +126,7 @@ struct Overlap {
     std::vector<int> remaining;                                // parameters not yet final, per bucket
     std::vector<char> launched;
     std::vector<std::pair<tensor *, std::vector<int>>> owners; // parameter -> buckets it touches
+    std::vector<tensor *> all_params;
     int rc = 0;
 };
 static Overlap g_ov;
@@ -165,12 +166,15 @@ bool dp_overlap_begin(tensor **params, int n_params) {
     // which costs as much as it hides (measured on 2 GPUs: 37.7 ms overlapped, 37.4 ms in sequence).
     const char *ov = getenv("DNN_CUDA_DP_OVERLAP");
     if (!ov || ov[0] != '1') return false;
+    // Parameters that own a gradient buffer take part.  On the first step none does (the buffers are allocated
+    // during backward): the exchange then runs after backward.  A parameter outside the graph (img_proj.* of the
+    // vision LM fed with images) never gets one and is skipped here as it is by AdamW; one that gets its first
+    // buffer during THIS backward is exchanged after backward (dp_overlap_finish).
     std::vector<Span> grads;
-    for (int i = 0; i < n_params; i++) {
-        if (!params[i]->grad) return false;                  // first step: buffers are allocated during backward
-        grads.push_back(Span{(char *)params[i]->grad, (size_t)numel_of(params[i]) * 4});
-    }
+    for (int i = 0; i < n_params; i++)
+        if (params[i]->grad) grads.push_back(Span{(char *)params[i]->grad, (size_t)numel_of(params[i]) * 4});
     if (grads.empty()) return false;
+    g_ov.all_params.assign(params, params + n_params);
     if (!g_ov.comm) {
         CUDA_OK(cudaStreamCreateWithFlags(&g_ov.comm, cudaStreamNonBlocking));
         CUDA_OK(cudaEventCreateWithFlags(&g_ov.done, cudaEventDisableTiming));
@@ -183,6 +187,7 @@ bool dp_overlap_begin(tensor **params, int n_params) {
     g_ov.owners.clear();
     g_ov.rc = 0;
     for (int i = 0; i < n_params; i++) {
+        if (!params[i]->grad) continue;
         char *lo = (char *)params[i]->grad, *hi = lo + (size_t)numel_of(params[i]) * 4;
         std::vector<int> touch;
         for (int b = 0; b < nb; b++) {
@@ -205,6 +210,15 @@ int dp_overlap_finish() {
     CUDA_OK(cudaEventRecord(g_ov.done, g_ov.comm));
     CUDA_OK(cudaStreamWaitEvent(stream(), g_ov.done, 0));
     if (g_ov.rc) return g_ov.rc;
+    // gradients that were allocated during this backward were not in the plan: exchange them now
+    std::vector<tensor *> late;
+    for (tensor *t : g_ov.all_params) {
+        if (!t->grad) continue;
+        bool planned = false;
+        for (auto &o : g_ov.owners) if (o.first == t) { planned = true; break; }
+        if (!planned) late.push_back(t);
+    }
+    if (!late.empty()) { int rc = dnn_cuda_dp_allreduce_grads(late.data(), (int)late.size()); if (rc) return rc; }
     ncclResult_t async = ncclSuccess;
     ncclResult_t r = g_nccl.CommGetAsyncError(g_comm, &async);
     if (r != ncclSuccess || async != ncclSuccess) return nccl_fail(r != ncclSuccess ? r : async, "ncclCommGetAsyncError");
