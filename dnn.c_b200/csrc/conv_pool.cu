@@ -22,103 +22,106 @@ struct ConvGeom { int N, C, H, W, out_C, kH, kW, stride, pad, H_out, W_out, M, K
 
 // col[k][m], k = (c, kh, kw), m = (n, oh, ow).  Row k of the column matrix is, image by image, a shifted
 // (and strided) copy of one input plane, so the index arithmetic is split by what it depends on:
-//   blockIdx.y = k            -> (c, kh, kw) once per CTA;
-//   threadIdx.x               -> four consecutive output positions of a plane, decoded once per thread into
-//                                source offsets and in-bounds flags;
-//   threadIdx.y + blockIdx.x  -> the image n, the only thing the inner loop changes.
-// The inner loop is four predicated loads and one 128-bit store.  HoWo must be a multiple of 4.
-__global__ void __launch_bounds__(256) im2col_v4_kernel(const float *__restrict__ x, float *__restrict__ col, ConvGeom g) {
-    const int k = blockIdx.y;
-    const int kw = k % g.kW, kh = (k / g.kW) % g.kH, c = k / (g.kW * g.kH);
-    const int HoWo = g.H_out * g.W_out, n4 = HoWo >> 2;
+//   blockIdx.y = c (taps kernel) or k (row kernel)   decoded once per CTA;
+//   threadIdx.x = one output position of a plane      decoded once per thread into the source offset of every
+//                                                     filter tap (-1: padding);
+//   threadIdx.y + blockIdx.x = the image n            the only thing the inner loop changes.
+// Consecutive lanes own consecutive positions, so every load and every store of a warp is one run of
+// consecutive floats (a 128-byte line per instruction).  An earlier version gave each thread four positions
+// and one 128-bit store; its four gather loads per store were 16 bytes apart from lane to lane, four L1
+// wavefronts each, and the kernel ran at half the bandwidth of this one.
+// Taps kernel (kH*kW <= 9): a CTA row reads its plane once (from L1 after the first tap) and writes all kH*kW rows.
+__global__ void __launch_bounds__(256) im2col_taps_kernel(const float *__restrict__ x, float *__restrict__ col, ConvGeom g) {
+    const int c = blockIdx.y, KK = g.kH * g.kW, HoWo = g.H_out * g.W_out;
     const int64_t plane = (int64_t)g.H * g.W;
-    for (int e = threadIdx.x; e < n4; e += blockDim.x) {
-        int off[4];
+    for (int o = threadIdx.x; o < HoWo; o += blockDim.x) {
+        const int oh = o / g.W_out, ow = o - oh * g.W_out;
+        int off[9];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int o = 4 * e + j, oh = o / g.W_out, ow = o - oh * g.W_out;
+        for (int t = 0; t < 9; t++) {
+            const int kh = t / g.kW, kw = t - kh * g.kW;
             const int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
-            off[j] = (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? ih * g.W + iw : -1;
+            off[t] = (t < KK && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? ih * g.W + iw : -1;
         }
-        float *dst = col + (int64_t)k * g.M + 4 * e;
         for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
             const float *src = x + ((int64_t)n * g.C + c) * plane;
-            float4 v;
-            v.x = off[0] >= 0 ? __ldg(src + off[0]) : 0.f; v.y = off[1] >= 0 ? __ldg(src + off[1]) : 0.f;
-            v.z = off[2] >= 0 ? __ldg(src + off[2]) : 0.f; v.w = off[3] >= 0 ? __ldg(src + off[3]) : 0.f;
-            *reinterpret_cast<float4 *>(dst + (int64_t)n * HoWo) = v;
+            float *dst = col + (int64_t)c * KK * g.M + (int64_t)n * HoWo + o;
+            float v[9];
+#pragma unroll
+            for (int t = 0; t < 9; t++) v[t] = off[t] >= 0 ? __ldg(src + off[t]) : 0.f;
+#pragma unroll
+            for (int t = 0; t < 9; t++) if (t < KK) dst[(int64_t)t * g.M] = v[t];
         }
     }
 }
-// Any geometry: one thread per element, m fastest.
-__global__ void im2col_kernel(const float *__restrict__ x, float *__restrict__ col, ConvGeom g) {
-    int64_t total = (int64_t)g.K * g.M;
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        int m = (int)(idx % g.M); int k = (int)(idx / g.M);
-        int ow = m % g.W_out; int t = m / g.W_out; int oh = t % g.H_out; int n = t / g.H_out;
-        int kw = k % g.kW; t = k / g.kW; int kh = t % g.kH; int c = t / g.kH;
-        int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
-        float v = 0.f;
-        if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = x[(((int64_t)n * g.C + c) * g.H + ih) * g.W + iw];
-        col[idx] = v;
+// Row kernel (any filter size): one CTA row per row k of the column matrix.
+__global__ void __launch_bounds__(256) im2col_row_kernel(const float *__restrict__ x, float *__restrict__ col, ConvGeom g) {
+    const int k = blockIdx.y;
+    const int kw = k % g.kW, kh = (k / g.kW) % g.kH, c = k / (g.kW * g.kH);
+    const int HoWo = g.H_out * g.W_out;
+    const int64_t plane = (int64_t)g.H * g.W;
+    for (int o = threadIdx.x; o < HoWo; o += blockDim.x) {
+        const int oh = o / g.W_out, ow = o - oh * g.W_out;
+        const int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
+        const int off = (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? ih * g.W + iw : -1;
+        float *dst = col + (int64_t)k * g.M + o;
+        for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y)
+            dst[(int64_t)n * HoWo] = off >= 0 ? __ldg(x + ((int64_t)n * g.C + c) * plane + off) : 0.f;
     }
 }
+// Thread block (bx, by): bx lanes over the positions of a plane, by images side by side; grid.x over the images.
+static void conv_launch_shape(int positions, int N, int rows, dim3 &grid, dim3 &block) {
+    int bx = ((positions + 31) / 32) * 32;
+    if (bx > 256) bx = 256;
+    const int by = 256 / bx;
+    int gx = (N + by - 1) / by;
+    const int cap = (kNumSMs * 16 + rows - 1) / rows;          // a few waves in total
+    if (gx > cap) gx = cap < 1 ? 1 : cap;
+    grid = dim3(gx, rows); block = dim3(bx, by);
+}
 static void run_im2col(const float *x, float *col, const ConvGeom &g) {
-    const int HoWo = g.H_out * g.W_out;
-    if (HoWo % 4 == 0 && g.M % 4 == 0 && aligned16(col) && g.K <= 65535) {
-        int bx = ((HoWo / 4 + 31) / 32) * 32;
-        if (bx > 256) bx = 256;
-        const int by = 256 / bx;
-        int gx = (g.N + by - 1) / by;
-        const int cap = (kNumSMs * 16 + g.K - 1) / g.K;       // a few waves in total
-        if (gx > cap) gx = cap < 1 ? 1 : cap;
-        im2col_v4_kernel<<<dim3(gx, g.K), dim3(bx, by), 0, stream()>>>(x, col, g);
+    dim3 grid, block;
+    if (g.kH * g.kW <= 9 && g.C <= 65535) {
+        conv_launch_shape(g.H_out * g.W_out, g.N, g.C, grid, block);
+        im2col_taps_kernel<<<grid, block, 0, stream()>>>(x, col, g);
     } else {
-        im2col_kernel<<<grid_for((int64_t)g.K * g.M, 256), 256, 0, stream()>>>(x, col, g);
+        DNN_CHECK(g.K <= 65535, "conv2d: C * kH * kW above 65535 is not supported");
+        conv_launch_shape(g.H_out * g.W_out, g.N, g.K, grid, block);
+        im2col_row_kernel<<<grid, block, 0, stream()>>>(x, col, g);
     }
     prof_work(4.0 * ((double)g.N * g.C * g.H * g.W + (double)g.K * g.M));
     LAUNCHED("im2col_kernel");
 }
 
 // dx[n,c,ih,iw] (=|+=) sum over the windows (kh,kw,oh,ow) that read this pixel of dcol[k][m]; gather form,
-// fixed order (kh, then kw), no atomics.  Same split of the index arithmetic as im2col: blockIdx.y = c,
-// a thread owns four consecutive pixels of a plane and decodes, once, for each of its pixels and each of
-// the (at most 9) filter taps the offset of the column-matrix element that tap contributed, and the
-// inner loop over images does nothing but loads and adds.  H*W must be a multiple of 4, kH*kW <= 9.
+// fixed order (kh, then kw), no atomics.  Same split of the index arithmetic and the same lane layout as im2col:
+// blockIdx.y = c, a thread owns one pixel of a plane and decodes, once, for each of the (at most 9) filter taps
+// the position of the column-matrix element that tap contributed (-1: none); the inner loop over images is
+// loads of consecutive floats per warp and adds.  kH*kW <= 9.
 template <bool ACC>
-__global__ void __launch_bounds__(256) col2im_v4_kernel(const float *__restrict__ dcol, float *__restrict__ dx, ConvGeom g) {
-    const int c = blockIdx.y, HW = g.H * g.W, n4 = HW >> 2, HoWo = g.H_out * g.W_out, KK = g.kH * g.kW;
-    for (int e = threadIdx.x; e < n4; e += blockDim.x) {
-        int pos[4][9];                       // position inside an image's run of a column-matrix row, or -1
+__global__ void __launch_bounds__(256) col2im_taps_kernel(const float *__restrict__ dcol, float *__restrict__ dx, ConvGeom g) {
+    const int c = blockIdx.y, HW = g.H * g.W, HoWo = g.H_out * g.W_out, KK = g.kH * g.kW;
+    for (int p = threadIdx.x; p < HW; p += blockDim.x) {
+        const int ih = p / g.W, iw = p - ih * g.W;
+        int pos[9];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int p = 4 * e + j, ih = p / g.W, iw = p - ih * g.W;
-#pragma unroll
-            for (int t = 0; t < 9; t++) {
-                pos[j][t] = -1;
-                if (t >= KK) continue;
-                const int kh = t / g.kW, kw = t - kh * g.kW;
-                const int a = ih + g.pad - kh, b = iw + g.pad - kw;
-                if (a < 0 || b < 0 || a % g.stride || b % g.stride) continue;
-                const int oh = a / g.stride, ow = b / g.stride;
-                if (oh >= g.H_out || ow >= g.W_out) continue;
-                pos[j][t] = oh * g.W_out + ow;
-            }
+        for (int t = 0; t < 9; t++) {
+            pos[t] = -1;
+            if (t >= KK) continue;
+            const int kh = t / g.kW, kw = t - kh * g.kW;
+            const int a = ih + g.pad - kh, b = iw + g.pad - kw;
+            if (a < 0 || b < 0 || a % g.stride || b % g.stride) continue;
+            const int oh = a / g.stride, ow = b / g.stride;
+            if (oh >= g.H_out || ow >= g.W_out) continue;
+            pos[t] = oh * g.W_out + ow;
         }
         for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
             const float *src = dcol + (int64_t)c * KK * g.M + (int64_t)n * HoWo;      // tap t: + t * M
-            float v[4];
+            float s = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float s = 0.f;
-#pragma unroll
-                for (int t = 0; t < 9; t++) if (pos[j][t] >= 0) s += __ldg(src + (int64_t)t * g.M + pos[j][t]);
-                v[j] = s;
-            }
-            float4 *dst = reinterpret_cast<float4 *>(dx + ((int64_t)n * g.C + c) * HW + 4 * e);
-            float4 o = make_float4(v[0], v[1], v[2], v[3]);
-            if (ACC) { const float4 old = *dst; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
-            *dst = o;
+            for (int t = 0; t < 9; t++) if (pos[t] >= 0) s += __ldg(src + (int64_t)t * g.M + pos[t]);
+            float *dst = dx + ((int64_t)n * g.C + c) * HW + p;
+            *dst = ACC ? *dst + s : s;
         }
     }
 }
@@ -149,15 +152,11 @@ __global__ void col2im_kernel(const float *__restrict__ dcol, float *__restrict_
 }
 static void run_col2im(const float *dcol, float *dx, const ConvGeom &g, bool accumulate) {
     const int HW = g.H * g.W;
-    if (HW % 4 == 0 && g.kH * g.kW <= 9 && aligned16(dx) && g.C <= 65535) {
-        int bx = ((HW / 4 + 31) / 32) * 32;
-        if (bx > 256) bx = 256;
-        const int by = 256 / bx;
-        int gx = (g.N + by - 1) / by;
-        const int cap = (kNumSMs * 16 + g.C - 1) / g.C;
-        if (gx > cap) gx = cap < 1 ? 1 : cap;
-        if (accumulate) col2im_v4_kernel<true><<<dim3(gx, g.C), dim3(bx, by), 0, stream()>>>(dcol, dx, g);
-        else col2im_v4_kernel<false><<<dim3(gx, g.C), dim3(bx, by), 0, stream()>>>(dcol, dx, g);
+    if (g.kH * g.kW <= 9 && g.C <= 65535) {
+        dim3 grid, block;
+        conv_launch_shape(HW, g.N, g.C, grid, block);
+        if (accumulate) col2im_taps_kernel<true><<<grid, block, 0, stream()>>>(dcol, dx, g);
+        else col2im_taps_kernel<false><<<grid, block, 0, stream()>>>(dcol, dx, g);
     } else {
         const int grid = grid_for((int64_t)g.N * g.C * HW, 256);
         if (accumulate) col2im_kernel<true><<<grid, 256, 0, stream()>>>(dcol, dx, g);
@@ -204,16 +203,23 @@ static void run_permute(float *dst, const float *src, int N, int OC, int HW) {
 }
 
 // dbias[oc] += sum_{n,hw} g[(n*OC + oc)*HW + hw].  CTA (oc, s) sums the images n = s, s + S, ... of its
-// channel into part[oc*S + s]; conv_dbias_final_kernel adds the S partials in order (fixed order).
-__global__ void conv_dbias_kernel(float *__restrict__ part, const float *__restrict__ g, int N, int OC, int HW) {
+// channel into part[oc*S + s]; conv_dbias_final_kernel adds the S partials in order (fixed order).  A thread
+// keeps four independent sums over four images at a time, so four loads are in flight per thread.
+__global__ void __launch_bounds__(256) conv_dbias_kernel(float *__restrict__ part, const float *__restrict__ g, int N, int OC, int HW) {
     __shared__ float sh[32];
     const int oc = blockIdx.x, S = gridDim.y;
-    float s = 0.f;
-    for (int n = blockIdx.y; n < N; n += S) {
-        const float *row = g + ((int64_t)n * OC + oc) * HW;
-        for (int hw = threadIdx.x; hw < HW; hw += blockDim.x) s += row[hw];
+    const int64_t img = (int64_t)OC * HW;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int hw = threadIdx.x; hw < HW; hw += blockDim.x) {
+        const float *col = g + (int64_t)oc * HW + hw;
+        int n = blockIdx.y;
+        for (; n + 3 * S < N; n += 4 * S) {
+            s0 += __ldg(col + (int64_t)n * img); s1 += __ldg(col + (int64_t)(n + S) * img);
+            s2 += __ldg(col + (int64_t)(n + 2 * S) * img); s3 += __ldg(col + (int64_t)(n + 3 * S) * img);
+        }
+        for (; n < N; n += S) s0 += __ldg(col + (int64_t)n * img);
     }
-    s = block_sum(s, sh);
+    const float s = block_sum((s0 + s1) + (s2 + s3), sh);
     if (threadIdx.x == 0) part[oc * S + blockIdx.y] = s;
 }
 __global__ void conv_dbias_final_kernel(float *__restrict__ db, const float *__restrict__ part, int OC, int S) {

@@ -178,6 +178,15 @@ struct ReluB4 { float4 *dx; const float4 *x, *g; int acc; __device__ void operat
 struct SiluF { float *o; const float *x; __device__ void operator()(int64_t i) const { float v = x[i]; o[i] = v / (1.0f + expf(-v)); } };
 struct SiluB { float *dx; const float *x, *g; int acc; __device__ void operator()(int64_t i) const {
     float v = x[i], s = sigmoidf_(v), r = s * (1.0f + v - v * s) * g[i]; dx[i] = acc ? dx[i] + r : r; } };
+// the same with 128-bit accesses (same expressions per element, so the same bits)
+__device__ __forceinline__ float silu1(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float silu_b1(float v, float g) { float s = sigmoidf_(v); return s * (1.0f + v - v * s) * g; }
+struct SiluF4 { float4 *o; const float4 *x; __device__ void operator()(int64_t i) const {
+    float4 v = x[i]; o[i] = make_float4(silu1(v.x), silu1(v.y), silu1(v.z), silu1(v.w)); } };
+struct SiluB4 { float4 *dx; const float4 *x, *g; int acc; __device__ void operator()(int64_t i) const {
+    float4 v = x[i], gg = g[i], d = acc ? dx[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 r = make_float4(silu_b1(v.x, gg.x), silu_b1(v.y, gg.y), silu_b1(v.z, gg.z), silu_b1(v.w, gg.w));
+    dx[i] = acc ? make_float4(d.x + r.x, d.y + r.y, d.z + r.z, d.w + r.w) : r; } };
 
 __device__ __forceinline__ float swiglu1(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 struct SwigluF  { float *o; const float *g, *u; __device__ void operator()(int64_t i) const { o[i] = swiglu1(g[i], u[i]); } };
@@ -274,7 +283,10 @@ static void silu_backward(grad_fn *fn, tensor *g) {
     const float *gd = (const float *)g->data;
     if (a->contiguous) {
         prof_work((acc ? 16.0 : 12.0) * n);
-        ew_launch("silu_bwd_kernel", n, SiluB{ag + a->offset, (const float *)a->data + a->offset, gd, acc});
+        float *dx = ag + a->offset;
+        const float *x = (const float *)a->data + a->offset;
+        if (v4ok(n, {dx, x, gd})) ew_launch("silu_bwd_kernel", n / 4, SiluB4{(float4 *)dx, (const float4 *)x, (const float4 *)gd, acc});
+        else ew_launch("silu_bwd_kernel", n, SiluB{dx, x, gd, acc});
     } else {
         float *xt = dev_alloc_t<float>(fn->pool, (size_t)n), *dt = dev_alloc_t<float>(fn->pool, (size_t)n);
         k_gather(xt, (const float *)a->data, view_of(a), n);
@@ -670,7 +682,9 @@ tensor *tensor_silu(struct mem_pool *scratch, const tensor *t) {
         k_gather(tmp, (const float *)t->data, view_of(t), n);
         x = tmp;
     }
-    ew_launch("silu_fwd_kernel", n, SiluF{(float *)out->data, x});
+    prof_work(8.0 * n);
+    if (v4ok(n, {(float *)out->data, x})) ew_launch("silu_fwd_kernel", n / 4, SiluF4{(float4 *)out->data, (const float4 *)x});
+    else ew_launch("silu_fwd_kernel", n, SiluF{(float *)out->data, x});
     if (dnn_grad_enabled() && t->requires_grad) {
         grad_fn *fn = attach(scratch, out, silu_backward, 1, 0);
         fn->inputs[0] = (tensor *)t;

@@ -182,28 +182,32 @@ __global__ void emb_count_kernel(const int *__restrict__ ids, int n, int vocab, 
     int id = ids[i];
     if (id >= 0 && id < vocab) atomicAdd(&count[id], 1);
 }
-// start[v] = sum of count[0..v).  One CTA of 1024 threads: every thread owns a contiguous run of
-// the vocabulary, the 1024 run totals are scanned with warp shuffles, then each thread writes the
-// exclusive prefix of its run.
-__global__ void emb_scan_kernel(const int *__restrict__ count, int vocab, int *__restrict__ start) {
+// start[v] = sum of count[0..v).  One CTA of 1024 threads walks the vocabulary in tiles of 1024 with coalesced
+// loads; inside a tile the counts are scanned with warp shuffles (lanes, then the 32 warp totals), and a running
+// total carries over from tile to tile.
+__global__ void __launch_bounds__(1024) emb_scan_kernel(const int *__restrict__ count, int vocab, int *__restrict__ start) {
     __shared__ int warp_tot[32];
-    const int per = (vocab + (int)blockDim.x - 1) / (int)blockDim.x;
-    const int lo = threadIdx.x * per, hi = min(lo + per, vocab);
-    int tot = 0;
-    for (int v = lo; v < hi; v++) tot += count[v];
+    __shared__ int tile_total;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    int incl = tot;
-    for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
-    if (lane == 31) warp_tot[wid] = incl;
-    __syncthreads();
-    if (wid == 0) {
-        int w = lane < (int)(blockDim.x >> 5) ? warp_tot[lane] : 0, wi = w;
-        for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
-        warp_tot[lane] = wi - w;                      // exclusive prefix of the warp totals
+    int carry = 0;                                        // the same value in every thread
+    for (int base = 0; base < vocab; base += 1024) {
+        const int v = base + threadIdx.x;
+        const int c = v < vocab ? count[v] : 0;
+        int incl = c;
+        for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        if (wid == 0) {
+            int w = warp_tot[lane], wi = w;
+            for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
+            warp_tot[lane] = wi - w;                      // exclusive prefix of the warp totals
+            if (lane == 31) tile_total = wi;
+        }
+        __syncthreads();
+        if (v < vocab) start[v] = carry + warp_tot[wid] + incl - c;
+        carry += tile_total;
+        __syncthreads();                                  // warp_tot and tile_total are rewritten by the next tile
     }
-    __syncthreads();
-    int run = warp_tot[wid] + incl - tot;             // exclusive prefix of this thread's run
-    for (int v = lo; v < hi; v++) { start[v] = run; run += count[v]; }
 }
 __global__ void emb_fill_kernel(const int *__restrict__ ids, int n, int vocab, const int *__restrict__ start,
                                 int *__restrict__ cursor, int *__restrict__ list) {
