@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(256) im2col_taps_kernel(const float *__restric
             const int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
             off[t] = (t < KK && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? ih * g.W + iw : -1;
         }
+#pragma unroll 2
         for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
             const float *src = x + ((int64_t)n * g.C + c) * plane;
             float *dst = col + (int64_t)c * KK * g.M + (int64_t)n * HoWo + o;
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__(256) col2im_taps_kernel(const float *__restric
             if (oh >= g.H_out || ow >= g.W_out) continue;
             pos[t] = oh * g.W_out + ow;
         }
+#pragma unroll 2
         for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
             const float *src = dcol + (int64_t)c * KK * g.M + (int64_t)n * HoWo;      // tap t: + t * M
             float s = 0.f;
@@ -203,21 +205,31 @@ static void run_permute(float *dst, const float *src, int N, int OC, int HW) {
 }
 
 // dbias[oc] += sum_{n,hw} g[(n*OC + oc)*HW + hw].  CTA (oc, s) sums the images n = s, s + S, ... of its
-// channel into part[oc*S + s]; conv_dbias_final_kernel adds the S partials in order (fixed order).  A thread
-// keeps four independent sums over four images at a time, so four loads are in flight per thread.
+// channel into part[oc*S + s]; conv_dbias_final_kernel adds the S partials in order (fixed order).  The CTA's
+// rows (one per image, HW floats each) are walked as one list of 128-bit pieces, four independent loads in
+// flight per thread; rows that are not a multiple of four floats long take the scalar loop.
 __global__ void __launch_bounds__(256) conv_dbias_kernel(float *__restrict__ part, const float *__restrict__ g, int N, int OC, int HW) {
     __shared__ float sh[32];
     const int oc = blockIdx.x, S = gridDim.y;
     const int64_t img = (int64_t)OC * HW;
+    const int rows = (N - (int)blockIdx.y + S - 1) / S;               // images n = blockIdx.y + r * S
+    const float *base = g + (int64_t)blockIdx.y * img + (int64_t)oc * HW;
+    const int64_t row_pitch = (int64_t)S * img;
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    for (int hw = threadIdx.x; hw < HW; hw += blockDim.x) {
-        const float *col = g + (int64_t)oc * HW + hw;
-        int n = blockIdx.y;
-        for (; n + 3 * S < N; n += 4 * S) {
-            s0 += __ldg(col + (int64_t)n * img); s1 += __ldg(col + (int64_t)(n + S) * img);
-            s2 += __ldg(col + (int64_t)(n + 2 * S) * img); s3 += __ldg(col + (int64_t)(n + 3 * S) * img);
+    if (HW % 4 == 0 && (((uintptr_t)g) & 15) == 0) {
+        const int w4 = HW >> 2, items = rows * w4;
+        auto piece = [&](int i) { const int r = i / w4, c4 = i - r * w4;
+                                  return __ldg(reinterpret_cast<const float4 *>(base + (int64_t)r * row_pitch) + c4); };
+        int i = threadIdx.x;
+        for (; i + 3 * 256 < items; i += 4 * 256) {
+            const float4 a = piece(i), b = piece(i + 256), c = piece(i + 512), d = piece(i + 768);
+            s0 += (a.x + a.y) + (a.z + a.w); s1 += (b.x + b.y) + (b.z + b.w);
+            s2 += (c.x + c.y) + (c.z + c.w); s3 += (d.x + d.y) + (d.z + d.w);
         }
-        for (; n < N; n += S) s0 += __ldg(col + (int64_t)n * img);
+        for (; i < items; i += 256) { const float4 a = piece(i); s0 += (a.x + a.y) + (a.z + a.w); }
+    } else {
+        for (int r = 0; r < rows; r++)
+            for (int hw = threadIdx.x; hw < HW; hw += blockDim.x) s0 += __ldg(base + (int64_t)r * row_pitch + hw);
     }
     const float s = block_sum((s0 + s1) + (s2 + s3), sh);
     if (threadIdx.x == 0) part[oc * S + blockIdx.y] = s;
