@@ -31,7 +31,6 @@ reference sources by oracle/Makefile).
 """
 import argparse
 import ctypes as C
-import glob
 import importlib.util
 import json
 import os
