@@ -435,7 +435,7 @@ def kernel_table(lib, B, steps, hbm_peak, tf32_peak):
         total += ms
         row = {"kernel": name, "launches_per_step": round(r.launches / steps, 1), "ms_per_step": round(ms, 4)}
         if r.work > 0 and r.ms > 0:
-            if name.startswith(("gemm_tf32", "attn_")):
+            if name.startswith(("gemm_tf32", "gemm_3xtf32", "attn_")):
                 a = r.work / (r.ms * 1e-3) / 1e12
                 row.update(flop_per_step=r.work / steps, achieved=round(a, 1), unit="TFLOP/s", frac=round(a / tf32_peak, 4))
                 tensor.append(row)

@@ -18,6 +18,16 @@
 // kernel serves A*B, A*B^T, dA and dW without transposing anything in memory.
 // Tails in M, N and K need no special code: TMA zero-fills out-of-bounds boxes.
 //
+// X3 (3xTF32 in one pass): the stages hold the RAW fp32 tiles (the tensor core reads the upper 19 bits
+// of each word, i.e. x truncated to TF32 = "big") next to a second copy that four more warps fill
+// with small = x - big as soon as a tile has landed; per K=8 step the issuing thread then runs
+// As*Bb, Ab*Bs and Ab*Bb.  Nothing is split in global memory.  X3 = 1: all three into one accumulator
+// (the two TMEM accumulators alternate between tiles as in the TF32 kernel).  X3 = 2: Ab*Bb into the
+// first and the two small terms into the second accumulator, added by the epilogue in fp32 -- the
+// tensor core truncates its accumulator on every add, and keeping the small terms out of the large
+// sum leaves that bias where one TF32 product per K step puts it; the price is that the epilogue of
+// a tile no longer overlaps the main loop of the next.
+//
 // Every mbarrier wait is bounded; a wait that runs out records an error code
 // that dnn_cuda_sync() reports, and the CTA still frees its TMEM and returns.
 #include "common.cuh"
@@ -30,6 +40,7 @@ constexpr int BM = 128;            // tile rows = MMA M
 constexpr int BK = 32;             // K per stage: 32 fp32 = one 128-byte swizzle row
 constexpr int UMMA_K = 8;          // K per tcgen05.mma for TF32
 constexpr int kGemmThreads = 192;
+constexpr int kGemmThreadsX3 = 192 + 128;      // four more warps split the landed tiles
 
 __device__ int g_gemm_error = 0;   // 0 ok; otherwise (role << 8 | detail) of the first wait that gave up
 
@@ -48,15 +59,24 @@ struct TcArgs {
     int rope_N, rope_d, rope_cols;
 };
 
-template <int BN, bool PAIR> struct TcCfg {
+template <int BN, bool PAIR, int X3 = 0> struct TcCfg {
     static constexpr int kRowsB = PAIR ? BN / 2 : BN;             // B rows (n) this CTA loads per stage
     static constexpr int kStageA = BM * BK * 4;                   // 16 KiB
     static constexpr int kStageB = kRowsB * BK * 4;
-    static constexpr int kStages = (kStageA + kStageB) == 49152 ? 4 : 6;
+    static constexpr int kCopies = X3 ? 2 : 1;                    // X3: the raw tile and its small part
+    static constexpr int kStages = X3 ? ((kStageA + kStageB) == 49152 ? 2 : 3) : ((kStageA + kStageB) == 49152 ? 4 : 6);
     static constexpr int kStore = 4 * 2 * 4096;                   // per epilogue warp: two 32x32 fp32 staging tiles
-    static constexpr int kSmem = kStages * (kStageA + kStageB) + kStore + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int kSmem = kStages * kCopies * (kStageA + kStageB) + kStore + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kThreads = X3 ? kGemmThreadsX3 : kGemmThreads;
 };
+
+// small part of x for the 3xTF32 products: x minus its upper 19 bits, with half a TF32 unit added to
+// the bits so that the tensor core's truncation of it rounds to nearest
+__device__ __forceinline__ float tf32_small(float v) {
+    float s = v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    return __uint_as_float(__float_as_uint(s) + 0x1000u);
+}
 
 // Work unit -> tile coordinates.  Units that run at the same time should share the operand that
 // does not fit in L2: walking along M re-reads the A rows once per N tile, walking along N
@@ -66,11 +86,12 @@ __device__ __forceinline__ void tile_of(const TcArgs &g, int tile, int &tm, int 
     else { tn = tile / g.tiles_m; tm = tile - tn * g.tiles_m; }
 }
 
-template <int BN, bool PAIR>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, bool PAIR, int X3>
+__global__ void __launch_bounds__(X3 ? kGemmThreadsX3 : kGemmThreads, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, TcArgs g) {
-    using Cfg = TcCfg<BN, PAIR>;
+    using Cfg = TcCfg<BN, PAIR, X3>;
+    constexpr int kStrideA = Cfg::kCopies * Cfg::kStageA, kStrideB = Cfg::kCopies * Cfg::kStageB;   // bytes per stage
     static_assert(!PAIR || BN == 256, "a CTA pair computes 256 x 256 tiles");
     // PAIR: the grid is made of clusters of two CTAs; a pair walks the work units together,
     // rank 0 (the leader) issues the MMAs for both.
@@ -80,15 +101,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int kTileM = PAIR ? 2 * BM : BM;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *sA = smem, *sB = smem + Cfg::kStages * Cfg::kStageA;
-    uint8_t *sC = smem + Cfg::kStages * (Cfg::kStageA + Cfg::kStageB);
+    uint8_t *sA = smem, *sB = smem + Cfg::kStages * kStrideA;
+    uint8_t *sC = smem + Cfg::kStages * (kStrideA + kStrideB);
     uint64_t *bars = (uint64_t *)(sC + Cfg::kStore);
     uint64_t *full = bars, *empty = bars + Cfg::kStages, *acc_full = bars + 2 * Cfg::kStages, *acc_empty = acc_full + 2;
-    uint32_t *tmem_slot = (uint32_t *)(acc_empty + 2);
+    uint64_t *conv = acc_empty + 2;        // X3: stage split, counted on the leader for both CTAs of a pair
+    uint32_t *tmem_slot = (uint32_t *)(conv + Cfg::kStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::kStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < Cfg::kStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&conv[s], PAIR ? 8 : 4); }
         for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 8 : 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -124,17 +146,20 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&empty[stage], phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 0x100 | stage); ok = false; break; }
-                    // both CTAs' bytes are counted on the leader's barrier, which alone is armed
-                    if (rank == 0) mbar_expect_tx(&full[stage], (PAIR ? 2 : 1) * (Cfg::kStageA + Cfg::kStageB));
-                    const uint32_t bar = PAIR ? map_to_rank(smem_u32(&full[stage]), 0) : smem_u32(&full[stage]);
+                    // both CTAs' bytes are counted on the leader's barrier, which alone is armed; X3: every CTA
+                    // counts its own bytes on its own barrier, because its own warps split the tiles next
+                    constexpr bool kToLeader = PAIR && !X3;
+                    if (X3) mbar_expect_tx(&full[stage], Cfg::kStageA + Cfg::kStageB);
+                    else if (rank == 0) mbar_expect_tx(&full[stage], (PAIR ? 2 : 1) * (Cfg::kStageA + Cfg::kStageB));
+                    const uint32_t bar = kToLeader ? map_to_rank(smem_u32(&full[stage]), 0) : smem_u32(&full[stage]);
                     auto load = [&](void *dst, const CUtensorMap *map, int x, int y) {
-                        if (PAIR) tma_load_2d_pair(dst, map, x, y, bar);
+                        if (kToLeader) tma_load_2d_pair(dst, map, x, y, bar);
                         else tma_load_2d(dst, map, x, y, &full[stage]);
                     };
-                    uint8_t *a = sA + stage * Cfg::kStageA, *b = sB + stage * Cfg::kStageB;
+                    uint8_t *a = sA + stage * kStrideA, *b = sB + stage * kStrideB;
                     int k = kb * BK;
                     auto load3 = [&](void *dst, const CUtensorMap *map, int y, int z) {
-                        if (PAIR) tma_load_3d_pair(dst, map, 0, y, z, bar);
+                        if (kToLeader) tma_load_3d_pair(dst, map, 0, y, z, bar);
                         else tma_load_3d(dst, map, 0, y, z, &full[stage]);
                     };
                     if (g.a_kmajor) load(a, &tmA, k, m0);                                          // box {32 k, 128 rows}
@@ -169,16 +194,30 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
                 if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 0x200 | acc); break; }
                 tc_fence_after();
-                uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t tmem_small = X3 == 2 ? tmem_base + (uint32_t)BN : tmem_d;      // X3 == 2: acc stays 0
                 for (int kb = kb0; kb < kb1; kb++) {
-                    if (!mbar_wait(&full[stage], phase)) { atomicCAS(&g_gemm_error, 0, 0x300 | stage); ok = false; break; }
+                    if (!(X3 ? mbar_wait_cluster(&conv[stage], phase) : mbar_wait(&full[stage], phase))) {
+                        atomicCAS(&g_gemm_error, 0, 0x300 | stage); ok = false; break;
+                    }
                     tc_fence_after();
-                    const uint64_t a_st = a_desc0 + (uint64_t)(stage * (Cfg::kStageA >> 4)), b_st = b_desc0 + (uint64_t)(stage * (Cfg::kStageB >> 4));
+                    const uint64_t a_st = a_desc0 + (uint64_t)(stage * (kStrideA >> 4)), b_st = b_desc0 + (uint64_t)(stage * (kStrideB >> 4));
+                    auto mma = [&](uint32_t d, uint64_t ad, uint64_t bd, uint32_t accum) {
+                        if (PAIR) tc_mma_tf32_pair(d, ad, bd, idesc, accum);
+                        else tc_mma_tf32(d, ad, bd, idesc, accum);
+                    };
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) {
                         const uint64_t ad = a_st + k * a_adv, bd = b_st + k * b_adv;
-                        if (PAIR) tc_mma_tf32_pair(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                        else tc_mma_tf32(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        const uint32_t first = (kb > kb0 || k > 0) ? 1u : 0u;
+                        if (X3) {       // the two small terms first, then big x big
+                            const uint64_t as = ad + (Cfg::kStageA >> 4), bs = bd + (Cfg::kStageB >> 4);
+                            mma(tmem_small, as, bd, first);
+                            mma(tmem_small, ad, bs, 1u);
+                            mma(tmem_d, ad, bd, X3 == 2 ? first : 1u);
+                        } else {
+                            mma(tmem_d, ad, bd, first);
+                        }
                     }
                     // frees the stage (in both CTAs of a pair) when these MMAs have read it
                     if (PAIR) tc_commit_pair(&empty[stage], 3); else tc_commit(&empty[stage]);
@@ -186,7 +225,42 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
                 if (!ok) break;
                 if (PAIR) tc_commit_pair(&acc_full[acc], 3); else tc_commit(&acc_full[acc]);      // accumulator complete
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                if (X3 == 2) acc_phase ^= 1;
+                else if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else if (X3 && warp >= 6) {
+        // split warps 6..9: small = x - trunc(x) of the stage that has just landed, element by element
+        // (the layout of the tile does not matter), then tell the leader's MMA thread
+        const int t = (int)threadIdx.x - kGemmThreads;
+        int stage = 0; uint32_t phase = 0;
+        bool ok = true;
+        for (int u = walker; u < num_units && ok; u += walkers) {
+            int split = u % g.splits;
+            int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
+            for (int kb = kb0; kb < kb1; kb++) {
+                if (!mbar_wait(&full[stage], phase)) { if (lane == 0) atomicCAS(&g_gemm_error, 0, 0x500 | stage); ok = false; break; }
+                const float4 *ra = reinterpret_cast<const float4 *>(sA + stage * kStrideA);
+                float4 *wa = reinterpret_cast<float4 *>(sA + stage * kStrideA + Cfg::kStageA);
+#pragma unroll
+                for (int i = 0; i < Cfg::kStageA / 16 / 128; i++) {
+                    const float4 v = ra[t + i * 128];
+                    wa[t + i * 128] = make_float4(tf32_small(v.x), tf32_small(v.y), tf32_small(v.z), tf32_small(v.w));
+                }
+                const float4 *rb = reinterpret_cast<const float4 *>(sB + stage * kStrideB);
+                float4 *wb = reinterpret_cast<float4 *>(sB + stage * kStrideB + Cfg::kStageB);
+#pragma unroll
+                for (int i = 0; i < Cfg::kStageB / 16 / 128; i++) {
+                    const float4 v = rb[t + i * 128];
+                    wb[t + i * 128] = make_float4(tf32_small(v.x), tf32_small(v.y), tf32_small(v.z), tf32_small(v.w));
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(map_to_rank(smem_u32(&conv[stage]), 0));
+                    else mbar_arrive(&conv[stage]);
+                }
+                if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
             }
         }
     } else {
@@ -213,6 +287,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; j++) v[j] = has_k ? __uint_as_float(r[j]) : 0.f;
+                if (X3 == 2 && has_k) {      // the small terms' accumulator
+                    tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), r);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] += __uint_as_float(r[j]);
+                }
                 if (use_bias) {
                     if (col0 + 32 <= g.N) {
 #pragma unroll
@@ -276,7 +355,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (PAIR) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[acc]), 0));
                 else mbar_arrive(&acc_empty[acc]);
             }
-            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            if (X3 == 2) acc_phase ^= 1;
+            else if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
         if (lane == 0) bulk_wait<0>();      // the staging tiles must outlive the copies that read them
     }
@@ -351,9 +431,32 @@ static EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// A tensor map is a pure function of its arguments, and a training loop asks for the same few hundred
+// over and over (bump pools hand out the same addresses every step), so the encoded maps are kept in
+// a small direct-mapped table per host thread; a miss costs one driver call, as before.
+struct MapKey {
+    const void *base; int64_t a, b, c; int32_t d, kind;
+    bool operator==(const MapKey &o) const { return base == o.base && a == o.a && b == o.b && c == o.c && d == o.d && kind == o.kind; }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+static constexpr int kMapSlots = 1024;
+template <typename Build> static CUtensorMap cached_map(const MapKey &k, Build build) {
+    static thread_local MapSlot *table = nullptr;
+    if (!table) table = (MapSlot *)calloc(kMapSlots, sizeof(MapSlot));
+    uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull;
+    h ^= ((uint64_t)k.a + 0x7F4A7C15ull) * 0xBF58476D1CE4E5B9ull; h ^= h >> 29;
+    h ^= ((uint64_t)k.b * 31 + (uint64_t)k.c * 131 + (uint64_t)k.d * 8191 + (uint64_t)k.kind) * 0x94D049BB133111EBull; h ^= h >> 32;
+    MapSlot &s = table[h % kMapSlots];
+    if (s.used && s.key == k) return s.map;
+    s.map = build(); s.key = k; s.used = true;
+    return s.map;
+}
+
 // 2-D map over a matrix whose contiguous dimension has `inner` elements and whose
 // other dimension has `outer` elements `pitch` floats apart; box = {32, box_outer}.
-static CUtensorMap make_map(const float *base, int64_t inner, int64_t outer, int64_t pitch, int box_outer, bool mn_major) {
+// `raw`: the words reach shared memory unrounded (the 3xTF32 kernel splits them there).
+static CUtensorMap make_map(const float *base, int64_t inner, int64_t outer, int64_t pitch, int box_outer, bool mn_major, bool raw = false) {
+  return cached_map(MapKey{base, inner, outer, pitch, box_outer, (mn_major ? 1 : 0) | (raw ? 8 : 0)}, [&] {
     CUtensorMap m;
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
@@ -361,16 +464,18 @@ static CUtensorMap make_map(const float *base, int64_t inner, int64_t outer, int
     cuuint32_t estr[2] = {1, 1};
     // TFLOAT32: the copy engine rounds fp32 to TF32 (nearest even) on the way into shared
     // memory; the tensor core on its own would truncate, which biases every product low.
-    CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)base, dims, strides, box, estr,
+    CUresult r = encode_tiled()(&m, raw ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)base, dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r); abort(); }
     return m;
+  });
 }
 
 // 3-D map {N, M, splits} over the output (or over the split-K partials); box = one 32 x 32 staging tile.
 static CUtensorMap make_out_map(float *base, int64_t N, int64_t M, int64_t ldc, int splits) {
+  return cached_map(MapKey{base, N, M, ldc, splits, 2}, [&] {
     CUtensorMap m;
     cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)splits};
     cuuint64_t strides[2] = {(cuuint64_t)ldc * 4, (cuuint64_t)M * (cuuint64_t)ldc * 4};
@@ -381,6 +486,7 @@ static CUtensorMap make_out_map(float *base, int64_t N, int64_t M, int64_t ldc, 
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled (output) failed (%d)\n", (int)r); abort(); }
     return m;
+  });
 }
 
 // MN-major operand whose contiguous extent is a multiple of 32: 3-D map {32, outer, inner/32} with
@@ -388,17 +494,19 @@ static CUtensorMap make_out_map(float *base, int64_t N, int64_t M, int64_t ldc, 
 // per-chunk 2-D copies produce -- with one copy instead of `chunks`.  (The split dimension cannot be
 // clipped by the copy engine, hence the multiple-of-32 condition; a chunk index beyond the last
 // chunk is out of bounds in the third dimension and reads zeros.)
-static CUtensorMap make_chunked_map(const float *base, int64_t inner, int64_t outer, int64_t pitch, int chunks) {
+static CUtensorMap make_chunked_map(const float *base, int64_t inner, int64_t outer, int64_t pitch, int chunks, bool raw = false) {
+  return cached_map(MapKey{base, inner, outer, pitch, chunks, 3 | (raw ? 8 : 0)}, [&] {
     CUtensorMap m;
     cuuint64_t dims[3] = {32, (cuuint64_t)outer, (cuuint64_t)(inner / 32)};
     cuuint64_t strides[2] = {(cuuint64_t)pitch * 4, 128};
     cuuint32_t box[3] = {32, 32, (cuuint32_t)chunks};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, (void *)base, dims, strides, box, estr,
+    CUresult r = encode_tiled()(&m, raw ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, (void *)base, dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled (chunked) failed (%d)\n", (int)r); abort(); }
     return m;
+  });
 }
 
 static bool operand_ok(const float *p, int64_t rs, int64_t cs, int64_t rows, int64_t cols) {
@@ -494,21 +602,21 @@ static int choose_splits(int tiles, int slots, int num_kb, int64_t M, int64_t N)
 // length that splitk_reduce adds in fp32 with round-to-nearest, in fixed order.
 static thread_local int g_chain_kb = 0;
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int X3>
 static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
-    using Cfg = TcCfg<BN, PAIR>;
+    using Cfg = TcCfg<BN, PAIR, X3>;
     constexpr int kTileM = PAIR ? 2 * BM : BM;
     static bool once = false;
     if (!once) {
-        CUDA_OK(cudaFuncSetAttribute(gemm_tf32_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        CUDA_OK(cudaFuncSetAttribute(gemm_tf32_kernel<BN, PAIR, X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
         once = true;
     }
     // A(m,k): K-major -> matrix [M rows][K contiguous]; MN-major -> [K rows][M contiguous]
     const bool a_chunked = !a_kmajor && g.M % 32 == 0, b_chunked = !b_kmajor && g.N % 32 == 0;
-    CUtensorMap tmA = a_kmajor ? make_map(g.A, g.K, g.M, g.a_rs, BM, false)
-                    : a_chunked ? make_chunked_map(g.A, g.M, g.K, g.a_cs, BM / 32) : make_map(g.A, g.M, g.K, g.a_cs, 32, true);
-    CUtensorMap tmB = b_kmajor ? make_map(g.B, g.K, g.N, g.b_cs, Cfg::kRowsB, false)
-                    : b_chunked ? make_chunked_map(g.B, g.N, g.K, g.b_rs, Cfg::kRowsB / 32) : make_map(g.B, g.N, g.K, g.b_rs, 32, true);
+    CUtensorMap tmA = a_kmajor ? make_map(g.A, g.K, g.M, g.a_rs, BM, false, X3 != 0)
+                    : a_chunked ? make_chunked_map(g.A, g.M, g.K, g.a_cs, BM / 32, X3 != 0) : make_map(g.A, g.M, g.K, g.a_cs, 32, true, X3 != 0);
+    CUtensorMap tmB = b_kmajor ? make_map(g.B, g.K, g.N, g.b_cs, Cfg::kRowsB, false, X3 != 0)
+                    : b_chunked ? make_chunked_map(g.B, g.N, g.K, g.b_rs, Cfg::kRowsB / 32, X3 != 0) : make_map(g.B, g.N, g.K, g.b_rs, 32, true, X3 != 0);
     TcArgs t;
     t.a_chunked = a_chunked ? 1 : 0; t.b_chunked = b_chunked ? 1 : 0;
     t.M = g.M; t.N = g.N; t.K = g.K; t.a_kmajor = a_kmajor; t.b_kmajor = b_kmajor;
@@ -547,7 +655,7 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3(PAIR ? 2 * walkers : walkers);
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(Cfg::kThreads);
     cfg.dynamicSmemBytes = Cfg::kSmem;
     cfg.stream = stream();
     cudaLaunchAttribute attr;
@@ -555,9 +663,9 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     attr.val.clusterDim.x = PAIR ? 2 : 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr; cfg.numAttrs = 1;
     prof_begin(0);
-    CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<BN, PAIR>, tmA, tmB, tmC, t));
+    CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<BN, PAIR, X3>, tmA, tmB, tmC, t));
     prof_work(2.0 * g.M * g.N * g.K);
-    LAUNCHED("gemm_tf32_kernel");
+    LAUNCHED(X3 ? "gemm_3xtf32_kernel" : "gemm_tf32_kernel");
     prof_end(0, 2.0 * g.M * g.N * g.K);
     if (splits > 1) {
         const bool v4 = g.N % 4 == 0 && g.c_rs % 4 == 0 && ((uintptr_t)g.C & 15) == 0 && ((uintptr_t)t.C & 15) == 0 &&
@@ -572,15 +680,16 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     }
 }
 
-static void run_tc(const GemmArgs &g) {
+template <int X3> static void run_tc_as(const GemmArgs &g) {
     bool a_k = g.a_cs == 1, b_k = g.b_rs == 1;
     // a [M,1]-shaped or [1,K]-shaped operand satisfies both; prefer K-major
     static int pair_ok = -1;
     if (pair_ok < 0) { const char *e = getenv("DNN_CUDA_GEMM_PAIR"); pair_ok = (e && e[0] == '0') ? 0 : 1; }
-    if (g.N > 128 && g.M > 128 && pair_ok) launch_tc<256, true>(g, a_k, b_k);
-    else if (g.N > 128) launch_tc<256, false>(g, a_k, b_k);
-    else launch_tc<128, false>(g, a_k, b_k);
+    if (g.N > 128 && g.M > 128 && pair_ok) launch_tc<256, true, X3>(g, a_k, b_k);
+    else if (g.N > 128) launch_tc<256, false, X3>(g, a_k, b_k);
+    else launch_tc<128, false, X3>(g, a_k, b_k);
 }
+static void run_tc(const GemmArgs &g) { run_tc_as<0>(g); }
 
 // Packed copies big/small of an operand, laid out row-major over its contiguous dimension.
 static void split_operand(const float *p, int64_t rs, int64_t cs, int64_t rows, int64_t cols, float *big, float *small,
@@ -597,6 +706,22 @@ void gemm_tc(const GemmArgs &in, bool split3) {
     bool ok = normalise(in, g);
     DNN_CHECK(ok, "gemm_tc called with an unsupported layout");
     if (!split3) { run_tc(g); return; }
+    static int chain = -1, fused = -1;
+    if (chain < 0) { const char *e = getenv("DNN_CUDA_3X_CHAIN_KB"); chain = e ? atoi(e) : 16; }
+    if (fused < 0) { const char *e = getenv("DNN_CUDA_3X_FUSED"); fused = e ? atoi(e) : 1; }
+    const bool exact_mode = gemm_mode() == DNN_CUDA_GEMM_3XTF32;
+    // One launch: raw tiles, split in shared memory, three products per K step.  Where the precision policy of the
+    // TF32 mode chose 3xTF32, all three go into one accumulator: that removes the operand rounding, which is all
+    // that is asked there.  In the exact mode the small terms get the second accumulator: with everything in one,
+    // the tensor core truncates the large sum three times per K step instead of once, and through a deep model
+    // that bias alone (measured 1.4e-5 .. 1.8e-5 on the gradients of the 64-image vision-LM step) exceeds 1e-5.
+    // DNN_CUDA_3X_FUSED: 1 as described (default), 0 the three launches with operands split in global memory.
+    if (fused) {
+        g_chain_kb = exact_mode ? chain : 0;
+        if (exact_mode) run_tc_as<2>(g); else run_tc_as<1>(g);     // a requested rotation or residual rides in the epilogue
+        g_chain_kb = 0;
+        return;
+    }
     g_rope.pending = false;            // an epilogue rotation cannot be split over the three partial products
     g_resid.pending = false;           // nor can a residual be added three times
     // 3xTF32: x = big + small with big exactly TF32; A*B ~= Ab*Bb + Ab*Bs + As*Bb, fp32 accumulation.
@@ -623,8 +748,6 @@ void gemm_tc(const GemmArgs &in, bool split3) {
     t.A = As; t.B = Bb; t.bias = nullptr; run_tc(t);
     t.accumulate = true;
     t.A = Ab; t.B = Bs; run_tc(t);
-    static int chain = -1;
-    if (chain < 0) { const char *e = getenv("DNN_CUDA_3X_CHAIN_KB"); chain = e ? atoi(e) : 16; }
     g_chain_kb = gemm_mode() == DNN_CUDA_GEMM_3XTF32 ? chain : 0;      // only the exact mode is after the last 1e-5
     t.A = Ab; t.B = Bb; t.bias = g.bias; run_tc(t);
     g_chain_kb = 0;

@@ -43,6 +43,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     }
     return false;
 }
+// The same for a barrier on which threads of the other CTA of a pair arrive (release at cluster
+// scope) after writing shared memory that this thread's MMAs read: acquire at cluster scope.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < kWaitSpins; it++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (it > 1024) __nanosleep(64);
+    }
+    return false;
+}
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");

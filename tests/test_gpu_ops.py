@@ -56,6 +56,55 @@ def test_tensor_core_modes_match_oracle(gpu, binding, case, mode, tol):
         gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
 
 
+X3_SHAPES = [  # (a shape, b shape, trans_b): one per tile configuration of the one-pass 3xTF32 kernel
+    ((100, 200), (200, 300), 0),      # at most 128 rows, wide output: single CTAs with 256-column tiles
+    ((100, 200), (300, 200), 1),
+    ((64, 4096), (4096, 64), 0),      # long K on few tiles: split-K partials and their reduction
+    ((520, 1000), (1000, 264), 0),    # CTA pairs, ragged in M, N and K, several k-blocks per stage ring
+    ((520, 1000), (264, 1000), 1),
+    ((2, 256, 96), (96, 128), 0),     # 128-column tiles
+]
+
+
+@pytest.mark.parametrize("sa,sb,tb", X3_SHAPES, ids=lambda v: str(v))
+@pytest.mark.parametrize("form", ["one-accumulator", "two-accumulators"])
+def test_3xtf32_products_hold_1e5_on_every_tile_configuration(gpu, binding, sa, sb, tb, form):
+    """Forward, dA and dW of a linear layer as 3xTF32 tensor-core products whatever their size (the kernel splits raw
+    tiles in shared memory).  one-accumulator: the form the TF32 mode's precision policy selects, here for every role;
+    two-accumulators: the exact mode's form, with its size rule switched off."""
+    from oracle import dnn_oracle as O
+    rng = np.random.default_rng(77)
+    n = sb[-2] if tb else sb[-1]
+    a = rng.standard_normal(sa).astype(np.float32)
+    b = (0.2 * rng.standard_normal(sb)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    g = rng.standard_normal(sa[:-1] + (n,)).astype(np.float32)
+    roles, max_flop = C.c_uint(0), C.c_double(0)
+    gpu.lib.dnn_cuda_get_tf32_policy(C.byref(roles), C.byref(max_flop))
+    simt = gpu.lib.dnn_cuda_get_exact_policy()
+    if form == "one-accumulator":
+        gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+        gpu.lib.dnn_cuda_set_tf32_policy(7, 0.0)
+    else:
+        gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_3XTF32)
+        gpu.lib.dnn_cuda_set_exact_policy(0.0)
+    try:
+        ta = gpu.tensor(a, gpu.scratch, True)
+        tw, tbias = gpu.param(b), gpu.param(bias)
+        y = gpu.lib.tensor_matmul_add(gpu.scratch, ta, tw, tb, tbias)
+        gpu.backward_from(y, g)
+        got = dict(y=gpu.download(y), da=gpu.download_grad(ta), db=gpu.download_grad(tw), dbias=gpu.download_grad(tbias))
+        gpu.reset_step()
+    finally:
+        gpu.lib.dnn_cuda_set_tf32_policy(roles.value, max_flop.value)
+        gpu.lib.dnn_cuda_set_exact_policy(simt)
+        gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
+    wy, wda, wdb, wdbias = O.matmul_add(a, b, tb, bias, g)
+    for name, want in (("y", wy), ("da", wda), ("db", wdb), ("dbias", wdbias)):
+        err = np.linalg.norm(got[name].astype(np.float64) - want) / np.linalg.norm(want)
+        assert err <= 1e-5, (name, err)
+
+
 def test_same_seed_twice_is_bit_identical(gpu, binding):
     """Determinism on one GPU: no atomics anywhere on the path."""
     gpu.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
