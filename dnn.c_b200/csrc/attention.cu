@@ -9,16 +9,19 @@
 // place of the reference's rowsum(P o dP) (the two are equal).
 //
 // This file holds the exact-fp32 kernels: 64x64 tiles staged in shared memory
-// (row-major, row pitch HD+1 floats so that the 16 rows a half-warp touches
-// fall in different banks), 256 threads, each thread owning rows ty+16*i and
-// columns tx+16*j of a tile.
+// (row-major, row pitch HD+4 floats: rows stay 16-byte aligned and the rows a
+// quarter-warp reads with one 128-bit load fall in different banks), 256 threads.
+// A score tile is owned as rows ty+16*i x columns tx+16*j; an output tile
+// ([64, d]) as rows ty+16*i (4*ty+i in the dK/dV kernel) x HD/16 adjacent
+// columns, so every inner loop reads shared memory 128 bits at a time: 8 loads
+// for 64 FMAs.
 #include "common.cuh"
 #include "device_utils.cuh"
 
 namespace dnnb {
 
 constexpr int TB = 64;           // tile rows (queries) and tile columns (keys)
-constexpr int PS = TB + 1;       // pitch of the probability tile
+constexpr int PS = TB + 4;       // pitch of the probability tile
 
 struct AttnParams {
     const float *q, *k, *v;      // [B,H,N,d]
@@ -45,36 +48,96 @@ __device__ __forceinline__ int visible_len(int i, int prefix, int nb) {
     return v < nb ? v : nb;
 }
 
-// Loads rows [r0, r0+TB) x d of a [N,d] slice into shared memory (pitch HD+1),
+// Loads rows [r0, r0+TB) x d of a [N,d] slice into shared memory (pitch HD+4),
 // zero-filling rows >= nrows and columns >= d.
 template <int HD>
 __device__ __forceinline__ void load_tile(float *sm, const float *g, int r0, int nrows, int d) {
+    constexpr int TP = HD + 4;
+    if ((d & 3) == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+        constexpr int C4 = HD / 4;
+        for (int idx = threadIdx.x; idx < TB * C4; idx += blockDim.x) {
+            int r = idx / C4, c = (idx - r * C4) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r0 + r < nrows && c < d) v = *reinterpret_cast<const float4 *>(g + (int64_t)(r0 + r) * d + c);
+            *reinterpret_cast<float4 *>(sm + r * TP + c) = v;
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < TB * HD; idx += blockDim.x) {
         int r = idx / HD, c = idx - r * HD;
         float v = 0.f;
         if (r0 + r < nrows && c < d) v = g[(int64_t)(r0 + r) * d + c];
-        sm[r * (HD + 1) + c] = v;
+        sm[r * TP + c] = v;
     }
 }
 
-// s[i][j] = sum_c A[ty+16i][c] * Bt[tx+16j][c]
+// The HD/16 output columns of thread column tx: adjacent, so one row's share is one 64- or 128-bit load
+// (two 128-bit loads, 64 columns apart, for HD = 128).
+template <int HD> __device__ __forceinline__ int col_of(int tx, int c) {
+    if (HD == 32) return 2 * tx + c;
+    if (HD == 64) return 4 * tx + c;
+    return (c < 4) ? 4 * tx + c : 64 + 4 * tx + (c - 4);
+}
+template <int HD> __device__ __forceinline__ void ld_cols(const float *row, int tx, float (&v)[HD / 16]) {
+    if (HD == 32) {
+        const float2 t = *reinterpret_cast<const float2 *>(row + 2 * tx);
+        v[0] = t.x; v[1] = t.y;
+    } else {
+        const float4 t = *reinterpret_cast<const float4 *>(row + 4 * tx);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        if (HD == 128) {
+            const float4 u = *reinterpret_cast<const float4 *>(row + 64 + 4 * tx);
+            v[4 % (HD / 16)] = u.x; v[5 % (HD / 16)] = u.y; v[6 % (HD / 16)] = u.z; v[7 % (HD / 16)] = u.w;
+        }
+    }
+}
+__device__ __forceinline__ float f4_at(const float4 &v, int k) { return k == 0 ? v.x : k == 1 ? v.y : k == 2 ? v.z : v.w; }
+
+// s[i][j] = sum_c A[ty+16i][c] * Bt[tx+16j][c], c ascending
 template <int HD>
 __device__ __forceinline__ void tile_dot(const float *A, const float *Bm, int ty, int tx, float s[4][4]) {
+    constexpr int TP = HD + 4;
 #pragma unroll
     for (int i = 0; i < 4; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) s[i][j] = 0.f;
-#pragma unroll 8
-    for (int c = 0; c < HD; c++) {
-        float a[4], b[4];
+#pragma unroll 4
+    for (int c = 0; c < HD; c += 4) {
+        float4 a[4], b[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) a[i] = A[(ty + 16 * i) * (HD + 1) + c];
+        for (int i = 0; i < 4; i++) a[i] = *reinterpret_cast<const float4 *>(A + (ty + 16 * i) * TP + c);
 #pragma unroll
-        for (int j = 0; j < 4; j++) b[j] = Bm[(tx + 16 * j) * (HD + 1) + c];
+        for (int j = 0; j < 4; j++) b[j] = *reinterpret_cast<const float4 *>(Bm + (tx + 16 * j) * TP + c);
 #pragma unroll
         for (int i = 0; i < 4; i++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) s[i][j] = fmaf(a[i], b[j], s[i][j]);
+            for (int j = 0; j < 4; j++) {
+                float t = s[i][j];
+                t = fmaf(a[i].x, b[j].x, t); t = fmaf(a[i].y, b[j].y, t);
+                t = fmaf(a[i].z, b[j].z, t); t = fmaf(a[i].w, b[j].w, t);
+                s[i][j] = t;
+            }
+    }
+}
+
+// acc[i][c] += sum_j W[ty+16i][j] * X[j][col_of(tx,c)] over the TB rows of X, j ascending
+template <int HD>
+__device__ __forceinline__ void tile_apply(const float *W, const float *X, int ty, int tx, float (&acc)[4][HD / 16]) {
+    constexpr int TP = HD + 4, CC = HD / 16;
+#pragma unroll 2
+    for (int j = 0; j < TB; j += 4) {
+        float4 w[4];
+        float x[4][CC];
+#pragma unroll
+        for (int i = 0; i < 4; i++) w[i] = *reinterpret_cast<const float4 *>(W + (ty + 16 * i) * PS + j);
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) ld_cols<HD>(X + (j + jj) * TP, tx, x[jj]);
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int c = 0; c < CC; c++) acc[i][c] = fmaf(f4_at(w[i], jj), x[jj][c], acc[i][c]);
     }
 }
 
@@ -92,8 +155,9 @@ __device__ __forceinline__ float half_warp_sum(float v) {
 // ---- forward -----------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(256) attn_fwd_kernel(AttnParams p) {
-    extern __shared__ float smem[];
-    float *Qs = smem, *Ks = Qs + TB * (HD + 1), *Vs = Ks + TB * (HD + 1), *Ps = Vs + TB * (HD + 1);
+    extern __shared__ __align__(16) float smem[];
+    constexpr int TP = HD + 4;
+    float *Qs = smem, *Ks = Qs + TB * TP, *Vs = Ks + TB * TP, *Ps = Vs + TB * TP;
     int b = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * TB;
     int nb = p.seq_lens ? p.seq_lens[b] : p.N;
     if (nb > p.N) nb = p.N;
@@ -155,18 +219,7 @@ __global__ void __launch_bounds__(256) attn_fwd_kernel(AttnParams p) {
             for (int c = 0; c < CC; c++) acc[i][c] *= corr;
         }
         __syncthreads();
-#pragma unroll 4
-        for (int j = 0; j < TB; j++) {
-            float pv[4], vv[CC];
-#pragma unroll
-            for (int i = 0; i < 4; i++) pv[i] = Ps[(ty + 16 * i) * PS + j];
-#pragma unroll
-            for (int c = 0; c < CC; c++) vv[c] = Vs[j * (HD + 1) + tx + 16 * c];
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int c = 0; c < CC; c++) acc[i][c] = fmaf(pv[i], vv[c], acc[i][c]);
-        }
+        tile_apply<HD>(Ps, Vs, ty, tx, acc);
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -176,7 +229,7 @@ __global__ void __launch_bounds__(256) attn_fwd_kernel(AttnParams p) {
         float inv = live ? 1.f / l[i] : 0.f;
 #pragma unroll
         for (int c = 0; c < CC; c++) {
-            int col = tx + 16 * c;
+            int col = col_of<HD>(tx, c);
             if (col < p.d) o[(int64_t)row * p.d + col] = live ? acc[i][c] * inv : 0.f;
         }
         if (tx == 0 && p.lse) p.lse[slice + row] = live ? m[i] + logf(l[i]) : 0.f;
@@ -221,8 +274,8 @@ __device__ __forceinline__ void recompute_p_ds(const AttnParams &p, const float 
 // One CTA per key tile: dK_j += sum_i dS_ij Q_i, dV_j += sum_i P_ij dO_i.
 template <int HD>
 __global__ void __launch_bounds__(256) attn_bwd_dkv_kernel(AttnParams p) {
-    extern __shared__ float smem[];
-    constexpr int TS = TB * (HD + 1);
+    extern __shared__ __align__(16) float smem[];
+    constexpr int TP = HD + 4, TS = TB * TP;
     float *Qs = smem, *Ks = Qs + TS, *Vs = Ks + TS, *dOs = Vs + TS, *Ps = dOs + TS, *dSs = Ps + TB * PS;
     float *lse_s = dSs + TB * PS, *d_s = lse_s + TB;
     int b = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * TB;
@@ -254,27 +307,28 @@ __global__ void __launch_bounds__(256) attn_bwd_dkv_kernel(AttnParams p) {
         __syncthreads();
         recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs, b, h);
         __syncthreads();
-        // this thread owns key rows ty+16*jj and feature columns tx+16*c
+        // this thread owns key rows 4*ty+jj (adjacent: their P and dS of one query are one 128-bit load each)
+        // and feature columns col_of(tx, c)
 #pragma unroll 4
         for (int i = 0; i < TB; i++) {
-            float pj[4], sj[4], go[CC], qq[CC];
-#pragma unroll
-            for (int jj = 0; jj < 4; jj++) { pj[jj] = Ps[i * PS + ty + 16 * jj]; sj[jj] = dSs[i * PS + ty + 16 * jj]; }
-#pragma unroll
-            for (int c = 0; c < CC; c++) { go[c] = dOs[i * (HD + 1) + tx + 16 * c]; qq[c] = Qs[i * (HD + 1) + tx + 16 * c]; }
+            const float4 pj = *reinterpret_cast<const float4 *>(Ps + i * PS + 4 * ty);
+            const float4 sj = *reinterpret_cast<const float4 *>(dSs + i * PS + 4 * ty);
+            float go[CC], qq[CC];
+            ld_cols<HD>(dOs + i * TP, tx, go);
+            ld_cols<HD>(Qs + i * TP, tx, qq);
 #pragma unroll
             for (int jj = 0; jj < 4; jj++)
 #pragma unroll
-                for (int c = 0; c < CC; c++) { dv[jj][c] = fmaf(pj[jj], go[c], dv[jj][c]); dk[jj][c] = fmaf(sj[jj], qq[c], dk[jj][c]); }
+                for (int c = 0; c < CC; c++) { dv[jj][c] = fmaf(f4_at(pj, jj), go[c], dv[jj][c]); dk[jj][c] = fmaf(f4_at(sj, jj), qq[c], dk[jj][c]); }
         }
     }
 #pragma unroll
     for (int jj = 0; jj < 4; jj++) {
-        int row = j0 + ty + 16 * jj;
+        int row = j0 + 4 * ty + jj;
         if (row >= nb) continue;
 #pragma unroll
         for (int c = 0; c < CC; c++) {
-            int col = tx + 16 * c;
+            int col = col_of<HD>(tx, c);
             if (col >= p.d) continue;
             int64_t at = (slice + row) * p.d + col;
             if (p.dk) p.dk[at] = (p.store & 2) ? dk[jj][c] : p.dk[at] + dk[jj][c];
@@ -286,8 +340,8 @@ __global__ void __launch_bounds__(256) attn_bwd_dkv_kernel(AttnParams p) {
 // One CTA per query tile: dQ_i += sum_j dS_ij K_j.
 template <int HD>
 __global__ void __launch_bounds__(256) attn_bwd_dq_kernel(AttnParams p) {
-    extern __shared__ float smem[];
-    constexpr int TS = TB * (HD + 1);
+    extern __shared__ __align__(16) float smem[];
+    constexpr int TP = HD + 4, TS = TB * TP;
     float *Qs = smem, *Ks = Qs + TS, *Vs = Ks + TS, *dOs = Vs + TS, *Ps = dOs + TS, *dSs = Ps + TB * PS;
     float *lse_s = dSs + TB * PS, *d_s = lse_s + TB;
     int b = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * TB;
@@ -320,18 +374,7 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_kernel(AttnParams p) {
         __syncthreads();
         recompute_p_ds<HD>(p, Qs, Ks, Vs, dOs, lse_s, d_s, i0, j0, nb, ty, tx, Ps, dSs, b, h);
         __syncthreads();
-#pragma unroll 4
-        for (int j = 0; j < TB; j++) {
-            float sv[4], kk[CC];
-#pragma unroll
-            for (int i = 0; i < 4; i++) sv[i] = dSs[(ty + 16 * i) * PS + j];
-#pragma unroll
-            for (int c = 0; c < CC; c++) kk[c] = Ks[j * (HD + 1) + tx + 16 * c];
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int c = 0; c < CC; c++) dq[i][c] = fmaf(sv[i], kk[c], dq[i][c]);
-        }
+        tile_apply<HD>(dSs, Ks, ty, tx, dq);
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -339,14 +382,14 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_kernel(AttnParams p) {
         if (row >= nb) continue;
 #pragma unroll
         for (int c = 0; c < CC; c++) {
-            int col = tx + 16 * c;
+            int col = col_of<HD>(tx, c);
             if (col < p.d) { int64_t at = (slice + row) * p.d + col; p.dq[at] = (p.store & 1) ? dq[i][c] : p.dq[at] + dq[i][c]; }
         }
     }
 }
 
-template <int HD> static size_t fwd_smem() { return (size_t)(3 * TB * (HD + 1) + TB * PS) * 4; }
-template <int HD> static size_t bwd_smem() { return (size_t)(4 * TB * (HD + 1) + 2 * TB * PS + 2 * TB) * 4; }
+template <int HD> static size_t fwd_smem() { return (size_t)(3 * TB * (HD + 4) + TB * PS) * 4; }
+template <int HD> static size_t bwd_smem() { return (size_t)(4 * TB * (HD + 4) + 2 * TB * PS + 2 * TB) * 4; }
 
 template <int HD>
 static void attn_fwd_launch(const AttnParams &p) {

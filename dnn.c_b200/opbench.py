@@ -129,11 +129,15 @@ def main():
     ap.add_argument("--shapes", default="", help="matmul_shapes only: indices of the shapes to run, e.g. 0,1,2,3")
     ap.add_argument("--rows", type=int, default=0, help="rows of the row-wise operators instead of 8192 (65536 makes every tensor larger than L2)")
     ap.add_argument("--batch", type=int, default=0, help="cnn_step / cnn_ops: images per batch instead of 512")
+    ap.add_argument("--roles-3x", type=int, default=-1,
+                    help="tf32 mode: bit set of the products that run as 3xTF32 (1 forward, 2 activation gradient, 4 weight gradient; 3 = strict)")
     args = ap.parse_args()
     B = load_binding()
     pm, sm = (int(x) for x in args.pools_mb.split(","))
     b = Bench(B, args.iters, args.small, pm, sm)
     b.lib.dnn_cuda_set_gemm_mode({"fp32": 0, "tf32": 1, "3xtf32": 2}[args.gemm])
+    if args.roles_3x >= 0:
+        b.lib.dnn_cuda_set_tf32_policy(args.roles_3x, 4e9)
     run_ops(b, args.op.split(","), args)
     b.d.close()
 
