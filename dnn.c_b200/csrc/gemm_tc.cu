@@ -51,6 +51,7 @@ struct TcArgs {
     int accumulate;
     int a_kmajor, b_kmajor;
     int splits, kb_per_split;          // split-K: work unit = (tile, split)
+    int chained;                       // the splits of a tile run one after the other on the tile's CTA and add into C
     int tiles_m, tiles_n;
     int n_fastest;                     // tile order: consecutive work units walk along N (1) or along M (0)
     int a_chunked, b_chunked;          // MN-major operand described as {32, K, extent/32}: one TMA copy per stage
@@ -84,6 +85,20 @@ __device__ __forceinline__ float tf32_small(float v) {
 __device__ __forceinline__ void tile_of(const TcArgs &g, int tile, int &tm, int &tn) {
     if (g.n_fastest) { tm = tile / g.tiles_n; tn = tile - tm * g.tiles_n; }
     else { tn = tile / g.tiles_m; tm = tile - tn * g.tiles_m; }
+}
+
+// The n-th work unit of a walker.  Split-K proper deals (tile, split) units round robin, so the pieces of a tile run
+// on different CTAs and meet in a buffer of partials.  Chained: a walker takes whole tiles and runs their pieces
+// one after the other; each piece has its own accumulator chain and the pieces meet in C itself.
+__device__ __forceinline__ bool unit_at(const TcArgs &g, int n, int walker, int walkers, int num_tiles, int &tile, int &split) {
+    if (g.chained) {
+        tile = walker + (n / g.splits) * walkers;
+        split = n % g.splits;
+        return tile < num_tiles;
+    }
+    const int u = walker + n * walkers;
+    tile = u / g.splits; split = u - tile * g.splits;
+    return u < num_tiles * g.splits;
 }
 
 template <int BN, bool PAIR, int X3>
@@ -130,15 +145,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_tiles = g.tiles_m * g.tiles_n;
-    const int num_units = num_tiles * g.splits;
     const int num_kb_total = (g.K + BK - 1) / BK;
 
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int u = walker; u < num_units && ok; u += walkers) {
-                int tile = u / g.splits, split = u - tile * g.splits;
+            int tile, split;
+            for (int n = 0; ok && unit_at(g, n, walker, walkers, num_tiles, tile, split); n++) {
                 int tm, tn;
                 tile_of(g, tile, tm, tn);
                 int m0 = tm * kTileM + (int)rank * BM;
@@ -188,9 +202,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint64_t a_adv = (g.a_kmajor ? UMMA_K * 4 : 1024) >> 4, b_adv = (g.b_kmajor ? UMMA_K * 4 : 1024) >> 4;   // per K=8 step
             int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
-            for (int u = walker; u < num_units && ok; u += walkers) {
-                int tile = u / g.splits, split = u - tile * g.splits;
-                (void)tile;
+            int tile, split;
+            for (int n = 0; ok && unit_at(g, n, walker, walkers, num_tiles, tile, split); n++) {
                 int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
                 if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) { atomicCAS(&g_gemm_error, 0, 0x200 | acc); break; }
                 tc_fence_after();
@@ -235,8 +248,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int t = (int)threadIdx.x - kGemmThreads;
         int stage = 0; uint32_t phase = 0;
         bool ok = true;
-        for (int u = walker; u < num_units && ok; u += walkers) {
-            int split = u % g.splits;
+        int tile, split;
+        for (int n = 0; ok && unit_at(g, n, walker, walkers, num_tiles, tile, split); n++) {
             int kb0 = split * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, num_kb_total);
             for (int kb = kb0; kb < kb1; kb++) {
                 if (!mbar_wait(&full[stage], phase)) { if (lane == 0) atomicCAS(&g_gemm_error, 0, 0x500 | stage); ok = false; break; }
@@ -268,8 +281,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int q = warp & 3;
         int acc = 0; uint32_t acc_phase = 0;
         uint32_t chunk = 0;
-        for (int u = walker; u < num_units; u += walkers) {
-            int tile = u / g.splits, split = u - tile * g.splits;
+        int tile, split;
+        for (int n = 0; unit_at(g, n, walker, walkers, num_tiles, tile, split); n++) {
             int tm, tn;
             tile_of(g, tile, tm, tn);
             int m0 = tm * kTileM + (int)rank * BM, n0 = tn * BN;
@@ -279,6 +292,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tc_fence_after();
             const int row0 = m0 + q * 32;
             const bool use_bias = g.bias != nullptr && split == 0;
+            // chained: the first piece of a tile is stored (or added to the C that was there), every later piece is
+            // added by the copy engine in L2, after this warp's earlier writes to the same rows have completed
+            const bool add_to_c = g.chained ? (g.accumulate != 0 || split > 0) : (g.accumulate != 0);
+            const int plane = g.chained ? 0 : split;
+            if (g.chained && split > 0) {
+                if (lane == 0) bulk_wait<0>();
+                __syncwarp();
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -344,7 +365,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                    if (col0 < g.N && row0 < g.M) tma_store_3d(&tmC, buf, col0, row0, split, g.accumulate != 0);
+                    if (col0 < g.N && row0 < g.M) tma_store_3d(&tmC, buf, col0, row0, plane, add_to_c);
                     bulk_commit();
                 }
                 chunk++;
@@ -631,10 +652,18 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     const int slots = PAIR ? kNumSMs / 2 : kNumSMs;      // work units in flight: one per CTA, or per CTA pair
     // split-K when the output has too few tiles to fill the SMs and K is long
     int splits = choose_splits(tiles, slots, num_kb, g.M, g.N);
-    if (g_chain_kb > 0 && (num_kb + splits - 1) / splits > g_chain_kb) splits = (num_kb + g_chain_kb - 1) / g_chain_kb;
+    bool chained = false;
+    if (g_chain_kb > 0 && (num_kb + splits - 1) / splits > g_chain_kb) {
+        // Pieces only because of the chain limit, with enough tiles to fill the SMs anyway: a tile's pieces run back to
+        // back on its CTA and add into C through L2 (fixed order, so still deterministic) instead of meeting in a
+        // buffer of partials that another kernel sums.
+        chained = splits == 1;
+        splits = (num_kb + g_chain_kb - 1) / g_chain_kb;
+    }
     t.kb_per_split = (num_kb + splits - 1) / splits;
     splits = (num_kb + t.kb_per_split - 1) / t.kb_per_split;
     t.splits = splits;
+    t.chained = chained ? 1 : 0;
     t.resid = nullptr; t.resid_ld = 0;
     if (g_resid.pending && splits == 1 && !g.accumulate && aligned16(g_resid.r) && g_resid.ld % 4 == 0) {
         t.resid = g_resid.r; t.resid_ld = g_resid.ld;
@@ -646,12 +675,12 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
         t.rope_c = g_rope.fc; t.rope_s = g_rope.fs; t.rope_N = g_rope.N; t.rope_d = g_rope.d; t.rope_cols = g_rope.cols;
         g_rope.pending = false; g_rope.honoured = true;
     }
-    if (splits == 1) { t.C = g.C; t.ldc = g.c_rs; t.bias = g.bias; t.accumulate = g.accumulate ? 1 : 0; }
+    if (splits == 1 || chained) { t.C = g.C; t.ldc = g.c_rs; t.bias = g.bias; t.accumulate = g.accumulate ? 1 : 0; }
     else { t.ldc = (g.N + 3) & ~(int64_t)3;      // rows of the partials padded to 16 bytes: the copy engine's stride rule
            t.C = scratch((size_t)splits * g.M * t.ldc * 4); t.bias = nullptr; t.accumulate = 0; }
-    int units = tiles * splits;
+    int units = chained ? tiles : tiles * splits;
     int walkers = units < slots ? units : slots;
-    CUtensorMap tmC = make_out_map(t.C, g.N, g.M, t.ldc, splits);
+    CUtensorMap tmC = make_out_map(t.C, g.N, g.M, t.ldc, chained ? 1 : splits);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3(PAIR ? 2 * walkers : walkers);
@@ -667,7 +696,7 @@ static void launch_tc(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     prof_work(2.0 * g.M * g.N * g.K);
     LAUNCHED(X3 ? "gemm_3xtf32_kernel" : "gemm_tf32_kernel");
     prof_end(0, 2.0 * g.M * g.N * g.K);
-    if (splits > 1) {
+    if (splits > 1 && !chained) {
         const bool v4 = g.N % 4 == 0 && g.c_rs % 4 == 0 && ((uintptr_t)g.C & 15) == 0 && ((uintptr_t)t.C & 15) == 0 &&
                         (!g.bias || ((uintptr_t)g.bias & 15) == 0);
         if (v4)
