@@ -286,6 +286,10 @@ def reference_arm(args, B, rank):
 
 
 # ── workloads: each returns step(resident) -> loss tensor, units per step and per-step host batches ──
+# The end-to-end loop takes its batches from a ring of HOST_RING different batches that were built in pinned host
+# memory before the clock started (the place a data loader would leave them); fill_host(step) only picks the slot,
+# so the timed region holds the upload, the step and the read-back, not numpy's random generator.
+HOST_RING = 4
 class LmWorkload:
     def __init__(self, dnn, B, rank, dp):
         self.dnn, self.B, self.rank, self.cfg = dnn, B, rank, CFG
@@ -294,21 +298,24 @@ class LmWorkload:
         self.units = CFG["B"] * CFG["N"]
         self.step_fn = lib.dnn_cuda_dp_decoder_lm_train_step if dp else lib.decoder_lm_train_step
         self.h2d = self.units * 4
-        self.pinned = lib.dnn_cuda_host_alloc(self.h2d)
-        self.pinned_np = np.ctypeslib.as_array(C.cast(self.pinned, C.POINTER(C.c_int32)), shape=(CFG["B"], CFG["N"]))
+        self.pinned = lib.dnn_cuda_host_alloc(HOST_RING * self.h2d)
+        ring = np.ctypeslib.as_array(C.cast(self.pinned, C.POINTER(C.c_int32)), shape=(HOST_RING, CFG["B"], CFG["N"]))
+        for i in range(HOST_RING):
+            ring[i] = token_batch(CFG, rank, 1000 + i)
+        self.slot = 0
         self.resident = dnn.tensor(token_batch(CFG, rank, 0), dnn.params)        # params pool: survives reset_step
         self.describe = {"workload": "gpt124m-shaped decoder LM train step (BASELINE config 5)", "vocab": CFG["V"], "d_model": CFG["D"],
                          "n_layers": CFG["L"], "n_heads": CFG["H"], "ffn_hidden": CFG["F"], "micro_batch_per_gpu": CFG["B"],
                          "seq_len": CFG["N"]}
 
     def fill_host(self, step):
-        self.pinned_np[...] = token_batch(CFG, self.rank, step)
+        self.slot = step % HOST_RING
 
     def step(self, from_host):
         lib, dnn, cfg = self.dnn.lib, self.dnn, self.cfg
         if from_host:
             ids = lib.tensor_scratch(dnn.data, 2, self.B.ints([cfg["B"], cfg["N"]]), 0)
-            lib.dnn_cuda_upload(ids, self.pinned, self.h2d)
+            lib.dnn_cuda_upload(ids, C.c_void_p(C.cast(self.pinned, C.c_void_p).value + self.slot * self.h2d), self.h2d)
         else:
             ids = self.resident
         tgt = lib.decoder_lm_shift_targets(dnn.data, ids)
@@ -333,27 +340,31 @@ class VlmWorkload:
         self.step_fn = lib.dnn_cuda_dp_vision_lm_train_step_padded if dp else lib.vision_lm_train_step_padded
         n_img, n_txt = c["B"] * 3 * c["img"] * c["img"], c["B"] * c["Tmax"]
         self.h2d = n_img * 4 + 3 * n_txt * 4
-        self.pinned = lib.dnn_cuda_host_alloc(self.h2d)
-        base = C.cast(self.pinned, C.c_void_p).value
-        self.h_img = np.ctypeslib.as_array(C.cast(base, C.POINTER(C.c_float)), shape=(c["B"], 3, c["img"], c["img"]))
-        self.h_ids = np.ctypeslib.as_array(C.cast(base + n_img * 4, C.POINTER(C.c_int32)), shape=(c["B"], c["Tmax"]))
-        self.h_tgt = np.ctypeslib.as_array(C.cast(base + n_img * 4 + n_txt * 4, C.POINTER(C.c_int32)), shape=(c["B"], c["Tmax"]))
-        self.h_mask = np.ctypeslib.as_array(C.cast(base + n_img * 4 + 2 * n_txt * 4, C.POINTER(C.c_float)), shape=(c["B"], c["Tmax"]))
+        self.pinned = lib.dnn_cuda_host_alloc(HOST_RING * self.h2d)
+        self.slots = []
+        for i in range(HOST_RING):
+            base = C.cast(self.pinned, C.c_void_p).value + i * self.h2d
+            h_img = np.ctypeslib.as_array(C.cast(base, C.POINTER(C.c_float)), shape=(c["B"], 3, c["img"], c["img"]))
+            h_ids = np.ctypeslib.as_array(C.cast(base + n_img * 4, C.POINTER(C.c_int32)), shape=(c["B"], c["Tmax"]))
+            h_tgt = np.ctypeslib.as_array(C.cast(base + n_img * 4 + n_txt * 4, C.POINTER(C.c_int32)), shape=(c["B"], c["Tmax"]))
+            h_mask = np.ctypeslib.as_array(C.cast(base + n_img * 4 + 2 * n_txt * 4, C.POINTER(C.c_float)), shape=(c["B"], c["Tmax"]))
+            rng = np.random.default_rng([c["seed"] + rank, i])
+            h_img[...] = rng.standard_normal(h_img.shape, dtype=np.float32)
+            lens = rng.integers(8, c["Tmax"] + 1, size=c["B"]).astype(np.int32)
+            h_ids[...] = rng.integers(0, c["V"], size=h_ids.shape)
+            h_tgt[...] = rng.integers(0, c["V"], size=h_tgt.shape)
+            h_mask[...] = (np.arange(c["Tmax"])[None, :] < (lens[:, None] - 1))
+            self.slots.append((h_img, h_ids, h_tgt, h_mask, lens))
         self.fill_host(0)
         P = dnn.params
         self.resident = (dnn.tensor(self.h_img.copy(), P), dnn.tensor(self.h_ids.copy(), P), dnn.tensor(self.h_tgt.copy(), P), dnn.tensor(self.h_mask.copy(), P))
+        self.resident_lens = self.lens
         self.describe = {"workload": "prefix-LM vision LM train step (BASELINE config 4)", "images_per_gpu": c["B"], "image": "3x224x224",
                          "image_tokens": 196, "text_tokens_max": c["Tmax"], "vocab": c["V"], "d_model": c["D"], "n_layers": c["L"],
                          "n_heads": c["H"], "ffn_hidden": c["F"]}
 
     def fill_host(self, step):
-        c = C4
-        rng = np.random.default_rng([c["seed"] + self.rank, step])
-        self.h_img[...] = rng.standard_normal(self.h_img.shape, dtype=np.float32)
-        self.lens = rng.integers(8, c["Tmax"] + 1, size=c["B"]).astype(np.int32)
-        self.h_ids[...] = rng.integers(0, c["V"], size=self.h_ids.shape)
-        self.h_tgt[...] = rng.integers(0, c["V"], size=self.h_tgt.shape)
-        self.h_mask[...] = (np.arange(c["Tmax"])[None, :] < (self.lens[:, None] - 1))
+        self.h_img, self.h_ids, self.h_tgt, self.h_mask, self.lens = self.slots[step % HOST_RING]
 
     def step(self, from_host):
         lib, dnn, c = self.dnn.lib, self.dnn, C4
@@ -365,7 +376,8 @@ class VlmWorkload:
         else:
             ts = self.resident
         gn = C.c_float(0)
-        return self.step_fn(dnn.scratch, self.vlm, ts[0], ts[1], ts[2], ts[3], self.lens.ctypes.data_as(C.POINTER(C.c_int)),
+        lens = self.lens if from_host else self.resident_lens
+        return self.step_fn(dnn.scratch, self.vlm, ts[0], ts[1], ts[2], ts[3], lens.ctypes.data_as(C.POINTER(C.c_int)),
                             self.opt, 1.0, C.byref(gn))
 
 
@@ -383,19 +395,23 @@ class CnnWorkload:
         self.opt = lib.adamw_create(dnn.params, self.arr, len(self.params), 1e-3, 0.9, 0.999, 1e-8, 0.01)
         self.units = n
         self.h2d = n * 784 * 4 + n * 4
-        self.pinned = lib.dnn_cuda_host_alloc(self.h2d)
-        base = C.cast(self.pinned, C.c_void_p).value
-        self.h_x = np.ctypeslib.as_array(C.cast(base, C.POINTER(C.c_float)), shape=(n, 1, 28, 28))
-        self.h_y = np.ctypeslib.as_array(C.cast(base + n * 784 * 4, C.POINTER(C.c_int32)), shape=(n,))
+        self.pinned = lib.dnn_cuda_host_alloc(HOST_RING * self.h2d)
+        self.slots = []
+        for i in range(HOST_RING):
+            base = C.cast(self.pinned, C.c_void_p).value + i * self.h2d
+            h_x = np.ctypeslib.as_array(C.cast(base, C.POINTER(C.c_float)), shape=(n, 1, 28, 28))
+            h_y = np.ctypeslib.as_array(C.cast(base + n * 784 * 4, C.POINTER(C.c_int32)), shape=(n,))
+            rng = np.random.default_rng([C3["seed"] + rank, i])
+            h_x[...] = rng.random(h_x.shape, dtype=np.float32)
+            h_y[...] = rng.integers(0, 10, size=h_y.shape)
+            self.slots.append((h_x, h_y))
         self.fill_host(0)
         self.resident = (dnn.tensor(self.h_x.copy(), dnn.params), dnn.tensor(self.h_y.copy(), dnn.params))
         self.describe = {"workload": "MNIST-shaped CNN train step (BASELINE config 3)", "images_per_gpu": n, "image": "1x28x28",
                          "layers": "conv3x3(1->32) relu avgpool2 conv3x3(32->64) relu avgpool2 linear(3136->128) relu linear(128->10)"}
 
     def fill_host(self, step):
-        rng = np.random.default_rng([C3["seed"] + self.rank, step])
-        self.h_x[...] = rng.random(self.h_x.shape, dtype=np.float32)
-        self.h_y[...] = rng.integers(0, 10, size=self.h_y.shape)
+        self.h_x, self.h_y = self.slots[step % HOST_RING]
 
     def step(self, from_host):
         lib, dnn, n = self.dnn.lib, self.dnn, C3["B"]
@@ -549,6 +565,10 @@ def main():
 
     # ── end to end: batch from pinned host memory every step, loss read back every step ──
     losses = []
+    for s in range(2):      # untimed: the first upload creates the data pool's device arena (a cudaMalloc, tens of ms once)
+        w.fill_host(s)
+        lib.dnn_cuda_download(w.step(True), loss_host.ctypes.data, 4)
+        reset()
     barrier()
     t_e2e0 = time.perf_counter()
     lib.dnn_cuda_timer_start()
@@ -647,7 +667,8 @@ def main():
                            l2_flush="inputs larger than L2 (the step touches tens of GB of activations)" if args.config != 3 else
                                     "the step's activations (about 0.5 GB) are larger than L2"),
             "roofline": roof,
-            "e2e": {"value": round(e2e_value, 1), "unit": unit, "h2d_bytes_per_step": int(w.h2d), "d2h_bytes_per_step": 4},
+            "e2e": {"value": round(e2e_value, 1), "unit": unit, "h2d_bytes_per_step": int(w.h2d), "d2h_bytes_per_step": 4,
+                    "host_batches": "ring of %d different batches prebuilt in pinned host memory; every step uploads one and reads its loss back" % HOST_RING},
             "gpu_launches": int(launches), "clocks": clocks, "loss_first_last": [losses[0], losses[-1]] if losses else None,
             "scratch_peak_gb": round(scratch_peak / 2 ** 30, 2),
         }
