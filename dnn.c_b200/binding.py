@@ -254,7 +254,7 @@ GEMM_FP32, GEMM_TF32, GEMM_3XTF32 = 0, 1, 2
 ATTENTION_CAUSAL, ATTENTION_PREFIX_LM = 0, 1
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-B200_LIB = os.path.join(HERE, "libdnn_b200.so")
+B200_LIB = os.environ.get("DNN_B200_LIB") or os.path.join(HERE, "libdnn_b200.so")       # another build of the library, for A/B timing
 
 
 def _ints(seq):

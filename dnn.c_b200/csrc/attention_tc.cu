@@ -161,7 +161,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * BM;
+    // grid = (batch x heads, query tiles): CTAs are dispatched x-fastest, so all heads' LAST query tiles -- which
+    // see the most keys under the causal and prefix rules -- go first and the shortest CTAs fill the tail
+    const int b = (int)blockIdx.x / p.H, h = (int)blockIdx.x % p.H, i0 = (int)(gridDim.y - 1 - blockIdx.y) * BM;
     int nb = p.seq_lens ? p.seq_lens[b] : p.N;
     if (nb > p.N) nb = p.N;
     float *o = p.o.p + (int64_t)b * p.o.sb + (int64_t)h * p.o.sh;
@@ -389,7 +391,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_co
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * BKEY;
+    // grid = (batch x heads, key tiles): the first key tiles are seen by the most queries and are dispatched first
+    const int b = (int)blockIdx.x / p.H, h = (int)blockIdx.x % p.H, j0 = (int)blockIdx.y * BKEY;
     int nb = p.seq_lens ? p.seq_lens[b] : p.N;
     if (nb > p.N) nb = p.N;
     if (j0 >= nb) return;
@@ -608,7 +611,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_con
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * BM;
+    // grid = (batch x heads, query tiles): CTAs are dispatched x-fastest, so all heads' LAST query tiles -- which
+    // see the most keys under the causal and prefix rules -- go first and the shortest CTAs fill the tail
+    const int b = (int)blockIdx.x / p.H, h = (int)blockIdx.x % p.H, i0 = (int)(gridDim.y - 1 - blockIdx.y) * BM;
     int nb = p.seq_lens ? p.seq_lens[b] : p.N;
     if (nb > p.N) nb = p.N;
     if (i0 >= nb) return;
@@ -757,6 +762,188 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_con
     if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem, Cfg::kTmemCols); }
 }
 
+// ════════════════════════ backward: dQ, two CTAs per SM ════════════════════════
+// The same work split as the kernel above, but lean enough for two CTAs to share an SM: one score
+// buffer instead of three (256 TMEM columns per CTA), one slot per operand ring instead of two
+// (112 KB of tiles per CTA).  Inside a CTA a tile then runs strictly in sequence -- S and dP, the
+// threads' dS, dQ -- and it is the OTHER CTA's products that keep the tensor core busy meanwhile; its
+// start-up (Q and dO, 64 KB) and its final dQ store hide behind the neighbour in the same way.
+template <int HD>
+struct Dq2Cfg {
+    static constexpr int BM = 128, BN = 64, KB = HD / 32;
+    static constexpr int kQ = KB * BM * 128;               // Q and dO tiles, K-major A operands
+    static constexpr int kKk = KB * BN * 128;              // K / V of one key tile, K-major B
+    static constexpr int kKm = KB * BN * 128;              // K of the same tile, MN-major B
+    static constexpr int kTiles = 2 * kQ + 2 * kKk + kKm;
+    // Two CTAs of head size 64 fit an SM only if tiles + padding + barriers stay within 113 KB each: the
+    // array is declared 1024-byte aligned and up to kPad bytes of round-up are tolerated; a base further
+    // off than that is reported as an error instead of running over the allocation.
+    static constexpr int kPad = 768;
+    static constexpr int kSmem = kTiles + kPad + 256;
+    static constexpr int kTmemCols = 256;                  // S 0.. ; dP/dS 64.. ; dQ 128..
+    static constexpr int kThreads = 352;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(352, 2)
+attn_bwd_dq2_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_constant__ CUtensorMap tmGa,
+                      const __grid_constant__ CUtensorMap tmKk, const __grid_constant__ CUtensorMap tmVk,
+                      const __grid_constant__ CUtensorMap tmKm, AttnTcParams p) {
+    using Cfg = Dq2Cfg<HD>;
+    constexpr int BM = Cfg::BM, BN = Cfg::BN, KB = Cfg::KB;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    if (smem - smem_raw > Cfg::kPad) {          // the same for every thread: nobody has touched a barrier or TMEM yet
+        if (threadIdx.x == 0) atomicCAS(&g_attn_error, 0, 0x3ff);
+        return;
+    }
+    uint8_t *sQ = smem, *sG = sQ + Cfg::kQ, *sKk = sG + Cfg::kQ, *sVk = sKk + Cfg::kKk, *sKm = sVk + Cfg::kKk;
+    uint64_t *bars = (uint64_t *)(sKm + Cfg::kKm);
+    // every barrier completes once per tile, so the completion that belongs to tile t has parity t & 1
+    uint64_t *bar_qg = bars, *in1_full = bars + 1, *in2_full = bars + 2, *bar_o = bars + 3, *bar_s = bars + 4, *bar_p = bars + 5;
+    uint32_t *tmem_slot = (uint32_t *)(bars + 6);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // grid = (batch x heads, query tiles): CTAs are dispatched x-fastest, so all heads' LAST query tiles -- which
+    // see the most keys under the causal and prefix rules -- go first and the shortest CTAs fill the tail
+    const int b = (int)blockIdx.x / p.H, h = (int)blockIdx.x % p.H, i0 = (int)(gridDim.y - 1 - blockIdx.y) * BM;
+    int nb = p.seq_lens ? p.seq_lens[b] : p.N;
+    if (nb > p.N) nb = p.N;
+    if (i0 >= nb) return;
+    const int64_t slice = (int64_t)(b * p.H + h) * p.N;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_qg, 1);
+        mbar_init(in1_full, 1); mbar_init(in2_full, 1); mbar_init(bar_o, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 8);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t t_s = tmem, t_dp = tmem + 64, t_dq = tmem + 128;
+
+    const int i_last = min(i0 + BM, nb) - 1;
+    const int jmax = vis_len(i_last, p.prefix, nb);
+    const int n_iter = (jmax + BN - 1) / BN;
+    bool ok = true;
+
+    if (warp == 8) {
+        if (lane == 0) {                 // ---- loader of Q, dO and of K, V K-major (their slot is free when S/dP of tile t-1 are done)
+            mbar_expect_tx(bar_qg, 2 * Cfg::kQ);
+            for (int kb = 0; kb < KB; kb++) {
+                tma_load_4d(sQ + kb * BM * 128, &tmQa, kb * 32, i0, h, b, bar_qg);
+                tma_load_4d(sG + kb * BM * 128, &tmGa, kb * 32, i0, h, b, bar_qg);
+            }
+            for (int t = 0; t < n_iter && ok; t++) {
+                const int jt = t * BN;
+                if (t >= 1) CTRL_WAIT(bar_s, (uint32_t)(t - 1) & 1u, 0x341)
+                if (!ok) break;
+                mbar_expect_tx(in1_full, 2 * Cfg::kKk);
+                for (int kb = 0; kb < KB; kb++) {
+                    tma_load_4d(sKk + kb * BN * 128, &tmKk, kb * 32, jt, h, b, in1_full);
+                    tma_load_4d(sVk + kb * BN * 128, &tmVk, kb * 32, jt, h, b, in1_full);
+                }
+            }
+        }
+    } else if (warp == 10) {
+        if (lane == 0) {                 // ---- loader of K MN-major (free when dQ of tile t-1 is done)
+            for (int t = 0; t < n_iter && ok; t++) {
+                const int jt = t * BN;
+                if (t >= 1) CTRL_WAIT(bar_o, (uint32_t)(t - 1) & 1u, 0x342)
+                if (!ok) break;
+                mbar_expect_tx(in2_full, Cfg::kKm);
+                for (int c = 0; c < KB; c++) tma_load_4d(sKm + c * BN * 128, &tmKm, c * 32, jt, h, b, in2_full);
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {                 // ---- MMA issuer
+            const uint32_t id_s = make_idesc_tf32(BN, false, false), id_q = make_idesc_tf32(HD, false, true);
+            const uint64_t dQ0 = kmajor_desc(smem_u32(sQ), BM, 0), dG0 = kmajor_desc(smem_u32(sG), BM, 0);
+            const uint64_t dKk0 = kmajor_desc(smem_u32(sKk), BN, 0);
+            const uint64_t dVk0 = kmajor_desc(smem_u32(sVk), BN, 0);
+            const uint64_t dKm0 = mnmajor_desc(smem_u32(sKm), BN, 0);
+            CTRL_WAIT(bar_qg, 0, 0x351)
+            for (int t = 0; t < n_iter && ok; t++) {
+                const uint32_t par = (uint32_t)t & 1u;
+                CTRL_WAIT(in1_full, par, 0x353)
+                if (t >= 1) CTRL_WAIT(bar_o, par ^ 1u, 0x354)          // dQ(t-1) has read dS(t-1): the score buffers are free
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 8; kk++) tc_mma_tf32(t_s, dQ0 + kmajor_step(BM, kk), dKk0 + kmajor_step(BN, kk), id_s, kk > 0);
+#pragma unroll
+                for (int kk = 0; kk < HD / 8; kk++) tc_mma_tf32(t_dp, dG0 + kmajor_step(BM, kk), dVk0 + kmajor_step(BN, kk), id_s, kk > 0);
+                tc_commit(bar_s);
+                CTRL_WAIT(bar_p, par, 0x355)
+                CTRL_WAIT(in2_full, par, 0x356)
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BN / 8; kk++)
+                    tc_mma_tf32_ts(t_dq, t_dp + kk * 8, dKm0 + mnmajor_step(kk), id_q, (t > 0 || kk > 0));
+                tc_commit(bar_o);
+            }
+        }
+    } else {
+        const int q4 = warp & 3, hq = warp >> 2;
+        const int r = q4 * 32 + lane, row = i0 + r;
+        const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+        const bool live = row < nb;
+        const int vis = live ? vis_len(row, p.prefix, nb) : 0;
+        const float sl2 = p.scale * 1.4426950408889634f;
+        const float lse2 = live ? p.lse_in[slice + row] * 1.4426950408889634f : 0.f;
+        const float dvec_s = live ? p.dvec[slice + row] * p.scale : 0.f;
+        const int vis_min = __reduce_min_sync(0xffffffffu, vis);
+        for (int t = 0; t < n_iter; t++) {
+            WARP_WAIT(bar_s, (uint32_t)t & 1u, 0x361);
+            if (ok) {
+                tc_fence_after();
+                uint32_t s[32], dp[32];
+                const uint32_t a_s = t_s + lane_base + hq * 32, a_dp = a_s + 64;
+                tc_ld32(a_s, s);
+                tc_ld32(a_dp, dp);
+                const int jb = t * BN + hq * 32;
+                if (jb + 32 <= vis_min) {          // all 32 keys visible to every row of the warp: no mask tests
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float pe = fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -lse2));
+                        dp[j] = tf32_bits(pe * fmaf(__uint_as_float(dp[j]), p.scale, -dvec_s));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float pe = (jb + j < vis) ? fast_exp2(fmaf(__uint_as_float(s[j]), sl2, -lse2)) : 0.f;
+                        dp[j] = tf32_bits(pe * fmaf(__uint_as_float(dp[j]), p.scale, -dvec_s));
+                    }
+                }
+                tc_st32(a_dp, dp);          // dS over dP
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_p);
+            }
+        }
+        if (ok) {
+            WARP_WAIT(bar_o, (uint32_t)(n_iter - 1) & 1u, 0x363);
+            tc_fence_after();
+            const int c0 = hq * 32;
+            if (ok && c0 < HD) {
+                uint32_t a[32];
+                tc_ld32(t_dq + lane_base + c0, a);
+                if (live && p.rope_c) unrotate32<HD>(a, p.rope_c, p.rope_s, row, c0);
+                if (live) emit_row32(p.dq.p + (int64_t)b * p.dq.sb + (int64_t)h * p.dq.sh + (int64_t)row * p.dq.sn + c0, a, (p.store & 1) != 0);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem, Cfg::kTmemCols); }
+}
+
 // ════════════════════════════════ host side ════════════════════════════════
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -820,7 +1007,7 @@ static void fwd_launch(const AttnHost &a) {
                 tv = map4d(a.v, a.B, a.H, a.N, HD, Cfg::BN, true);
     AttnTcParams p; memset(&p, 0, sizeof p);
     p.o = a.o; p.lse = a.lse; p.seq_lens = a.seq_lens; p.B = a.B; p.H = a.H; p.N = a.N; p.prefix = a.prefix; p.scale = a.scale;
-    dim3 grid((a.N + Cfg::BM - 1) / Cfg::BM, a.H, a.B);
+    dim3 grid(a.B * a.H, (a.N + Cfg::BM - 1) / Cfg::BM);
     attn_fwd_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tq, tk, tv, p);
     prof_work(4.0 * HD * visible_pairs(a));                      // S = Q K^T and O = P V
     LAUNCHED("attn_fwd_tc_kernel");
@@ -836,6 +1023,7 @@ static void bwd_launch(const AttnHost &a) {
     if (!once) {
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HD>::kSmem));
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<HD>::kSmem));
+        CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq2_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq2Cfg<HD>::kSmem));
         once = true;
     }
     if (a.dk.p || a.dv.p) {
@@ -843,7 +1031,7 @@ static void bwd_launch(const AttnHost &a) {
         CUtensorMap tka = map4d(a.k, a.B, a.H, a.N, HD, Cfg::BKEY, false), tva = map4d(a.v, a.B, a.H, a.N, HD, Cfg::BKEY, false);
         CUtensorMap tqk = map4d(a.q, a.B, a.H, a.N, HD, Cfg::BQ, false), tgk = map4d(a.dout, a.B, a.H, a.N, HD, Cfg::BQ, false);
         CUtensorMap tqm = map4d(a.q, a.B, a.H, a.N, HD, Cfg::BQ, true), tgm = map4d(a.dout, a.B, a.H, a.N, HD, Cfg::BQ, true);
-        dim3 grid((a.N + Cfg::BKEY - 1) / Cfg::BKEY, a.H, a.B);
+        dim3 grid(a.B * a.H, (a.N + Cfg::BKEY - 1) / Cfg::BKEY);
         attn_bwd_dkv_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tka, tva, tqk, tgk, tqm, tgm, p);
         prof_work(6.0 * HD * visible_pairs(a));                  // dV, dP, dK (the recomputed S is not counted)
         LAUNCHED("attn_bwd_dkv_tc_kernel");
@@ -853,8 +1041,12 @@ static void bwd_launch(const AttnHost &a) {
         CUtensorMap tqa = map4d(a.q, a.B, a.H, a.N, HD, Cfg::BM, false), tga = map4d(a.dout, a.B, a.H, a.N, HD, Cfg::BM, false);
         CUtensorMap tkk = map4d(a.k, a.B, a.H, a.N, HD, Cfg::BN, false), tvk = map4d(a.v, a.B, a.H, a.N, HD, Cfg::BN, false);
         CUtensorMap tkm = map4d(a.k, a.B, a.H, a.N, HD, Cfg::BN, true);
-        dim3 grid((a.N + Cfg::BM - 1) / Cfg::BM, a.H, a.B);
-        attn_bwd_dq_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tqa, tga, tkk, tvk, tkm, p);
+        dim3 grid(a.B * a.H, (a.N + Cfg::BM - 1) / Cfg::BM);
+        // DNN_CUDA_ATTN_DQ: 2 (default) two lean CTAs per SM, 1 one CTA per SM with three score buffers and two-slot rings
+        static int lean = -1;
+        if (lean < 0) { const char *e = getenv("DNN_CUDA_ATTN_DQ"); lean = (e && e[0] == '1') ? 0 : 1; }
+        if (lean) attn_bwd_dq2_tc_kernel<HD><<<grid, Dq2Cfg<HD>::kThreads, Dq2Cfg<HD>::kSmem, stream()>>>(tqa, tga, tkk, tvk, tkm, p);
+        else attn_bwd_dq_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tqa, tga, tkk, tvk, tkm, p);
         prof_work(2.0 * HD * visible_pairs(a));                  // dQ (recomputed S and dP not counted)
         LAUNCHED("attn_bwd_dq_tc_kernel");
     }
