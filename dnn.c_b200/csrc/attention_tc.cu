@@ -51,6 +51,7 @@ struct AttnTcParams {
     int store;                           // bit 0/1/2: dq/dk/dv are written, not added to
     const float *rope_c, *rope_s;        // backward: [N, d/2] tables; when set, dQ and dK leave the kernel rotated back
                                          // (the gradient of the RoPE that produced Q and K), which needs store mode
+    int tma_out;                         // backward: gradients leave through the copy engine (tile store / tile add)
 };
 
 __device__ __forceinline__ int vis_len(int i, int prefix, int nb) {
@@ -129,6 +130,16 @@ __device__ __forceinline__ void emit_row32(float *dst, const uint32_t (&a)[32], 
         v.x += __uint_as_float(a[j]); v.y += __uint_as_float(a[j + 1]); v.z += __uint_as_float(a[j + 2]); v.w += __uint_as_float(a[j + 3]);
         d4[j >> 2] = v;
     }
+}
+
+// The same 32 x 32 piece (one row of 32 floats per lane) written as a 128-byte-swizzled tile for the copy engine:
+// 16-byte piece j of row `lane` lands at piece j ^ (lane & 7).  One tile store (or tile add) then writes whole
+// 128-byte row segments, where 32 lanes storing 16 bytes each to 32 different rows cost 32 transactions per instruction
+// (measured: the dK/dV kernel spent 6-11 thousand cycles per CTA issuing those stores).
+__device__ __forceinline__ void stage_tile32(uint8_t *tile, const uint32_t (&a)[32], int lane) {
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        *reinterpret_cast<uint4 *>(tile + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_uint4(a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
 }
 
 // ════════════════════════════════ forward ════════════════════════════════
@@ -375,7 +386,8 @@ template <int HD>
 __global__ void __launch_bounds__(352, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_constant__ CUtensorMap tmVa,
                        const __grid_constant__ CUtensorMap tmQk, const __grid_constant__ CUtensorMap tmGk,
-                       const __grid_constant__ CUtensorMap tmQm, const __grid_constant__ CUtensorMap tmGm, AttnTcParams p) {
+                       const __grid_constant__ CUtensorMap tmQm, const __grid_constant__ CUtensorMap tmGm,
+                       const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV, AttnTcParams p) {
     using Cfg = DkvCfg<HD>;
     constexpr int BKEY = Cfg::BKEY, BQ = Cfg::BQ, KB = Cfg::KB;
     extern __shared__ uint8_t smem_raw[];
@@ -567,11 +579,28 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmKa, const __grid_co
                 uint32_t a[32], c[32];
                 tc_ld32(t_dv + lane_base + c0, a);
                 tc_ld32(t_dk + lane_base + c0, c);
-                if (p.dv.p && key < nb)
-                    emit_row32(p.dv.p + (int64_t)b * p.dv.sb + (int64_t)h * p.dv.sh + (int64_t)key * p.dv.sn + c0, a, (p.store & 4) != 0);
                 if (p.dk.p && key < nb && p.rope_c) unrotate32<HD>(c, p.rope_c, p.rope_s, key, c0);
-                if (p.dk.p && key < nb)
-                    emit_row32(p.dk.p + (int64_t)b * p.dk.sb + (int64_t)h * p.dk.sh + (int64_t)key * p.dk.sn + c0, c, (p.store & 2) != 0);
+                if (p.tma_out) {
+                    // every product has completed (bar_o of the last tile), so the operand rings are free: two staging
+                    // tiles per warp in ring 2.  Keys at or beyond the sequence's length have exact zero rows (their
+                    // probabilities are zero) and only occur in add mode; rows beyond N are clipped by the copy engine.
+                    uint8_t *st = sQm + (hq * 4 + q4) * 8192;
+                    stage_tile32(st, a, lane);
+                    stage_tile32(st + 4096, c, lane);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (p.dv.p) tma_store_4d(&tmDV, st, c0, j0 + q4 * 32, h, b, (p.store & 4) == 0);
+                        if (p.dk.p) tma_store_4d(&tmDK, st + 4096, c0, j0 + q4 * 32, h, b, (p.store & 2) == 0);
+                        bulk_commit();
+                        bulk_wait<0>();
+                    }
+                } else {
+                    if (p.dv.p && key < nb)
+                        emit_row32(p.dv.p + (int64_t)b * p.dv.sb + (int64_t)h * p.dv.sh + (int64_t)key * p.dv.sn + c0, a, (p.store & 4) != 0);
+                    if (p.dk.p && key < nb)
+                        emit_row32(p.dk.p + (int64_t)b * p.dk.sb + (int64_t)h * p.dk.sh + (int64_t)key * p.dk.sn + c0, c, (p.store & 2) != 0);
+                }
             }
         }
     }
@@ -787,8 +816,8 @@ struct Dq2Cfg {
 template <int HD>
 __global__ void __launch_bounds__(352, 2)
 attn_bwd_dq2_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_constant__ CUtensorMap tmGa,
-                      const __grid_constant__ CUtensorMap tmKk, const __grid_constant__ CUtensorMap tmVk,
-                      const __grid_constant__ CUtensorMap tmKm, AttnTcParams p) {
+                       const __grid_constant__ CUtensorMap tmKk, const __grid_constant__ CUtensorMap tmVk,
+                       const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmDQ, AttnTcParams p) {
     using Cfg = Dq2Cfg<HD>;
     constexpr int BM = Cfg::BM, BN = Cfg::BN, KB = Cfg::KB;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -935,7 +964,19 @@ attn_bwd_dq2_tc_kernel(const __grid_constant__ CUtensorMap tmQa, const __grid_co
                 uint32_t a[32];
                 tc_ld32(t_dq + lane_base + c0, a);
                 if (live && p.rope_c) unrotate32<HD>(a, p.rope_c, p.rope_s, row, c0);
-                if (live) emit_row32(p.dq.p + (int64_t)b * p.dq.sb + (int64_t)h * p.dq.sh + (int64_t)row * p.dq.sn + c0, a, (p.store & 1) != 0);
+                if (p.tma_out) {            // all products are done: the Q tile's shared memory stages the output (see the dK/dV kernel)
+                    uint8_t *st = sQ + (hq * 4 + q4) * 4096;
+                    stage_tile32(st, a, lane);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_4d(&tmDQ, st, c0, i0 + q4 * 32, h, b, (p.store & 1) == 0);
+                        bulk_commit();
+                        bulk_wait<0>();
+                    }
+                } else if (live) {
+                    emit_row32(p.dq.p + (int64_t)b * p.dq.sb + (int64_t)h * p.dq.sh + (int64_t)row * p.dq.sn + c0, a, (p.store & 1) != 0);
+                }
             }
         }
     }
@@ -972,6 +1013,19 @@ static CUtensorMap map4d(const HeadView &v, int B, int H, int N, int d, int box_
                              mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled (attention) failed (%d)\n", (int)r); abort(); }
+    return m;
+}
+
+// The same view as the destination of 32 x 32 tile stores (rows beyond N are clipped).
+static CUtensorMap map4d_out(const HeadView &v, int B, int H, int N, int d) {
+    CUtensorMap m;
+    cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)v.sn * 4, (cuuint64_t)v.sh * 4, (cuuint64_t)v.sb * 4};
+    cuuint32_t box[4] = {32, 32, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)v.p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "dnn_b200: cuTensorMapEncodeTiled (attention output) failed (%d)\n", (int)r); abort(); }
     return m;
 }
 
@@ -1032,7 +1086,12 @@ static void bwd_launch(const AttnHost &a) {
         CUtensorMap tqk = map4d(a.q, a.B, a.H, a.N, HD, Cfg::BQ, false), tgk = map4d(a.dout, a.B, a.H, a.N, HD, Cfg::BQ, false);
         CUtensorMap tqm = map4d(a.q, a.B, a.H, a.N, HD, Cfg::BQ, true), tgm = map4d(a.dout, a.B, a.H, a.N, HD, Cfg::BQ, true);
         dim3 grid(a.B * a.H, (a.N + Cfg::BKEY - 1) / Cfg::BKEY);
-        attn_bwd_dkv_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tka, tva, tqk, tgk, tqm, tgm, p);
+        // gradients leave as tile stores when their views can be described to the copy engine (16-byte aligned base and strides)
+        static int tma_epilogue = -1;
+        if (tma_epilogue < 0) { const char *e = getenv("DNN_CUDA_ATTN_TMA_OUT"); tma_epilogue = (e && e[0] == '0') ? 0 : 1; }
+        p.tma_out = tma_epilogue && (!a.dk.p || view_ok(a.dk)) && (!a.dv.p || view_ok(a.dv));
+        CUtensorMap tdk = map4d_out(a.dk.p && p.tma_out ? a.dk : a.k, a.B, a.H, a.N, HD), tdv = map4d_out(a.dv.p && p.tma_out ? a.dv : a.v, a.B, a.H, a.N, HD);
+        attn_bwd_dkv_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tka, tva, tqk, tgk, tqm, tgm, tdk, tdv, p);
         prof_work(6.0 * HD * visible_pairs(a));                  // dV, dP, dK (the recomputed S is not counted)
         LAUNCHED("attn_bwd_dkv_tc_kernel");
     }
@@ -1045,7 +1104,11 @@ static void bwd_launch(const AttnHost &a) {
         // DNN_CUDA_ATTN_DQ: 2 (default) two lean CTAs per SM, 1 one CTA per SM with three score buffers and two-slot rings
         static int lean = -1;
         if (lean < 0) { const char *e = getenv("DNN_CUDA_ATTN_DQ"); lean = (e && e[0] == '1') ? 0 : 1; }
-        if (lean) attn_bwd_dq2_tc_kernel<HD><<<grid, Dq2Cfg<HD>::kThreads, Dq2Cfg<HD>::kSmem, stream()>>>(tqa, tga, tkk, tvk, tkm, p);
+        static int tma_epilogue = -1;
+        if (tma_epilogue < 0) { const char *e = getenv("DNN_CUDA_ATTN_TMA_OUT"); tma_epilogue = (e && e[0] == '0') ? 0 : 1; }
+        p.tma_out = lean && tma_epilogue && view_ok(a.dq);
+        CUtensorMap tdq = map4d_out(p.tma_out ? a.dq : a.q, a.B, a.H, a.N, HD);
+        if (lean) attn_bwd_dq2_tc_kernel<HD><<<grid, Dq2Cfg<HD>::kThreads, Dq2Cfg<HD>::kSmem, stream()>>>(tqa, tga, tkk, tvk, tkm, tdq, p);
         else attn_bwd_dq_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tqa, tga, tkk, tvk, tkm, p);
         prof_work(2.0 * HD * visible_pairs(a));                  // dQ (recomputed S and dP not counted)
         LAUNCHED("attn_bwd_dq_tc_kernel");
