@@ -160,7 +160,7 @@ struct FwdCfg {
 template <int HD>
 __global__ void __launch_bounds__(192, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, AttnTcParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, AttnTcParams p) {
     using Cfg = FwdCfg<HD>;
     constexpr int BM = Cfg::BM, BN = Cfg::BN, KB = Cfg::KB;
     extern __shared__ uint8_t smem_raw[];
@@ -350,7 +350,29 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc_fence_after();
             if (ok) fold_pv(n_iter - 1, corr_prev);
         }
-        if (ok && row < p.N) {
+        if (ok && p.tma_out) {
+            // every product has completed, so the Q tile's shared memory stages the output: one 32 x 32 tile per
+            // 32 columns and warp, handed to the copy engine (rows beyond N are clipped, rows beyond the
+            // sequence's length are written as zeros like before)
+            const bool live = row < nb;
+            const float inv = live ? 1.f / l : 0.f;
+            uint8_t *st = sQ + warp * (HD / 32) * 4096;
+#pragma unroll
+            for (int cc = 0; cc < HD / 32; cc++) {
+                uint32_t a[32];
+#pragma unroll
+                for (int j = 0; j < 32; j++) a[j] = __float_as_uint(acc[cc * 32 + j] * inv);
+                stage_tile32(st + cc * 4096, a, lane);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                for (int cc = 0; cc < HD / 32; cc++) tma_store_4d(&tmO, st + cc * 4096, cc * 32, i0 + warp * 32, h, b, false);
+                bulk_commit();
+                bulk_wait<0>();
+            }
+            if (p.lse && row < p.N) p.lse[slice + row] = live ? (m + log2f(l)) * 0.6931471805599453f : 0.f;
+        } else if (ok && row < p.N) {
             const bool live = row < nb;
             const float inv = live ? 1.f / l : 0.f;
             float4 *dst = reinterpret_cast<float4 *>(o + (int64_t)row * p.o.sn);
@@ -1062,7 +1084,11 @@ static void fwd_launch(const AttnHost &a) {
     AttnTcParams p; memset(&p, 0, sizeof p);
     p.o = a.o; p.lse = a.lse; p.seq_lens = a.seq_lens; p.B = a.B; p.H = a.H; p.N = a.N; p.prefix = a.prefix; p.scale = a.scale;
     dim3 grid(a.B * a.H, (a.N + Cfg::BM - 1) / Cfg::BM);
-    attn_fwd_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tq, tk, tv, p);
+    static int tma_epilogue = -1;
+    if (tma_epilogue < 0) { const char *e = getenv("DNN_CUDA_ATTN_TMA_OUT"); tma_epilogue = (e && e[0] == '0') ? 0 : 1; }
+    p.tma_out = tma_epilogue && view_ok(a.o);
+    CUtensorMap to = map4d_out(p.tma_out ? a.o : a.q, a.B, a.H, a.N, HD);
+    attn_fwd_tc_kernel<HD><<<grid, Cfg::kThreads, Cfg::kSmem, stream()>>>(tq, tk, tv, to, p);
     prof_work(4.0 * HD * visible_pairs(a));                      // S = Q K^T and O = P V
     LAUNCHED("attn_fwd_tc_kernel");
 }
