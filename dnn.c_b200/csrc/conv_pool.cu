@@ -43,7 +43,6 @@ __global__ void __launch_bounds__(256) im2col_taps_kernel(const float *__restric
             const int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
             off[t] = (t < KK && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? ih * g.W + iw : -1;
         }
-#pragma unroll 2
         for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
             const float *src = x + ((int64_t)n * g.C + c) * plane;
             float *dst = col + (int64_t)c * KK * g.M + (int64_t)n * HoWo + o;
@@ -116,7 +115,6 @@ __global__ void __launch_bounds__(256) col2im_taps_kernel(const float *__restric
             if (oh >= g.H_out || ow >= g.W_out) continue;
             pos[t] = oh * g.W_out + ow;
         }
-#pragma unroll 2
         for (int n = blockIdx.x * blockDim.y + threadIdx.y; n < g.N; n += gridDim.x * blockDim.y) {
             const float *src = dcol + (int64_t)c * KK * g.M + (int64_t)n * HoWo;      // tap t: + t * M
             float s = 0.f;
