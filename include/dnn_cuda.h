@@ -62,8 +62,9 @@ int  dnn_cuda_get_gemm_mode(void);
  *   roles_3x    GEMM kinds that take the 3xTF32 path: bit 0 forward products (Y = A B), bit 1 activation
  *               gradients (dA = dY B^T), bit 2 weight gradients (dW = A^T dY) -- of matmul, matmul_add and
  *               conv2d.  Default 0.  roles_3x = 3 ("strict") is what brings every parameter gradient of a
- *               12-block transformer within 1e-3 of the reference (plain TF32: up to 1.9e-3), at about twice
- *               the GEMM time.
+ *               12-block transformer within 1e-3 of the reference (plain TF32: up to 1.9e-3); such a product
+ *               takes three times the tensor-core time of a TF32 one (one kernel that splits the raw
+ *               operand tiles in shared memory), the step about 1.7 times as long.
  *   max_flop_3x every GEMM of a CONVOLUTION (forward, input gradient, filter gradient) of at most this many FLOP
  *               (2 M N K) takes the 3xTF32 path.  Default 4e9: with reductions of 9 .. 288 and 32 .. 64 output
  *               channels these products use a fraction of the tensor core and are bound by the traffic of the
@@ -73,6 +74,10 @@ int  dnn_cuda_get_gemm_mode(void);
  * 3xTF32 mode (dnn_cuda_set_exact_policy):
  *   simt_max_flop  every GEMM of at most this many FLOP takes the fp32 FMA kernel.  Default 8e9.
  * Environment: DNN_CUDA_TF32_3X_ROLES, DNN_CUDA_TF32_3X_MAX_GFLOP, DNN_CUDA_3X_SIMT_MAX_GFLOP.
+ * Switches for measuring against earlier forms of a kernel, read once at the first launch: DNN_CUDA_3X_FUSED=0
+ * (3xTF32 as three launches over operands split in global memory), DNN_CUDA_ATTN_DQ=1 (attention dQ with one
+ * CTA per SM), DNN_CUDA_ATTN_TMA_OUT=0 (attention outputs and gradients stored by the threads instead of the
+ * copy engine), DNN_CUDA_GEMM_PAIR=0 (no CTA pairs).  None of them changes a result beyond rounding.
  * No counterpart in the reference. */
 int  dnn_cuda_set_tf32_policy(unsigned roles_3x, double max_flop_3x);
 int  dnn_cuda_get_tf32_policy(unsigned *roles_3x, double *max_flop_3x);

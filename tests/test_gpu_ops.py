@@ -166,3 +166,18 @@ def test_second_backward_accumulates(gpu, binding, case):
     factor = 1.0 if case.name.startswith(OVERWRITING) else 2.0
     want = {k: (v * factor if k.startswith("d") else v) for k, v in want.items()}
     compare(case, got, want)
+
+
+def test_attention_kernel_variants_behind_switches_match_oracle():
+    """The tensor-core attention has two forms that the defaults do not run: the dQ kernel with one CTA per SM, and
+    gradients / outputs written by the threads themselves (taken when a view cannot be described to the copy engine).
+    Both are selected by environment switches read at the first launch, so the cases run in a child process."""
+    import subprocess
+    import sys
+    env = dict(os.environ, DNN_CUDA_ATTN_DQ="1", DNN_CUDA_ATTN_TMA_OUT="0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_ops.py"), "-q", "-x", "-p", "no:cacheprovider",
+                        "-k", "test_tensor_core_modes_match_oracle and attention and tf32 and not 3xtf32"],
+                       capture_output=True, text=True, timeout=900, env=env, cwd=root)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout and "failed" not in r.stdout, r.stdout[-2000:]
