@@ -394,7 +394,11 @@ template <int HD> static size_t bwd_smem() { return (size_t)(4 * TB * (HD + 4) +
 template <int HD>
 static void attn_fwd_launch(const AttnParams &p) {
     static bool once = false;
-    if (!once) { CUDA_OK(cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem<HD>())); once = true; }
+    if (!once) {
+        CUDA_OK(cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem<HD>()));
+        CUDA_OK(cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        once = true;
+    }
     dim3 grid((p.N + TB - 1) / TB, p.H, p.B);
     attn_fwd_kernel<HD><<<grid, 256, fwd_smem<HD>(), stream()>>>(p);
     LAUNCHED("attn_fwd_kernel");
@@ -405,6 +409,8 @@ static void attn_bwd_launch(const AttnParams &p) {
     if (!once) {
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem<HD>()));
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem<HD>()));
+        CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         once = true;
     }
     dim3 grid((p.N + TB - 1) / TB, p.H, p.B);

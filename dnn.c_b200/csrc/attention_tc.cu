@@ -1078,7 +1078,13 @@ template <int HD>
 static void fwd_launch(const AttnHost &a) {
     using Cfg = FwdCfg<HD>;
     static bool once = false;
-    if (!once) { CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem)); once = true; }
+    if (!once) {
+        CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        // two CTAs per SM need the largest shared-memory carve-out; left to the driver's choice, the kernel sometimes
+        // ran with room for one (forward 2.1 instead of 1.4 ms per step in one run out of several)
+        CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        once = true;
+    }
     CUtensorMap tq = map4d(a.q, a.B, a.H, a.N, HD, Cfg::BM, false), tk = map4d(a.k, a.B, a.H, a.N, HD, Cfg::BN, false),
                 tv = map4d(a.v, a.B, a.H, a.N, HD, Cfg::BN, true);
     AttnTcParams p; memset(&p, 0, sizeof p);
@@ -1104,6 +1110,7 @@ static void bwd_launch(const AttnHost &a) {
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HD>::kSmem));
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<HD>::kSmem));
         CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq2_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq2Cfg<HD>::kSmem));
+        CUDA_OK(cudaFuncSetAttribute(attn_bwd_dq2_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         once = true;
     }
     if (a.dk.p || a.dv.p) {

@@ -355,7 +355,11 @@ static void launch_bwd(const float *x, const float *w, const float *g, const flo
     const size_t smem = staged_smem(d);
     if (staged_ok(d)) {
         static bool once = false;
-        if (!once) { CUDA_OK(cudaFuncSetAttribute(norm_bwd_staged_kernel<LN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)); once = true; }
+        if (!once) {
+            CUDA_OK(cudaFuncSetAttribute(norm_bwd_staged_kernel<LN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+            CUDA_OK(cudaFuncSetAttribute(norm_bwd_staged_kernel<LN, T>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            once = true;
+        }
         norm_bwd_staged_kernel<LN, T><<<grid, kWarpsPerCta * 32, smem, stream()>>>(x, w, g, mean, rstd, dx, dwp, dbp, rows, d, addend);
         prof_work((addend ? 16.0 : 12.0) * rows * d);            // read x, g (and the residual gradient), write dx
         LAUNCHED(LN ? "layernorm_bwd_kernel" : "rmsnorm_bwd_kernel");
