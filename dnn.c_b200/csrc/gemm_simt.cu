@@ -88,6 +88,157 @@ void gemm_simt(const GemmArgs &g) {
     }
 }
 
+// ---- products with at most four output rows (a decoding step: one token per sequence) ----------------------
+// Such a product reads its whole weight matrix to produce a few thousand numbers: it is bound by the bandwidth at which
+// W streams in, and a 64- or 128-row tile kernel gives it a handful of CTAs (9 for a [1,768] x [768,2304] product).
+// Two fp32 kernels that put every SM on the stream instead:
+//   W with N contiguous ([K,N], a linear layer's weight): a thread owns four adjacent columns and walks a slice of K
+//     (x staged in shared memory), the slices' partial sums are added in fixed order by gemv_reduce_kernel;
+//   W with K contiguous ([N,K], the tied vocabulary projection): a warp owns one output column.
+constexpr int kGemvRows = 4, kGemvSlice = 256, kGemvSplits = 32;
+
+template <int MM>
+__global__ void __launch_bounds__(128)
+gemv_kn_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restrict__ W, int64_t w_rs, float *__restrict__ part,
+               int N, int K, int k_per_split, int vec) {
+    __shared__ float xs[MM][kGemvSlice];
+    const int k0 = blockIdx.y * k_per_split, k1 = min(K, k0 + k_per_split);
+    for (int i = threadIdx.x; i < MM * (k1 - k0); i += blockDim.x) {
+        int m = i / (k1 - k0), k = i - m * (k1 - k0);
+        xs[m][k] = x[(int64_t)m * x_rs + k0 + k];
+    }
+    __syncthreads();
+    const int n = (blockIdx.x * 128 + threadIdx.x) * 4;
+    if (n >= N) return;
+    float acc[MM][4];
+#pragma unroll
+    for (int m = 0; m < MM; m++) { acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f; }
+    if (vec) {
+#pragma unroll 4
+        for (int k = k0; k < k1; k++) {
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(W + (int64_t)k * w_rs + n));
+#pragma unroll
+            for (int m = 0; m < MM; m++) {
+                const float xv = xs[m][k - k0];
+                acc[m][0] = fmaf(xv, w.x, acc[m][0]); acc[m][1] = fmaf(xv, w.y, acc[m][1]);
+                acc[m][2] = fmaf(xv, w.z, acc[m][2]); acc[m][3] = fmaf(xv, w.w, acc[m][3]);
+            }
+        }
+    } else {
+        for (int k = k0; k < k1; k++) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (n + j >= N) break;
+                const float w = W[(int64_t)k * w_rs + n + j];
+#pragma unroll
+                for (int m = 0; m < MM; m++) acc[m][j] = fmaf(xs[m][k - k0], w, acc[m][j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MM; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (n + j < N) part[((int64_t)blockIdx.y * MM + m) * N + n + j] = acc[m][j];
+}
+
+__global__ void gemv_reduce_kernel(float *__restrict__ C, int64_t c_rs, const float *__restrict__ part, int splits, int M, int N,
+                                   const float *__restrict__ bias, int accumulate) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * N) return;
+    const int m = i / N, n = i - m * N;
+    float s = 0.f;
+    for (int k = 0; k < splits; k++) s += part[((int64_t)k * M + m) * N + n];
+    if (bias) s += bias[n];
+    float *c = C + (int64_t)m * c_rs + n;
+    *c = accumulate ? *c + s : s;
+}
+
+template <int MM>
+__global__ void __launch_bounds__(256)
+gemv_nk_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restrict__ W, int64_t w_cs, float *__restrict__ C, int64_t c_rs,
+               int N, int K, const float *__restrict__ bias, int accumulate, int vec) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const float *w = W + (int64_t)n * w_cs;
+    float acc[MM];
+#pragma unroll
+    for (int m = 0; m < MM; m++) acc[m] = 0.f;
+    if (vec) {
+        for (int k = lane * 4; k < K; k += 128) {
+            const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + k));
+#pragma unroll
+            for (int m = 0; m < MM; m++) {
+                const float4 xv = *reinterpret_cast<const float4 *>(x + (int64_t)m * x_rs + k);
+                acc[m] = fmaf(xv.x, wv.x, acc[m]); acc[m] = fmaf(xv.y, wv.y, acc[m]);
+                acc[m] = fmaf(xv.z, wv.z, acc[m]); acc[m] = fmaf(xv.w, wv.w, acc[m]);
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32)
+#pragma unroll
+            for (int m = 0; m < MM; m++) acc[m] = fmaf(x[(int64_t)m * x_rs + k], w[k], acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < MM; m++) {
+        float s = warp_sum(acc[m]);
+        if (lane == 0) {
+            if (bias) s += bias[n];
+            float *c = C + (int64_t)m * c_rs + n;
+            *c = accumulate ? *c + s : s;
+        }
+    }
+}
+
+static bool gemv_applicable(const GemmArgs &g) {
+    return g.batch == 1 && g.M >= 1 && g.M <= kGemvRows && g.a_cs == 1 && g.c_cs == 1 && g.K >= 64 && g.N >= 64 &&
+           (g.b_cs == 1 || g.b_rs == 1);
+}
+
+static void gemv(const GemmArgs &g) {
+    if (g.b_cs == 1) {                                            // [K,N], N contiguous
+        const int blocks_n = (g.N + 511) / 512;
+        int splits = (2 * kNumSMs + blocks_n - 1) / blocks_n;
+        if (splits > kGemvSplits) splits = kGemvSplits;
+        int kps = (g.K + splits - 1) / splits;
+        if (kps > kGemvSlice) kps = kGemvSlice;
+        if (kps < 8) kps = 8;
+        splits = (g.K + kps - 1) / kps;
+        static float *part = nullptr; static size_t cap = 0;
+        const size_t need = (size_t)splits * g.M * g.N * sizeof(float);
+        if (need > cap) {
+            CUDA_OK(cudaStreamSynchronize(stream()));
+            if (part) CUDA_OK(cudaFree(part));
+            cap = need + (need >> 1);
+            CUDA_OK(cudaMalloc((void **)&part, cap));
+        }
+        const int vec = (g.N % 4 == 0 && g.b_rs % 4 == 0 && (reinterpret_cast<uintptr_t>(g.B) & 15) == 0) ? 1 : 0;
+        dim3 grid(blocks_n, splits);
+        switch (g.M) {
+            case 1: gemv_kn_kernel<1><<<grid, 128, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_rs, part, g.N, g.K, kps, vec); break;
+            case 2: gemv_kn_kernel<2><<<grid, 128, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_rs, part, g.N, g.K, kps, vec); break;
+            case 3: gemv_kn_kernel<3><<<grid, 128, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_rs, part, g.N, g.K, kps, vec); break;
+            default: gemv_kn_kernel<4><<<grid, 128, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_rs, part, g.N, g.K, kps, vec); break;
+        }
+        prof_work(4.0 * g.K * g.N);
+        LAUNCHED("gemv_kn_kernel");
+        gemv_reduce_kernel<<<(g.M * g.N + 255) / 256, 256, 0, stream()>>>(g.C, g.c_rs, part, splits, g.M, g.N, g.bias, g.accumulate ? 1 : 0);
+        LAUNCHED("gemv_reduce_kernel");
+        return;
+    }
+    const int vec = (g.K % 4 == 0 && g.b_cs % 4 == 0 && g.a_rs % 4 == 0 && ((reinterpret_cast<uintptr_t>(g.B) | reinterpret_cast<uintptr_t>(g.A)) & 15) == 0) ? 1 : 0;
+    const int grid = (g.N + 7) / 8;
+    switch (g.M) {
+        case 1: gemv_nk_kernel<1><<<grid, 256, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_cs, g.C, g.c_rs, g.N, g.K, g.bias, g.accumulate ? 1 : 0, vec); break;
+        case 2: gemv_nk_kernel<2><<<grid, 256, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_cs, g.C, g.c_rs, g.N, g.K, g.bias, g.accumulate ? 1 : 0, vec); break;
+        case 3: gemv_nk_kernel<3><<<grid, 256, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_cs, g.C, g.c_rs, g.N, g.K, g.bias, g.accumulate ? 1 : 0, vec); break;
+        default: gemv_nk_kernel<4><<<grid, 256, 0, stream()>>>(g.A, g.a_rs, g.B, g.b_cs, g.C, g.c_rs, g.N, g.K, g.bias, g.accumulate ? 1 : 0, vec); break;
+    }
+    prof_work(4.0 * g.K * g.N);
+    LAUNCHED("gemv_nk_kernel");
+}
+
 // Which product of an op a GEMM is: the precision policy of TF32 mode can send each kind to 3xTF32.
 static thread_local int g_role = GEMM_ROLE_FORWARD;
 void gemm_set_role(int role) { g_role = role; }
@@ -121,6 +272,7 @@ static void read_shape_rules() {
 void gemm_reread_env() { g_shapes_read = false; }
 
 void gemm(const GemmArgs &g) {
+    if (gemv_applicable(g)) { gemv(g); return; }          // a few output rows: bandwidth-bound on W, exact fp32 in every mode
     int mode = gemm_mode();
     if (mode == DNN_CUDA_GEMM_FP32 || !gemm_tc_supported(g)) { gemm_simt(g); return; }
     if (!g_policy_env_read) {

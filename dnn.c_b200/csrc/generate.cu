@@ -55,9 +55,94 @@ __global__ void attn_cached_kernel(const float *__restrict__ q, const float *__r
     }
 }
 
+// One decoding step of one block's attention for ONE new token per sequence, with the position read from device
+// memory so that the launch does not depend on it (and a whole token step can be replayed as a graph).  CTA (h, b):
+// takes the token's q, k, v from the fused projection [B, 3*H*d], rotates q and k at position pos (the arithmetic
+// of tensor_rope), appends k and v to the cache at row pos, attends over rows 0..pos and writes the head's d outputs
+// token-major into out[B, H*d] -- what split_qkv_heads, two rope passes, two cache copies, attn_cached_kernel and
+// merge_heads do in seven launches, with the same arithmetic per element.
+__global__ void decode_attn_kernel(const float *__restrict__ qkv, const float *__restrict__ fc, const float *__restrict__ fs,
+                                   float *__restrict__ kc, float *__restrict__ vc, int64_t c_sb, int64_t c_sh,
+                                   float *__restrict__ out, const int *__restrict__ pos_dev, int H, int d, int max_seq, float scale) {
+    extern __shared__ float sc[];                 // d floats of q, max_seq scores, 32 floats of reduction scratch
+    float *qs = sc, *scr = sc + d, *red = scr + max_seq;
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int pos = *pos_dev;
+    if (pos < 0 || pos >= max_seq) return;        // a full cache is refused on the host; nothing is written out of range
+    const int S = pos + 1;
+    const float *tok = qkv + (int64_t)b * 3 * H * d + (int64_t)h * d;
+    float *kb = kc + (int64_t)b * c_sb + (int64_t)h * c_sh, *vb = vc + (int64_t)b * c_sb + (int64_t)h * c_sh;
+    const int dh = d >> 1;
+    for (int m = threadIdx.x; m < dh; m += blockDim.x) {
+        float q0 = tok[2 * m], q1 = tok[2 * m + 1], k0 = tok[(int64_t)H * d + 2 * m], k1 = tok[(int64_t)H * d + 2 * m + 1];
+        if (fc) {
+            const float c = fc[(int64_t)pos * dh + m], sn = fs[(int64_t)pos * dh + m];
+            float ox, oy;
+            rope_fwd_pair(q0, q1, c, sn, ox, oy); q0 = ox; q1 = oy;
+            rope_fwd_pair(k0, k1, c, sn, ox, oy); k0 = ox; k1 = oy;
+        }
+        qs[2 * m] = q0; qs[2 * m + 1] = q1;
+        kb[(int64_t)pos * d + 2 * m] = k0; kb[(int64_t)pos * d + 2 * m + 1] = k1;
+    }
+    for (int c = threadIdx.x; c < d; c += blockDim.x) vb[(int64_t)pos * d + c] = tok[(int64_t)2 * H * d + c];
+    __syncthreads();                              // this CTA's own cache row is read back below
+    float mx = -INFINITY;
+    for (int j = threadIdx.x; j < S; j += blockDim.x) {
+        const float *kr = kb + (int64_t)j * d;
+        float s = 0.f;
+        for (int c = 0; c < d; c++) s += qs[c] * kr[c];
+        s *= scale;
+        scr[j] = s;
+        mx = fmaxf(mx, s);
+    }
+    mx = block_max(mx, red);
+    float se = 0.f;
+    for (int j = threadIdx.x; j < S; j += blockDim.x) { float e = expf(scr[j] - mx); scr[j] = e; se += e; }
+    se = block_sum(se, red);
+    __syncthreads();
+    const float inv = 1.0f / se;
+    float *orow = out + (int64_t)b * H * d + (int64_t)h * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < S; j++) acc += scr[j] * vb[(int64_t)j * d + c];
+        orow[c] = acc * inv;
+    }
+}
+__global__ void bump_pos_kernel(int *pos) { *pos += 1; }
+
 }  // namespace dnnb
 
 using namespace dnnb;
+
+// One token through one block with the position in device memory (see decode_attn_kernel): x [B, 1, d_model].
+static tensor *block_decode_step(struct mem_pool *scratch, transformer_block *block, const tensor *x, kv_cache *cache, const int *pos_dev) {
+    const int B = x->shape[0], H = block->n_heads, d = block->d_k;
+    tensor *h = rms_norm_forward(scratch, block->attn_norm, x);
+    tensor *qkv = linear_forward(scratch, block->qkv_proj, h);
+    int shape[3] = {B, 1, H * d};
+    tensor *merged = tensor_scratch(scratch, 3, shape, 0);
+    const bool rope = block->freqs_cos && block->freqs_sin;
+    const tensor *kc = cache->k_cache, *vc = cache->v_cache;
+    const size_t smem = ((size_t)d + cache->max_seq + 32) * sizeof(float);
+    DNN_CHECK(smem <= 200 * 1024, "decode step: sequence too long for the score buffer");
+    static size_t smem_set = 0;
+    if (smem > 48 * 1024 && smem > smem_set) {
+        CUDA_OK(cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        smem_set = 200 * 1024;
+    }
+    decode_attn_kernel<<<dim3(H, B), 128, smem, stream()>>>(
+        (const float *)qkv->data + qkv->offset,
+        rope ? (const float *)block->freqs_cos->data + block->freqs_cos->offset : nullptr,
+        rope ? (const float *)block->freqs_sin->data + block->freqs_sin->offset : nullptr,
+        (float *)kc->data + kc->offset, (float *)vc->data + vc->offset, kc->strides[0], kc->strides[1],
+        (float *)merged->data, pos_dev, H, d, cache->max_seq, 1.0f / sqrtf((float)d));
+    LAUNCHED("decode_attn_kernel");
+    tensor *proj = linear_forward(scratch, block->out_proj, merged);
+    tensor *x1 = tensor_add(scratch, x, proj);
+    h = rms_norm_forward(scratch, block->ffn_norm, x1);
+    tensor *ffn = swiglu_ffn_forward(scratch, block->ffn, h);
+    return tensor_add(scratch, x1, ffn);
+}
 
 extern "C" {
 
@@ -212,17 +297,74 @@ int *decoder_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_po
             output[cur++] = next;
             if (next == kEosId) goto done_cached;
         }
-        while (cur < max_len) {
-            DNN_CHECK(dnn_cuda_upload(single, &output[cur - 1], sizeof(int)) == 0, "generate: upload failed");
-            tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, single);
-            int hs[3] = {1, 1, D};
-            tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
-            for (int i = 0; i < lm->n_layers; i++) h = transformer_block_forward_cached(scratch_pool, lm->blocks[i], h, caches[(size_t)i]);
-            tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, h));
-            int next = pick(logits, 0);
+        {
+            // Token steps.  The position lives in device memory (decode_attn_kernel), the scratch pool hands out the
+            // same addresses for every token, and the token id arrives in a fixed buffer, so nothing in a step
+            // depends on a host value that changes: the first step runs eagerly (and grows whatever buffers need
+            // growing), the second is recorded with stream capture, and every later token is one graph launch
+            // between the upload of its id and the read-back of its logits.  DNN_CUDA_GEN_GRAPH=0: every step eager.
+            const char *ge = getenv("DNN_CUDA_GEN_GRAPH");
+            const bool want_graph = !(ge && ge[0] == '0');
+            tensor *pos_t = tensor_zeros_data(data_pool, 1, one_shape);
+            const int *pos_dev = (const int *)pos_t->data;
+            int pos_host = caches[0]->seq_len;
+            DNN_CHECK(dnn_cuda_upload(pos_t, &pos_host, sizeof(int)) == 0, "generate: upload failed");
+            cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
+            const float *logits_dev = nullptr;
+            long long graph_kernels = 0;
+            auto token_step = [&]() {                  // the kernels of one token; returns where its logits land
+                tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, single);
+                int hs[3] = {1, 1, D};
+                tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
+                for (int i = 0; i < lm->n_layers; i++) h = block_decode_step(scratch_pool, lm->blocks[i], h, caches[(size_t)i], pos_dev);
+                tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, h));
+                bump_pos_kernel<<<1, 1, 0, stream()>>>((int *)pos_t->data);
+                LAUNCHED("bump_pos_kernel");
+                return (const float *)logits->data + logits->offset;
+            };
+            int steps = 0;
+            while (cur < max_len) {
+                DNN_CHECK(caches[0]->seq_len < caches[0]->max_seq, "generate: cache full");
+                DNN_CHECK(!lm->blocks[0]->freqs_cos || caches[0]->seq_len < lm->blocks[0]->freqs_cos->shape[0],
+                          "generate: position beyond the rotary tables (decoder_lm_enable_rope max_seq_len)");
+                DNN_CHECK(dnn_cuda_upload(single, &output[cur - 1], sizeof(int)) == 0, "generate: upload failed");
+                if (exec) {
+                    DNN_CHECK(cudaGraphLaunch(exec, stream()) == cudaSuccess, "generate: graph launch failed");
+                    add_launches(graph_kernels);
+                } else if (want_graph && steps == 1) {
+                    const long long before = dnn_cuda_launch_count();
+                    cudaError_t e = cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal);
+                    DNN_CHECK(e == cudaSuccess, "generate: cudaStreamBeginCapture failed");
+                    logits_dev = token_step();
+                    e = cudaStreamEndCapture(stream(), &graph);
+                    graph_kernels = dnn_cuda_launch_count() - before;
+                    add_launches(-graph_kernels);                  // recorded, not run
+                    mem_pool_reset(scratch_pool);
+                    if (e == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+                        DNN_CHECK(cudaGraphLaunch(exec, stream()) == cudaSuccess, "generate: graph launch failed");
+                        add_launches(graph_kernels);
+                    } else {                                       // recording refused: this and all later steps run eagerly
+                        cudaGetLastError();
+                        if (graph) { cudaGraphDestroy(graph); graph = nullptr; }
+                        exec = nullptr;
+                        logits_dev = token_step();
+                    }
+                } else {
+                    logits_dev = token_step();
+                }
+                DNN_CHECK(dnn_cuda_memcpy_d2h(logits_host.data(), logits_dev, (size_t)V * sizeof(float)) == 0, "generate: cannot read logits");
+                int next = temperature == 0.0f ? decoder_lm_argmax_token(logits_host.data(), V)
+                                               : decoder_lm_sample_with_temp(logits_host.data(), V, temperature);
+                if (!exec) mem_pool_reset(scratch_pool);
+                for (int i = 0; i < lm->n_layers; i++) caches[(size_t)i]->seq_len += 1;
+                steps++;
+                output[cur++] = next;
+                if (next == kEosId) break;
+            }
+            dnn_cuda_sync();
+            if (exec) cudaGraphExecDestroy(exec);
+            if (graph) cudaGraphDestroy(graph);
             mem_pool_reset(scratch_pool);
-            output[cur++] = next;
-            if (next == kEosId) break;
         }
 done_cached:
         dnn_cuda_sync();

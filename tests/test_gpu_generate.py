@@ -47,6 +47,25 @@ def test_cache_and_full_forward_agree(binding):
     assert out[0] == out[1]
 
 
+def test_replayed_token_steps_equal_eager_token_steps(binding):
+    """From the third new token on, a cached decoding step is one graph launch; with DNN_CUDA_GEN_GRAPH=0 every step
+    launches its kernels one by one.  Greedy and sampled sequences have to be the same either way."""
+    cfg = dict(models.lm_config("tiny")); cfg.update(V=96, D=128, L=2, H=4, F=256)
+    for temp in (0.0, 0.8):
+        out = []
+        for graph in ("1", "0"):
+            os.environ["DNN_CUDA_GEN_GRAPH"] = graph
+            try:
+                d = binding.Dnn(binding.B200_LIB, params_mb=64, scratch_mb=512, data_mb=64)
+                d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_FP32)
+                out.append(models.run_generate(d, cfg, [5, 6, 7, 8], 24, temp, 1, seed=5))
+                d.lib.dnn_cuda_set_gemm_mode(binding.GEMM_TF32)
+                d.close()
+            finally:
+                os.environ.pop("DNN_CUDA_GEN_GRAPH", None)
+        assert out[0] == out[1] and len(out[0]) > 8
+
+
 @pytest.mark.parametrize("mode", ["fp32", "tf32"])
 @pytest.mark.parametrize("case", models.VLM_GEN_CASES, ids=[c[0] for c in models.VLM_GEN_CASES])
 def test_vision_lm_generated_tokens_equal_the_reference(binding, case, mode):
