@@ -144,6 +144,82 @@ static tensor *block_decode_step(struct mem_pool *scratch, transformer_block *bl
     return tensor_add(scratch, x1, ffn);
 }
 
+// Cached token steps until max_len or end-of-sequence; output[cur - 1] is the last token so far and the caches hold
+// everything before it.
+static void decode_tokens(struct mem_pool *scratch_pool, struct mem_pool *data_pool, decoder_lm *lm, std::vector<kv_cache *> &caches,
+                          tensor *single, int *output, int &cur, int max_len, float temperature, std::vector<float> &logits_host) {
+    const int V = lm->vocab_size, D = lm->d_model;
+    int one_shape[1] = {1};
+    // Token steps.  The position lives in device memory (decode_attn_kernel), the scratch pool hands out the
+    // same addresses for every token, and the token id arrives in a fixed buffer, so nothing in a step
+    // depends on a host value that changes: the first step runs eagerly (and grows whatever buffers need
+    // growing), the second is recorded with stream capture, and every later token is one graph launch
+    // between the upload of its id and the read-back of its logits.  DNN_CUDA_GEN_GRAPH=0: every step eager.
+    const char *ge = getenv("DNN_CUDA_GEN_GRAPH");
+    const bool want_graph = !(ge && ge[0] == '0');
+    tensor *pos_t = tensor_zeros_data(data_pool, 1, one_shape);
+    const int *pos_dev = (const int *)pos_t->data;
+    int pos_host = caches[0]->seq_len;
+    DNN_CHECK(dnn_cuda_upload(pos_t, &pos_host, sizeof(int)) == 0, "generate: upload failed");
+    cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
+    const float *logits_dev = nullptr;
+    long long graph_kernels = 0;
+    auto token_step = [&]() {                  // the kernels of one token; returns where its logits land
+        tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, single);
+        int hs[3] = {1, 1, D};
+        tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
+        for (int i = 0; i < lm->n_layers; i++) h = block_decode_step(scratch_pool, lm->blocks[i], h, caches[(size_t)i], pos_dev);
+        tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, h));
+        bump_pos_kernel<<<1, 1, 0, stream()>>>((int *)pos_t->data);
+        LAUNCHED("bump_pos_kernel");
+        return (const float *)logits->data + logits->offset;
+    };
+    int steps = 0;
+    while (cur < max_len) {
+        DNN_CHECK(caches[0]->seq_len < caches[0]->max_seq, "generate: cache full");
+        DNN_CHECK(!lm->blocks[0]->freqs_cos || caches[0]->seq_len < lm->blocks[0]->freqs_cos->shape[0],
+                  "generate: position beyond the rotary tables (decoder_lm_enable_rope max_seq_len)");
+        DNN_CHECK(dnn_cuda_upload(single, &output[cur - 1], sizeof(int)) == 0, "generate: upload failed");
+        if (exec) {
+            DNN_CHECK(cudaGraphLaunch(exec, stream()) == cudaSuccess, "generate: graph launch failed");
+            add_launches(graph_kernels);
+        } else if (want_graph && steps == 1) {
+            const long long before = dnn_cuda_launch_count();
+            cudaError_t e = cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal);
+            DNN_CHECK(e == cudaSuccess, "generate: cudaStreamBeginCapture failed");
+            logits_dev = token_step();
+            e = cudaStreamEndCapture(stream(), &graph);
+            graph_kernels = dnn_cuda_launch_count() - before;
+            add_launches(-graph_kernels);                  // recorded, not run
+            mem_pool_reset(scratch_pool);
+            if (e == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+                DNN_CHECK(cudaGraphLaunch(exec, stream()) == cudaSuccess, "generate: graph launch failed");
+                add_launches(graph_kernels);
+            } else {                                       // recording refused: this and all later steps run eagerly
+                cudaGetLastError();
+                if (graph) { cudaGraphDestroy(graph); graph = nullptr; }
+                exec = nullptr;
+                logits_dev = token_step();
+            }
+        } else {
+            logits_dev = token_step();
+        }
+        DNN_CHECK(dnn_cuda_memcpy_d2h(logits_host.data(), logits_dev, (size_t)V * sizeof(float)) == 0, "generate: cannot read logits");
+        int next = temperature == 0.0f ? decoder_lm_argmax_token(logits_host.data(), V)
+                                       : decoder_lm_sample_with_temp(logits_host.data(), V, temperature);
+        if (!exec) mem_pool_reset(scratch_pool);
+        for (int i = 0; i < lm->n_layers; i++) caches[(size_t)i]->seq_len += 1;
+        steps++;
+        output[cur++] = next;
+        if (next == kEosId) break;
+    }
+    dnn_cuda_sync();
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    mem_pool_reset(scratch_pool);
+
+}
+
 extern "C" {
 
 kv_cache *kv_cache_create(struct mem_pool *params_pool, int B, int H, int max_seq, int d_k) {
@@ -297,75 +373,7 @@ int *decoder_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_po
             output[cur++] = next;
             if (next == kEosId) goto done_cached;
         }
-        {
-            // Token steps.  The position lives in device memory (decode_attn_kernel), the scratch pool hands out the
-            // same addresses for every token, and the token id arrives in a fixed buffer, so nothing in a step
-            // depends on a host value that changes: the first step runs eagerly (and grows whatever buffers need
-            // growing), the second is recorded with stream capture, and every later token is one graph launch
-            // between the upload of its id and the read-back of its logits.  DNN_CUDA_GEN_GRAPH=0: every step eager.
-            const char *ge = getenv("DNN_CUDA_GEN_GRAPH");
-            const bool want_graph = !(ge && ge[0] == '0');
-            tensor *pos_t = tensor_zeros_data(data_pool, 1, one_shape);
-            const int *pos_dev = (const int *)pos_t->data;
-            int pos_host = caches[0]->seq_len;
-            DNN_CHECK(dnn_cuda_upload(pos_t, &pos_host, sizeof(int)) == 0, "generate: upload failed");
-            cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
-            const float *logits_dev = nullptr;
-            long long graph_kernels = 0;
-            auto token_step = [&]() {                  // the kernels of one token; returns where its logits land
-                tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, single);
-                int hs[3] = {1, 1, D};
-                tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
-                for (int i = 0; i < lm->n_layers; i++) h = block_decode_step(scratch_pool, lm->blocks[i], h, caches[(size_t)i], pos_dev);
-                tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, h));
-                bump_pos_kernel<<<1, 1, 0, stream()>>>((int *)pos_t->data);
-                LAUNCHED("bump_pos_kernel");
-                return (const float *)logits->data + logits->offset;
-            };
-            int steps = 0;
-            while (cur < max_len) {
-                DNN_CHECK(caches[0]->seq_len < caches[0]->max_seq, "generate: cache full");
-                DNN_CHECK(!lm->blocks[0]->freqs_cos || caches[0]->seq_len < lm->blocks[0]->freqs_cos->shape[0],
-                          "generate: position beyond the rotary tables (decoder_lm_enable_rope max_seq_len)");
-                DNN_CHECK(dnn_cuda_upload(single, &output[cur - 1], sizeof(int)) == 0, "generate: upload failed");
-                if (exec) {
-                    DNN_CHECK(cudaGraphLaunch(exec, stream()) == cudaSuccess, "generate: graph launch failed");
-                    add_launches(graph_kernels);
-                } else if (want_graph && steps == 1) {
-                    const long long before = dnn_cuda_launch_count();
-                    cudaError_t e = cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal);
-                    DNN_CHECK(e == cudaSuccess, "generate: cudaStreamBeginCapture failed");
-                    logits_dev = token_step();
-                    e = cudaStreamEndCapture(stream(), &graph);
-                    graph_kernels = dnn_cuda_launch_count() - before;
-                    add_launches(-graph_kernels);                  // recorded, not run
-                    mem_pool_reset(scratch_pool);
-                    if (e == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
-                        DNN_CHECK(cudaGraphLaunch(exec, stream()) == cudaSuccess, "generate: graph launch failed");
-                        add_launches(graph_kernels);
-                    } else {                                       // recording refused: this and all later steps run eagerly
-                        cudaGetLastError();
-                        if (graph) { cudaGraphDestroy(graph); graph = nullptr; }
-                        exec = nullptr;
-                        logits_dev = token_step();
-                    }
-                } else {
-                    logits_dev = token_step();
-                }
-                DNN_CHECK(dnn_cuda_memcpy_d2h(logits_host.data(), logits_dev, (size_t)V * sizeof(float)) == 0, "generate: cannot read logits");
-                int next = temperature == 0.0f ? decoder_lm_argmax_token(logits_host.data(), V)
-                                               : decoder_lm_sample_with_temp(logits_host.data(), V, temperature);
-                if (!exec) mem_pool_reset(scratch_pool);
-                for (int i = 0; i < lm->n_layers; i++) caches[(size_t)i]->seq_len += 1;
-                steps++;
-                output[cur++] = next;
-                if (next == kEosId) break;
-            }
-            dnn_cuda_sync();
-            if (exec) cudaGraphExecDestroy(exec);
-            if (graph) cudaGraphDestroy(graph);
-            mem_pool_reset(scratch_pool);
-        }
+        decode_tokens(scratch_pool, data_pool, lm, caches, single, output, cur, max_len, temperature, logits_host);
 done_cached:
         dnn_cuda_sync();
         mem_pool_release(data_pool, mark);
@@ -402,7 +410,7 @@ int *vision_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_poo
     DNN_CHECK(max_new_tokens > 0 && temperature >= 0.0f, "vision_lm_generate: bad max_new_tokens / temperature");
     decoder_lm *lm = vlm->lm;
     const int prompt_len = prompt_ids->shape[1], max_len = prompt_len + max_new_tokens;
-    const int V = vlm->vocab_size, D = vlm->d_model, I = vlm->n_img_tokens;
+    const int V = vlm->vocab_size, I = vlm->n_img_tokens;
     // the image moves to the data pool so that it survives the scratch resets between tokens
     tensor *img_keep = tensor_zeros_data(data_pool, image->ndim, image->shape);
     CUDA_OK(cudaMemcpyAsync(img_keep->data, (const float *)image->data + image->offset, (size_t)numel_of(image) * sizeof(float),
@@ -440,17 +448,7 @@ int *vision_lm_generate(struct mem_pool *scratch_pool, struct mem_pool *data_poo
             mem_pool_reset(scratch_pool);
             output[cur++] = next;
         }
-        while (next != kEosId && cur < max_len) {
-            DNN_CHECK(dnn_cuda_upload(single, &output[cur - 1], sizeof(int)) == 0, "vision_lm_generate: upload failed");
-            tensor *emb = embedding_forward(scratch_pool, nullptr, lm->embed, single);
-            int hs[3] = {1, 1, D};
-            tensor *h = tensor_reshape(scratch_pool, emb, 3, hs);
-            for (int i = 0; i < lm->n_layers; i++) h = transformer_block_forward_cached(scratch_pool, lm->blocks[i], h, caches[(size_t)i]);
-            tensor *logits = decoder_lm_lm_head_forward(scratch_pool, lm, rms_norm_forward(scratch_pool, lm->norm, h));
-            next = pick(logits, 0);
-            mem_pool_reset(scratch_pool);
-            output[cur++] = next;
-        }
+        if (next != kEosId) decode_tokens(scratch_pool, data_pool, lm, caches, single, output, cur, max_len, temperature, logits_host);
         dnn_cuda_sync();
         mem_pool_release(data_pool, mark);
     } else {
