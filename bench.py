@@ -471,7 +471,7 @@ def other_configs(B, local, tf32_peak):
     ob = load_opbench()
     out = {}
     b = ob.Bench(B, 5, False, params_mb=8192, scratch_mb=24 * 1024, echo=False, device=local, tf32_peak=tf32_peak)
-    ob.run_ops(b, ["step_graph", "cnn_step", "vlm_step"], ob.Args(iters=5))
+    ob.run_ops(b, ["step_graph", "cnn_step", "vlm_step", "generate"], ob.Args(iters=5))
     for r in b.rows:
         if r["op"] == "step_graph":
             out["config1_tiny_lm"] = {"workload": r["workload"], "eager": {"value": r["eager_tokens_per_s"], "unit": "tokens/s", "ms_per_step": r["eager_ms_per_step"]},
@@ -480,6 +480,8 @@ def other_configs(B, local, tf32_peak):
         elif r["op"] == "cnn_step":
             out["config3_cnn"] = {"workload": r["workload"], "value": r["images_per_s"], "unit": "images/s", "ms_per_step": r["ms_per_step"],
                                   "kernels_per_step": r["kernels_per_step"]}
+        elif r["op"] == "generate":
+            out["generation_124m"] = {k: r[k] for k in r if k != "op"}
         elif r["op"] == "vlm_step":
             out["config4_vision_lm"] = {"workload": r["workload"], "value": r["images_per_s"], "unit": "images/s", "ms_per_step": r["ms_per_step"],
                                         "tokens_per_s": r["tokens_per_s"], "kernels_per_step": r["kernels_per_step"]}

@@ -418,6 +418,27 @@ def run_ops(b, ops, args):
                           "pipeline_ms_per_batch": round(ms_e2e, 3), "pipeline_images_per_s": round(Bsz / ms_e2e * 1e3),
                           "h2d_bytes_per_batch": Bsz * Hh * Ww * Cc + Bsz * (2 + Tm) * 4,
                           "float_upload_ms_per_batch": round(ms_float, 3), "float_h2d_bytes_per_batch": Bsz * Cc * Hh * Ww * 4}))
+    if "generate" in ops:
+        # KV-cache generation on the 124M-shaped decoder LM: batch 1, prompt of 128 tokens, greedy; the time of the
+        # extra new tokens of a longer run over a shorter one is the cost of a token step (prefill and set-up cancel).
+        lm = lib.decoder_lm_create(d.params, 32000, 768, 12, 12, 64, 2048)
+        lib.decoder_lm_enable_rope(d.params, lm, 1024, 10000.0)
+        lib.dnn_seed(1); lib.decoder_lm_init_weights(lm)
+        ids = d.tensor((np.arange(1, 129, dtype=np.int32).reshape(1, -1) % 250), d.params)
+        n = C.c_int(0)
+        res = {}
+        for new in (8, 8, 136):
+            lib.dnn_cuda_sync(); t0 = time.perf_counter(); k0 = lib.dnn_cuda_launch_count()
+            lib.decoder_lm_generate(d.scratch, d.data, lm, ids, new, 0.0, 1, C.byref(n))
+            lib.dnn_cuda_sync()
+            res[new] = (time.perf_counter() - t0, lib.dnn_cuda_launch_count() - k0, n.value - 128)
+            d.reset_step()
+        extra = res[136][2] - res[8][2]
+        ms_tok = (res[136][0] - res[8][0]) / max(extra, 1) * 1e3
+        b.emit({"op": "generate", "workload": "decoder LM V32000 d768 L12, batch 1, prompt 128, greedy, KV cache",
+                "ms_per_new_token": round(ms_tok, 3), "tokens_per_s": round(1e3 / ms_tok, 1),
+                "kernels_per_token": int((res[136][1] - res[8][1]) // max(extra, 1)), "new_tokens": res[136][2],
+                "ms_prefill_and_8_tokens": round(res[8][0] * 1e3, 2)})
     if want("adamw"):
         P = (16 if args.small else 124) * 1000 * 1000
         t = lib.tensor_zeros(d.params, 1, B.ints([P]), 1)
