@@ -84,6 +84,10 @@ __global__ void decode_attn_kernel(const float *__restrict__ qkv, const float *_
         qs[2 * m] = q0; qs[2 * m + 1] = q1;
         kb[(int64_t)pos * d + 2 * m] = k0; kb[(int64_t)pos * d + 2 * m + 1] = k1;
     }
+    if ((d & 1) && threadIdx.x == 0) {            // an odd last element has no partner and is not rotated
+        qs[d - 1] = tok[d - 1];
+        kb[(int64_t)pos * d + d - 1] = tok[(int64_t)H * d + d - 1];
+    }
     for (int c = threadIdx.x; c < d; c += blockDim.x) vb[(int64_t)pos * d + c] = tok[(int64_t)2 * H * d + c];
     __syncthreads();                              // this CTA's own cache row is read back below
     float mx = -INFINITY;
