@@ -95,7 +95,7 @@ void gemm_simt(const GemmArgs &g) {
 //   W with N contiguous ([K,N], a linear layer's weight): a thread owns four adjacent columns and walks a slice of K
 //     (x staged in shared memory), the slices' partial sums are added in fixed order by gemv_reduce_kernel;
 //   W with K contiguous ([N,K], the tied vocabulary projection): a warp owns one output column.
-constexpr int kGemvRows = 4, kGemvSlice = 256, kGemvSplits = 32;
+constexpr int kGemvRows = 4, kGemvSlice = 256, kGemvSplits = 128;
 
 template <int MM>
 __global__ void __launch_bounds__(128)
@@ -114,7 +114,7 @@ gemv_kn_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restric
 #pragma unroll
     for (int m = 0; m < MM; m++) { acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f; }
     if (vec) {
-#pragma unroll 4
+#pragma unroll 8
         for (int k = k0; k < k1; k++) {
             const float4 w = __ldg(reinterpret_cast<const float4 *>(W + (int64_t)k * w_rs + n));
 #pragma unroll
@@ -142,13 +142,20 @@ gemv_kn_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restric
             if (n + j < N) part[((int64_t)blockIdx.y * MM + m) * N + n + j] = acc[m][j];
 }
 
+// Eight lanes per output: lane l adds slices l, l + 8, ... in order, then the eight sums meet in a fixed shuffle tree, so
+// the result does not depend on timing; adjacent outputs sit in adjacent groups of lanes (32-byte segments per slice).
 __global__ void gemv_reduce_kernel(float *__restrict__ C, int64_t c_rs, const float *__restrict__ part, int splits, int M, int N,
                                    const float *__restrict__ bias, int accumulate) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= M * N) return;
-    const int m = i / N, n = i - m * N;
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = t >> 3, l = t & 7;
+    const bool live = i < M * N;
+    const int m = live ? i / N : 0, n = live ? i - m * N : 0;
     float s = 0.f;
-    for (int k = 0; k < splits; k++) s += part[((int64_t)k * M + m) * N + n];
+    if (live) for (int k = l; k < splits; k += 8) s += part[((int64_t)k * M + m) * N + n];
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    if (!live || l != 0) return;
     if (bias) s += bias[n];
     float *c = C + (int64_t)m * c_rs + n;
     *c = accumulate ? *c + s : s;
@@ -199,7 +206,7 @@ static bool gemv_applicable(const GemmArgs &g) {
 static void gemv(const GemmArgs &g) {
     if (g.b_cs == 1) {                                            // [K,N], N contiguous
         const int blocks_n = (g.N + 511) / 512;
-        int splits = (2 * kNumSMs + blocks_n - 1) / blocks_n;
+        int splits = (4 * kNumSMs + blocks_n - 1) / blocks_n;
         if (splits > kGemvSplits) splits = kGemvSplits;
         int kps = (g.K + splits - 1) / splits;
         if (kps > kGemvSlice) kps = kGemvSlice;
@@ -223,7 +230,7 @@ static void gemv(const GemmArgs &g) {
         }
         prof_work(4.0 * g.K * g.N);
         LAUNCHED("gemv_kn_kernel");
-        gemv_reduce_kernel<<<(g.M * g.N + 255) / 256, 256, 0, stream()>>>(g.C, g.c_rs, part, splits, g.M, g.N, g.bias, g.accumulate ? 1 : 0);
+        gemv_reduce_kernel<<<(g.M * g.N * 8 + 255) / 256, 256, 0, stream()>>>(g.C, g.c_rs, part, splits, g.M, g.N, g.bias, g.accumulate ? 1 : 0);
         LAUNCHED("gemv_reduce_kernel");
         return;
     }

@@ -61,11 +61,13 @@ __global__ void attn_cached_kernel(const float *__restrict__ q, const float *__r
 // of tensor_rope), appends k and v to the cache at row pos, attends over rows 0..pos and writes the head's d outputs
 // token-major into out[B, H*d] -- what split_qkv_heads, two rope passes, two cache copies, attn_cached_kernel and
 // merge_heads do in seven launches, with the same arithmetic per element.
-__global__ void decode_attn_kernel(const float *__restrict__ qkv, const float *__restrict__ fc, const float *__restrict__ fs,
+constexpr int kDecodeGroups = 16;      // key groups of the output sum (256 threads / (d / 4) column groups at d = 64)
+__global__ void __launch_bounds__(256) decode_attn_kernel(const float *__restrict__ qkv, const float *__restrict__ fc, const float *__restrict__ fs,
                                    float *__restrict__ kc, float *__restrict__ vc, int64_t c_sb, int64_t c_sh,
                                    float *__restrict__ out, const int *__restrict__ pos_dev, int H, int d, int max_seq, float scale) {
-    extern __shared__ float sc[];                 // d floats of q, max_seq scores, 32 floats of reduction scratch
-    float *qs = sc, *scr = sc + d, *red = scr + max_seq;
+    extern __shared__ __align__(16) float sc[];   // q (d, padded to 4), scores (max_seq, padded), reduction scratch (32), output partials (groups x d)
+    const int dp = (d + 3) & ~3, sp = (max_seq + 3) & ~3;
+    float *qs = sc, *scr = sc + dp, *red = scr + sp, *part = red + 32;
     const int h = blockIdx.x, b = blockIdx.y;
     const int pos = *pos_dev;
     if (pos < 0 || pos >= max_seq) return;        // a full cache is refused on the host; nothing is written out of range
@@ -90,11 +92,22 @@ __global__ void decode_attn_kernel(const float *__restrict__ qkv, const float *_
     }
     for (int c = threadIdx.x; c < d; c += blockDim.x) vb[(int64_t)pos * d + c] = tok[(int64_t)2 * H * d + c];
     __syncthreads();                              // this CTA's own cache row is read back below
+    // scores: a thread per key; with d a multiple of 4 its row is read as independent 128-bit loads
+    const bool v4 = (d & 3) == 0 && ((c_sb | c_sh) & 3) == 0 && ((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0;
     float mx = -INFINITY;
     for (int j = threadIdx.x; j < S; j += blockDim.x) {
         const float *kr = kb + (int64_t)j * d;
         float s = 0.f;
-        for (int c = 0; c < d; c++) s += qs[c] * kr[c];
+        if (v4) {
+            const float4 *k4 = reinterpret_cast<const float4 *>(kr), *q4 = reinterpret_cast<const float4 *>(qs);
+#pragma unroll 8
+            for (int c = 0; c < (d >> 2); c++) {
+                const float4 kv = k4[c], qv = q4[c];
+                s += qv.x * kv.x; s += qv.y * kv.y; s += qv.z * kv.z; s += qv.w * kv.w;
+            }
+        } else {
+            for (int c = 0; c < d; c++) s += qs[c] * kr[c];
+        }
         s *= scale;
         scr[j] = s;
         mx = fmaxf(mx, s);
@@ -106,10 +119,34 @@ __global__ void decode_attn_kernel(const float *__restrict__ qkv, const float *_
     __syncthreads();
     const float inv = 1.0f / se;
     float *orow = out + (int64_t)b * H * d + (int64_t)h * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < S; j++) acc += scr[j] * vb[(int64_t)j * d + c];
-        orow[c] = acc * inv;
+    const int d4 = d >> 2;
+    int groups = v4 && d4 > 0 ? (int)blockDim.x / d4 : 0;
+    if (groups > kDecodeGroups) groups = kDecodeGroups;
+    if (groups >= 2) {
+        // output: thread (cg, kg) sums keys kg, kg + groups, ... for four adjacent columns; the groups' sums are added in order
+        const int cg = threadIdx.x % d4, kg = threadIdx.x / d4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (kg < groups) {
+#pragma unroll 4
+            for (int j = kg; j < S; j += groups) {
+                const float p = scr[j];
+                const float4 v = *reinterpret_cast<const float4 *>(vb + (int64_t)j * d + 4 * cg);
+                acc.x += p * v.x; acc.y += p * v.y; acc.z += p * v.z; acc.w += p * v.w;
+            }
+            *reinterpret_cast<float4 *>(part + (int64_t)kg * d + 4 * cg) = acc;
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < d; c += blockDim.x) {
+            float a = 0.f;
+            for (int g = 0; g < groups; g++) a += part[(int64_t)g * d + c];
+            orow[c] = a * inv;
+        }
+    } else {
+        for (int c = threadIdx.x; c < d; c += blockDim.x) {
+            float acc = 0.f;
+            for (int j = 0; j < S; j++) acc += scr[j] * vb[(int64_t)j * d + c];
+            orow[c] = acc * inv;
+        }
     }
 }
 __global__ void bump_pos_kernel(int *pos) { *pos += 1; }
@@ -127,14 +164,14 @@ static tensor *block_decode_step(struct mem_pool *scratch, transformer_block *bl
     tensor *merged = tensor_scratch(scratch, 3, shape, 0);
     const bool rope = block->freqs_cos && block->freqs_sin;
     const tensor *kc = cache->k_cache, *vc = cache->v_cache;
-    const size_t smem = ((size_t)d + cache->max_seq + 32) * sizeof(float);
+    const size_t smem = ((size_t)d + cache->max_seq + 8 + 32 + (size_t)kDecodeGroups * d) * sizeof(float);
     DNN_CHECK(smem <= 200 * 1024, "decode step: sequence too long for the score buffer");
     static size_t smem_set = 0;
     if (smem > 48 * 1024 && smem > smem_set) {
         CUDA_OK(cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         smem_set = 200 * 1024;
     }
-    decode_attn_kernel<<<dim3(H, B), 128, smem, stream()>>>(
+    decode_attn_kernel<<<dim3(H, B), 256, smem, stream()>>>(
         (const float *)qkv->data + qkv->offset,
         rope ? (const float *)block->freqs_cos->data + block->freqs_cos->offset : nullptr,
         rope ? (const float *)block->freqs_sin->data + block->freqs_sin->offset : nullptr,
