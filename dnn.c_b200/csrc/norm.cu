@@ -65,6 +65,41 @@ __global__ void norm_fwd_kernel(const float *__restrict__ x, const float *__rest
     }
 }
 
+// A handful of rows (a decoding step: one token per sequence): one CTA per row instead of one warp, so that a row of
+// 768 floats is two loads per thread and not two dozen in a row.  d a multiple of 4, 16-byte aligned pointers.
+template <bool LN>
+__global__ void __launch_bounds__(256)
+norm_fwd_row_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b,
+                    float *__restrict__ y, float *__restrict__ mean_out, float *__restrict__ rstd_out, int d, float eps) {
+    __shared__ float red[32];
+    const int64_t r = blockIdx.x;
+    const float *xr = x + r * d;
+    float *yr = y + r * d;
+    const float inv_d = 1.0f / (float)d;
+    float s = 0.f, mu = 0.f;
+    if (LN) {
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) { float4 v = ld4(xr + j); s += v.x + v.y + v.z + v.w; }
+        mu = block_sum(s, red) * inv_d;
+        s = 0.f;
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) { float4 v = ld4(xr + j);
+            float a = v.x - mu, bb = v.y - mu, c = v.z - mu, e = v.w - mu; s += a * a + bb * bb + c * c + e * e; }
+    } else {
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) { float4 v = ld4(xr + j); s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+    }
+    s = block_sum(s, red);
+    const float rs = 1.0f / sqrtf(s * inv_d + eps);
+    if (threadIdx.x == 0) { rstd_out[r] = rs; if (LN) mean_out[r] = mu; }
+    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+        float4 v = ld4(xr + j);
+        float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+        float4 bb = (LN && b) ? ld4(b + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 o;
+        o.x = (v.x - mu) * rs * ww.x + bb.x; o.y = (v.y - mu) * rs * ww.y + bb.y;
+        o.z = (v.z - mu) * rs * ww.z + bb.z; o.w = (v.w - mu) * rs * ww.w + bb.w;
+        st4(yr + j, o);
+    }
+}
+
 // ---- backward --------------------------------------------------------------
 // T = float4 slots per lane (d <= 128*T).  Per row:
 //   dy = g*w
@@ -339,7 +374,8 @@ static void norm_forward(const float *x, const float *w, const float *b, float *
     int grid = (int)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
     int cap = kNumSMs * 8;
     if (grid > cap) grid = cap;
-    if (vec) norm_fwd_kernel<LN, true><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
+    if (vec && rows <= 8 && d >= 256) norm_fwd_row_kernel<LN><<<(unsigned)rows, 256, 0, stream()>>>(x, w, b, y, mean, rstd, d, eps);
+    else if (vec) norm_fwd_kernel<LN, true><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
     else     norm_fwd_kernel<LN, false><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
     prof_work(8.0 * rows * d);                                   // read x, write y
     LAUNCHED(LN ? "layernorm_fwd_kernel" : "rmsnorm_fwd_kernel");
