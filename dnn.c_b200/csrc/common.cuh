@@ -188,6 +188,7 @@ void gemm_reread_env();                // the next gemm() reads DNN_CUDA_TF32_3X
 // Same protocol for a residual: the next tensor-core GEMM computes C = A*B + bias + resid.
 void gemm_residual_request(const float *resid, int64_t ld);
 bool gemm_residual_take();
+bool gemm_residual_claim(const float **resid, int64_t *ld);
 // x + (a*b + bias) with the addition done in the GEMM epilogue when possible (ops_matrix.cu);
 // equal to tensor_add(scratch, x, tensor_matmul_add(scratch, a, b, trans_b, bias)) bit for bit.
 tensor *matmul_add_residual(struct mem_pool *scratch, const tensor *a, const tensor *b, int trans_b, const tensor *bias, const tensor *x);

@@ -145,7 +145,7 @@ gemv_kn_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restric
 // Eight lanes per output: lane l adds slices l, l + 8, ... in order, then the eight sums meet in a fixed shuffle tree, so
 // the result does not depend on timing; adjacent outputs sit in adjacent groups of lanes (32-byte segments per slice).
 __global__ void gemv_reduce_kernel(float *__restrict__ C, int64_t c_rs, const float *__restrict__ part, int splits, int M, int N,
-                                   const float *__restrict__ bias, int accumulate) {
+                                   const float *__restrict__ bias, int accumulate, const float *__restrict__ resid, int64_t resid_ld) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     const int i = t >> 3, l = t & 7;
     const bool live = i < M * N;
@@ -157,6 +157,7 @@ __global__ void gemv_reduce_kernel(float *__restrict__ C, int64_t c_rs, const fl
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     if (!live || l != 0) return;
     if (bias) s += bias[n];
+    if (resid) s += resid[(int64_t)m * resid_ld + n];          // x + (a W + b), the value a separate add would give
     float *c = C + (int64_t)m * c_rs + n;
     *c = accumulate ? *c + s : s;
 }
@@ -230,7 +231,10 @@ static void gemv(const GemmArgs &g) {
         }
         prof_work(4.0 * g.K * g.N);
         LAUNCHED("gemv_kn_kernel");
-        gemv_reduce_kernel<<<(g.M * g.N * 8 + 255) / 256, 256, 0, stream()>>>(g.C, g.c_rs, part, splits, g.M, g.N, g.bias, g.accumulate ? 1 : 0);
+        const float *resid = nullptr; int64_t resid_ld = 0;
+        if (!g.accumulate) gemm_residual_claim(&resid, &resid_ld);     // a pending request of matmul_add_residual
+        gemv_reduce_kernel<<<(g.M * g.N * 8 + 255) / 256, 256, 0, stream()>>>(g.C, g.c_rs, part, splits, g.M, g.N, g.bias, g.accumulate ? 1 : 0,
+                                                                              resid, resid_ld);
         LAUNCHED("gemv_reduce_kernel");
         return;
     }

@@ -567,6 +567,13 @@ bool gemm_tc_supported(const GemmArgs &in) {
 struct ResidEpilogue { const float *r; int64_t ld; bool pending, honoured; };
 static thread_local ResidEpilogue g_resid = {nullptr, 0, false, false};
 void gemm_residual_request(const float *resid, int64_t ld) { g_resid.r = resid; g_resid.ld = ld; g_resid.pending = true; g_resid.honoured = false; }
+// For a kernel outside this file that can add the residual itself: hands the pending request over and marks it honoured.
+bool gemm_residual_claim(const float **resid, int64_t *ld) {
+    if (!g_resid.pending) return false;
+    *resid = g_resid.r; *ld = g_resid.ld;
+    g_resid.pending = false; g_resid.honoured = true;
+    return true;
+}
 bool gemm_residual_take() {
     bool h = g_resid.honoured;
     g_resid.pending = false; g_resid.honoured = false;

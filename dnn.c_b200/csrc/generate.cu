@@ -178,11 +178,14 @@ static tensor *block_decode_step(struct mem_pool *scratch, transformer_block *bl
         (float *)kc->data + kc->offset, (float *)vc->data + vc->offset, kc->strides[0], kc->strides[1],
         (float *)merged->data, pos_dev, H, d, cache->max_seq, 1.0f / sqrtf((float)d));
     LAUNCHED("decode_attn_kernel");
-    tensor *proj = linear_forward(scratch, block->out_proj, merged);
-    tensor *x1 = tensor_add(scratch, x, proj);
+    // the two residual additions ride in the reduction of the projection that feeds them: x + (a W + b)
+    tensor *x1 = matmul_add_residual(scratch, merged, block->out_proj->weight, 0, block->out_proj->bias, x);
     h = rms_norm_forward(scratch, block->ffn_norm, x1);
-    tensor *ffn = swiglu_ffn_forward(scratch, block->ffn, h);
-    return tensor_add(scratch, x1, ffn);
+    swiglu_ffn *f = block->ffn;
+    tensor *gate = linear_forward(scratch, f->gate_proj, h);
+    tensor *up = linear_forward(scratch, f->up_proj, h);
+    tensor *hidden = tensor_swiglu(scratch, gate, up);
+    return matmul_add_residual(scratch, hidden, f->down_proj->weight, 0, f->down_proj->bias, x1);
 }
 
 // Cached token steps until max_len or end-of-sequence; output[cur - 1] is the last token so far and the caches hold

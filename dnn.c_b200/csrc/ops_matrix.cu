@@ -207,11 +207,12 @@ static tensor *mm_out(struct mem_pool *scratch, const MM &p) {
 
 tensor *matmul_add_residual(struct mem_pool *scratch, const tensor *a, const tensor *b, int trans_b, const tensor *bias, const tensor *x) {
     // the fused form needs x to have exactly the output's shape, packed
-    bool fits = gemm_mode() == DNN_CUDA_GEMM_TF32 && x && x->contiguous && a->ndim >= 2 && b->ndim == 2 && bias && bias->ndim == 1;
+    // (TF32 mode: the tensor-core kernel's epilogue; at most four rows, any mode: the sliced kernel's reduction)
+    bool fits = x && x->contiguous && a->ndim >= 2 && b->ndim == 2 && bias && bias->ndim == 1;
     if (fits) {
         int64_t rows = numel_of(a) / a->shape[a->ndim - 1];
         int ncols = trans_b ? b->shape[0] : b->shape[1];
-        fits = x->ndim == a->ndim && numel_of(x) == rows * ncols && x->shape[x->ndim - 1] == ncols && ncols % 4 == 0;
+        fits = (gemm_mode() == DNN_CUDA_GEMM_TF32 || rows <= 4) && x->ndim == a->ndim && numel_of(x) == rows * ncols && x->shape[x->ndim - 1] == ncols && ncols % 4 == 0;
         for (int d = 0; fits && d < a->ndim - 1; d++) fits = x->shape[d] == a->shape[d];
     }
     if (!fits) return tensor_add(scratch, x, tensor_matmul_add(scratch, a, b, trans_b, bias));
