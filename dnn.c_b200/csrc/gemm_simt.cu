@@ -142,20 +142,17 @@ gemv_kn_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restric
             if (n + j < N) part[((int64_t)blockIdx.y * MM + m) * N + n + j] = acc[m][j];
 }
 
-// Eight lanes per output: lane l adds slices l, l + 8, ... in order, then the eight sums meet in a fixed shuffle tree, so
-// the result does not depend on timing; adjacent outputs sit in adjacent groups of lanes (32-byte segments per slice).
+// A warp per output: lane l adds slices l, l + 32, ... in order, then the 32 sums meet in a fixed shuffle tree, so the result
+// does not depend on timing.  (One thread per output walked up to 128 dependent loads; eight lanes still a dozen.)
 __global__ void gemv_reduce_kernel(float *__restrict__ C, int64_t c_rs, const float *__restrict__ part, int splits, int M, int N,
                                    const float *__restrict__ bias, int accumulate, const float *__restrict__ resid, int64_t resid_ld) {
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    const int i = t >> 3, l = t & 7;
-    const bool live = i < M * N;
-    const int m = live ? i / N : 0, n = live ? i - m * N : 0;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), l = threadIdx.x & 31;
+    if (i >= M * N) return;                                        // whole warps leave together
+    const int m = i / N, n = i - m * N;
     float s = 0.f;
-    if (live) for (int k = l; k < splits; k += 8) s += part[((int64_t)k * M + m) * N + n];
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    if (!live || l != 0) return;
+    for (int k = l; k < splits; k += 32) s += part[((int64_t)k * M + m) * N + n];
+    s = warp_sum(s);
+    if (l != 0) return;
     if (bias) s += bias[n];
     if (resid) s += resid[(int64_t)m * resid_ld + n];          // x + (a W + b), the value a separate add would give
     float *c = C + (int64_t)m * c_rs + n;
@@ -233,7 +230,7 @@ static void gemv(const GemmArgs &g) {
         LAUNCHED("gemv_kn_kernel");
         const float *resid = nullptr; int64_t resid_ld = 0;
         if (!g.accumulate) gemm_residual_claim(&resid, &resid_ld);     // a pending request of matmul_add_residual
-        gemv_reduce_kernel<<<(g.M * g.N * 8 + 255) / 256, 256, 0, stream()>>>(g.C, g.c_rs, part, splits, g.M, g.N, g.bias, g.accumulate ? 1 : 0,
+        gemv_reduce_kernel<<<(g.M * g.N + 7) / 8, 256, 0, stream()>>>(g.C, g.c_rs, part, splits, g.M, g.N, g.bias, g.accumulate ? 1 : 0,
                                                                               resid, resid_ld);
         LAUNCHED("gemv_reduce_kernel");
         return;
