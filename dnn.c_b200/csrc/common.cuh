@@ -189,6 +189,9 @@ void gemm_reread_env();                // the next gemm() reads DNN_CUDA_TF32_3X
 void gemm_residual_request(const float *resid, int64_t ld);
 bool gemm_residual_take();
 bool gemm_residual_claim(const float **resid, int64_t *ld);
+// out[M,N] = silu(x Wg + bg) * (x Wu + bu) for at most four rows (gemm_simt.cu); false when the shapes do not qualify
+bool gemv_swiglu(const float *x, int64_t x_rs, int M, const float *Wg, const float *bg, const float *Wu, const float *bu,
+                 int K, int N, float *out);
 // x + (a*b + bias) with the addition done in the GEMM epilogue when possible (ops_matrix.cu);
 // equal to tensor_add(scratch, x, tensor_matmul_add(scratch, a, b, trans_b, bias)) bit for bit.
 tensor *matmul_add_residual(struct mem_pool *scratch, const tensor *a, const tensor *b, int trans_b, const tensor *bias, const tensor *x);

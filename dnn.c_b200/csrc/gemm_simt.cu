@@ -100,8 +100,9 @@ constexpr int kGemvRows = 4, kGemvSlice = 256, kGemvSplits = 128;
 template <int MM>
 __global__ void __launch_bounds__(128)
 gemv_kn_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restrict__ W, int64_t w_rs, float *__restrict__ part,
-               int N, int K, int k_per_split, int vec) {
+               int N, int K, int k_per_split, int vec, const float *__restrict__ W2 = nullptr, float *__restrict__ part2 = nullptr) {
     __shared__ float xs[MM][kGemvSlice];
+    if (blockIdx.z == 1) { W = W2; part = part2; }            // a second product of the same x in the same launch
     const int k0 = blockIdx.y * k_per_split, k1 = min(K, k0 + k_per_split);
     for (int i = threadIdx.x; i < MM * (k1 - k0); i += blockDim.x) {
         int m = i / (k1 - k0), k = i - m * (k1 - k0);
@@ -159,6 +160,22 @@ __global__ void gemv_reduce_kernel(float *__restrict__ C, int64_t c_rs, const fl
     *c = accumulate ? *c + s : s;
 }
 
+// out = silu(g) * u for two products of the same x that are still in slices (gate and up projection of a SwiGLU layer):
+// a warp per output adds the slices of both in the order of gemv_reduce_kernel and applies tensor_swiglu's arithmetic.
+__global__ void gemv_reduce_swiglu_kernel(float *__restrict__ out, const float *__restrict__ pg, const float *__restrict__ pu, int splits,
+                                          int M, int N, const float *__restrict__ bg, const float *__restrict__ bu) {
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), l = threadIdx.x & 31;
+    if (i >= M * N) return;
+    const int m = i / N, n = i - m * N;
+    float g = 0.f, u = 0.f;
+    for (int k = l; k < splits; k += 32) { g += pg[((int64_t)k * M + m) * N + n]; u += pu[((int64_t)k * M + m) * N + n]; }
+    g = warp_sum(g); u = warp_sum(u);
+    if (l != 0) return;
+    if (bg) g += bg[n];
+    if (bu) u += bu[n];
+    out[(int64_t)m * N + n] = (g / (1.0f + expf(-g))) * u;
+}
+
 template <int MM>
 __global__ void __launch_bounds__(256)
 gemv_nk_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restrict__ W, int64_t w_cs, float *__restrict__ C, int64_t c_rs,
@@ -194,6 +211,40 @@ gemv_nk_kernel(const float *__restrict__ x, int64_t x_rs, const float *__restric
             *c = accumulate ? *c + s : s;
         }
     }
+}
+
+// out[M,N] = silu(x Wg + bg) * (x Wu + bu) for at most four rows: both products in one launch, one reduction.
+// Wg, Wu: [K,N] row-major with N a multiple of 4 and 16-byte aligned; returns false when the shapes do not qualify.
+bool gemv_swiglu(const float *x, int64_t x_rs, int M, const float *Wg, const float *bg, const float *Wu, const float *bu,
+                 int K, int N, float *out) {
+    if (M < 1 || M > kGemvRows || K < 64 || N < 64 || N % 4 != 0 || ((reinterpret_cast<uintptr_t>(Wg) | reinterpret_cast<uintptr_t>(Wu)) & 15) != 0) return false;
+    const int blocks_n = (N + 511) / 512;
+    int splits = (2 * kNumSMs + blocks_n - 1) / blocks_n;          // the launch holds two products
+    if (splits > kGemvSplits) splits = kGemvSplits;
+    int kps = (K + splits - 1) / splits;
+    if (kps > kGemvSlice) kps = kGemvSlice;
+    if (kps < 8) kps = 8;
+    splits = (K + kps - 1) / kps;
+    static float *part = nullptr; static size_t cap = 0;
+    const size_t one = (size_t)splits * M * N, need = 2 * one * sizeof(float);
+    if (need > cap) {
+        CUDA_OK(cudaStreamSynchronize(stream()));
+        if (part) CUDA_OK(cudaFree(part));
+        cap = need + (need >> 1);
+        CUDA_OK(cudaMalloc((void **)&part, cap));
+    }
+    dim3 grid(blocks_n, splits, 2);
+    switch (M) {
+        case 1: gemv_kn_kernel<1><<<grid, 128, 0, stream()>>>(x, x_rs, Wg, N, part, N, K, kps, 1, Wu, part + one); break;
+        case 2: gemv_kn_kernel<2><<<grid, 128, 0, stream()>>>(x, x_rs, Wg, N, part, N, K, kps, 1, Wu, part + one); break;
+        case 3: gemv_kn_kernel<3><<<grid, 128, 0, stream()>>>(x, x_rs, Wg, N, part, N, K, kps, 1, Wu, part + one); break;
+        default: gemv_kn_kernel<4><<<grid, 128, 0, stream()>>>(x, x_rs, Wg, N, part, N, K, kps, 1, Wu, part + one); break;
+    }
+    prof_work(8.0 * K * N);
+    LAUNCHED("gemv_kn_kernel");
+    gemv_reduce_swiglu_kernel<<<(M * N + 7) / 8, 256, 0, stream()>>>(out, part, part + one, splits, M, N, bg, bu);
+    LAUNCHED("gemv_reduce_swiglu_kernel");
+    return true;
 }
 
 static bool gemv_applicable(const GemmArgs &g) {

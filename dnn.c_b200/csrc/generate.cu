@@ -182,9 +182,23 @@ static tensor *block_decode_step(struct mem_pool *scratch, transformer_block *bl
     tensor *x1 = matmul_add_residual(scratch, merged, block->out_proj->weight, 0, block->out_proj->bias, x);
     h = rms_norm_forward(scratch, block->ffn_norm, x1);
     swiglu_ffn *f = block->ffn;
-    tensor *gate = linear_forward(scratch, f->gate_proj, h);
-    tensor *up = linear_forward(scratch, f->up_proj, h);
-    tensor *hidden = tensor_swiglu(scratch, gate, up);
+    // gate and up projection in one launch, SwiGLU in their reduction, when the weights are plain [K,N] matrices
+    const tensor *wg = f->gate_proj->weight, *wu = f->up_proj->weight, *bg = f->gate_proj->bias, *bu = f->up_proj->bias;
+    tensor *hidden = nullptr;
+    if (wg->ndim == 2 && wu->ndim == 2 && wg->contiguous && wu->contiguous && wg->shape[0] == wu->shape[0] && wg->shape[1] == wu->shape[1] &&
+        (!bg || bg->contiguous) && (!bu || bu->contiguous) && h->contiguous) {
+        int fs[3] = {B, 1, wg->shape[1]};
+        hidden = tensor_scratch(scratch, 3, fs, 0);
+        if (!gemv_swiglu((const float *)h->data + h->offset, wg->shape[0], B, (const float *)wg->data + wg->offset,
+                         bg ? (const float *)bg->data + bg->offset : nullptr, (const float *)wu->data + wu->offset,
+                         bu ? (const float *)bu->data + bu->offset : nullptr, wg->shape[0], wg->shape[1], (float *)hidden->data))
+            hidden = nullptr;
+    }
+    if (!hidden) {
+        tensor *gate = linear_forward(scratch, f->gate_proj, h);
+        tensor *up = linear_forward(scratch, f->up_proj, h);
+        hidden = tensor_swiglu(scratch, gate, up);
+    }
     return matmul_add_residual(scratch, hidden, f->down_proj->weight, 0, f->down_proj->bias, x1);
 }
 
