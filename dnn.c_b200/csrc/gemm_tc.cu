@@ -19,7 +19,7 @@
 // Tails in M, N and K need no special code: TMA zero-fills out-of-bounds boxes.
 //
 // X3 (3xTF32 in one pass): the stages hold the RAW fp32 tiles (the tensor core reads the upper 19 bits
-// of each word, i.e. x truncated to TF32 = "big") next to a second copy that four more warps fill
+// of each word, i.e. x truncated to TF32 = "big") next to a second copy that eight more warps fill
 // with small = x - big as soon as a tile has landed; per K=8 step the issuing thread then runs
 // As*Bb, Ab*Bs and Ab*Bb.  Nothing is split in global memory.  X3 = 1: all three into one accumulator
 // (the two TMEM accumulators alternate between tiles as in the TF32 kernel).  X3 = 2: Ab*Bb into the
@@ -40,7 +40,8 @@ constexpr int BM = 128;            // tile rows = MMA M
 constexpr int BK = 32;             // K per stage: 32 fp32 = one 128-byte swizzle row
 constexpr int UMMA_K = 8;          // K per tcgen05.mma for TF32
 constexpr int kGemmThreads = 192;
-constexpr int kGemmThreadsX3 = 192 + 128;      // four more warps split the landed tiles
+constexpr int kSplitWarps = 8;                  // warps that split the landed tiles of the 3xTF32 kernel
+constexpr int kGemmThreadsX3 = 192 + kSplitWarps * 32;
 
 __device__ int g_gemm_error = 0;   // 0 ok; otherwise (role << 8 | detail) of the first wait that gave up
 
@@ -125,7 +126,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::kStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&conv[s], PAIR ? 8 : 4); }
+        for (int s = 0; s < Cfg::kStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&conv[s], PAIR ? 2 * kSplitWarps : kSplitWarps); }
         for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 8 : 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -243,7 +244,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
         }
     } else if (X3 && warp >= 6) {
-        // split warps 6..9: small = x - trunc(x) of the stage that has just landed, element by element
+        // split warps 6..13: small = x - trunc(x) of the stage that has just landed, element by element
         // (the layout of the tile does not matter), then tell the leader's MMA thread
         const int t = (int)threadIdx.x - kGemmThreads;
         int stage = 0; uint32_t phase = 0;
@@ -256,16 +257,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const float4 *ra = reinterpret_cast<const float4 *>(sA + stage * kStrideA);
                 float4 *wa = reinterpret_cast<float4 *>(sA + stage * kStrideA + Cfg::kStageA);
 #pragma unroll
-                for (int i = 0; i < Cfg::kStageA / 16 / 128; i++) {
-                    const float4 v = ra[t + i * 128];
-                    wa[t + i * 128] = make_float4(tf32_small(v.x), tf32_small(v.y), tf32_small(v.z), tf32_small(v.w));
+                for (int i = 0; i < Cfg::kStageA / 16 / (kSplitWarps * 32); i++) {
+                    const float4 v = ra[t + i * kSplitWarps * 32];
+                    wa[t + i * kSplitWarps * 32] = make_float4(tf32_small(v.x), tf32_small(v.y), tf32_small(v.z), tf32_small(v.w));
                 }
                 const float4 *rb = reinterpret_cast<const float4 *>(sB + stage * kStrideB);
                 float4 *wb = reinterpret_cast<float4 *>(sB + stage * kStrideB + Cfg::kStageB);
 #pragma unroll
-                for (int i = 0; i < Cfg::kStageB / 16 / 128; i++) {
-                    const float4 v = rb[t + i * 128];
-                    wb[t + i * 128] = make_float4(tf32_small(v.x), tf32_small(v.y), tf32_small(v.z), tf32_small(v.w));
+                for (int i = 0; i < Cfg::kStageB / 16 / (kSplitWarps * 32); i++) {
+                    const float4 v = rb[t + i * kSplitWarps * 32];
+                    wb[t + i * kSplitWarps * 32] = make_float4(tf32_small(v.x), tf32_small(v.y), tf32_small(v.z), tf32_small(v.w));
                 }
                 fence_proxy_async();
                 __syncwarp();
