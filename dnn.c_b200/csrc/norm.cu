@@ -65,6 +65,51 @@ __global__ void norm_fwd_kernel(const float *__restrict__ x, const float *__rest
     }
 }
 
+// The same with the row held in registers (T 128-bit slots per lane, d <= 128 T, d a multiple of 4): one read of x with all
+// of a lane's loads in flight at once instead of two passes; the sums run over the same elements in the same order.
+template <bool LN, int T>
+__global__ void norm_fwd_reg_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b,
+                                    float *__restrict__ y, float *__restrict__ mean_out, float *__restrict__ rstd_out,
+                                    int64_t rows, int d, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5), nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+    const float inv_d = 1.0f / (float)d;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const float *xr = x + r * d;
+        float *yr = y + r * d;
+        float4 v[T];
+#pragma unroll
+        for (int t = 0; t < T; t++) { const int j = (lane + 32 * t) * 4; v[t] = j < d ? ld4(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f); }
+        float s = 0.f, mu = 0.f;
+        if (LN) {
+#pragma unroll
+            for (int t = 0; t < T; t++) if ((lane + 32 * t) * 4 < d) s += v[t].x + v[t].y + v[t].z + v[t].w;
+            mu = warp_sum(s) * inv_d;
+            s = 0.f;
+#pragma unroll
+            for (int t = 0; t < T; t++) if ((lane + 32 * t) * 4 < d) {
+                float a = v[t].x - mu, bb = v[t].y - mu, c = v[t].z - mu, e = v[t].w - mu; s += a * a + bb * bb + c * c + e * e; }
+        } else {
+#pragma unroll
+            for (int t = 0; t < T; t++) if ((lane + 32 * t) * 4 < d) s += v[t].x * v[t].x + v[t].y * v[t].y + v[t].z * v[t].z + v[t].w * v[t].w;
+        }
+        s = warp_sum(s);
+        const float rs = 1.0f / sqrtf(s * inv_d + eps);
+        if (lane == 0) { rstd_out[r] = rs; if (LN) mean_out[r] = mu; }
+#pragma unroll
+        for (int t = 0; t < T; t++) {
+            const int j = (lane + 32 * t) * 4;
+            if (j >= d) continue;
+            float4 ww = w ? ld4(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+            float4 bb = (LN && b) ? ld4(b + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 o;
+            o.x = (v[t].x - mu) * rs * ww.x + bb.x; o.y = (v[t].y - mu) * rs * ww.y + bb.y;
+            o.z = (v[t].z - mu) * rs * ww.z + bb.z; o.w = (v[t].w - mu) * rs * ww.w + bb.w;
+            st4(yr + j, o);
+        }
+    }
+}
+
 // A handful of rows (a decoding step: one token per sequence): one CTA per row instead of one warp, so that a row of
 // 768 floats is two loads per thread and not two dozen in a row.  d a multiple of 4, 16-byte aligned pointers.
 template <bool LN>
@@ -374,7 +419,12 @@ static void norm_forward(const float *x, const float *w, const float *b, float *
     int grid = (int)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
     int cap = kNumSMs * 8;
     if (grid > cap) grid = cap;
+    const int T = (d + 127) / 128;
     if (vec && rows <= 8 && d >= 256) norm_fwd_row_kernel<LN><<<(unsigned)rows, 256, 0, stream()>>>(x, w, b, y, mean, rstd, d, eps);
+    else if (vec && T <= 2) norm_fwd_reg_kernel<LN, 2><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
+    else if (vec && T <= 4) norm_fwd_reg_kernel<LN, 4><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
+    else if (vec && T <= 6) norm_fwd_reg_kernel<LN, 6><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
+    else if (vec && T <= 8) norm_fwd_reg_kernel<LN, 8><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
     else if (vec) norm_fwd_kernel<LN, true><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
     else     norm_fwd_kernel<LN, false><<<grid, kWarpsPerCta * 32, 0, stream()>>>(x, w, b, y, mean, rstd, rows, d, eps);
     prof_work(8.0 * rows * d);                                   // read x, write y
