@@ -83,7 +83,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 // single-thread roles (loader, MMA issuer)
 #define CTRL_WAIT(bar, parity, code)                                                     \
     if (ok && !wait_or_abort((bar), (parity), abort_flag)) { atomicCAS(&g_attn_error, 0, (code)); *abort_flag = 1; ok = false; }
-// compute warps: lane 0 polls the barrier and the warp takes its verdict (one poller per warp
+// compute warps: lane 0 polls the barrier and the warp takes its answer (one poller per warp
 // keeps 256 threads from hammering a shared-memory barrier that the tensor core's operand reads
 // share a port with); every lane then passes the tcgen05 fence that follows the wait
 #define WARP_WAIT(bar, parity, code)                                                     \
